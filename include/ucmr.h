@@ -1,0 +1,192 @@
+/*
+ * ucmr.h - C ABI of the B200 (sm_100a) hash-code top-k block retrieval library.
+ *
+ * Every entry point takes raw device pointers, sizes and an explicit CUDA
+ * stream (a cudaStream_t passed as void*; NULL = legacy default stream),
+ * launches asynchronously on that stream, allocates nothing, keeps no global
+ * state and returns an int status (0 = ok, negative = error, see UCMR_ERR_*).
+ * Nothing here throws or aborts.  The caller owns all buffers.
+ *
+ * Each declaration names the interface of the reference project
+ * (ModelEngine-Group/unified-cache-management, paths relative to its root) that it
+ * stands in for.
+ *
+ * Data layouts
+ *   codes        uint32 [NB, BS, Hkv, W]   paged hash-code cache; bit b of word w is projection
+ *                                          column 32*w+b (little-endian view of the reference's
+ *                                          LSB-first uint8 packing, hash_encoder.py:445-448)
+ *   q_codes      uint32 [B, Hq, W]         one code per query head; G = Hq/Hkv heads share a kv head
+ *   block_table  int32  [B, max_blocks]    logical block -> physical block (row stride in elements)
+ *   seq_lens     int32  [B]                tokens per request
+ */
+#ifndef UCMR_H_
+#define UCMR_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define UCMR_VERSION 100
+
+#define UCMR_OK 0
+#define UCMR_ERR_BAD_ARG (-1)     /* null pointer, negative size, k > max_blocks, ...            */
+#define UCMR_ERR_UNSUPPORTED (-2) /* shape outside what the kernels are built for                */
+#define UCMR_ERR_LAUNCH (-3)      /* the CUDA runtime refused the launch (see ucmr_last_cuda_error) */
+#define UCMR_ERR_DEVICE (-4)      /* a kernel recorded a problem in the workspace status word     */
+#define UCMR_ERR_WORKSPACE (-5)   /* workspace missing or too small                               */
+
+/* Bits of the device status word (first int32 of a workspace). */
+#define UCMR_DEV_BAD_BLOCK_ID 1 /* a block-table entry or selected id was outside [0, NB)        */
+#define UCMR_DEV_WAIT_TIMEOUT 2 /* a bounded wait inside a kernel gave up                        */
+#define UCMR_DEV_BAD_SLOT 4     /* reserved                                                      */
+
+#define UCMR_REDUCE_MIN 0 /* block score = min over tokens (reference behaviour)                 */
+#define UCMR_REDUCE_SUM 1 /* block score = sum over tokens (mean * BS * G)                       */
+
+#define UCMR_MAX_MUST_SELECT 16
+#define UCMR_WORKSPACE_HEADER_BYTES 256
+
+int ucmr_version(void);
+const char* ucmr_status_string(int status);
+/* Text of the last CUDA runtime error seen by this thread inside the library ("" if none). */
+const char* ucmr_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * (1) Hash encode.  Replaces HashEncoder.compute_hash / triton_hash_code
+ *     (ucm/sparse/gsa_on_device/hash_encoder.py:37-134, 450-507; CPU form torch_hash_code :359-370).
+ *     codes_out[r, w] bit b = (sum_k x[r,k] * R[k, 32w+b] > 0), bf16 inputs, float32 accumulate.
+ *     x: bf16 [rows, in_dim], row stride in elements (multiple of 8); R: bf16 [in_dim, hash_bits]
+ *     row-major.  in_dim and hash_bits are 128 on the tensor-core path; other multiples of 32 up to
+ *     1024 run on a slower CUDA-core path.  status_word (device int32*, may be NULL) receives
+ *     UCMR_DEV_WAIT_TIMEOUT if a bounded wait inside the tensor-core kernel gave up.
+ * ------------------------------------------------------------------------------------------ */
+int ucmr_hash_encode(const void* x, int64_t rows, int64_t row_stride, const void* R, int in_dim,
+                     int hash_bits, uint32_t* codes_out, int32_t* status_word, void* stream);
+
+/*     Query path of GSAOnDevice.hash_code (ucm/sparse/gsa_on_device/gsa_on_device.py:396-412):
+ *     q bf16 [T, Hq, in_dim] (strides in elements).  group_mean = G > 1 first averages each run of
+ *     G consecutive heads (float32 sum, one rounding to bf16, as torch's bf16 mean does) and emits
+ *     Hq/G codes per token; group_mean = 1 emits one code per head.  codes_out [T, Hq/G, W].      */
+int ucmr_hash_encode_query(const void* q, int64_t T, int Hq, int64_t stride_t, int64_t stride_h,
+                           int group_mean, const void* R, int in_dim, int hash_bits,
+                           uint32_t* codes_out, int32_t* status_word, void* stream);
+
+/*     Replaces HashEncoder.compute_hash_and_cache / fused_hash_and_cache_kernel
+ *     (hash_encoder.py:263-356, 548-662): encode x[T,H,in_dim] and write the codes of token t to
+ *     slot slot_mapping[t] (= block*BS + row) of cache[NB,BS,H,W].  Slots < 0 or >= NB*BS are
+ *     skipped (hash_encoder.py:340-344).  slot_mapping is int64 when slot_is_int64 != 0, else int32. */
+int ucmr_hash_encode_and_cache(const void* x, int64_t T, int H, int64_t stride_t, int64_t stride_h,
+                               const void* R, int in_dim, int hash_bits, const void* slot_mapping,
+                               int slot_is_int64, uint32_t* cache, int64_t NB, int BS,
+                               int32_t* status_word, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Workspace.  Holds the device status word and the block scores between the scan and the
+ * selection kernel.  Clear it once with ucmr_workspace_init after allocating it; the status word
+ * is sticky until the next init.  ucmr_workspace_status copies the word to the host and waits for
+ * the stream.
+ * ------------------------------------------------------------------------------------------ */
+size_t ucmr_hamming_topk_workspace_bytes(int B, int Hkv, int max_blocks, int reduce_kvhead);
+int ucmr_workspace_init(void* workspace, size_t bytes, void* stream);
+int ucmr_workspace_status(const void* workspace, int* host_status, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * (2)+(3) Hamming scan + per-request exact top-k.  Replaces cuda_hamming_topk
+ *     (ucm/sparse/gsa_on_device/hamming_topk.py:15-54) = hamming.hamming_score
+ *     (ucm/sparse/gsa_on_device/csrc/cuda/ham_dist/paged_ham_dist_mla.cu:332-443, kernel :111-248)
+ *     followed by torch.min / topk / sort / gather, and update_seq_lens (hamming_topk.py:7-12).
+ *
+ *     Token distance d[b,h,p] = sum_{g<G} popcount(codes[..p.., h, :] ^ q_codes[b, h*G+g, :]).
+ *     Block score S[b,h,j] = min or sum of d over the valid tokens of logical block j;
+ *     reduce_kvhead != 0 further combines the kv heads with the same operator (Hout = 1),
+ *     otherwise Hout = Hkv.  Forced blocks: entries of must_select (HOST array; >= 0 counts from
+ *     the start, < 0 from the request's block count) and every block overlapping [0, sink_tokens)
+ *     or [seq_len - recent_tokens, seq_len).  Forced blocks count toward k.  Selection = first k
+ *     blocks under the order (forced first, then score ascending, ties by lower block id; blocks
+ *     past the request's length last); the k results are written in ascending logical order.
+ *
+ *     k_per_request (device int32 [B], may be NULL): row b uses min(k_per_request[b], k) and pads
+ *     with logical -1 / physical 0.  request_mask (device uint8 [B], may be NULL): rows with 0 are
+ *     not retrieved; they get logical 0..k-1, the head of their own block table and their own
+ *     seq_len.
+ *
+ *     Outputs (device; any of out_logical / out_scores / out_valid_count / out_new_seq_lens may
+ *     be NULL): out_physical, out_logical, out_scores int32 [B, Hout, k]; out_valid_count,
+ *     out_new_seq_lens int32 [B].  out_scores holds the raw block score (-1 for padding).
+ * ------------------------------------------------------------------------------------------ */
+int ucmr_hamming_topk(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
+                      const uint32_t* q_codes, int Hq, const int32_t* block_table, int max_blocks,
+                      int64_t block_table_stride, const int32_t* seq_lens, int B, int k,
+                      const int32_t* k_per_request, const uint8_t* request_mask, int reduce_mode,
+                      int reduce_kvhead, const int32_t* must_select, int n_must, int sink_tokens,
+                      int recent_tokens, int32_t* out_physical, int32_t* out_logical,
+                      int32_t* out_scores, int32_t* out_valid_count, int32_t* out_new_seq_lens,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/*     Scan only: block scores int32 [B, Hout, max_blocks] (-1 past the request's length).
+ *     Same kernel as the first half of ucmr_hamming_topk.  status_word (device int32*, may be
+ *     NULL) receives UCMR_DEV_* bits.                                                             */
+int ucmr_block_scores(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
+                      const uint32_t* q_codes, int Hq, const int32_t* block_table, int max_blocks,
+                      int64_t block_table_stride, const int32_t* seq_lens, int B, int reduce_mode,
+                      int reduce_kvhead, int32_t* out_scores, int32_t* status_word, void* stream);
+
+/*     Per-token output of the reference op hamming.hamming_score
+ *     (ucm/sparse/gsa_on_device/csrc/cuda/ham_dist/cpy/hamming.cpp:5, paged_ham_dist_mla.cu:189-247):
+ *     fp16 [B, reduce_kvhead ? 1 : Hkv, max_blocks*BS]; positions < sink or in
+ *     [seq_len-recent, seq_len) -> 0, positions >= seq_len -> +inf, min over kv heads when
+ *     reduce_kvhead.  Kept for callers of the old op; the retrieval path never materialises it.  */
+int ucmr_hamming_score(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
+                       const uint32_t* q_codes, int Hq, const int32_t* block_table, int max_blocks,
+                       int64_t block_table_stride, const int32_t* seq_lens, int B, int sink_tokens,
+                       int recent_tokens, int reduce_kvhead, void* out_fp16, void* stream);
+
+/*     update_seq_lens (hamming_topk.py:7-12): out[b] = seq - ceil(max(seq - topk_tokens, 0)/BS)*BS. */
+int ucmr_update_seq_lens(const int32_t* seq_lens, int B, int topk_tokens, int BS, int32_t* out,
+                         void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Sequence-sharded retrieval (no counterpart in the reference, whose plugin is not
+ * context-parallel aware; the per-shard computation is the same scan + selection as above).
+ *     ucmr_topk_candidates: this shard holds logical blocks [block_id_offset, block_id_offset +
+ *     ceil(seq_lens_local[b]/BS)) of request b.  Writes its best k blocks as records
+ *     (float32 score, int32 global block id) [B, Hout, k], ascending id, padding = (+inf, -1).
+ *     score = block score * score_scale; forced blocks (decided from the global block index and
+ *     seq_lens_global) carry -1.0 so that they survive the merge.
+ *     ucmr_merge_topk: cand_* [R, B, Hout, kl] gathered in ascending shard order -> first k under
+ *     (score, id), written in ascending id order to out_* [B, Hout, k]; padding = (+inf, -1).
+ * ------------------------------------------------------------------------------------------ */
+int ucmr_topk_candidates(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
+                         const uint32_t* q_codes, int Hq, const int32_t* block_table,
+                         int max_blocks, int64_t block_table_stride,
+                         const int32_t* seq_lens_local, const int32_t* seq_lens_global, int B,
+                         int k, int block_id_offset, float score_scale, int reduce_mode,
+                         int reduce_kvhead, const int32_t* must_select, int n_must,
+                         int sink_tokens, int recent_tokens, float* cand_scores,
+                         int32_t* cand_ids, void* workspace, size_t workspace_bytes, void* stream);
+
+int ucmr_merge_topk(const float* cand_scores, const int32_t* cand_ids, int R, int B, int Hout,
+                    int kl, int k, float* out_scores, int32_t* out_ids, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * (4) Paged-KV gather.  out[b, i*BS + t, h, :] = pool[sel[b,(h),i], t, h, :] for the K pool and
+ *     the V pool (either may be NULL).  Device-to-device form of the reference's
+ *     kv_cache[block_ids] (ucm/sparse/gsa_on_device/gsa_on_device.py:579-580) and of the
+ *     scattered-blocks-to-one-buffer copy CudaCopyKernel (ucm/shared/trans/cuda/cuda_sm_kernel.cu:66-78).
+ *     block_bytes = BS*Hkv*D*elem_size (multiple of 16).  per_head = 0: sel is int32 [B, k] and
+ *     whole blocks are copied.  per_head != 0: sel is int32 [B, Hkv, k] and each kv head takes its
+ *     own blocks (row_bytes = D*elem_size, multiple of 16).  Ids outside [0, NB) are skipped and
+ *     flagged in status_word (device int32*, may be NULL).
+ * ------------------------------------------------------------------------------------------ */
+int ucmr_gather_kv(const void* k_pool, const void* v_pool, int64_t NB, int64_t block_bytes,
+                   const int32_t* sel, int B, int k, int per_head, int BS, int Hkv,
+                   int64_t row_bytes, void* out_k, void* out_v, int32_t* status_word,
+                   void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* UCMR_H_ */

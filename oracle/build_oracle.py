@@ -1,0 +1,82 @@
+"""Build recipes for the CPU checkers (TEST INFRASTRUCTURE ONLY).
+
+* ``build_oracle_c()`` compiles ``oracle_c.c`` (this repository's own C
+  restatement) into ``oracle/_build/liboracle.so``.
+* ``build_ref()`` compiles the reference project's CPU retrieval backend
+  (``ucm/sparse/gsa_on_device/csrc/cuda/hash_retrieval/cpy/hash_retrieval_backend.cpp``)
+  straight from the reference checkout into ``oracle/_ref/``; no reference
+  source is copied.  It is skipped when the checkout is not present (the
+  prebuilt module, if any, is used as is).
+
+Run ``python oracle/build_oracle.py`` to build both.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+import sysconfig
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+BUILD_DIR = os.path.join(HERE, "_build")
+REF_DIR = os.path.join(HERE, "_ref")
+ORACLE_SO = os.path.join(BUILD_DIR, "liboracle.so")
+REF_SRC_REL = "ucm/sparse/gsa_on_device/csrc/cuda/hash_retrieval/cpy/hash_retrieval_backend.cpp"
+
+
+def _newer(target: str, *sources: str) -> bool:
+    if not os.path.exists(target):
+        return False
+    t = os.path.getmtime(target)
+    return all(os.path.getmtime(s) <= t for s in sources if os.path.exists(s))
+
+
+def build_oracle_c(force: bool = False) -> str:
+    src = os.path.join(HERE, "oracle_c.c")
+    if not force and _newer(ORACLE_SO, src):
+        return ORACLE_SO
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    cmd = ["gcc", "-O3", "-march=x86-64-v2", "-mpopcnt", "-fopenmp", "-shared", "-fPIC", "-std=c11",
+           src, "-o", ORACLE_SO, "-lm"]
+    subprocess.check_call(cmd)
+    return ORACLE_SO
+
+
+def ref_module_path() -> str:
+    suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+    return os.path.join(REF_DIR, "hash_retrieval_backend" + suffix)
+
+
+def build_ref(reference_root: str | None = None, force: bool = False) -> str | None:
+    """Returns the module path, or None when neither source nor prebuilt module exists."""
+    reference_root = reference_root or os.environ.get("UCM_REFERENCE_ROOT", "/root/reference")
+    src = os.path.join(reference_root, REF_SRC_REL)
+    out = ref_module_path()
+    if not os.path.exists(src):
+        return out if os.path.exists(out) else None
+    if not force and _newer(out, src):
+        return out
+    import pybind11
+    os.makedirs(REF_DIR, exist_ok=True)
+    cmd = ["g++", "-O3", "-march=x86-64-v2", "-mpopcnt", "-msse4.2", "-shared", "-fPIC", "-fopenmp",
+           "-std=c++17", "-I" + pybind11.get_include(), "-I" + sysconfig.get_paths()["include"],
+           src, "-o", out, "-lpthread"]
+    subprocess.check_call(cmd)
+    return out
+
+
+def load_ref():
+    """Import the compiled reference backend, or return None if it was never built."""
+    path = ref_module_path()
+    if not os.path.exists(path):
+        return None
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("hash_retrieval_backend", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+if __name__ == "__main__":
+    print(build_oracle_c(force="--force" in sys.argv))
+    print(build_ref(force="--force" in sys.argv))

@@ -1,0 +1,153 @@
+"""GPU parity: hash encode (tensor-core and CUDA-core paths) vs the CPU oracle.
+
+Tolerance (stated by the task): a code bit may differ from sign(projection) only where the
+float64 projection magnitude is below 1e-3; such flips are counted and must stay rare.
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-3
+
+
+def _r_matrix(seed, in_dim=128, bits=128):
+    rng = np.random.default_rng(seed)
+    return O.f32_to_bf16_bits((rng.standard_normal((in_dim, bits)) / np.sqrt(in_dim)).astype(np.float32))
+
+
+def _check(dev_codes, x_bits, r_bits, max_soft_frac=1e-3):
+    want_codes, p64 = O.hash_encode(x_bits, r_bits)
+    hard, soft = O.count_code_mismatches(dev_codes.reshape(want_codes.shape), p64, TOL)
+    assert hard == 0, f"{hard} bits differ where |projection| >= {TOL}"
+    assert soft <= max_soft_frac * p64.size + 2, f"{soft} near-zero flips"
+    return soft
+
+
+@pytest.mark.parametrize("rows", [1, 5, 127, 128, 129, 1000, 148 * 128 * 3 + 77])
+def test_encode_rows(cuda_device, rows):
+    import torch
+    from unified_cache_management_b200 import ops
+    rng = np.random.default_rng(rows)
+    x = H.bf16_normal(rng, (rows, 128))
+    r = _r_matrix(1)
+    out = ops.hash_encode(H.bf16_to_dev(x, cuda_device), H.bf16_to_dev(r, cuda_device))
+    torch.cuda.synchronize()
+    _check(H.dev_to_u32(out), x, r)
+
+
+def test_encode_bit_order_and_sign_rule(cuda_device):
+    """Identity projection: bit b of word w is exactly (x[32w+b] > 0); zeros, -0 and NaN give 0."""
+    import torch
+    from unified_cache_management_b200 import ops
+    eye = O.f32_to_bf16_bits(np.eye(128, dtype=np.float32))
+    x = np.zeros((4, 128), dtype=np.float32)
+    x[0, [0, 31, 32, 127]] = 1.0
+    x[1, :] = -1.0
+    x[2, 5] = 2.0 ** -120
+    x[2, 6] = -0.0
+    x[3, 7] = np.nan
+    x[3, 8] = 3.0
+    xb = O.f32_to_bf16_bits(x)
+    out = H.dev_to_u32(ops.hash_encode(H.bf16_to_dev(xb, cuda_device), H.bf16_to_dev(eye, cuda_device)))
+    torch.cuda.synchronize()
+    assert out[0].tolist() == [0x80000001, 0x00000001, 0, 0x80000000]
+    assert out[1].tolist() == [0, 0, 0, 0]
+    assert out[2].tolist() == [1 << 5, 0, 0, 0]
+    # NaN * 0 poisons the whole row's sums: every comparison is false
+    assert out[3].tolist() == [0, 0, 0, 0]
+
+
+def test_encode_strided_rows(cuda_device):
+    """Keys sliced out of a fused qkv buffer: row stride larger than in_dim."""
+    import torch
+    from unified_cache_management_b200 import ops
+    rng = np.random.default_rng(7)
+    T, Hkv, D = 300, 8, 128
+    q_size, kv_size = 32 * D, Hkv * D
+    qkv = H.bf16_normal(rng, (T, q_size + 2 * kv_size))
+    r = _r_matrix(1)
+    qkv_d = H.bf16_to_dev(qkv, cuda_device)
+    key = qkv_d[:, q_size:q_size + kv_size].view(T, Hkv, D)
+    out = ops.hash_encode_query(key, H.bf16_to_dev(r, cuda_device))
+    torch.cuda.synchronize()
+    xk = qkv[:, q_size:q_size + kv_size].reshape(T, Hkv, D)
+    _check(H.dev_to_u32(out), xk, r)
+
+
+@pytest.mark.parametrize("slot_dtype", ["int64", "int32"])
+@pytest.mark.parametrize("T,Hh", [(1, 8), (100, 8), (700, 4), (33, 1)])
+def test_encode_and_cache(cuda_device, T, Hh, slot_dtype):
+    """Fused encode + scatter into the paged cache; out-of-range slots are skipped."""
+    import torch
+    from unified_cache_management_b200 import ops
+    rng = np.random.default_rng(T * 10 + Hh)
+    NB, BS = 40, 16
+    x = H.bf16_normal(rng, (T, Hh, 128))
+    r = _r_matrix(1)
+    slots = rng.permutation(NB * BS)[:T].astype(np.int64)
+    if T > 3:
+        slots[1] = -1
+        slots[2] = NB * BS + 5
+    cache0 = H.rand_codes(rng, (NB, BS, Hh, 4))
+    cache = H.to_dev_i32(cache0, cuda_device)
+    sl = torch.from_numpy(slots.astype(slot_dtype)).to(cuda_device)
+    ops.hash_encode_and_cache(H.bf16_to_dev(x, cuda_device), sl, cache, H.bf16_to_dev(r, cuda_device))
+    torch.cuda.synchronize()
+    got = H.dev_to_u32(cache).reshape(NB * BS, Hh, 4)
+    want = cache0.reshape(NB * BS, Hh, 4).copy()
+    ok = (slots >= 0) & (slots < NB * BS)
+    codes, p64 = O.hash_encode(x, r)
+    # untouched slots keep their old contents
+    untouched = np.ones(NB * BS, dtype=bool)
+    untouched[slots[ok]] = False
+    assert np.array_equal(got[untouched], want[untouched])
+    hard, soft = O.count_code_mismatches(got[slots[ok]], p64[ok], TOL)
+    assert hard == 0 and soft <= 2
+
+
+@pytest.mark.parametrize("G", [1, 4, 8])
+def test_encode_query_group_mean(cuda_device, G):
+    """Plugin query path: mean over the G heads of a group in bf16, then encode."""
+    import torch
+    from unified_cache_management_b200 import ops
+    rng = np.random.default_rng(G)
+    T, Hkv = 16, 8
+    q = H.bf16_normal(rng, (T, Hkv * G, 128))
+    r = _r_matrix(1)
+    out = ops.hash_encode_query(H.bf16_to_dev(q, cuda_device), H.bf16_to_dev(r, cuda_device), group_mean=G)
+    torch.cuda.synchronize()
+    qm = O.group_mean_bf16(q, Hkv) if G > 1 else q
+    _check(H.dev_to_u32(out), qm, r)
+
+
+@pytest.mark.parametrize("in_dim,bits", [(64, 64), (512, 512), (128, 256), (96, 32)])
+def test_encode_other_shapes(cuda_device, in_dim, bits):
+    """Shapes off the tensor-core path (e.g. the 512/64-wide MLA encoders) run on CUDA cores."""
+    import torch
+    from unified_cache_management_b200 import ops
+    rng = np.random.default_rng(in_dim + bits)
+    x = H.bf16_normal(rng, (77, in_dim))
+    r = _r_matrix(2, in_dim, bits)
+    out = ops.hash_encode(H.bf16_to_dev(x, cuda_device), H.bf16_to_dev(r, cuda_device))
+    torch.cuda.synchronize()
+    _check(H.dev_to_u32(out), x, r)
+
+
+def test_tensor_core_and_cuda_core_paths_agree(cuda_device):
+    """Same rows through both kernels (group_mean=1 with 3 heads cannot tile 128 -> CUDA-core path)."""
+    import torch
+    from unified_cache_management_b200 import ops
+    rng = np.random.default_rng(99)
+    x = H.bf16_normal(rng, (510, 3, 128))
+    r = _r_matrix(1)
+    xd, rd = H.bf16_to_dev(x, cuda_device), H.bf16_to_dev(r, cuda_device)
+    a = ops.hash_encode(xd.reshape(-1, 128), rd)            # tensor cores
+    b = ops.hash_encode_query(xd, rd)                       # H=3 -> CUDA cores
+    torch.cuda.synchronize()
+    _, p64 = O.hash_encode(x.reshape(-1, 128), r)
+    diff = O.unpack_bits_u32(H.dev_to_u32(a)) != O.unpack_bits_u32(H.dev_to_u32(b).reshape(-1, 4))
+    assert (np.abs(p64[diff]) < TOL).all()

@@ -1,0 +1,201 @@
+"""GPU parity: Hamming scan + exact top-k through the C ABI vs the CPU oracle (bit-exact)."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from oracle import oracle_c as OC
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+MODES = {"min": O.REDUCE_MIN, "sum": O.REDUCE_SUM}
+
+
+def _run_dev(case, dev, k, **kw):
+    import torch
+    from unified_cache_management_b200 import ops
+    out = ops.hamming_topk(H.to_dev_i32(case["codes"], dev), H.to_dev_i32(case["q"], dev),
+                           H.to_dev_i32(case["block_table"], dev), H.to_dev_i32(case["seq_lens"], dev), k, **kw)
+    torch.cuda.synchronize()
+    return out
+
+
+def _cmp(out, ref):
+    for name in ("logical", "physical", "scores", "valid_count", "new_seq_lens"):
+        got = getattr(out, name).cpu().numpy()
+        want = np.asarray(ref[name])
+        assert np.array_equal(got, want), f"{name} differs"
+
+
+@pytest.mark.parametrize("mode", ["min", "sum"])
+@pytest.mark.parametrize("reduce_kvhead", [False, True])
+@pytest.mark.parametrize("shape", [
+    # (B, Hkv, G, W, BS, max_blocks)
+    (3, 8, 4, 4, 128, 12),   # the Llama-3-8B layer shape
+    (2, 1, 4, 4, 128, 40),   # one kv head per device (TP=8): several blocks per CTA
+    (2, 2, 8, 4, 128, 17),   # Llama-3-70B at TP=4
+    (2, 8, 4, 8, 64, 20),    # 256-bit codes, block 64
+    (2, 4, 1, 4, 16, 33),    # plugin path: one code per kv head, vLLM block 16
+    (2, 8, 1, 16, 32, 9),    # 512-bit codes
+    (1, 2, 3, 4, 128, 6),    # G outside {1,2,4,8}: query codes in shared memory
+    (2, 1, 16, 18, 64, 7),   # 576-bit MLA codes, W=18: generic kernel
+    (2, 3, 2, 4, 128, 5),    # non power-of-two kv heads: generic kernel
+])
+def test_topk_matches_oracle(cuda_device, shape, mode, reduce_kvhead):
+    B, Hkv, G, W, BS, mb = shape
+    case = H.make_paged_case(hash(shape) % 1000, B, Hkv, G, W, BS, mb)
+    k = min(5, mb)
+    kw = dict(must_select=(0, -2, -1))
+    out = _run_dev(case, cuda_device, k, reduce=mode, reduce_kvhead=reduce_kvhead, **kw)
+    ref = O.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], k, MODES[mode],
+                         reduce_kvhead, **kw)
+    _cmp(out, ref)
+
+
+def test_block_scores_match_oracle(cuda_device):
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    for mode in ("min", "sum"):
+        for red in (False, True):
+            case = H.make_paged_case(5, 4, 8, 4, 4, 128, 9)
+            s = ops.block_scores(H.to_dev_i32(case["codes"], dev), H.to_dev_i32(case["q"], dev),
+                                 H.to_dev_i32(case["block_table"], dev), H.to_dev_i32(case["seq_lens"], dev),
+                                 reduce=mode, reduce_kvhead=red)
+            torch.cuda.synchronize()
+            want = O.block_scores(case["codes"], case["q"], case["block_table"], case["seq_lens"], MODES[mode], red)
+            assert np.array_equal(s.cpu().numpy(), want)
+
+
+def test_sink_recent_and_ragged(cuda_device):
+    """Plugin-style forcing by token ranges; seq_lens not multiples of the block; k above the valid blocks."""
+    B, Hkv, G, W, BS, mb = 5, 8, 1, 4, 16, 24
+    case = H.make_paged_case(11, B, Hkv, G, W, BS, mb, seq_lens=[1, 17, 100, 383, 384])
+    k = 8
+    kw = dict(sink_tokens=BS, recent_tokens=4 * BS)
+    out = _run_dev(case, cuda_device, k, reduce="min", reduce_kvhead=True, **kw)
+    ref = O.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], k, O.REDUCE_MIN, True, **kw)
+    _cmp(out, ref)
+    # fewer valid blocks than k: the tail points at block-table padding, valid_count says how many are real
+    assert out.valid_count.cpu().tolist() == [1, 2, 7, 8, 8]
+
+
+def test_ties_break_by_lower_id(cuda_device):
+    """All keys equal: the selection must be the first k ids; duplicated scores split at the boundary."""
+    B, Hkv, G, W, BS, mb = 2, 2, 1, 4, 16, 50
+    case = H.make_paged_case(3, B, Hkv, G, W, BS, mb, seq_lens=[mb * BS, mb * BS])
+    case["codes"][:] = 0x12345678   # every token identical -> every block score identical
+    out = _run_dev(case, cuda_device, 7, reduce="sum")
+    assert np.array_equal(out.logical.cpu().numpy(), np.broadcast_to(np.arange(7, dtype=np.int32), (B, Hkv, 7)))
+    ref = O.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], 7, O.REDUCE_SUM)
+    _cmp(out, ref)
+    # two score values only: the boundary falls inside a run of equal scores
+    case["codes"][case["block_table"][0, 10:30]] = 0x0F0F0F0F
+    out = _run_dev(case, cuda_device, 25, reduce="sum")
+    ref = O.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], 25, O.REDUCE_SUM)
+    _cmp(out, ref)
+
+
+def test_k_per_request_and_mask(cuda_device):
+    import torch
+    B, Hkv, G, W, BS, mb = 4, 4, 2, 4, 32, 16
+    case = H.make_paged_case(21, B, Hkv, G, W, BS, mb, seq_lens=[512, 300, 64, 512])
+    kpr = np.array([6, 2, 6, 0], dtype=np.int32)
+    mask = np.array([1, 1, 0, 1], dtype=np.uint8)
+    dev = cuda_device
+    out = _run_dev(case, dev, 6, reduce="min", must_select=(0, -1),
+                   k_per_request=torch.from_numpy(kpr).to(dev), request_mask=torch.from_numpy(mask).to(dev))
+    ref = O.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], 6, O.REDUCE_MIN, False,
+                         must_select=(0, -1), k_per_request=kpr, request_mask=mask)
+    _cmp(out, ref)
+
+
+def test_strided_block_table_and_empty_batch(cuda_device):
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    case = H.make_paged_case(8, 3, 8, 4, 4, 128, 10)
+    wide = np.zeros((3, 37), dtype=np.int32)
+    wide[:, :10] = case["block_table"]
+    bt = torch.from_numpy(wide).to(dev)[:, :10]          # row stride 37
+    out = ops.hamming_topk(H.to_dev_i32(case["codes"], dev), H.to_dev_i32(case["q"], dev), bt,
+                           H.to_dev_i32(case["seq_lens"], dev), 4, reduce="sum", must_select=(0, -2, -1))
+    ref = O.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], 4, O.REDUCE_SUM,
+                         must_select=(0, -2, -1))
+    torch.cuda.synchronize()
+    _cmp(out, ref)
+    empty = ops.hamming_topk(H.to_dev_i32(case["codes"], dev), torch.empty((0, 32, 4), dtype=torch.int32, device=dev),
+                             torch.empty((0, 10), dtype=torch.int32, device=dev),
+                             torch.empty((0,), dtype=torch.int32, device=dev), 4)
+    assert empty.physical.shape == (0, 8, 4)
+
+
+def test_bad_block_id_is_flagged_not_read(cuda_device):
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    case = H.make_paged_case(9, 2, 8, 4, 4, 128, 6, seq_lens=[768, 768])
+    case["block_table"][1, 2] = case["NB"] + 1000   # outside the pool
+    ws = ops.new_workspace(2, 8, 6, dev)
+    out = ops.hamming_topk(H.to_dev_i32(case["codes"], dev), H.to_dev_i32(case["q"], dev),
+                           H.to_dev_i32(case["block_table"], dev), H.to_dev_i32(case["seq_lens"], dev), 3,
+                           workspace=ws)
+    assert ops.workspace_status(ws) & 1
+    assert 2 not in out.logical[1].cpu().numpy()     # the bad block scores as invalid
+
+
+def test_argument_errors(cuda_device):
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    case = H.make_paged_case(1, 2, 8, 4, 4, 128, 6)
+    c, q, bt, sl = (H.to_dev_i32(case[n], dev) for n in ("codes", "q", "block_table", "seq_lens"))
+    with pytest.raises(ValueError):
+        ops.hamming_topk(c, q, bt, sl, 7)                      # k > max_blocks
+    with pytest.raises(RuntimeError):
+        ops.hamming_topk(c, q, bt[:1], sl, 2)                  # batch mismatch (reference: TORCH_CHECK)
+    with pytest.raises(ValueError):
+        ops.hamming_topk(c, q[:, :30], bt, sl, 2)              # heads not a multiple
+    with pytest.raises(ValueError):
+        ops.hamming_topk(c, q, bt, sl, 2, reduce="median")
+
+
+def test_hamming_score_per_token(cuda_device):
+    """The old op's fp16 per-token output (sink/recent -> 0, past the end -> inf)."""
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    B, Hkv, G, W, BS, mb = 3, 4, 2, 4, 16, 12
+    case = H.make_paged_case(31, B, Hkv, G, W, BS, mb)
+    for red in (True, False):
+        got = ops.hamming_score(H.to_dev_i32(case["codes"], dev), H.to_dev_i32(case["q"], dev).unsqueeze(1),
+                                H.to_dev_i32(case["block_table"], dev), H.to_dev_i32(case["seq_lens"], dev),
+                                mb * BS, BS, 2 * BS, red)
+        torch.cuda.synchronize()
+        want = O.hamming_score_fp16(case["codes"], case["q"], case["block_table"], case["seq_lens"], BS, 2 * BS, red)
+        assert np.array_equal(got.cpu().numpy().view(np.uint16), want.view(np.uint16))
+
+
+def test_config0_full_size(cuda_device):
+    """Benchmark config 0 at full size: 32768 tokens, 8 kv heads, 32 query heads, 128-bit codes, k=64."""
+    rng = np.random.default_rng(0)
+    B, Hkv, G, W, BS, mb = 1, 8, 4, 4, 128, 256
+    case = H.make_paged_case(0, B, Hkv, G, W, BS, mb, seq_lens=[32768])
+    for red in (False, True):
+        out = _run_dev(case, cuda_device, 64, reduce="sum", reduce_kvhead=red, must_select=(0, -2, -1))
+        ref = OC.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], 64, O.REDUCE_SUM, red,
+                              must_select=(0, -2, -1))
+        _cmp(out, ref)
+        lg = out.logical.cpu().numpy()
+        assert (lg[..., 0] == 0).all() and (lg[..., -1] == 255).all() and (lg[..., -2] == 254).all()
+        assert (np.diff(lg, axis=-1) > 0).all()
+
+
+def test_large_row_select(cuda_device):
+    """65536 blocks per request (the million-token shape): keys do not all fit in shared memory."""
+    B, Hkv, G, W, BS, mb = 1, 1, 1, 4, 2, 65536
+    case = H.make_paged_case(4, B, Hkv, G, W, BS, mb, seq_lens=[mb * BS], identity=True)
+    out = _run_dev(case, cuda_device, 256, reduce="sum", must_select=(0, -2, -1))
+    ref = OC.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], 256, O.REDUCE_SUM, False,
+                          must_select=(0, -2, -1))
+    _cmp(out, ref)

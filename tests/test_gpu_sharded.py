@@ -1,0 +1,73 @@
+"""GPU parity: sequence-sharded retrieval (local candidates + merge) on one device.
+
+The shards are processed one after the other on the same GPU and their records concatenated the way
+an all-gather would deliver them; the merged result must equal the unsharded top-k.
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("R", [2, 8])
+@pytest.mark.parametrize("reduce_kvhead", [False, True])
+def test_sharded_equals_unsharded(cuda_device, R, reduce_kvhead):
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    B, Hkv, G, W, BS = 2, 8, 4, 8, 64
+    nblk = 64 * R
+    k = 24
+    seq = np.array([nblk * BS, nblk * BS - 3 * BS - 5], dtype=np.int32)   # second request is ragged
+    case = H.make_paged_case(40 + R, B, Hkv, G, W, BS, nblk, seq_lens=seq)
+    must = (0, -2, -1)
+    scale = 1.0 / (BS * G)
+    codes, q = H.to_dev_i32(case["codes"], dev), H.to_dev_i32(case["q"], dev)
+    seq_g = H.to_dev_i32(seq, dev)
+    per = nblk // R
+    cs, ci = [], []
+    for r in range(R):
+        bt_local = np.ascontiguousarray(case["block_table"][:, r * per:(r + 1) * per])
+        seq_local = np.clip(seq - r * per * BS, 0, per * BS).astype(np.int32)
+        s, i = ops.topk_candidates(codes, q, H.to_dev_i32(bt_local, dev), H.to_dev_i32(seq_local, dev), seq_g, k,
+                                   r * per, scale, reduce="sum", reduce_kvhead=reduce_kvhead, must_select=must)
+        # oracle for the shard
+        forced = np.stack([O.forced_blocks(seq[b], BS, nblk, must)[r * per:(r + 1) * per] for b in range(B)])
+        ws, wi = O.topk_candidates(case["codes"], case["q"], bt_local, seq_local, k, r * per, scale, forced,
+                                   O.REDUCE_SUM, reduce_kvhead)
+        torch.cuda.synchronize()
+        assert np.array_equal(i.cpu().numpy(), wi)
+        assert np.array_equal(s.cpu().numpy().view(np.uint32), ws.view(np.uint32))
+        cs.append(s)
+        ci.append(i)
+    ms, mi = ops.merge_topk(torch.stack(cs), torch.stack(ci), k)
+    torch.cuda.synchronize()
+    full = O.hamming_topk(case["codes"], case["q"], case["block_table"], seq, k, O.REDUCE_SUM, reduce_kvhead,
+                          must_select=must)
+    assert np.array_equal(mi.cpu().numpy(), full["logical"])
+    ws, wi = O.merge_topk(np.stack([c.cpu().numpy() for c in cs]), np.stack([c.cpu().numpy() for c in ci]), k)
+    assert np.array_equal(mi.cpu().numpy(), wi)
+    assert np.array_equal(ms.cpu().numpy().view(np.uint32), ws.view(np.uint32))
+
+
+def test_merge_with_short_shards(cuda_device):
+    """Shards that hold fewer than k blocks pad with (+inf, -1); padding never wins over a real record."""
+    import torch
+    from unified_cache_management_b200 import ops
+    rng = np.random.default_rng(5)
+    R, B, Hh, kl, k = 4, 2, 3, 16, 20
+    sc = rng.integers(0, 50, size=(R, B, Hh, kl)).astype(np.float32) / 8
+    ids = np.sort(rng.permutation(1000)[:R * kl]).reshape(R, 1, 1, kl).repeat(B, 1).repeat(Hh, 2).astype(np.int32)
+    sc[1, :, :, 5:] = np.inf
+    ids = ids.copy()
+    ids[1, :, :, 5:] = -1
+    sc[3, 0] = np.inf
+    ids[3, 0] = -1
+    ms, mi = ops.merge_topk(torch.from_numpy(sc).to(cuda_device), torch.from_numpy(ids).to(cuda_device), k)
+    torch.cuda.synchronize()
+    ws, wi = O.merge_topk(sc, ids, k)
+    assert np.array_equal(mi.cpu().numpy(), wi)
+    assert np.array_equal(ms.cpu().numpy().view(np.uint32), ws.view(np.uint32))

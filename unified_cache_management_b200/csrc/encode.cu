@@ -1,0 +1,509 @@
+// Hash encode (sm_100a): codes = signbits(X * R), X bf16 rows, R bf16 [in_dim, hash_bits].
+//
+// Tensor-core path (in_dim = hash_bits = 128): persistent, warp-specialised CTA per SM.
+//   warp 0   TMA producer: 128-row X tiles (two 64-column boxes, 128-byte swizzle) into a ring of
+//            shared-memory stages.
+//   warp 1   allocates TMEM; one thread issues eight tcgen05.mma (M=128, N=128, K=16) per tile into
+//            one of two 128-column fp32 accumulators and commits to the stage's / accumulator's
+//            mbarrier.
+//   warps 2-5 epilogue: tcgen05.ld gives each thread one full row of the accumulator; the thread
+//            packs the 128 sign bits into four words and issues a single 16-byte store (to the
+//            output array, or to the row's slot in the paged code cache).
+// R^T is written once per CTA into shared memory in the K-major 128-byte-swizzled layout the MMA
+// descriptors expect; every CTA keeps its own copy.  X is read exactly once from HBM; the only
+// other traffic is 16 bytes per row out.  All mbarrier waits are time-bounded.
+//
+// CUDA-core path: any in_dim / hash_bits (multiples of 32), optional group mean over G query heads
+// with one rounding to bf16; used for the decode-step query codes of the plugin path and for
+// shapes the tensor-core path does not cover.
+//
+// Stands in for triton_hash_code_kernel, fused_hash_and_cache_kernel and
+// _reshape_and_cache_khash_kernel (ucm/sparse/gsa_on_device/hash_encoder.py:37-134, 263-356,
+// 136-261); numerics follow torch_hash_code (:359-370): fp32 accumulate, strict "> 0".
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace ucmr {
+
+// ---------------------------------------------------------------------------------------------
+// tensor-core path
+// ---------------------------------------------------------------------------------------------
+constexpr int kEncTileM = 128;
+constexpr int kEncD = 128;      // in_dim
+constexpr int kEncBits = 128;   // hash_bits
+constexpr int kEncStages = 5;   // X ring depth (32 KiB each)
+constexpr int kEncAccs = 2;     // TMEM accumulators
+constexpr int kEncThreads = 192;
+constexpr int kEncHalfBytes = kEncTileM * 128;          // one 64-column box: 128 rows x 128 B
+constexpr int kEncStageBytes = 2 * kEncHalfBytes;       // 32 KiB
+constexpr int kEncTmemCols = kEncAccs * kEncBits;       // 256
+constexpr size_t kEncSmemBytes = 1024 /*align slack*/ + 2 * kEncHalfBytes /*R^T*/ +
+                                 (size_t)kEncStages * kEncStageBytes + 256 /*barriers*/;
+
+struct EncParams {
+    int64_t rows;    // T * H
+    int H;           // rows per token (heads)
+    int64_t n_tiles;
+    uint32_t* out;   // direct: [rows, 4]; paged: cache [NB*BS, H, 4]
+    const void* slot_mapping;  // null = direct
+    int slot_is_int64;
+    int64_t n_slots;           // NB * BS
+    const __nv_bfloat16* R;    // [128, 128] row-major
+    int32_t* status;           // may be null
+};
+
+__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr)
+{
+    // K-major, 128-byte swizzle: start address >> 4, leading byte offset 1 (unused), stride byte
+    // offset 1024 >> 4 between 8-row groups, descriptor version 1, layout type 2 (SWIZZLE_128B).
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// kind::f16 instruction descriptor: D = f32, A = B = bf16, both K-major, N = 128, M = 128.
+constexpr uint32_t kEncIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kEncBits >> 3) << 17) | ((kEncTileM >> 4) << 24);
+
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int x, int y, int z,
+                                            uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
+            "r"(smem_u32(smem_dst)),
+        "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_commit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack_signs(const uint32_t (&r)[32])
+{
+    uint32_t w = 0;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) w |= (uint32_t)(__uint_as_float(r[i]) > 0.0f) << i;
+    return w;
+}
+
+__global__ void __launch_bounds__(kEncThreads, 1)
+encode_tc_kernel(const __grid_constant__ CUtensorMap x_map, const EncParams p)
+{
+    extern __shared__ uint8_t s_raw[];
+    // 1024-byte alignment: the swizzle pattern is a function of the shared-memory address bits
+    uint8_t* s_base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(s_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* s_b = s_base;                                  // R^T, two K halves of [128 n][64 k]
+    uint8_t* s_a = s_base + 2 * kEncHalfBytes;              // stages
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_a + (size_t)kEncStages * kEncStageBytes);
+    uint64_t* full = bars;                       // [kEncStages]
+    uint64_t* empty = bars + kEncStages;         // [kEncStages]
+    uint64_t* acc_full = bars + 2 * kEncStages;  // [kEncAccs]
+    uint64_t* acc_empty = acc_full + kEncAccs;   // [kEncAccs]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kEncAccs);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    if (tid == 0) {
+        for (int s = 0; s < kEncStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < kEncAccs; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+        fence_mbar_init();
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&x_map) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)kEncTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // R[k][n] (row-major) -> B[n][k] K-major with the 128-byte swizzle: 16-byte chunk c of row n
+    // lives at chunk c ^ (n & 7) of that row.
+    for (int i = tid; i < kEncD * (kEncBits / 8); i += kEncThreads) {
+        const int k = i / (kEncBits / 8), n0 = (i % (kEncBits / 8)) * 8;
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.R + (size_t)k * kEncBits + n0));
+        const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
+        const int half = k >> 6, kk = k & 63, chunk = kk >> 3;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int n = n0 + j;
+            const uint32_t off = (uint32_t)half * kEncHalfBytes + (uint32_t)n * 128u +
+                                 ((uint32_t)(chunk ^ (n & 7)) << 4) + (uint32_t)(kk & 7) * 2u;
+            *reinterpret_cast<uint16_t*>(s_b + off) = e[j];
+        }
+    }
+    fence_proxy_async();  // generic-proxy writes of R^T become visible to the MMA's async-proxy reads
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int64_t first = blockIdx.x, step = gridDim.x;
+    const int64_t my_tiles = first < p.n_tiles ? (p.n_tiles - first + step - 1) / step : 0;
+    const int tok_per_tile = kEncTileM / p.H;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int64_t it = 0; it < my_tiles; ++it) {
+                const int s = (int)(it % kEncStages);
+                const uint32_t ph = (uint32_t)((it / kEncStages) & 1);
+                if (!mbar_wait(&empty[s], ph ^ 1u)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
+                const int64_t tile = first + it * step;
+                const int t0 = (int)(tile * tok_per_tile);
+                uint8_t* dst = s_a + (size_t)s * kEncStageBytes;
+                mbar_expect_tx(&full[s], kEncStageBytes);
+                tma_load_3d(dst, &x_map, 0, 0, t0, &full[s]);
+                tma_load_3d(dst + kEncHalfBytes, &x_map, 64, 0, t0, &full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t b_addr = smem_u32(s_b);
+            for (int64_t it = 0; it < my_tiles; ++it) {
+                const int s = (int)(it % kEncStages);
+                const uint32_t ph = (uint32_t)((it / kEncStages) & 1);
+                const int a = (int)(it % kEncAccs);
+                const uint32_t aph = (uint32_t)((it / kEncAccs) & 1);
+                if (!mbar_wait(&acc_empty[a], aph ^ 1u) || !mbar_wait(&full[s], ph)) {
+                    flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(s_a + (size_t)s * kEncStageBytes);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(a * kEncBits);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint32_t off = (uint32_t)half * kEncHalfBytes + (uint32_t)ks * 32u;
+                        tc_mma_bf16(d_tmem, make_smem_desc_sw128(a_addr + off), make_smem_desc_sw128(b_addr + off),
+                                    kEncIdesc, (half | ks) ? 1u : 0u);
+                    }
+                }
+                tc_commit(&empty[s]);     // the stage may be refilled once these MMAs have read it
+                tc_commit(&acc_full[a]);  // the accumulator is complete
+            }
+        }
+    } else {
+        const int q = warp & 3;  // TMEM lane quadrant this warp may read
+        for (int64_t it = 0; it < my_tiles; ++it) {
+            const int a = (int)(it % kEncAccs);
+            const uint32_t aph = (uint32_t)((it / kEncAccs) & 1);
+            if (!mbar_wait(&acc_full[a], aph)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kEncBits);
+            uint4 code;
+            uint32_t r[32];
+            tc_ld32(taddr + 0, r);  tc_wait_ld(); code.x = pack_signs(r);
+            tc_ld32(taddr + 32, r); tc_wait_ld(); code.y = pack_signs(r);
+            tc_ld32(taddr + 64, r); tc_wait_ld(); code.z = pack_signs(r);
+            tc_ld32(taddr + 96, r); tc_wait_ld(); code.w = pack_signs(r);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[a]);
+            const int64_t tile = first + it * step;
+            const int64_t row = tile * kEncTileM + q * 32 + lane;
+            if (row < p.rows) {
+                if (p.slot_mapping == nullptr) {
+                    *reinterpret_cast<uint4*>(p.out + row * 4) = code;
+                } else {
+                    const int64_t tok = row / p.H;
+                    const int h = (int)(row - tok * p.H);
+                    const int64_t slot = p.slot_is_int64 ? static_cast<const int64_t*>(p.slot_mapping)[tok]
+                                                         : (int64_t) static_cast<const int32_t*>(p.slot_mapping)[tok];
+                    if (slot >= 0 && slot < p.n_slots)
+                        *reinterpret_cast<uint4*>(p.out + (slot * p.H + h) * 4) = code;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kEncTmemCols)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// CUDA-core path
+// ---------------------------------------------------------------------------------------------
+constexpr int kSimtThreads = 128;
+constexpr int kSimtRowsPerWarp = 4;
+constexpr int kSimtRowsPerCta = kSimtRowsPerWarp * (kSimtThreads / 32);
+
+struct SimtParams {
+    const __nv_bfloat16* x;
+    int64_t T;
+    int H_in, G;  // input heads per token; G consecutive heads are averaged (1 = none)
+    int64_t stride_t, stride_h;
+    const __nv_bfloat16* R;
+    int in_dim, bits;
+    uint32_t* out;  // direct: [T*H_out, W]; paged: [n_slots, H_out, W]
+    const void* slot_mapping;
+    int slot_is_int64;
+    int64_t n_slots;
+};
+
+__global__ void __launch_bounds__(kSimtThreads) encode_simt_kernel(const SimtParams p)
+{
+    extern __shared__ float s_x[];  // [kSimtRowsPerCta][in_dim]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int H_out = p.H_in / p.G;
+    const int64_t rows = p.T * H_out;
+    const int64_t row0 = (int64_t)blockIdx.x * kSimtRowsPerCta;
+    const int W = p.bits / 32;
+
+    for (int i = tid; i < kSimtRowsPerCta * p.in_dim; i += kSimtThreads) {
+        const int r = i / p.in_dim, k = i - r * p.in_dim;
+        const int64_t row = row0 + r;
+        float v = 0.f;
+        if (row < rows) {
+            const int64_t t = row / H_out;
+            const int ho = (int)(row - t * H_out);
+            const __nv_bfloat16* src = p.x + t * p.stride_t + (int64_t)ho * p.G * p.stride_h + k;
+            if (p.G == 1) {
+                v = __bfloat162float(*src);
+            } else {
+                float acc = 0.f;
+                for (int g = 0; g < p.G; ++g) acc += __bfloat162float(src[(int64_t)g * p.stride_h]);
+                v = __bfloat162float(__float2bfloat16_rn(acc / (float)p.G));
+            }
+        }
+        s_x[i] = v;
+    }
+    __syncthreads();
+
+    const float* xr = s_x + warp * kSimtRowsPerWarp * p.in_dim;
+    for (int w0 = 0; w0 < W; w0 += 4) {
+        float acc[kSimtRowsPerWarp][4];
+#pragma unroll
+        for (int r = 0; r < kSimtRowsPerWarp; ++r)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
+        const int wn = min(4, W - w0);
+        for (int k = 0; k < p.in_dim; ++k) {
+            float rv[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                rv[c] = (c < wn) ? __bfloat162float(p.R[(size_t)k * p.bits + (w0 + c) * 32 + lane]) : 0.f;
+#pragma unroll
+            for (int r = 0; r < kSimtRowsPerWarp; ++r) {
+                const float xv = xr[r * p.in_dim + k];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[r][c] = fmaf(xv, rv[c], acc[r][c]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kSimtRowsPerWarp; ++r) {
+            const int64_t row = row0 + warp * kSimtRowsPerWarp + r;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t word = __ballot_sync(0xffffffffu, acc[r][c] > 0.f);
+                if (lane == 0 && c < wn && row < rows) {
+                    int64_t dst_row = row;
+                    if (p.slot_mapping != nullptr) {
+                        const int64_t t = row / H_out;
+                        const int ho = (int)(row - t * H_out);
+                        const int64_t slot = p.slot_is_int64 ? static_cast<const int64_t*>(p.slot_mapping)[t]
+                                                             : (int64_t) static_cast<const int32_t*>(p.slot_mapping)[t];
+                        dst_row = (slot >= 0 && slot < p.n_slots) ? slot * H_out + ho : -1;
+                    }
+                    if (dst_row >= 0) p.out[dst_row * W + w0 + c] = word;
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_tiled()
+{
+    static EncodeTiledFn fn = nullptr;  // resolving twice is harmless
+    if (fn) return fn;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !ptr) {
+        if (e != cudaSuccess) note_cuda_error(e);
+        return nullptr;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    return fn;
+}
+
+static bool tc_path_ok(const void* x, int64_t T, int H, int64_t stride_t, int64_t stride_h, int in_dim, int bits)
+{
+    if (in_dim != kEncD || bits != kEncBits) return false;
+    if (H <= 0 || H > kEncTileM || kEncTileM % H != 0) return false;
+    if (reinterpret_cast<uintptr_t>(x) % 16 != 0) return false;
+    if (stride_t % 8 != 0 || (H > 1 && stride_h % 8 != 0)) return false;
+    if (stride_h < in_dim && H > 1) return false;
+    if (T <= 0 || T > 0x7FFFFFFF) return false;
+    if ((uint64_t)stride_t * 2 >= (1ull << 40) || (uint64_t)stride_h * 2 >= (1ull << 40)) return false;
+    return true;
+}
+
+static int launch_tc(const void* x, int64_t T, int H, int64_t stride_t, int64_t stride_h, const void* R,
+                     uint32_t* out, const void* slot_mapping, int slot_is_int64, int64_t n_slots,
+                     int32_t* status, cudaStream_t st)
+{
+    EncodeTiledFn encode = get_encode_tiled();
+    if (!encode) return UCMR_ERR_LAUNCH;
+    CUtensorMap map;
+    const cuuint64_t dims[3] = {(cuuint64_t)kEncD, (cuuint64_t)H, (cuuint64_t)T};
+    const cuuint64_t strides[2] = {(cuuint64_t)(H > 1 ? stride_h : kEncD) * 2, (cuuint64_t)stride_t * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)H, (cuuint32_t)(kEncTileM / H)};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(x), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return UCMR_ERR_LAUNCH;
+
+    EncParams p{};
+    p.rows = T * H; p.H = H;
+    const int tok_per_tile = kEncTileM / H;
+    p.n_tiles = (T + tok_per_tile - 1) / tok_per_tile;
+    p.out = out; p.slot_mapping = slot_mapping; p.slot_is_int64 = slot_is_int64; p.n_slots = n_slots;
+    p.R = static_cast<const __nv_bfloat16*>(R); p.status = status;
+
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(encode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kEncSmemBytes);
+        if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
+        attr_set = true;
+    }
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = (int)(p.n_tiles < sms ? p.n_tiles : sms);
+    encode_tc_kernel<<<grid, kEncThreads, kEncSmemBytes, st>>>(map, p);
+    return check_launch();
+}
+
+static int launch_simt(const void* x, int64_t T, int H_in, int G, int64_t stride_t, int64_t stride_h, const void* R,
+                       int in_dim, int bits, uint32_t* out, const void* slot_mapping, int slot_is_int64,
+                       int64_t n_slots, cudaStream_t st)
+{
+    SimtParams p{};
+    p.x = static_cast<const __nv_bfloat16*>(x); p.T = T; p.H_in = H_in; p.G = G;
+    p.stride_t = stride_t; p.stride_h = stride_h;
+    p.R = static_cast<const __nv_bfloat16*>(R); p.in_dim = in_dim; p.bits = bits;
+    p.out = out; p.slot_mapping = slot_mapping; p.slot_is_int64 = slot_is_int64; p.n_slots = n_slots;
+    const int64_t rows = T * (H_in / G);
+    const int64_t grid = (rows + kSimtRowsPerCta - 1) / kSimtRowsPerCta;
+    if (grid > 0x7FFFFFFF) return UCMR_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)kSimtRowsPerCta * in_dim * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(encode_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
+    }
+    encode_simt_kernel<<<(int)grid, kSimtThreads, smem, st>>>(p);
+    return check_launch();
+}
+
+static int check_dims(int in_dim, int bits)
+{
+    if (in_dim <= 0 || bits <= 0) return UCMR_ERR_BAD_ARG;
+    if (bits % 32 != 0 || in_dim > 1024 || bits > 1024) return UCMR_ERR_UNSUPPORTED;
+    return UCMR_OK;
+}
+
+// UCMR_FORCE_SIMT_ENCODE=1 routes every encode through the CUDA-core kernel (debug aid).
+static bool force_simt()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("UCMR_FORCE_SIMT_ENCODE");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+
+}  // namespace ucmr
+
+using namespace ucmr;
+
+extern "C" int ucmr_hash_encode(const void* x, int64_t rows, int64_t row_stride, const void* R, int in_dim,
+                                int hash_bits, uint32_t* codes_out, int32_t* status_word, void* stream)
+{
+    if (!x || !R || !codes_out || rows < 0 || row_stride < in_dim) return UCMR_ERR_BAD_ARG;
+    int rc = check_dims(in_dim, hash_bits);
+    if (rc != UCMR_OK) return rc;
+    if (rows == 0) return UCMR_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!force_simt() && tc_path_ok(x, rows, 1, row_stride, in_dim, in_dim, hash_bits) &&
+        reinterpret_cast<uintptr_t>(codes_out) % 16 == 0 && reinterpret_cast<uintptr_t>(R) % 16 == 0)
+        return launch_tc(x, rows, 1, row_stride, in_dim, R, codes_out, nullptr, 0, 0, status_word, st);
+    return launch_simt(x, rows, 1, 1, row_stride, in_dim, R, in_dim, hash_bits, codes_out, nullptr, 0, 0, st);
+}
+
+extern "C" int ucmr_hash_encode_query(const void* q, int64_t T, int Hq, int64_t stride_t, int64_t stride_h,
+                                      int group_mean, const void* R, int in_dim, int hash_bits,
+                                      uint32_t* codes_out, int32_t* status_word, void* stream)
+{
+    if (!q || !R || !codes_out || T < 0 || Hq <= 0 || group_mean <= 0 || Hq % group_mean != 0) return UCMR_ERR_BAD_ARG;
+    if (stride_h < in_dim || stride_t < in_dim) return UCMR_ERR_BAD_ARG;
+    int rc = check_dims(in_dim, hash_bits);
+    if (rc != UCMR_OK) return rc;
+    if (T == 0) return UCMR_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (group_mean == 1 && !force_simt() && tc_path_ok(q, T, Hq, stride_t, stride_h, in_dim, hash_bits) &&
+        reinterpret_cast<uintptr_t>(codes_out) % 16 == 0 && reinterpret_cast<uintptr_t>(R) % 16 == 0)
+        return launch_tc(q, T, Hq, stride_t, stride_h, R, codes_out, nullptr, 0, 0, status_word, st);
+    return launch_simt(q, T, Hq, group_mean, stride_t, stride_h, R, in_dim, hash_bits, codes_out, nullptr, 0, 0, st);
+}
+
+extern "C" int ucmr_hash_encode_and_cache(const void* x, int64_t T, int H, int64_t stride_t, int64_t stride_h,
+                                          const void* R, int in_dim, int hash_bits, const void* slot_mapping,
+                                          int slot_is_int64, uint32_t* cache, int64_t NB, int BS,
+                                          int32_t* status_word, void* stream)
+{
+    if (!x || !R || !slot_mapping || !cache || T < 0 || H <= 0 || NB <= 0 || BS <= 0) return UCMR_ERR_BAD_ARG;
+    if (stride_h < in_dim || stride_t < in_dim) return UCMR_ERR_BAD_ARG;
+    int rc = check_dims(in_dim, hash_bits);
+    if (rc != UCMR_OK) return rc;
+    if (T == 0) return UCMR_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t n_slots = NB * BS;
+    if (!force_simt() && tc_path_ok(x, T, H, stride_t, stride_h, in_dim, hash_bits) &&
+        reinterpret_cast<uintptr_t>(cache) % 16 == 0 && reinterpret_cast<uintptr_t>(R) % 16 == 0)
+        return launch_tc(x, T, H, stride_t, stride_h, R, cache, slot_mapping, slot_is_int64 ? 1 : 0, n_slots, status_word, st);
+    return launch_simt(x, T, H, 1, stride_t, stride_h, R, in_dim, hash_bits, cache, slot_mapping,
+                       slot_is_int64 ? 1 : 0, n_slots, st);
+}

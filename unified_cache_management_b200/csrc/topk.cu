@@ -1,0 +1,454 @@
+// Exact per-row top-k over block scores (sm_100a): radix select in shared memory + ordered
+// compaction.  One CTA per (request, kv head) row.
+//
+// Each candidate j has a 32-bit key (forced block -> 0, valid block -> score + 1, past the
+// request's length -> 0xFFFFFFFF).  Four 8-bit histogram passes find the k-th smallest key T and how
+// many keys equal to T are still needed; a single ordered pass then emits every j with key < T and
+// the first `need` j with key == T, which is exactly "first k under (key, id)", already in ascending
+// id order.  No sort is involved.
+//
+// Stands in for torch.topk + torch.sort + torch.gather of the reference
+// (ucm/sparse/gsa_on_device/hamming_topk.py:49-54) and for update_seq_lens (:7-12), with the
+// (score, id) total order the reference leaves unspecified.
+#include <limits.h>
+#include <math.h>
+
+#include "common.cuh"
+
+namespace ucmr {
+
+int run_scan(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const uint32_t* q, int Hq,
+             const int32_t* bt, int max_blocks, int64_t bt_stride, const int32_t* seq_lens, int B,
+             int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, cudaStream_t st);
+
+constexpr int kSelThreads = 512;
+constexpr int kSelWarps = kSelThreads / 32;
+constexpr int kSelMaxCachedKeys = 48 * 1024;  // 192 KiB of keys in shared memory at most
+constexpr uint32_t kKeyInvalid = 0xFFFFFFFFu;
+
+struct ForcedSpec {
+    int must[UCMR_MAX_MUST_SELECT];
+    int n_must, sink, recent;
+};
+
+__device__ __forceinline__ bool block_is_forced(const ForcedSpec& f, int j, int nb, int seq, int BS)
+{
+    if (j >= nb) return false;
+    for (int m = 0; m < f.n_must; ++m) {
+        const int t = f.must[m] >= 0 ? f.must[m] : nb + f.must[m];
+        if (t == j) return true;
+    }
+    const int lo = j * BS;
+    const int hi = min(lo + BS, seq);
+    if (f.sink > 0 && lo < f.sink) return true;
+    if (f.recent > 0 && hi > seq - f.recent) return true;
+    return false;
+}
+
+struct SelScratch {
+    int hist[256];
+    int warp_a[kSelWarps], warp_b[kSelWarps];
+    uint32_t prefix;
+    int remaining;
+};
+
+// Finds the first kb entries of keys[0..n) under (key, position) and calls emit(pos, j) for each,
+// pos = rank of j among the chosen in ascending j.  key_of(j) must be pure.  s_keys caches the
+// first n_cached keys.  All threads of the CTA must call this.
+template <typename KeyFn, typename EmitFn>
+__device__ void select_row(int n, int kb, KeyFn key_of, EmitFn emit, uint32_t* s_keys, int n_cached,
+                           SelScratch& sc)
+{
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (kb <= 0 || n <= 0) return;
+    if (kb > n) kb = n;
+
+    for (int j = tid; j < n_cached; j += kSelThreads) s_keys[j] = key_of(j);
+    if (tid == 0) { sc.prefix = 0u; sc.remaining = kb; }
+    __syncthreads();
+    auto get = [&](int j) -> uint32_t { return j < n_cached ? s_keys[j] : key_of(j); };
+
+    uint32_t known = 0u;  // mask of the key bits fixed so far
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int i = tid; i < 256; i += kSelThreads) sc.hist[i] = 0;
+        __syncthreads();
+        const uint32_t prefix = sc.prefix;
+        const int n_round = (n + kSelThreads - 1) / kSelThreads * kSelThreads;
+        for (int j = tid; j < n_round; j += kSelThreads) {
+            const bool in = j < n;
+            const uint32_t key = in ? get(j) : 0u;
+            const bool hit = in && ((key & known) == prefix);
+            const uint32_t digit = hit ? ((key >> shift) & 255u) : 256u;
+            // one atomic per distinct digit in the warp
+            const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+            if (hit && lane == (__ffs(peers) - 1)) atomicAdd(&sc.hist[digit], __popc(peers));
+        }
+        __syncthreads();
+        if (warp == 0) {
+            int loc[8];
+            int sum = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { loc[i] = sc.hist[lane * 8 + i]; sum += loc[i]; }
+            int incl = sum;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, incl, off);
+                if (lane >= off) incl += o;
+            }
+            const int excl = incl - sum;
+            const int rem = sc.remaining;
+            if (rem > excl && rem <= incl) {  // exactly one lane
+                int run = excl;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (rem > run && rem <= run + loc[i]) {
+                        sc.prefix = prefix | ((uint32_t)(lane * 8 + i) << shift);
+                        sc.remaining = rem - run;
+                    }
+                    run += loc[i];
+                }
+            }
+        }
+        known |= 255u << shift;
+        __syncthreads();
+    }
+    const uint32_t T = sc.prefix;
+    const int need = sc.remaining;  // how many keys equal to T are taken, lowest positions first
+
+    const int ipt = (n + kSelThreads - 1) / kSelThreads;
+    const int j_begin = min(n, tid * ipt), j_end = min(n, j_begin + ipt);
+    int lt = 0, eq = 0;
+    for (int j = j_begin; j < j_end; ++j) {
+        const uint32_t key = get(j);
+        lt += key < T;
+        eq += key == T;
+    }
+    int lt_incl = lt, eq_incl = eq;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int a = __shfl_up_sync(0xffffffffu, lt_incl, off);
+        const int b = __shfl_up_sync(0xffffffffu, eq_incl, off);
+        if (lane >= off) { lt_incl += a; eq_incl += b; }
+    }
+    if (lane == 31) { sc.warp_a[warp] = lt_incl; sc.warp_b[warp] = eq_incl; }
+    __syncthreads();
+    int lt_before = lt_incl - lt, eq_before = eq_incl - eq;
+    for (int w = 0; w < warp; ++w) { lt_before += sc.warp_a[w]; eq_before += sc.warp_b[w]; }
+    for (int j = j_begin; j < j_end; ++j) {
+        const uint32_t key = get(j);
+        if (key < T) {
+            emit(lt_before + min(eq_before, need), j);
+            ++lt_before;
+        } else if (key == T) {
+            if (eq_before < need) emit(lt_before + eq_before, j);
+            ++eq_before;
+        }
+    }
+    __syncthreads();
+}
+
+struct SelectParams {
+    const int32_t* scores;  // [B, Hout, max_blocks]
+    int Hout, max_blocks, BS;
+    const int32_t* bt;
+    int64_t bt_stride;
+    const int32_t* seq_local;
+    const int32_t* seq_global;  // null = same as local
+    int k;
+    const int32_t* k_per_request;
+    const uint8_t* mask;
+    ForcedSpec forced;
+    int id_offset;
+    int n_cached;
+    // block-id outputs
+    int32_t *out_phys, *out_logical, *out_scores, *out_valid, *out_newseq;
+    // candidate-record outputs
+    float* cand_scores;
+    int32_t* cand_ids;
+    float scale;
+};
+
+template <bool CANDIDATES>
+__global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams p)
+{
+    extern __shared__ uint32_t s_keys[];
+    __shared__ SelScratch sc;
+    const int tid = threadIdx.x;
+    const int row = blockIdx.x;
+    const int b = row / p.Hout;
+    const int n = p.max_blocks;
+    const int seq_l = p.seq_local[b];
+    const int nb_l = min(n, (seq_l + p.BS - 1) / p.BS);
+    const int seq_g = p.seq_global ? p.seq_global[b] : seq_l;
+    const int nb_g = (seq_g + p.BS - 1) / p.BS;
+    const int32_t* srow = p.scores + (int64_t)row * n;
+    const int32_t* btrow = p.bt + (int64_t)b * p.bt_stride;
+    int kb = p.k;
+    if (p.k_per_request) kb = max(0, min(p.k_per_request[b], p.k));
+    const bool masked = p.mask != nullptr && p.mask[b] == 0;
+    const int64_t obase = (int64_t)row * p.k;
+
+    // padding first; the chosen entries overwrite positions [0, kb)
+    for (int i = tid; i < p.k; i += kSelThreads) {
+        if (CANDIDATES) {
+            p.cand_scores[obase + i] = INFINITY;
+            p.cand_ids[obase + i] = -1;
+        } else {
+            const bool pass = masked && i < kb;
+            p.out_phys[obase + i] = pass ? btrow[i] : 0;
+            if (p.out_logical) p.out_logical[obase + i] = pass ? i : -1;
+            if (p.out_scores) p.out_scores[obase + i] = pass ? (i < nb_l ? srow[i] : -1) : -1;
+        }
+    }
+    if (!CANDIDATES && tid == 0 && row % p.Hout == 0) {
+        if (p.out_valid) p.out_valid[b] = min(kb, nb_l);
+        if (p.out_newseq) {
+            int ns = seq_l;
+            if (!masked) {
+                const int over = max(seq_l - kb * p.BS, 0);
+                ns = seq_l - (over + p.BS - 1) / p.BS * p.BS;
+            }
+            p.out_newseq[b] = ns;
+        }
+    }
+    if (masked) return;
+    __syncthreads();  // padding stores precede the emits of the same CTA
+
+    auto key_of = [&](int j) -> uint32_t {
+        if (j >= nb_l) return kKeyInvalid;
+        const int s = srow[j];
+        if (s < 0) return kKeyInvalid;
+        if (block_is_forced(p.forced, j + p.id_offset, nb_g, seq_g, p.BS)) return 0u;
+        return (uint32_t)s + 1u;
+    };
+    auto emit = [&](int pos, int j) {
+        const bool valid = j < nb_l && srow[j] >= 0;
+        if (CANDIDATES) {
+            if (valid) {
+                const bool forced = block_is_forced(p.forced, j + p.id_offset, nb_g, seq_g, p.BS);
+                p.cand_scores[obase + pos] = forced ? -1.0f : (float)srow[j] * p.scale;
+                p.cand_ids[obase + pos] = j + p.id_offset;
+            }
+        } else {
+            p.out_phys[obase + pos] = btrow[j];
+            if (p.out_logical) p.out_logical[obase + pos] = j;
+            if (p.out_scores) p.out_scores[obase + pos] = valid ? srow[j] : -1;
+        }
+    };
+    select_row(n, kb, key_of, emit, s_keys, p.n_cached, sc);
+}
+
+__device__ __forceinline__ uint32_t f32_order_key(float x)
+{
+    const uint32_t u = __float_as_uint(x);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+struct MergeParams {
+    const float* cand_scores;  // [R, B, H, kl]
+    const int32_t* cand_ids;
+    int R, B, H, kl, k, n_cached;
+    float* out_scores;  // [B, H, k]
+    int32_t* out_ids;
+};
+
+__global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
+{
+    extern __shared__ uint32_t s_keys[];
+    __shared__ SelScratch sc;
+    const int tid = threadIdx.x;
+    const int row = blockIdx.x;  // b*H + h
+    const int n = p.R * p.kl;
+    const int64_t rows = (int64_t)p.B * p.H;
+    const int64_t obase = (int64_t)row * p.k;
+    for (int i = tid; i < p.k; i += kSelThreads) {
+        p.out_scores[obase + i] = INFINITY;
+        p.out_ids[obase + i] = -1;
+    }
+    __syncthreads();
+    auto at = [&](int i) -> int64_t {
+        const int r = i / p.kl, c = i - r * p.kl;
+        return ((int64_t)r * rows + row) * p.kl + c;
+    };
+    auto key_of = [&](int i) -> uint32_t {
+        const int64_t a = at(i);
+        if (p.cand_ids[a] < 0) return kKeyInvalid;
+        const uint32_t key = f32_order_key(p.cand_scores[a]);
+        return key == kKeyInvalid ? kKeyInvalid - 1u : key;
+    };
+    auto emit = [&](int pos, int i) {
+        const int64_t a = at(i);
+        if (p.cand_ids[a] >= 0) {
+            p.out_scores[obase + pos] = p.cand_scores[a];
+            p.out_ids[obase + pos] = p.cand_ids[a];
+        }
+    };
+    select_row(n, min(p.k, n), key_of, emit, s_keys, p.n_cached, sc);
+}
+
+__global__ void update_seq_lens_kernel(const int32_t* seq, int B, int topk_tokens, int BS, int32_t* out)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= B) return;
+    const int s = seq[i];
+    const int over = max(s - topk_tokens, 0);
+    out[i] = s - (over + BS - 1) / BS * BS;
+}
+
+static int fill_forced(ForcedSpec& f, const int32_t* must, int n_must, int sink, int recent)
+{
+    if (n_must < 0 || n_must > UCMR_MAX_MUST_SELECT || (n_must > 0 && !must)) return UCMR_ERR_BAD_ARG;
+    if (sink < 0 || recent < 0) return UCMR_ERR_BAD_ARG;
+    for (int i = 0; i < n_must; ++i) f.must[i] = must[i];
+    f.n_must = n_must; f.sink = sink; f.recent = recent;
+    return UCMR_OK;
+}
+
+template <typename K>
+static int set_dyn_smem(K kernel, size_t bytes)
+{
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
+    }
+    return UCMR_OK;
+}
+
+static size_t scores_bytes(int B, int Hout, int max_blocks)
+{
+    size_t b = (size_t)B * Hout * max_blocks * sizeof(int32_t);
+    return (b + 255) / 256 * 256;
+}
+
+}  // namespace ucmr
+
+using namespace ucmr;
+
+extern "C" size_t ucmr_hamming_topk_workspace_bytes(int B, int Hkv, int max_blocks, int reduce_kvhead)
+{
+    if (B < 0 || Hkv <= 0 || max_blocks <= 0) return 0;
+    return UCMR_WORKSPACE_HEADER_BYTES + scores_bytes(B, reduce_kvhead ? 1 : Hkv, max_blocks);
+}
+
+extern "C" int ucmr_workspace_init(void* workspace, size_t bytes, void* stream)
+{
+    if (!workspace || bytes < UCMR_WORKSPACE_HEADER_BYTES) return UCMR_ERR_WORKSPACE;
+    cudaError_t e = cudaMemsetAsync(workspace, 0, UCMR_WORKSPACE_HEADER_BYTES, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
+    return UCMR_OK;
+}
+
+extern "C" int ucmr_workspace_status(const void* workspace, int* host_status, void* stream)
+{
+    if (!workspace || !host_status) return UCMR_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(host_status, workspace, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
+    return *host_status == 0 ? UCMR_OK : UCMR_ERR_DEVICE;
+}
+
+static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
+                      const uint32_t* q_codes, int Hq, const int32_t* bt, int max_blocks, int64_t bt_stride,
+                      const int32_t* seq_local, const int32_t* seq_global, int B, int k,
+                      const int32_t* k_per_request, const uint8_t* mask, int reduce_mode, int reduce_kvhead,
+                      const int32_t* must, int n_must, int sink, int recent, int id_offset, float scale,
+                      int32_t* out_phys, int32_t* out_logical, int32_t* out_scores, int32_t* out_valid,
+                      int32_t* out_newseq, float* cand_scores, int32_t* cand_ids, void* workspace,
+                      size_t workspace_bytes, cudaStream_t st)
+{
+    if (k < 0 || k > max_blocks) return UCMR_ERR_BAD_ARG;
+    if (candidates ? (!cand_scores || !cand_ids) : !out_phys) return UCMR_ERR_BAD_ARG;
+    if (!workspace) return UCMR_ERR_WORKSPACE;
+    if (workspace_bytes < ucmr_hamming_topk_workspace_bytes(B, Hkv, max_blocks, reduce_kvhead)) return UCMR_ERR_WORKSPACE;
+    SelectParams p{};
+    int rc = fill_forced(p.forced, must, n_must, sink, recent);
+    if (rc != UCMR_OK) return rc;
+    int32_t* status = static_cast<int32_t*>(workspace);
+    int32_t* scores = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + UCMR_WORKSPACE_HEADER_BYTES);
+    rc = run_scan(codes, NB, BS, Hkv, W, q_codes, Hq, bt, max_blocks, bt_stride, seq_local, B, reduce_mode,
+                  reduce_kvhead, scores, status, st);
+    if (rc != UCMR_OK || B == 0 || k == 0) return rc;
+
+    p.scores = scores;
+    p.Hout = reduce_kvhead ? 1 : Hkv; p.max_blocks = max_blocks; p.BS = BS;
+    p.bt = bt; p.bt_stride = bt_stride;
+    p.seq_local = seq_local; p.seq_global = seq_global;
+    p.k = k; p.k_per_request = k_per_request; p.mask = mask;
+    p.id_offset = id_offset;
+    p.n_cached = max_blocks < kSelMaxCachedKeys ? max_blocks : kSelMaxCachedKeys;
+    p.out_phys = out_phys; p.out_logical = out_logical; p.out_scores = out_scores;
+    p.out_valid = out_valid; p.out_newseq = out_newseq;
+    p.cand_scores = cand_scores; p.cand_ids = cand_ids; p.scale = scale;
+    const size_t smem = (size_t)p.n_cached * sizeof(uint32_t);
+    const int rows = B * p.Hout;
+    if (candidates) {
+        rc = set_dyn_smem(select_kernel<true>, smem);
+        if (rc != UCMR_OK) return rc;
+        select_kernel<true><<<rows, kSelThreads, smem, st>>>(p);
+    } else {
+        rc = set_dyn_smem(select_kernel<false>, smem);
+        if (rc != UCMR_OK) return rc;
+        select_kernel<false><<<rows, kSelThreads, smem, st>>>(p);
+    }
+    return check_launch();
+}
+
+extern "C" int ucmr_hamming_topk(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
+                                 const uint32_t* q_codes, int Hq, const int32_t* block_table, int max_blocks,
+                                 int64_t block_table_stride, const int32_t* seq_lens, int B, int k,
+                                 const int32_t* k_per_request, const uint8_t* request_mask, int reduce_mode,
+                                 int reduce_kvhead, const int32_t* must_select, int n_must, int sink_tokens,
+                                 int recent_tokens, int32_t* out_physical, int32_t* out_logical,
+                                 int32_t* out_scores, int32_t* out_valid_count, int32_t* out_new_seq_lens,
+                                 void* workspace, size_t workspace_bytes, void* stream)
+{
+    return run_select(false, codes, NB, BS, Hkv, W, q_codes, Hq, block_table, max_blocks, block_table_stride,
+                      seq_lens, nullptr, B, k, k_per_request, request_mask, reduce_mode, reduce_kvhead,
+                      must_select, n_must, sink_tokens, recent_tokens, 0, 1.0f, out_physical, out_logical,
+                      out_scores, out_valid_count, out_new_seq_lens, nullptr, nullptr, workspace,
+                      workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ucmr_topk_candidates(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
+                                    const uint32_t* q_codes, int Hq, const int32_t* block_table, int max_blocks,
+                                    int64_t block_table_stride, const int32_t* seq_lens_local,
+                                    const int32_t* seq_lens_global, int B, int k, int block_id_offset,
+                                    float score_scale, int reduce_mode, int reduce_kvhead,
+                                    const int32_t* must_select, int n_must, int sink_tokens, int recent_tokens,
+                                    float* cand_scores, int32_t* cand_ids, void* workspace,
+                                    size_t workspace_bytes, void* stream)
+{
+    if (block_id_offset < 0) return UCMR_ERR_BAD_ARG;
+    return run_select(true, codes, NB, BS, Hkv, W, q_codes, Hq, block_table, max_blocks, block_table_stride,
+                      seq_lens_local, seq_lens_global, B, k, nullptr, nullptr, reduce_mode, reduce_kvhead,
+                      must_select, n_must, sink_tokens, recent_tokens, block_id_offset, score_scale, nullptr,
+                      nullptr, nullptr, nullptr, nullptr, cand_scores, cand_ids, workspace, workspace_bytes,
+                      static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ucmr_merge_topk(const float* cand_scores, const int32_t* cand_ids, int R, int B, int Hout,
+                               int kl, int k, float* out_scores, int32_t* out_ids, void* stream)
+{
+    if (!cand_scores || !cand_ids || !out_scores || !out_ids) return UCMR_ERR_BAD_ARG;
+    if (R <= 0 || B < 0 || Hout <= 0 || kl <= 0 || k < 0) return UCMR_ERR_BAD_ARG;
+    if ((int64_t)R * kl > INT_MAX) return UCMR_ERR_UNSUPPORTED;
+    if (B == 0 || k == 0) return UCMR_OK;
+    MergeParams p{cand_scores, cand_ids, R, B, Hout, kl, k, 0, out_scores, out_ids};
+    const int n = R * kl;
+    p.n_cached = n < kSelMaxCachedKeys ? n : kSelMaxCachedKeys;
+    const size_t smem = (size_t)p.n_cached * sizeof(uint32_t);
+    int rc = set_dyn_smem(merge_kernel, smem);
+    if (rc != UCMR_OK) return rc;
+    merge_kernel<<<B * Hout, kSelThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
+    return check_launch();
+}
+
+extern "C" int ucmr_update_seq_lens(const int32_t* seq_lens, int B, int topk_tokens, int BS, int32_t* out,
+                                    void* stream)
+{
+    if (!seq_lens || !out || B < 0 || BS <= 0 || topk_tokens < 0) return UCMR_ERR_BAD_ARG;
+    if (B == 0) return UCMR_OK;
+    update_seq_lens_kernel<<<(B + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(seq_lens, B, topk_tokens, BS, out);
+    return check_launch();
+}

@@ -1,0 +1,379 @@
+"""Tensor-level wrappers over the C ABI (``include/ucmr.h``).
+
+Every function takes CUDA tensors, passes raw pointers plus the current torch stream to
+``libucmr_b200.so`` and returns without synchronising.  torch is only used to own memory; there
+is no PyTorch or CPU implementation behind these functions.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from . import lib as _l
+
+REDUCE_MIN = _l.REDUCE_MIN
+REDUCE_SUM = _l.REDUCE_SUM
+_REDUCE_NAMES = {"min": REDUCE_MIN, "max": REDUCE_MIN, "sum": REDUCE_SUM, "mean": REDUCE_SUM}
+
+
+def reduce_mode(mode) -> int:
+    """'min' (the reference: closest token; its config spells it 'max' similarity), 'sum'/'mean'."""
+    if isinstance(mode, str):
+        if mode not in _REDUCE_NAMES:
+            raise ValueError(f"reduce mode should be one of {sorted(_REDUCE_NAMES)}, got {mode!r}")
+        return _REDUCE_NAMES[mode]
+    if mode not in (REDUCE_MIN, REDUCE_SUM):
+        raise ValueError(f"bad reduce mode {mode!r}")
+    return int(mode)
+
+
+def _stream(t: torch.Tensor) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need_cuda(name: str, t: torch.Tensor, dtype=None, contiguous=True) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if dtype is not None and t.dtype not in (dtype if isinstance(dtype, tuple) else (dtype,)):
+        raise ValueError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def as_words(t: torch.Tensor) -> torch.Tensor:
+    """Reinterpret a packed-code tensor (uint8 / bf16 / int32 ...) as int32 words, last dim = W."""
+    if t.dtype == torch.int32:
+        return t
+    if (t.shape[-1] * t.element_size()) % 4 != 0:
+        raise ValueError("packed codes must be a whole number of 32-bit words per row")
+    return t.view(torch.int32)
+
+
+# ----------------------------------------------------------------------------------------------
+# (1) encode
+# ----------------------------------------------------------------------------------------------
+def _check_r(r: torch.Tensor, in_dim: int) -> int:
+    _need_cuda("hash weights", r, torch.bfloat16)
+    if r.dim() != 2 or r.shape[0] != in_dim:
+        raise ValueError(f"hash weights must be [{in_dim}, hash_bits], got {tuple(r.shape)}")
+    return int(r.shape[1])
+
+
+def hash_encode(x: torch.Tensor, r: torch.Tensor, out: Optional[torch.Tensor] = None,
+                status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x bf16 [..., in_dim] -> int32 codes [..., hash_bits/32]."""
+    _need_cuda("x", x, torch.bfloat16, contiguous=False)
+    in_dim = x.shape[-1]
+    bits = _check_r(r, in_dim)
+    x2 = x.reshape(-1, in_dim)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    rows = x2.shape[0]
+    w = bits // 32
+    if out is None:
+        out = torch.empty(x.shape[:-1] + (w,), dtype=torch.int32, device=x.device)
+    else:
+        _need_cuda("out", out, torch.int32)
+        if out.numel() != rows * w:
+            raise ValueError("out has the wrong size")
+    lib = _l.load_library()
+    _l.check(lib.ucmr_hash_encode(_ptr(x2), rows, x2.stride(0) if rows > 1 else in_dim, _ptr(r), in_dim, bits,
+                                  _ptr(out), _ptr(status), _stream(x)), "ucmr_hash_encode")
+    return out
+
+
+def hash_encode_query(q: torch.Tensor, r: torch.Tensor, group_mean: int = 1,
+                      out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q bf16 [T, Hq, in_dim] -> int32 [T, Hq/group_mean, W]; group_mean>1 averages head groups first."""
+    _need_cuda("q", q, torch.bfloat16, contiguous=False)
+    if q.dim() != 3 or q.stride(2) != 1:
+        raise ValueError("q must be [T, Hq, in_dim] with a unit inner stride")
+    t, hq, in_dim = q.shape
+    bits = _check_r(r, in_dim)
+    if group_mean <= 0 or hq % group_mean != 0:
+        raise ValueError("group_mean must divide the number of query heads")
+    w = bits // 32
+    if out is None:
+        out = torch.empty((t, hq // group_mean, w), dtype=torch.int32, device=q.device)
+    else:
+        _need_cuda("out", out, torch.int32)
+    lib = _l.load_library()
+    _l.check(lib.ucmr_hash_encode_query(_ptr(q), t, hq, q.stride(0), q.stride(1), group_mean, _ptr(r), in_dim, bits,
+                                        _ptr(out), _ptr(status), _stream(q)), "ucmr_hash_encode_query")
+    return out
+
+
+def hash_encode_and_cache(x: torch.Tensor, slot_mapping: torch.Tensor, cache: torch.Tensor, r: torch.Tensor,
+                          status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Encode x bf16 [T, H, in_dim] and scatter token t's codes to slot ``slot_mapping[t]`` of the paged
+    cache [NB, BS, H, W] (int32 words, or any dtype that views to them)."""
+    _need_cuda("x", x, torch.bfloat16, contiguous=False)
+    if x.dim() != 3 or x.stride(2) != 1:
+        raise ValueError(f"x must be [T,H,K] with a unit inner stride, got {tuple(x.shape)}")
+    _need_cuda("slot_mapping", slot_mapping, (torch.int64, torch.int32))
+    if slot_mapping.dim() != 1 or slot_mapping.shape[0] != x.shape[0]:
+        raise ValueError(f"slot_mapping length {tuple(slot_mapping.shape)} != T {x.shape[0]}")
+    _need_cuda("cache", cache)
+    cw = as_words(cache)
+    t, h, in_dim = x.shape
+    bits = _check_r(r, in_dim)
+    if cw.dim() != 4 or cw.shape[2] != h or cw.shape[3] != bits // 32:
+        raise ValueError(f"cache shape {tuple(cw.shape)} does not match [NB, BS, {h}, {bits // 32}]")
+    lib = _l.load_library()
+    _l.check(lib.ucmr_hash_encode_and_cache(_ptr(x), t, h, x.stride(0), x.stride(1), _ptr(r), in_dim, bits,
+                                            _ptr(slot_mapping), int(slot_mapping.dtype == torch.int64), _ptr(cw),
+                                            cw.shape[0], cw.shape[1], _ptr(status), _stream(x)),
+             "ucmr_hash_encode_and_cache")
+    return cache
+
+
+# ----------------------------------------------------------------------------------------------
+# (2)+(3) scan + top-k
+# ----------------------------------------------------------------------------------------------
+def workspace_bytes(batch: int, num_kv_heads: int, max_blocks: int, reduce_kvhead: bool = False) -> int:
+    return int(_l.load_library().ucmr_hamming_topk_workspace_bytes(batch, num_kv_heads, max_blocks,
+                                                                   int(bool(reduce_kvhead))))
+
+
+def new_workspace(batch: int, num_kv_heads: int, max_blocks: int, device, reduce_kvhead: bool = False) -> torch.Tensor:
+    """Allocates and clears a workspace big enough for the given shapes (either head mode)."""
+    n = max(workspace_bytes(batch, num_kv_heads, max_blocks, False),
+            workspace_bytes(batch, num_kv_heads, max_blocks, reduce_kvhead))
+    ws = torch.empty(n, dtype=torch.uint8, device=device)
+    _l.check(_l.load_library().ucmr_workspace_init(_ptr(ws), n, _stream(ws)), "ucmr_workspace_init")
+    return ws
+
+
+def workspace_status(ws: torch.Tensor) -> int:
+    """Reads the sticky device status word (synchronises the current stream)."""
+    host = C.c_int(0)
+    rc = _l.load_library().ucmr_workspace_status(_ptr(ws), C.byref(host), _stream(ws))
+    if rc not in (_l.UCMR_OK, _l.UCMR_ERR_DEVICE):
+        _l.check(rc, "ucmr_workspace_status")
+    return int(host.value)
+
+
+@dataclass
+class Retrieval:
+    physical: torch.Tensor       # int32 [B, Hout, k]  block-table entries of the chosen blocks
+    logical: torch.Tensor        # int32 [B, Hout, k]  ascending logical block index (-1 = padding)
+    scores: Optional[torch.Tensor]  # int32 [B, Hout, k]  raw block scores (-1 = padding)
+    valid_count: torch.Tensor    # int32 [B]
+    new_seq_lens: torch.Tensor   # int32 [B]
+
+
+def _scan_args(codes, q_codes, block_table, seq_lens):
+    _need_cuda("codes", codes)
+    codes = as_words(codes)
+    _need_cuda("q_codes", q_codes)
+    q_codes = as_words(q_codes)
+    if codes.dim() != 4:
+        raise ValueError("codes must be [NB, BS, Hkv, W]")
+    if q_codes.dim() != 3 or q_codes.shape[2] != codes.shape[3]:
+        raise ValueError("q_codes must be [B, Hq, W] with the cache's W")
+    _need_cuda("block_table", block_table, torch.int32, contiguous=False)
+    if block_table.dim() != 2 or block_table.stride(1) != 1:
+        raise ValueError("block_table must be [B, max_blocks] with a unit inner stride")
+    _need_cuda("seq_lens", seq_lens, torch.int32)
+    b = q_codes.shape[0]
+    if block_table.shape[0] != b:
+        raise RuntimeError("batch size mismatch between query_code and block_table")
+    if seq_lens.shape[0] < b:
+        raise ValueError("seq_lens shorter than the batch")
+    if q_codes.shape[1] % codes.shape[2] != 0:
+        raise ValueError("number of query heads must be a multiple of the kv heads")
+    bt_stride = block_table.stride(0) if b > 1 else max(block_table.stride(0), block_table.shape[1])
+    return codes, q_codes, bt_stride
+
+
+def _must_array(must_select: Sequence[int]):
+    must = list(must_select or ())
+    if len(must) > _l.MAX_MUST_SELECT:
+        raise ValueError(f"at most {_l.MAX_MUST_SELECT} must_select entries")
+    arr = (C.c_int32 * max(1, len(must)))(*must)
+    return arr, len(must)
+
+
+def hamming_topk(codes: torch.Tensor, q_codes: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
+                 k: int, *, reduce="sum", reduce_kvhead: bool = False, must_select: Sequence[int] = (),
+                 sink_tokens: int = 0, recent_tokens: int = 0, k_per_request: Optional[torch.Tensor] = None,
+                 request_mask: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
+                 out: Optional[Retrieval] = None, want_scores: bool = True) -> Retrieval:
+    """Scan + exact top-k in two launches.  See ``ucmr_hamming_topk`` in include/ucmr.h."""
+    codes, q_codes, bt_stride = _scan_args(codes, q_codes, block_table, seq_lens)
+    nb, bs, hkv, w = codes.shape
+    b, hq, _ = q_codes.shape
+    mb = block_table.shape[1]
+    if k < 0 or k > mb:
+        raise ValueError(f"k={k} outside [0, max_blocks={mb}]")
+    hout = 1 if reduce_kvhead else hkv
+    dev = codes.device
+    if workspace is None:
+        workspace = new_workspace(b, hkv, mb, dev, reduce_kvhead)
+    if k_per_request is not None:
+        _need_cuda("k_per_request", k_per_request, torch.int32)
+    if request_mask is not None:
+        _need_cuda("request_mask", request_mask, (torch.uint8, torch.bool))
+    if out is None:
+        out = Retrieval(
+            physical=torch.empty((b, hout, k), dtype=torch.int32, device=dev),
+            logical=torch.empty((b, hout, k), dtype=torch.int32, device=dev),
+            scores=torch.empty((b, hout, k), dtype=torch.int32, device=dev) if want_scores else None,
+            valid_count=torch.empty((b,), dtype=torch.int32, device=dev),
+            new_seq_lens=torch.empty((b,), dtype=torch.int32, device=dev))
+    must, n_must = _must_array(must_select)
+    lib = _l.load_library()
+    _l.check(lib.ucmr_hamming_topk(
+        _ptr(codes), nb, bs, hkv, w, _ptr(q_codes), hq, _ptr(block_table), mb, bt_stride, _ptr(seq_lens), b, k,
+        _ptr(k_per_request), _ptr(request_mask), reduce_mode(reduce), int(bool(reduce_kvhead)), must, n_must,
+        int(sink_tokens), int(recent_tokens), _ptr(out.physical), _ptr(out.logical), _ptr(out.scores),
+        _ptr(out.valid_count), _ptr(out.new_seq_lens), _ptr(workspace), workspace.numel(), _stream(codes)),
+        "ucmr_hamming_topk")
+    return out
+
+
+def block_scores(codes, q_codes, block_table, seq_lens, *, reduce="sum", reduce_kvhead=False,
+                 out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """int32 [B, Hout, max_blocks] block scores (-1 past each request's length)."""
+    codes, q_codes, bt_stride = _scan_args(codes, q_codes, block_table, seq_lens)
+    nb, bs, hkv, w = codes.shape
+    b, hq, _ = q_codes.shape
+    mb = block_table.shape[1]
+    hout = 1 if reduce_kvhead else hkv
+    if out is None:
+        out = torch.empty((b, hout, mb), dtype=torch.int32, device=codes.device)
+    lib = _l.load_library()
+    _l.check(lib.ucmr_block_scores(_ptr(codes), nb, bs, hkv, w, _ptr(q_codes), hq, _ptr(block_table), mb, bt_stride,
+                                   _ptr(seq_lens), b, reduce_mode(reduce), int(bool(reduce_kvhead)), _ptr(out),
+                                   _ptr(status), _stream(codes)), "ucmr_block_scores")
+    return out
+
+
+def hamming_score(key_codes, query_code, block_table, seq_len, max_seq_len: int, sink: int, recent: int,
+                  reduce_kvhead: bool) -> torch.Tensor:
+    """Signature of the reference op ``hamming.hamming_score`` (block mode): per-token fp16 scores
+    [B, 1 or Hkv, max_seq_len].  query_code is [B, 1, Hq, W]."""
+    if block_table is None:
+        raise ValueError("only the paged (block_table) form is provided")
+    q = as_words(query_code)
+    if q.dim() == 4:
+        q = q.reshape(q.shape[0], q.shape[2], q.shape[3])
+    codes, q, bt_stride = _scan_args(key_codes, q, block_table, seq_len)
+    nb, bs, hkv, w = codes.shape
+    b, hq, _ = q.shape
+    mb = block_table.shape[1]
+    if max_seq_len != mb * bs:
+        raise ValueError("max_seq_len must equal block_size * block_table.shape[1]")
+    out = torch.empty((b, 1 if reduce_kvhead else hkv, max_seq_len), dtype=torch.float16, device=codes.device)
+    lib = _l.load_library()
+    _l.check(lib.ucmr_hamming_score(_ptr(codes), nb, bs, hkv, w, _ptr(q), hq, _ptr(block_table), mb, bt_stride,
+                                    _ptr(seq_len), b, int(sink), int(recent), int(bool(reduce_kvhead)), _ptr(out),
+                                    _stream(codes)), "ucmr_hamming_score")
+    return out
+
+
+def update_seq_lens(seq_lens: torch.Tensor, topk_token: int, block_size: int) -> torch.Tensor:
+    _need_cuda("seq_lens", seq_lens, torch.int32)
+    out = torch.empty_like(seq_lens)
+    _l.check(_l.load_library().ucmr_update_seq_lens(_ptr(seq_lens), seq_lens.numel(), int(topk_token),
+                                                    int(block_size), _ptr(out), _stream(seq_lens)),
+             "ucmr_update_seq_lens")
+    return out
+
+
+# ----------------------------------------------------------------------------------------------
+# sequence-sharded retrieval
+# ----------------------------------------------------------------------------------------------
+def topk_candidates(codes, q_codes, block_table, seq_lens_local, seq_lens_global, k: int, block_id_offset: int,
+                    score_scale: float, *, reduce="sum", reduce_kvhead=False, must_select=(), sink_tokens=0,
+                    recent_tokens=0, workspace=None, out_scores=None, out_ids=None):
+    """Local top-k of one sequence shard as (float32 score, int32 global block id) records [B,Hout,k]."""
+    codes, q_codes, bt_stride = _scan_args(codes, q_codes, block_table, seq_lens_local)
+    _need_cuda("seq_lens_global", seq_lens_global, torch.int32)
+    nb, bs, hkv, w = codes.shape
+    b, hq, _ = q_codes.shape
+    mb = block_table.shape[1]
+    if k < 0 or k > mb:
+        raise ValueError(f"k={k} outside [0, max_blocks={mb}]")
+    hout = 1 if reduce_kvhead else hkv
+    dev = codes.device
+    if workspace is None:
+        workspace = new_workspace(b, hkv, mb, dev, reduce_kvhead)
+    if out_scores is None:
+        out_scores = torch.empty((b, hout, k), dtype=torch.float32, device=dev)
+    if out_ids is None:
+        out_ids = torch.empty((b, hout, k), dtype=torch.int32, device=dev)
+    must, n_must = _must_array(must_select)
+    lib = _l.load_library()
+    _l.check(lib.ucmr_topk_candidates(
+        _ptr(codes), nb, bs, hkv, w, _ptr(q_codes), hq, _ptr(block_table), mb, bt_stride, _ptr(seq_lens_local),
+        _ptr(seq_lens_global), b, k, int(block_id_offset), float(score_scale), reduce_mode(reduce),
+        int(bool(reduce_kvhead)), must, n_must, int(sink_tokens), int(recent_tokens), _ptr(out_scores),
+        _ptr(out_ids), _ptr(workspace), workspace.numel(), _stream(codes)), "ucmr_topk_candidates")
+    return out_scores, out_ids
+
+
+def merge_topk(cand_scores: torch.Tensor, cand_ids: torch.Tensor, k: int, out_scores=None, out_ids=None):
+    """cand_* [R, B, Hout, kl] (ascending shard order) -> global top-k [B, Hout, k], ascending id."""
+    _need_cuda("cand_scores", cand_scores, torch.float32)
+    _need_cuda("cand_ids", cand_ids, torch.int32)
+    if cand_scores.dim() != 4 or cand_scores.shape != cand_ids.shape:
+        raise ValueError("candidates must be [R, B, Hout, kl]")
+    r, b, h, kl = cand_scores.shape
+    dev = cand_scores.device
+    if out_scores is None:
+        out_scores = torch.empty((b, h, k), dtype=torch.float32, device=dev)
+    if out_ids is None:
+        out_ids = torch.empty((b, h, k), dtype=torch.int32, device=dev)
+    _l.check(_l.load_library().ucmr_merge_topk(_ptr(cand_scores), _ptr(cand_ids), r, b, h, kl, int(k),
+                                               _ptr(out_scores), _ptr(out_ids), _stream(cand_scores)),
+             "ucmr_merge_topk")
+    return out_scores, out_ids
+
+
+# ----------------------------------------------------------------------------------------------
+# (4) paged-KV gather
+# ----------------------------------------------------------------------------------------------
+def gather_kv(k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], sel: torch.Tensor,
+              out_k: Optional[torch.Tensor] = None, out_v: Optional[torch.Tensor] = None,
+              status: Optional[torch.Tensor] = None):
+    """pools [NB, BS, Hkv, D]; sel int32 [B, k] (whole blocks) or [B, Hkv, k] (per kv head).
+    Returns (out_k, out_v), each [B, k*BS, Hkv, D] (None for a pool that was not given)."""
+    pool = k_pool if k_pool is not None else v_pool
+    if pool is None:
+        raise ValueError("give at least one pool")
+    for name, t in (("k_pool", k_pool), ("v_pool", v_pool)):
+        if t is not None:
+            _need_cuda(name, t)
+            if t.shape != pool.shape or t.dtype != pool.dtype:
+                raise ValueError("pools must agree in shape and dtype")
+    _need_cuda("sel", sel, torch.int32)
+    if pool.dim() != 4 or sel.dim() not in (2, 3):
+        raise ValueError("pool must be [NB,BS,Hkv,D]; sel [B,k] or [B,Hkv,k]")
+    nb, bs, hkv, d = pool.shape
+    per_head = sel.dim() == 3
+    if per_head and sel.shape[1] != hkv:
+        raise ValueError("per-head sel must be [B, Hkv, k]")
+    b, k = sel.shape[0], sel.shape[-1]
+    shape = (b, k * bs, hkv, d)
+    if k_pool is not None and out_k is None:
+        out_k = torch.empty(shape, dtype=pool.dtype, device=pool.device)
+    if v_pool is not None and out_v is None:
+        out_v = torch.empty(shape, dtype=pool.dtype, device=pool.device)
+    for name, t in (("out_k", out_k), ("out_v", out_v)):
+        if t is not None:
+            _need_cuda(name, t, pool.dtype)
+            if t.numel() != b * k * bs * hkv * d:
+                raise ValueError(f"{name} has the wrong size")
+    row_bytes = d * pool.element_size()
+    _l.check(_l.load_library().ucmr_gather_kv(_ptr(k_pool), _ptr(v_pool), nb, bs * hkv * row_bytes, _ptr(sel), b, k,
+                                              int(per_head), bs, hkv, row_bytes, _ptr(out_k), _ptr(out_v),
+                                              _ptr(status), _stream(pool)), "ucmr_gather_kv")
+    return out_k, out_v
