@@ -85,7 +85,7 @@ def test_encode_and_cache(cuda_device, T, Hh, slot_dtype):
     import torch
     from unified_cache_management_b200 import ops
     rng = np.random.default_rng(T * 10 + Hh)
-    NB, BS = 40, 16
+    NB, BS = 50, 16
     x = H.bf16_normal(rng, (T, Hh, 128))
     r = _r_matrix(1)
     slots = rng.permutation(NB * BS)[:T].astype(np.int64)

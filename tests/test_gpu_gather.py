@@ -33,7 +33,7 @@ def test_gather_matches_indexing(cuda_device, shape, per_head):
     # one pool only
     ok2, none = ops.gather_kv(kd, None, torch.from_numpy(sel).to(cuda_device))
     torch.cuda.synchronize()
-    assert none is None and torch.equal(ok2, ok)
+    assert none is None and torch.equal(ok2.view(torch.int16), ok.view(torch.int16))
 
 
 def test_gather_many_blocks(cuda_device):

@@ -20,6 +20,8 @@
 // Stands in for triton_hash_code_kernel, fused_hash_and_cache_kernel and
 // _reshape_and_cache_khash_kernel (ucm/sparse/gsa_on_device/hash_encoder.py:37-134, 263-356,
 // 136-261); numerics follow torch_hash_code (:359-370): fp32 accumulate, strict "> 0".
+#include <stdlib.h>
+
 #include <cuda.h>
 #include <cuda_bf16.h>
 

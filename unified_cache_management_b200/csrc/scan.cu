@@ -10,6 +10,7 @@
 // (ucm/sparse/gsa_on_device/csrc/cuda/ham_dist/paged_ham_dist_mla.cu:111-248,
 //  ucm/sparse/gsa_on_device/hamming_topk.py:45-47).
 #include <limits.h>
+#include <stdlib.h>
 
 #include <cuda_fp16.h>
 
@@ -284,6 +285,22 @@ int validate_scan_args(const void* codes, int64_t NB, int BS, int Hkv, int W, co
     return UCMR_OK;
 }
 
+int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const uint32_t* q, int Hq,
+                  const int32_t* bt, int max_blocks, int64_t bt_stride, const int32_t* seq_lens, int B,
+                  int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, cudaStream_t st);
+
+// UCMR_SCAN=register routes every scan through the register kernel of this file (debug aid; the
+// staged kernel in scan_ring.cu is the default wherever it covers the shape).
+static bool force_register_scan()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("UCMR_SCAN");
+        v = (e && e[0] == 'r') ? 1 : 0;
+    }
+    return v == 1;
+}
+
 // Launches the scan into `out` ([B,Hout,max_blocks] int32).  Shared by the C entry points.
 int run_scan(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const uint32_t* q, int Hq,
              const int32_t* bt, int max_blocks, int64_t bt_stride, const int32_t* seq_lens, int B,
@@ -294,6 +311,12 @@ int run_scan(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const ui
     if (!out) return UCMR_ERR_BAD_ARG;
     if (reduce_mode != UCMR_REDUCE_MIN && reduce_mode != UCMR_REDUCE_SUM) return UCMR_ERR_BAD_ARG;
     if (B == 0) return UCMR_OK;
+
+    if (!force_register_scan()) {
+        rc = run_scan_ring(codes, NB, BS, Hkv, W, q, Hq, bt, max_blocks, bt_stride, seq_lens, B, reduce_mode,
+                           reduce_kvhead, out, status, st);
+        if (rc != UCMR_ERR_UNSUPPORTED) return rc;
+    }
 
     ScanParams p{};
     p.codes = reinterpret_cast<const uint4*>(codes);

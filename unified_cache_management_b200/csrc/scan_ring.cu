@@ -1,0 +1,462 @@
+// Hamming scan, staged variant (sm_100a): one persistent CTA per SM streams paged code blocks through
+// a shared-memory ring with the bulk-copy (TMA) engine and reduces them with eight consumer warps.
+//
+//   producer warp   resolves the next 32 work items in parallel (request, logical block, block-table
+//                   lookup), then one lane issues cp.async.bulk global->shared for each item onto the
+//                   stage's mbarrier.  Up to kRingBytes of loads are in flight per SM at any time, so
+//                   the block-table -> code-block dependency never stalls the memory pipe.
+//   consumer warps  item i belongs to warp i % 8.
+//     sum mode: the distance sum over a block only depends on how many of its tokens have each code
+//       bit set.  A lane owns one 32-bit column (kv head, word) of the block and folds all its tokens
+//       into bit-sliced vertical counters with carry-save adders (about 2.4 LOP3 per code word, no
+//       per-token popcount); the block score is then
+//           sum_g sum_i (q_g[i] ? n - c[i] : c[i]) = n * popc(q) + sum_p 2^p * (G*popc(P_p) - 2*sum_g popc(P_p & q_g)),
+//       i.e. (1+G) popcounts per counter plane instead of G per token.  This keeps the kernel
+//       bandwidth-bound: the per-token popcount form is limited by the SM's POPC rate (16/clk) once
+//       G >= 4.
+//     min mode: per-token distances are needed, so a lane owns a 16-byte piece of each token
+//       (XOR + popcount per query head) and keeps the running minimum.
+//
+// Output: int32 [B, Hout, max_blocks] block scores, bit-identical to the register kernel in scan.cu,
+// which remains the path for shapes this one does not cover.
+//
+// Stands in for HammingScoreContiKernel + torch.min of the reference
+// (ucm/sparse/gsa_on_device/csrc/cuda/ham_dist/paged_ham_dist_mla.cu:111-248,
+//  ucm/sparse/gsa_on_device/hamming_topk.py:45-47).
+#include <limits.h>
+
+#include "common.cuh"
+
+namespace ucmr {
+
+constexpr int kRingConsumerWarps = 8;
+constexpr int kRingThreads = 32 * (1 + kRingConsumerWarps);
+constexpr int kRingBytes = 192 * 1024;
+constexpr int kRingMaxStages = 32;
+constexpr int kRingMaxBatch = 1024;  // requests per launch (prefix table in shared memory)
+constexpr int kRingMaxBps = 8;       // blocks per stage
+constexpr int kRingMaxG = 16;
+
+struct RingParams {
+    const char* codes;
+    int64_t NB;
+    int BS, Hkv, W, G, Hq;
+    const uint32_t* q;
+    const int32_t* bt;
+    int max_blocks;
+    int64_t bt_stride;
+    const int32_t* seq_lens;
+    int B;
+    int reduce_kvhead;
+    int32_t* out;
+    int32_t* status;
+    int RW;            // words per token row = Hkv * W
+    int bps;           // blocks per stage
+    int block_bytes;   // BS * RW * 4
+    int block_stride;  // block_bytes (+16 when several blocks share a stage: spreads them over banks)
+    int stage_bytes;   // bps * block_stride, rounded up to 128
+    int n_stages;
+};
+
+struct StageMeta {
+    int b, j0, seq;
+    uint32_t valid_mask;  // bit k: block j0+k was loaded
+};
+
+// 3 -> 2 carry-save adder on bit-sliced values: (h, l) = a + b + c.
+__device__ __forceinline__ void csa(uint32_t& h, uint32_t& l, uint32_t a, uint32_t b, uint32_t c)
+{
+    const uint32_t u = a ^ b;
+    h = (a & b) | (u & c);
+    l = u ^ c;
+}
+
+constexpr int kPlanes = 8;        // vertical counters hold up to 255 tokens between flushes
+constexpr int kFlushTokens = 192;  // multiple of 64, below 256
+
+// Adds a one-bit-per-position value of weight 2^LEVEL into the counters (ripple carry).
+template <int LEVEL>
+__device__ __forceinline__ void ripple_add(uint32_t (&pl)[kPlanes], uint32_t v)
+{
+#pragma unroll
+    for (int p = LEVEL; p < kPlanes; ++p) {
+        const uint32_t carry = pl[p] & v;
+        pl[p] ^= v;
+        v = carry;
+    }
+}
+
+// Folds 16 words into planes 0..3 (carry-save) and returns the carry of weight 16.
+__device__ __forceinline__ uint32_t fold16(uint32_t (&pl)[kPlanes], const uint32_t (&x)[16])
+{
+    uint32_t ones = pl[0], twos = pl[1], fours = pl[2], eights = pl[3];
+    uint32_t t2a, t2b, t4a, t4b, t8a, t8b, t16;
+    csa(t2a, ones, ones, x[0], x[1]);
+    csa(t2b, ones, ones, x[2], x[3]);
+    csa(t4a, twos, twos, t2a, t2b);
+    csa(t2a, ones, ones, x[4], x[5]);
+    csa(t2b, ones, ones, x[6], x[7]);
+    csa(t4b, twos, twos, t2a, t2b);
+    csa(t8a, fours, fours, t4a, t4b);
+    csa(t2a, ones, ones, x[8], x[9]);
+    csa(t2b, ones, ones, x[10], x[11]);
+    csa(t4a, twos, twos, t2a, t2b);
+    csa(t2a, ones, ones, x[12], x[13]);
+    csa(t2b, ones, ones, x[14], x[15]);
+    csa(t4b, twos, twos, t2a, t2b);
+    csa(t8b, fours, fours, t4a, t4b);
+    csa(t16, eights, eights, t8a, t8b);
+    pl[0] = ones; pl[1] = twos; pl[2] = fours; pl[3] = eights;
+    return t16;
+}
+
+// One column of a block: folds tokens [0, ntok) of the 32-bit column at colp (row stride RW words)
+// into vertical counters and returns sum_g sum_tokens popc(word ^ q[g]).
+// RW_T / G_T > 0 fix the stride / group size at compile time (immediate offsets, unrolled popcounts).
+template <int RW_T, int G_T>
+__device__ __forceinline__ int column_sum(const uint32_t* colp, int ntok, int rw_rt, int g_rt, const uint32_t* qw)
+{
+    const int RW = RW_T > 0 ? RW_T : rw_rt;
+    const int G = G_T > 0 ? G_T : g_rt;
+    constexpr int GMAX = G_T > 0 ? G_T : kRingMaxG;
+    int qpop = 0;
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g)
+        if (g < G) qpop += __popc(qw[g]);
+    int acc = 0;
+    for (int t0 = 0; t0 < ntok; t0 += kFlushTokens) {
+        uint32_t pl[kPlanes];
+#pragma unroll
+        for (int i = 0; i < kPlanes; ++i) pl[i] = 0u;
+        const int t1 = min(ntok, t0 + kFlushTokens);
+        const uint32_t* cp = colp + (size_t)t0 * RW;
+        int t = t0;
+        for (; t + 64 <= t1; t += 64, cp += 64 * RW) {
+            uint32_t c16[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                uint32_t x[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) x[i] = cp[(u * 16 + i) * RW];
+                c16[u] = fold16(pl, x);
+            }
+            uint32_t t32a, t32b, t64, p4 = pl[4], p5 = pl[5];
+            csa(t32a, p4, p4, c16[0], c16[1]);
+            csa(t32b, p4, p4, c16[2], c16[3]);
+            csa(t64, p5, p5, t32a, t32b);
+            pl[4] = p4; pl[5] = p5;
+            ripple_add<6>(pl, t64);
+        }
+        for (; t < t1; t += 16, cp += 16 * RW) {
+            uint32_t x[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = (t + i < t1) ? cp[i * RW] : 0u;
+            ripple_add<4>(pl, fold16(pl, x));
+        }
+        acc += (t1 - t0) * qpop;
+#pragma unroll
+        for (int i = 0; i < kPlanes; ++i) {
+            int d = G * __popc(pl[i]);
+#pragma unroll
+            for (int g = 0; g < GMAX; ++g)
+                if (g < G) d -= 2 * __popc(pl[i] & qw[g]);
+            acc += d * (1 << i);
+        }
+    }
+    return acc;
+}
+
+// MIN selects the per-token-minimum consumer; RW_T / G_T (sum mode only) are compile-time copies of
+// the row width and group size for the common shapes, 0 = read them from the parameters.
+template <bool MIN, int RW_T, int G_T>
+__global__ void __launch_bounds__(kRingThreads, 1) scan_ring_kernel(const RingParams p)
+{
+    extern __shared__ __align__(128) uint8_t s_ring[];
+    __shared__ __align__(8) uint64_t s_full[kRingMaxStages];
+    __shared__ __align__(8) uint64_t s_empty[kRingMaxStages];
+    __shared__ StageMeta s_meta[kRingMaxStages];
+    __shared__ int s_cum[kRingMaxBatch + 1];  // s_cum[b] = work items before request b
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int Hout = p.reduce_kvhead ? 1 : p.Hkv;
+
+    if (tid == 0) {
+        for (int s = 0; s < p.n_stages; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 1); }
+        fence_mbar_init();
+    }
+    if (warp == 0) {  // prefix sum of items per request
+        int run = 0;
+        for (int b0 = 0; b0 < p.B; b0 += 32) {
+            const int b = b0 + lane;
+            int n = 0;
+            if (b < p.B) {
+                const int nb = min(p.max_blocks, (p.seq_lens[b] + p.BS - 1) / p.BS);
+                n = (max(nb, 0) + p.bps - 1) / p.bps;
+            }
+            int incl = n;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, incl, off);
+                if (lane >= off) incl += o;
+            }
+            if (b < p.B) s_cum[b] = run + incl - n;
+            run += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) s_cum[p.B] = run;
+    }
+    __syncthreads();
+    const int total_items = s_cum[p.B];
+
+    // scores of blocks past each request's length
+    for (int64_t i = (int64_t)blockIdx.x * kRingThreads + tid; i < (int64_t)p.B * p.max_blocks;
+         i += (int64_t)gridDim.x * kRingThreads) {
+        const int b = (int)(i / p.max_blocks), j = (int)(i - (int64_t)b * p.max_blocks);
+        const int nb = (p.seq_lens[b] + p.BS - 1) / p.BS;
+        if (j >= nb)
+            for (int h = 0; h < Hout; ++h) p.out[((int64_t)b * Hout + h) * p.max_blocks + j] = -1;
+    }
+
+    const int first = blockIdx.x, step = gridDim.x;
+    const int my_items = first < total_items ? (total_items - first + step - 1) / step : 0;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        for (int base = 0; base < my_items; base += 32) {
+            const int it = base + lane;
+            int b = 0, j0 = 0, seq = 0;
+            int phys[kRingMaxBps];
+#pragma unroll
+            for (int k = 0; k < kRingMaxBps; ++k) phys[k] = -1;
+            if (it < my_items) {
+                const int flat = first + it * step;
+                int lo = 0, hi = p.B - 1;  // last b with s_cum[b] <= flat
+                while (lo < hi) {
+                    const int mid = (lo + hi + 1) >> 1;
+                    if (s_cum[mid] <= flat) lo = mid; else hi = mid - 1;
+                }
+                b = lo;
+                j0 = (flat - s_cum[b]) * p.bps;
+                seq = p.seq_lens[b];
+                const int nb = min(p.max_blocks, (seq + p.BS - 1) / p.BS);
+#pragma unroll
+                for (int k = 0; k < kRingMaxBps; ++k) {
+                    if (k < p.bps && j0 + k < nb) {
+                        const int v = p.bt[(int64_t)b * p.bt_stride + j0 + k];
+                        if (v >= 0 && v < p.NB) phys[k] = v;
+                        else flag_status(p.status, UCMR_DEV_BAD_BLOCK_ID);
+                    }
+                }
+            }
+            const int n_here = min(32, my_items - base);
+            bool dead = false;
+            for (int i = 0; i < n_here; ++i) {
+                const int bi = __shfl_sync(0xffffffffu, b, i);
+                const int ji = __shfl_sync(0xffffffffu, j0, i);
+                const int si = __shfl_sync(0xffffffffu, seq, i);
+                int ph[kRingMaxBps];
+#pragma unroll
+                for (int k = 0; k < kRingMaxBps; ++k) ph[k] = __shfl_sync(0xffffffffu, phys[k], i);
+                if (lane == 0 && !dead) {
+                    const int gi = base + i;
+                    const int s = gi % p.n_stages;
+                    const uint32_t phase = (uint32_t)((gi / p.n_stages) & 1);
+                    if (!mbar_wait(&s_empty[s], phase ^ 1u)) {
+                        flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT);
+                        dead = true;
+                    } else {
+                        uint32_t mask = 0;
+                        int n_valid = 0;
+#pragma unroll
+                        for (int k = 0; k < kRingMaxBps; ++k)
+                            if (ph[k] >= 0) { mask |= 1u << k; ++n_valid; }
+                        s_meta[s] = StageMeta{bi, ji, si, mask};
+                        mbar_expect_tx(&s_full[s], (uint32_t)(n_valid * p.block_bytes));
+                        uint8_t* dst = s_ring + (size_t)s * p.stage_bytes;
+#pragma unroll
+                        for (int k = 0; k < kRingMaxBps; ++k)
+                            if (ph[k] >= 0)
+                                bulk_g2s(dst + k * p.block_stride, p.codes + (int64_t)ph[k] * p.block_bytes,
+                                         (uint32_t)p.block_bytes, &s_full[s]);
+                    }
+                }
+            }
+            if (__shfl_sync(0xffffffffu, (int)dead, 0)) break;
+        }
+    } else {
+        // ------------------------------------------------------------------ consumers
+        const int cw = warp - 1;
+        int cur_b = -1;
+        if constexpr (!MIN) {
+            // lane <-> (block in stage, column); a column is one 32-bit word of one kv head
+            const int RW = RW_T > 0 ? RW_T : p.RW;
+            const int G = G_T > 0 ? G_T : p.G;
+            constexpr int GMAX = G_T > 0 ? G_T : kRingMaxG;
+            const int cols = min(RW, 32);
+            const int passes = RW / cols;
+            const int blk = (RW < 32) ? lane / RW : 0;
+            const int col0 = (RW < 32) ? lane % RW : lane;
+            uint32_t qw[GMAX];
+            for (int it = cw; it < my_items; it += kRingConsumerWarps) {
+                const int s = it % p.n_stages;
+                const uint32_t phase = (uint32_t)((it / p.n_stages) & 1);
+                if (!mbar_wait(&s_full[s], phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
+                const StageMeta m = s_meta[s];
+                const int j = m.j0 + blk;
+                const bool have = blk < p.bps && ((m.valid_mask >> blk) & 1u);
+                const int ntok = have ? min(p.BS, m.seq - j * p.BS) : 0;
+                const uint8_t* sb = s_ring + (size_t)s * p.stage_bytes + blk * p.block_stride;
+                int total = 0;  // per-head (or all-head) score, complete in the lanes that write
+                for (int ps = 0; ps < passes; ++ps) {
+                    const int col = col0 + ps * 32;
+                    const int head = col / p.W, w = col - head * p.W;
+                    if (m.b != cur_b || passes > 1) {
+#pragma unroll
+                        for (int g = 0; g < GMAX; ++g)
+                            if (g < G) qw[g] = __ldg(p.q + ((int64_t)m.b * p.Hq + head * G + g) * p.W + w);
+                    }
+                    const uint32_t* colp = reinterpret_cast<const uint32_t*>(sb) + col;
+                    int acc = column_sum<RW_T, G_T>(colp, ntok, RW, G, qw);
+                    // fold the words of a head; with reduce_kvhead also the heads of this pass
+                    const int span = p.reduce_kvhead ? cols : p.W;
+                    for (int off = 1; off < span && off < 32; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+                    if (p.reduce_kvhead) {
+                        total += acc;
+                    } else if (have && w == 0) {
+                        p.out[((int64_t)m.b * Hout + head) * p.max_blocks + j] = acc;
+                    }
+                }
+                cur_b = m.b;
+                if (p.reduce_kvhead && have && col0 == 0) p.out[(int64_t)m.b * p.max_blocks + j] = total;
+                if (!have && blk < p.bps && col0 == 0 && j < p.max_blocks) {
+                    // block inside the stage but not loaded: past the request's end or a bad id
+                    for (int h = 0; h < Hout; ++h) p.out[((int64_t)m.b * Hout + h) * p.max_blocks + j] = -1;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_empty[s]);
+            }
+        } else {
+            // lane <-> (block in stage, 16-byte piece of a token row, token slot)
+            const int PW = p.W / 4, P = p.Hkv * PW;
+            const int LG = 32 / p.bps;     // lanes per block
+            const int TS = LG / P;         // token slots per block (>= 1 by construction)
+            const int blk = lane / LG, lam = lane % LG;
+            const int hp = lam % P, slot = lam / P;
+            const int head = hp / PW, part = hp % PW;
+            uint4 qv[kRingMaxG];
+            for (int it = cw; it < my_items; it += kRingConsumerWarps) {
+                const int s = it % p.n_stages;
+                const uint32_t phase = (uint32_t)((it / p.n_stages) & 1);
+                if (!mbar_wait(&s_full[s], phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
+                const StageMeta m = s_meta[s];
+                const int j = m.j0 + blk;
+                const bool have = (m.valid_mask >> blk) & 1u;
+                const int ntok = have ? min(p.BS, m.seq - j * p.BS) : 0;
+                if (m.b != cur_b) {
+                    const uint4* q4 = reinterpret_cast<const uint4*>(p.q) + ((int64_t)m.b * p.Hq + head * p.G) * PW + part;
+#pragma unroll
+                    for (int g = 0; g < kRingMaxG; ++g)
+                        if (g < p.G) qv[g] = __ldg(q4 + g * PW);
+                    cur_b = m.b;
+                }
+                const uint4* sb = reinterpret_cast<const uint4*>(s_ring + (size_t)s * p.stage_bytes + blk * p.block_stride);
+                int best = INT_MAX;
+                const int rounds = (p.BS + TS - 1) / TS;  // same trip count in every lane (shuffles inside)
+                for (int r = 0; r < rounds; ++r) {
+                    const int tok = r * TS + slot;
+                    const bool ok = tok < ntok;
+                    int d = 0;
+                    if (ok) {
+                        const uint4 kv = sb[tok * P + hp];
+#pragma unroll
+                        for (int g = 0; g < kRingMaxG; ++g)
+                            if (g < p.G)
+                                d += __popc(kv.x ^ qv[g].x) + __popc(kv.y ^ qv[g].y) + __popc(kv.z ^ qv[g].z) +
+                                     __popc(kv.w ^ qv[g].w);
+                    }
+                    for (int off = 1; off < PW; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+                    best = min(best, ok ? d : INT_MAX);
+                }
+                // lanes of the same block that differ in the token slot (>= P), or with reduce_kvhead in
+                // the head bits as well, fold by min
+                for (int off = p.reduce_kvhead ? PW : P; off < LG; off <<= 1)
+                    best = min(best, __shfl_xor_sync(0xffffffffu, best, off));
+                if (j < p.max_blocks) {
+                    if (p.reduce_kvhead) {
+                        if (lam == 0) p.out[(int64_t)m.b * p.max_blocks + j] = have ? best : -1;
+                    } else if (slot == 0 && part == 0) {
+                        p.out[((int64_t)m.b * Hout + head) * p.max_blocks + j] = have ? best : -1;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_empty[s]);
+            }
+        }
+    }
+}
+
+// Returns UCMR_OK after launching, or UCMR_ERR_UNSUPPORTED when the shape is not covered (the caller
+// then uses the register kernel).
+int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const uint32_t* q, int Hq,
+                  const int32_t* bt, int max_blocks, int64_t bt_stride, const int32_t* seq_lens, int B,
+                  int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, cudaStream_t st)
+{
+    const int G = Hq / Hkv;
+    const int64_t RW = (int64_t)Hkv * W;
+    if (!is_pow2(W) || !is_pow2(Hkv) || W > 32 || RW < 4 || RW > 1024) return UCMR_ERR_UNSUPPORTED;
+    if (G > kRingMaxG || B > kRingMaxBatch) return UCMR_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(codes) % 16 != 0) return UCMR_ERR_UNSUPPORTED;
+    const int64_t block_bytes = (int64_t)BS * RW * 4;
+    if (block_bytes % 16 != 0 || block_bytes > 32 * 1024) return UCMR_ERR_UNSUPPORTED;
+    const bool is_min = reduce_mode == UCMR_REDUCE_MIN;
+    int bps = 1;
+    if (is_min) {
+        if (W % 4 != 0 || reinterpret_cast<uintptr_t>(q) % 16 != 0) return UCMR_ERR_UNSUPPORTED;
+        const int P = Hkv * (W / 4);
+        if (P > 32) return UCMR_ERR_UNSUPPORTED;
+        // several small blocks share a stage so that a warp-load still spans >= 16 tokens per block
+        while (bps < kRingMaxBps && 32 / (bps * 2) >= P && block_bytes * bps * 2 <= 16 * 1024 &&
+               BS / (32 / (bps * 2) / P) >= 16)
+            bps *= 2;
+    } else {
+        if (RW < 32) bps = (int)(32 / RW);
+        if (bps > kRingMaxBps) return UCMR_ERR_UNSUPPORTED;
+    }
+    RingParams p{};
+    p.codes = reinterpret_cast<const char*>(codes);
+    p.NB = NB; p.BS = BS; p.Hkv = Hkv; p.W = W; p.G = G; p.Hq = Hq;
+    p.q = q; p.bt = bt; p.max_blocks = max_blocks; p.bt_stride = bt_stride; p.seq_lens = seq_lens; p.B = B;
+    p.reduce_kvhead = reduce_kvhead ? 1 : 0; p.out = out; p.status = status;
+    p.RW = (int)RW; p.bps = bps; p.block_bytes = (int)block_bytes;
+    p.block_stride = (int)block_bytes + (bps > 1 ? 16 : 0);
+    p.stage_bytes = (bps * p.block_stride + 127) / 128 * 128;
+    p.n_stages = kRingBytes / p.stage_bytes;
+    if (p.n_stages > kRingMaxStages) p.n_stages = kRingMaxStages;
+    if (p.n_stages < 4) return UCMR_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)p.n_stages * p.stage_bytes;
+
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    // upper bound of the work items; the kernel computes the exact count from seq_lens
+    const int64_t max_items = (int64_t)B * ((max_blocks + bps - 1) / bps);
+    const int grid = (int)(max_items < sms ? (max_items > 0 ? max_items : 1) : sms);
+
+    void (*kernel)(const RingParams) = nullptr;
+    if (is_min) {
+        kernel = scan_ring_kernel<true, 0, 0>;
+    } else {
+#define UCMR_RING_CASE(RWV, GV) \
+    if (p.RW == RWV && G == GV) kernel = scan_ring_kernel<false, RWV, GV>;
+#define UCMR_RING_ROW(RWV) UCMR_RING_CASE(RWV, 1) UCMR_RING_CASE(RWV, 2) UCMR_RING_CASE(RWV, 4) UCMR_RING_CASE(RWV, 8)
+        UCMR_RING_ROW(4) UCMR_RING_ROW(8) UCMR_RING_ROW(16) UCMR_RING_ROW(32) UCMR_RING_ROW(64)
+#undef UCMR_RING_ROW
+#undef UCMR_RING_CASE
+        if (!kernel) kernel = scan_ring_kernel<false, 0, 0>;
+    }
+    // idempotent attribute, set on every call: cheap, and correct on every device of a process
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
+    if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
+    kernel<<<grid, kRingThreads, smem, st>>>(p);
+    return check_launch();
+}
+
+}  // namespace ucmr

@@ -228,6 +228,8 @@ def hamming_topk(codes: torch.Tensor, q_codes: torch.Tensor, block_table: torch.
             scores=torch.empty((b, hout, k), dtype=torch.int32, device=dev) if want_scores else None,
             valid_count=torch.empty((b,), dtype=torch.int32, device=dev),
             new_seq_lens=torch.empty((b,), dtype=torch.int32, device=dev))
+    if b == 0:
+        return out
     must, n_must = _must_array(must_select)
     lib = _l.load_library()
     _l.check(lib.ucmr_hamming_topk(
