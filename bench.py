@@ -1,0 +1,425 @@
+"""Benchmark of the hash-code top-k block retrieval path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one decode-step retrieval of ONE decoder layer for a whole batch:
+    encode the new K token of every request into the paged code cache   (ucmr_hash_encode_and_cache)
+    encode the query heads                                               (ucmr_hash_encode_query)
+    Hamming scan of every cached token + exact top-k per (request, kv head)   (ucmr_hamming_topk)
+on synthetic data of the shapes the workload names.  "Tokens scored" = cached KV positions scanned.
+
+Default workload `llama3_8b_decode16` (benchmark config 1): batch 16, 131072 tokens per request,
+8 kv heads, 32 query heads, head_dim 128, 128-bit codes, block 128, top-k 16 blocks, first 1 and last 2
+blocks forced, block score = sum of distances (mean * BS * G).  Four layers' code caches (256 MiB each)
+are resident and the steps rotate over them, so every timed scan reads data that is not in L2.
+
+With N > 1 (launched by torch.distributed.run) every rank runs the same workload on its own GPU
+(independent replicas, no collective: requests are data-parallel) and rank 0 reports the aggregate.
+
+`--impl reference` times the CPU implementation (the C port of the reference's algorithm under
+oracle/, all host threads) on the same workload, rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: B, seq_len, Hkv, Hq, D, bits, BS, k, layers resident
+    "llama3_8b_decode16": dict(B=16, seq=131072, Hkv=8, Hq=32, D=128, bits=128, BS=128, k=16, layers=4),
+    "single_request_32k": dict(B=1, seq=32768, Hkv=8, Hq=32, D=128, bits=128, BS=128, k=64, layers=32),
+}
+MUST_SELECT = (0, -2, -1)
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx = float(parts[2])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------
+# workload construction (device)
+# ----------------------------------------------------------------------------------------------
+def build_workload(cfg, dev, seed=1):
+    """Paged code caches filled by the encode kernel from synthetic bf16 keys (prefill), plus the
+    per-step inputs.  Returns a dict of device tensors and the prefill-encode timing."""
+    import torch
+    from unified_cache_management_b200 import ops
+    B, seq, Hkv, Hq, D, BS, L = cfg["B"], cfg["seq"], cfg["Hkv"], cfg["Hq"], cfg["D"], cfg["BS"], cfg["layers"]
+    W = cfg["bits"] // 32
+    mb = seq // BS
+    NB = B * mb + 8
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    R = (torch.randn((D, cfg["bits"]), device=dev, generator=g) / D ** 0.5).to(torch.bfloat16)
+    bt = torch.randperm(NB, device=dev, generator=g)[:B * mb].to(torch.int32).view(B, mb).contiguous()
+    seq_lens = torch.full((B,), seq, dtype=torch.int32, device=dev)
+    caches = [torch.zeros((NB, BS, Hkv, W), dtype=torch.int32, device=dev) for _ in range(L)]
+    # slot of logical position p of request b
+    pos = torch.arange(seq, device=dev)
+    enc_ms, enc_rows = [], 0
+    chunk = min(seq, 65536)
+    for layer in range(L):
+        for b in range(B):
+            slots_all = bt[b].to(torch.int64)[pos // BS] * BS + (pos % BS)
+            for c0 in range(0, seq, chunk):
+                g.manual_seed(seed * 1000003 + layer * 4099 + b * 17 + c0)
+                k = torch.randn((chunk, Hkv, D), device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                ops.hash_encode_and_cache(k, slots_all[c0:c0 + chunk], caches[layer], R)
+                e1.record()
+                torch.cuda.synchronize()
+                enc_ms.append(e0.elapsed_time(e1))
+                enc_rows += chunk * Hkv
+                del k
+    q = torch.randn((L, B, Hq, D), device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    k_new = torch.randn((L, B, Hkv, D), device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    last_slot = (bt[:, mb - 1].to(torch.int64) * BS + (BS - 1)).contiguous()
+    rows_per_call = chunk * Hkv
+    t = float(np.median(enc_ms)) * 1e-3
+    prefill = dict(rows_per_launch=rows_per_call, launches=len(enc_ms), median_ms=float(np.median(enc_ms)),
+                   gbs=(rows_per_call * (D * 2 + W * 4)) / t / 1e9, tflops=2.0 * rows_per_call * D * cfg["bits"] / t / 1e12)
+    return dict(R=R, bt=bt, seq_lens=seq_lens, caches=caches, q=q, k_new=k_new, last_slot=last_slot, NB=NB, mb=mb,
+                W=W), prefill
+
+
+def make_step(cfg, wl, dev):
+    """Returns step(layer) running the three C-ABI calls of one decode-step retrieval on device data."""
+    import torch
+    from unified_cache_management_b200 import ops
+    B, Hkv, Hq, k = cfg["B"], cfg["Hkv"], cfg["Hq"], cfg["k"]
+    ws = ops.new_workspace(B, Hkv, wl["mb"], dev)
+    q_codes = torch.empty((B, Hq, wl["W"]), dtype=torch.int32, device=dev)
+    out = ops.Retrieval(physical=torch.empty((B, Hkv, k), dtype=torch.int32, device=dev),
+                        logical=torch.empty((B, Hkv, k), dtype=torch.int32, device=dev), scores=None,
+                        valid_count=torch.empty((B,), dtype=torch.int32, device=dev),
+                        new_seq_lens=torch.empty((B,), dtype=torch.int32, device=dev))
+
+    def step(layer, q=None, k_new=None):
+        qq = wl["q"][layer] if q is None else q
+        kk = wl["k_new"][layer] if k_new is None else k_new
+        ops.hash_encode_and_cache(kk, wl["last_slot"], wl["caches"][layer], wl["R"])
+        ops.hash_encode_query(qq, wl["R"], out=q_codes)
+        ops.hamming_topk(wl["caches"][layer], q_codes, wl["bt"], wl["seq_lens"], k, reduce="sum",
+                         must_select=MUST_SELECT, workspace=ws, out=out, want_scores=False)
+        return out
+
+    return step, ws, q_codes, out
+
+
+def scan_bytes(cfg, wl):
+    """Algorithmic bytes of one scan launch: codes + query codes + block table + block scores out."""
+    B, seq, Hkv, Hq = cfg["B"], cfg["seq"], cfg["Hkv"], cfg["Hq"]
+    W = wl["W"]
+    return B * seq * Hkv * W * 4 + B * Hq * W * 4 + B * wl["mb"] * 4 + B * Hkv * wl["mb"] * 4
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm
+# ----------------------------------------------------------------------------------------------
+def cpu_step_factory(cfg, codes_host, bt_host, seq_host, r_host, q_host, k_new_host, n_req):
+    """One CPU step on the first n_req requests with the C port of the reference algorithm."""
+    from oracle import oracle as O
+    from oracle import oracle_c as OC
+    bt = np.ascontiguousarray(bt_host[:n_req])
+    sl = np.ascontiguousarray(seq_host[:n_req])
+
+    def step():
+        OC.hash_encode(k_new_host[:n_req], r_host)
+        qc = OC.hash_encode(q_host[:n_req], r_host)
+        return OC.hamming_topk(codes_host, qc, bt, sl, cfg["k"], O.REDUCE_SUM, False, must_select=MUST_SELECT)
+
+    return step
+
+
+def host_copies(cfg, wl, layer=0):
+    import torch
+    codes = wl["caches"][layer].cpu().numpy().view(np.uint32)
+    bt = wl["bt"].cpu().numpy()
+    sl = wl["seq_lens"].cpu().numpy()
+    r = wl["R"].view(torch.int16).cpu().numpy().view(np.uint16)
+    q = wl["q"][layer].view(torch.int16).cpu().numpy().view(np.uint16)
+    kn = wl["k_new"][layer].view(torch.int16).cpu().numpy().view(np.uint16)
+    return codes, bt, sl, r, q, kn
+
+
+def time_cpu(cfg, host, budget_s=12.0, max_steps=5):
+    """Times the CPU arm on a bounded sample: as many requests as fit in about budget_s/max_steps per step."""
+    from oracle import oracle_c as OC
+    codes, bt, sl, r, q, kn = host
+    probe = cpu_step_factory(cfg, codes, bt, sl, r, q, kn, 1)
+    t0 = time.perf_counter()
+    probe()
+    t1 = time.perf_counter() - t0
+    n_req = int(max(1, min(cfg["B"], (budget_s / max_steps) / max(t1, 1e-6))))
+    step = cpu_step_factory(cfg, codes, bt, sl, r, q, kn, n_req)
+    times = []
+    for _ in range(max_steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+        if sum(times) > budget_s:
+            break
+    best = min(times)
+    return dict(value=n_req * cfg["seq"] / best, unit="tokens/s", cores=OC.num_threads(), kind="port",
+                sample=f"{n_req} of {cfg['B']} requests x {cfg['seq']} tokens, one layer, best of {len(times)} steps "
+                       f"({best * 1e3:.1f} ms per step), C port of the reference algorithm with OpenMP"), n_req, best
+
+
+# ----------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="llama3_8b_decode16", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    cfg = dict(WORKLOADS[args.workload])
+    W = max(args.warmup, 3)
+    K = max(args.steps, 1)
+    config = dict(workload=args.workload, batch=cfg["B"], seq_len=cfg["seq"], kv_heads=cfg["Hkv"],
+                  query_heads=cfg["Hq"], head_dim=cfg["D"], hash_bits=cfg["bits"], block_size=cfg["BS"],
+                  topk_blocks=cfg["k"], must_select_blocks=list(MUST_SELECT), block_reduce="sum",
+                  selection="per kv head", layers_resident=cfg["layers"],
+                  l2="steps rotate over resident layer caches: inputs larger than L2",
+                  parallelism=f"dp{world} (independent replicas, no collective)")
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        # The CPU arm needs the same synthetic cache: build it on the GPU when there is one (fast),
+        # else with the CPU port of the encode.
+        dev = torch.device(f"cuda:{local_rank}") if torch.cuda.is_available() else None
+        if dev is None:
+            print(json.dumps({"impl": "reference", "unavailable": "no CUDA device to build the synthetic code cache"}))
+            return
+        torch.cuda.set_device(dev)
+        cfg_small = dict(cfg, layers=1)
+        wl, _ = build_workload(cfg_small, dev)
+        host = host_copies(cfg_small, wl)
+        del wl
+        torch.cuda.empty_cache()
+        codes, bt, sl, r, q, kn = host
+        probe = cpu_step_factory(cfg, codes, bt, sl, r, q, kn, 1)
+        t0 = time.perf_counter(); probe(); t1 = time.perf_counter() - t0
+        n_req = int(max(1, min(cfg["B"], 1.0 / max(t1, 1e-6))))   # about a second per step at most
+        step = cpu_step_factory(cfg, codes, bt, sl, r, q, kn, n_req)
+        for _ in range(min(W, 3)):
+            step()
+        t0 = time.perf_counter()
+        for _ in range(K):
+            step()
+            if time.perf_counter() - t0 > 150.0:   # keep the whole run within a few minutes
+                K = _ + 1
+                break
+        dt = time.perf_counter() - t0
+        from oracle import oracle_c as OC
+        val = n_req * cfg["seq"] * K / dt
+        sample = f"{n_req} of {cfg['B']} requests x {cfg['seq']} tokens per step, one layer"
+        print(json.dumps({"impl": "reference", "metric": "tokens_scored_per_sec", "value": val, "unit": "tokens/s",
+                          "n_gpus": args.gpus, "steps": K, "warmup": min(W, 3), "ms_per_step": dt / K * 1e3,
+                          "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32",
+                          "data": "synthetic", "config": config,
+                          "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": OC.num_threads(), "kind": "port",
+                                           "sample": sample},
+                          "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    # ------------------------------------------------------------------ our arm
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the retrieval kernels)")
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    from unified_cache_management_b200 import ops
+
+    wl, prefill = build_workload(cfg, dev, seed=1 + rank)
+    step, ws, q_codes, out = make_step(cfg, wl, dev)
+    L = cfg["layers"]
+    tokens_per_step = cfg["B"] * cfg["seq"]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # one CUDA graph per resident layer: the step has no allocation and no host sync
+    side = torch.cuda.Stream()
+    graphs = []
+    with torch.cuda.stream(side):
+        for layer in range(L):
+            step(layer)
+        torch.cuda.synchronize()
+        for layer in range(L):
+            gph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gph, stream=side):
+                step(layer)
+            graphs.append(gph)
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    for i in range(W):
+        graphs[i % L].replay()
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(K):
+        graphs[i % L].replay()
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+
+    # dominant kernel alone (the scan), one event pair per launch, same rotation over the layer caches
+    scores = torch.empty((cfg["B"], cfg["Hkv"], wl["mb"]), dtype=torch.int32, device=dev)
+    evs = []
+    for i in range(W + K):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        ops.block_scores(wl["caches"][i % L], q_codes, wl["bt"], wl["seq_lens"], reduce="sum", out=scores)
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    scan_ms = [a.elapsed_time(b) for a, b in evs[W:]]
+    clocks = sampler.stop()
+
+    # end to end through the public ops with host buffers: H2D of the step's inputs, D2H of its result
+    q_host = wl["q"].cpu().pin_memory()
+    k_host = wl["k_new"].cpu().pin_memory()
+    q_dev = torch.empty_like(wl["q"][0])
+    k_dev = torch.empty_like(wl["k_new"][0])
+    res_host = torch.empty((cfg["B"], cfg["Hkv"], cfg["k"]), dtype=torch.int32).pin_memory()
+
+    def e2e_step(i):
+        layer = i % L
+        q_dev.copy_(q_host[layer], non_blocking=True)
+        k_dev.copy_(k_host[layer], non_blocking=True)
+        o = step(layer, q_dev, k_dev)
+        res_host.copy_(o.physical, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(W):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(K):
+        e2e_step(i)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    h2d = q_dev.numel() * 2 + k_dev.numel() * 2
+    d2h = res_host.numel() * 4
+    status = ops.workspace_status(ws)
+
+    times = torch.tensor([ms_total, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms = (float(v) for v in times.cpu())
+
+    if rank == 0:
+        peaks, peak_kind = _peaks()
+        scan_t = float(np.mean(scan_ms)) * 1e-3
+        sb = scan_bytes(cfg, wl)
+        achieved = sb / scan_t / 1e9
+        line = {
+            "metric": "tokens_scored_per_sec", "value": world * tokens_per_step * K / (ms_total * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+            "config": config,
+            "per_gpu": tokens_per_step * K / (ms_total * 1e-3),
+            "retrieval_latency_us": ms_total / K * 1e3,
+            "roofline": {"bound": "hbm", "kernel": "scan_ring_kernel (Hamming scan)", "achieved": achieved,
+                         "peak": peaks["hbm_gbs"], "peak_kind": f"{peak_kind} copy bandwidth", "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "frac_of_8tbs_spec": achieved / 8000.0,
+                         "traffic": None, "algorithmic_bytes_per_launch": sb,
+                         "launch_us_mean": scan_t * 1e6, "launch_us_min": float(np.min(scan_ms)) * 1e3},
+            "prefill_encode": {"kernel": "encode_tc_kernel (tcgen05)", **prefill,
+                               "frac_hbm": prefill["gbs"] / peaks["hbm_gbs"]},
+            "e2e": {"value": world * tokens_per_step * K / (e2e_ms * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / K},
+            "gpu_launches": 4 * K, "device_status_word": status, "clocks": clocks,
+        }
+        if not args.no_cpu_baseline:
+            base, _, _ = time_cpu(cfg, host_copies(cfg, wl))
+            line["cpu_baseline"] = base
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

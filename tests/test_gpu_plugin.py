@@ -1,0 +1,182 @@
+"""GPU test of the GSAOnDevice plugin driven the way the patched vLLM drives it:
+build_sparse_meta -> attention_begin (per layer) -> attention_finished -> execute_finished."""
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests import fake_vllm as F
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf16_bits(t):
+    import torch
+    return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def test_prefill_then_decode_rewrites_and_restores_block_table(cuda_device):
+    import torch
+    from unified_cache_management_b200.base import UcmSparseRole
+    from unified_cache_management_b200.gsa_on_device import GSAOnDevice
+    dev = cuda_device
+    BS, Hq, Hkv, D = 16, 8, 2, 128
+    topk_tokens = 8 * BS
+    cfg = F.make_vllm_config(block_size=BS, num_q_heads=Hq, num_kv_heads=Hkv, max_model_len=64 * BS, max_num_seqs=4,
+                             overrides=dict(vllm_hash_attention_topk=topk_tokens, gpu_seq_len_threshold=topk_tokens,
+                                            gpu_concurrency_threshold=2, vllm_hash_attention_rollback_layers=[0],
+                                            vllm_hash_attention_skip_layers=[False, False, True]))
+    plugin = GSAOnDevice(cfg, UcmSparseRole.WORKER)
+    assert plugin.estimate_num_slots_sparsed(None) == -1
+
+    n_req, NB, mb = 3, 200, 64
+    lens = [40 * BS + 3, 25 * BS, 9 * BS + 1]
+    rng = np.random.default_rng(0)
+    perm = rng.permutation(NB)
+    bt = np.zeros((n_req, mb), dtype=np.int32)
+    off = 0
+    for b, ln in enumerate(lens):
+        n = -(-(ln + 1) // BS)
+        bt[b, :n] = perm[off:off + n]
+        off += n
+    kv_caches = {f"model.layers.{i}.self_attn.attn": torch.zeros((2, NB, BS, Hkv, D), dtype=torch.bfloat16, device=dev)
+                 for i in range(3)}
+    plugin.initialize_kv_hash_cache_tensors(kv_caches, dev)
+    assert kv_caches["model.layers.0.self_attn.attn"][1] is None            # rollback layer: no code cache
+    k_hash = kv_caches["model.layers.1.self_attn.attn"][1]
+    assert k_hash.shape == (NB, BS, Hkv, D // 16) and k_hash.dtype == torch.bfloat16
+
+    requests = {f"r{b}": F.FakeRequest(num_computed_tokens=0, num_prompt_tokens=lens[b]) for b in range(n_req)}
+    input_batch = SimpleNamespace(req_id_to_index={f"r{b}": b for b in range(n_req)})
+    layer = "model.layers.1.self_attn.attn"
+
+    # ---- step 1: prefill of all three prompts -------------------------------------------------------
+    keys = [H.bf16_normal(rng, (ln, Hkv, D)) for ln in lens]
+    key_all = torch.cat([H.bf16_to_dev(k, dev) for k in keys])
+    slots = np.concatenate([bt[b, np.arange(ln) // BS].astype(np.int64) * BS + np.arange(ln) % BS
+                            for b, ln in enumerate(lens)])
+    qsl = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    meta = SimpleNamespace(seq_lens=torch.tensor(lens, dtype=torch.int32, device=dev),
+                           block_table=torch.from_numpy(bt).to(dev), slot_mapping=torch.from_numpy(slots).to(dev),
+                           query_start_loc=torch.from_numpy(qsl).to(dev))
+    fc = SimpleNamespace(attn_metadata={layer: meta}, no_compile_layers={}, virtual_engine=0)
+    so = F.scheduler_output({f"r{b}": lens[b] for b in range(n_req)})
+    plugin.update_states(so)
+    plugin.build_sparse_meta(so, requests, input_batch, {layer: meta})
+    assert plugin.gsa_enabled and not plugin.has_decode                      # long enough, but no decode yet
+    q_dummy = torch.zeros((sum(lens), Hq, D), dtype=torch.bfloat16, device=dev)
+    plugin.attention_begin(q_dummy, key_all, key_all, layer, fc, k_hash=k_hash)
+    plugin.attention_finished(q_dummy, key_all, key_all, None, layer, fc)
+    plugin.execute_finished(None)
+    torch.cuda.synchronize()
+    r_bits = _bf16_bits(plugin.hash_encoder.hash_weights_bf16)
+    codes_dev = k_hash.view(torch.int32).cpu().numpy().view(np.uint32)       # [NB,BS,Hkv,4]
+    for b, ln in enumerate(lens):
+        want, p64 = O.hash_encode(keys[b], r_bits)
+        got = codes_dev.reshape(NB * BS, Hkv, 4)[slots[qsl[b]:qsl[b + 1]]]
+        hard, soft = O.count_code_mismatches(got, p64)
+        assert hard == 0
+
+    # ---- step 2: decode of all three (one new token each) --------------------------------------------
+    for r in requests.values():
+        r.num_computed_tokens = r.num_prompt_tokens
+    new_lens = [ln + 1 for ln in lens]
+    new_keys = H.bf16_normal(rng, (n_req, Hkv, D))
+    new_slots = np.array([bt[b, lens[b] // BS].astype(np.int64) * BS + lens[b] % BS for b in range(n_req)])
+    q_bits = H.bf16_normal(rng, (n_req, Hq, D))
+    bt_dev = torch.from_numpy(bt).to(dev)
+    meta = SimpleNamespace(seq_lens=torch.tensor(new_lens, dtype=torch.int32, device=dev), block_table=bt_dev,
+                           slot_mapping=torch.from_numpy(new_slots).to(dev),
+                           query_start_loc=torch.arange(n_req + 1, dtype=torch.int32, device=dev))
+    fc = SimpleNamespace(attn_metadata={layer: meta}, no_compile_layers={}, virtual_engine=0)
+    so = F.scheduler_output({f"r{b}": 1 for b in range(n_req)})
+    plugin.build_sparse_meta(so, requests, input_batch, {layer: meta})
+    assert plugin.gsa_enabled and plugin.has_decode and plugin.decode_only
+    kd = H.bf16_to_dev(new_keys, dev)
+    plugin.attention_begin(H.bf16_to_dev(q_bits, dev), kd, kd, layer, fc, k_hash=k_hash)
+    torch.cuda.synchronize()
+    k = topk_tokens // BS
+    sel = meta.block_table[:, :k].cpu().numpy()
+    assert (meta.block_table[:, k:] == 0).all()
+    new_seq = meta.seq_lens.cpu().numpy()
+
+    # oracle on the cache contents as the device holds them now
+    codes_now = k_hash.view(torch.int32).cpu().numpy().view(np.uint32)
+    qm = O.group_mean_bf16(q_bits, Hkv)
+    q_codes, _ = O.hash_encode(qm, r_bits)
+    ref = O.hamming_topk(codes_now, q_codes, bt, np.array(new_lens), k, O.REDUCE_MIN, True, sink_tokens=BS,
+                         recent_tokens=4 * BS)
+    assert np.array_equal(sel, ref["physical"][:, 0, :])
+    assert np.array_equal(new_seq, O.update_seq_lens(np.array(new_lens), topk_tokens, BS))
+
+    # skip layer reuses the selection; attention_finished restores the original table and lengths
+    layer2 = "model.layers.2.self_attn.attn"
+    meta2 = SimpleNamespace(seq_lens=meta.seq_lens, block_table=meta.block_table, slot_mapping=meta.slot_mapping,
+                            query_start_loc=meta.query_start_loc)
+    fc2 = SimpleNamespace(attn_metadata={layer2: meta2}, no_compile_layers={}, virtual_engine=0)
+    plugin.attention_begin(H.bf16_to_dev(q_bits, dev), kd, kd, layer2, fc2, k_hash=None)
+    assert meta2.block_table is plugin.topk_block_table
+    plugin.attention_finished(None, None, None, None, layer, fc)
+    assert np.array_equal(meta.block_table.cpu().numpy(), bt)
+    assert meta.seq_lens.cpu().tolist() == new_lens
+    plugin.execute_finished(None)
+    assert not plugin.gsa_enabled and not plugin.has_decode
+
+    # finished requests drop their state; a resumed one starts as a prefill again
+    so = F.scheduler_output({}, finished=["r0"], resumed=[("r1", True)])
+    plugin.update_states(so)
+    assert "r0" not in plugin.is_prefill_flag and "r1" not in plugin.is_prefill_flag and "r2" in plugin.is_prefill_flag
+
+
+def test_reference_hamming_topk_module_interface(cuda_device):
+    """cuda_hamming_topk / update_seq_lens with the reference's argument list."""
+    import torch
+    from unified_cache_management_b200 import hamming_topk as HT
+    dev = cuda_device
+    B, Hkv, W, BS, mb = 3, 4, 4, 16, 20
+    case = H.make_paged_case(13, B, Hkv, 1, W, BS, mb)
+    k_hash = H.to_dev_i32(case["codes"], dev).view(torch.bfloat16)           # the plugin stores codes as bf16
+    q_hash = H.to_dev_i32(case["q"], dev).view(torch.bfloat16).unsqueeze(1)
+    bt, sl = H.to_dev_i32(case["block_table"], dev), H.to_dev_i32(case["seq_lens"], dev)
+    out = HT.cuda_hamming_topk(q_hash, k_hash, bt, sl, 6 * BS, BS, 2 * BS, False)
+    torch.cuda.synchronize()
+    ref = O.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], 6, O.REDUCE_MIN, True,
+                         sink_tokens=BS, recent_tokens=2 * BS)
+    assert np.array_equal(out.cpu().numpy(), ref["physical"][:, 0])
+    with pytest.raises(AssertionError):
+        HT.cuda_hamming_topk(q_hash, k_hash, bt, sl, 6 * BS + 1, BS, 2 * BS, False)
+    with pytest.raises(AssertionError):
+        HT.cuda_hamming_topk(q_hash, k_hash, bt, sl, 2 * BS, BS, 2 * BS, False)
+    got = HT.update_seq_lens(sl, 6 * BS, BS).cpu().numpy()
+    assert np.array_equal(got, O.update_seq_lens(case["seq_lens"], 6 * BS, BS))
+    assert np.array_equal(HT.update_seq_lens(sl.cpu(), 6 * BS, BS).numpy(), got)
+    assert HT.fake_hamming_topk(q_hash, k_hash, bt, sl, 6 * BS, BS, 2 * BS).shape == (B, 6)
+
+
+def test_hash_encoder_interface(cuda_device):
+    import torch
+    from unified_cache_management_b200.hash_encoder import HashEncoder
+    dev = cuda_device
+    enc = HashEncoder(128, 128, torch.bfloat16, dev)
+    w = enc.hash_weights
+    assert w.dtype == torch.float32                                          # bf16 models keep a float32 master
+    eye = (w.T @ w)
+    assert torch.allclose(eye, torch.eye(128, device=dev), atol=1e-4)        # orthogonal projection
+    with pytest.raises(ValueError):
+        HashEncoder(128, 100, torch.bfloat16, dev)
+    with pytest.raises(ValueError):
+        enc.set_hash_weight(torch.zeros((64, 128), device=dev))
+    with pytest.raises(ValueError):
+        enc.compute_hash(torch.zeros((4, 64), dtype=torch.bfloat16, device=dev))
+    rng = np.random.default_rng(1)
+    x = H.bf16_normal(rng, (5, 7, 128))
+    codes = enc.compute_hash(H.bf16_to_dev(x, dev))
+    assert codes.shape == (5, 7, 16) and codes.dtype == torch.uint8
+    _, p64 = O.hash_encode(x, _bf16_bits(enc.hash_weights_bf16))
+    hard, _ = O.count_code_mismatches(codes.cpu().numpy().view("<u4"), p64)
+    assert hard == 0
+    pm = enc._unpack_hash(codes)
+    assert pm.shape == (5, 7, 128) and set(pm.unique().tolist()) <= {-1.0, 1.0}
+    assert torch.equal(pm > 0, torch.from_numpy(O.unpack_bits_u32(codes.cpu().numpy().view("<u4"))).to(dev))

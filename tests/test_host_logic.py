@@ -1,0 +1,83 @@
+"""CPU tests of the host-side mirror: config keys, model lookup, hook surface, role handling."""
+import json
+import os
+
+import pytest
+
+from tests import fake_vllm as F
+from unified_cache_management_b200 import base
+from unified_cache_management_b200.gsa_on_device_config import GSAOnDeviceConfig
+
+
+def test_config_round_trip_and_validation(tmp_path):
+    cfg = GSAOnDeviceConfig()
+    assert cfg.must_select_blocks == [0, -2, -1] and cfg.chunk_repre_method == "max" and cfg.reduce == "min"
+    cfg.generate_config_data("m", "random", 4, 2048, 128, "sum", 128, 128, [0.3] * 4, [-1] * 4, [0, -1])
+    assert cfg.reduce == "sum"
+    p = tmp_path / "c.json"
+    cfg.to_json(str(p))
+    again = GSAOnDeviceConfig.from_json(str(p))
+    assert again.must_select_blocks == [0, -1] and again.num_hidden_layers == 4
+    with pytest.raises(ValueError):
+        cfg.generate_config_data("m", "learned", 4, 2048, 128, "sum", 128, 128, [0.3] * 4, [-1] * 4, [0])
+    with pytest.raises(ValueError):
+        cfg.generate_config_data("m", "random", 4, 2048, 100, "sum", 128, 128, [0.3] * 4, [-1] * 4, [0])
+    with pytest.raises(ValueError):
+        cfg.generate_config_data("m", "random", 4, 2048, 128, "median", 128, 128, [0.3] * 4, [-1] * 4, [0])
+    with pytest.raises(ValueError):
+        cfg.generate_config_data("m", "random", 4, 2048, 128, "sum", 128, 128, [0.3] * 3, [-1] * 4, [0])
+    with pytest.raises(ValueError):
+        cfg.set_hash_weight([[0.0]])
+    cfg.apply_overrides({"init_window_sz": 1, "local_window_sz": 2, "vllm_hash_attention_topk": 4096}, 128)
+    assert cfg.must_select_blocks == [0, -2, -1] and cfg.vllm_hash_attention_topk == 4096
+
+
+def test_reference_json_files_load_unchanged():
+    """Every key of the shipped per-model files is a field of the dataclass (same names as the reference)."""
+    d = os.path.join(os.path.dirname(base.__file__), "configs")
+    files = [f for f in os.listdir(d) if f.endswith(".json")]
+    assert files
+    for f in files:
+        cfg = GSAOnDeviceConfig.from_json(os.path.join(d, f))
+        assert cfg.vllm_hash_attention_topk % 128 == 0
+        assert len(cfg.top_k_ratio_per_layer) == cfg.num_hidden_layers
+
+
+def test_model_lookup():
+    from unified_cache_management_b200.gsa_on_device import gsa_on_device_config_path_for_model
+    assert gsa_on_device_config_path_for_model(F.make_vllm_config("Qwen/Qwen3-32B")).endswith("qwen3_32B_config.json")
+    assert gsa_on_device_config_path_for_model(F.make_vllm_config("meta-llama/Meta-Llama-3-70B-Instruct")).endswith(
+        "llama3_70B_config.json")
+    with pytest.raises(ValueError):
+        gsa_on_device_config_path_for_model(F.make_vllm_config("mistralai/Mixtral"))
+
+
+def test_hook_surface_matches_reference_names():
+    from unified_cache_management_b200.gsa_on_device import GSAOnDevice
+    hooks = ["register_kv_caches", "execute_begin", "execute_finished", "attention_begin", "attention_finished",
+             "update_states", "ffn_begin", "ffn_finished", "layer_begin", "layer_finished", "request_finished_in_worker",
+             "request_begin", "request_finished_in_scheduler", "estimate_num_slots_sparsed", "update_state_after_alloc",
+             "build_sparse_meta", "allocate_slots", "initialize_kv_hash_cache_tensors", "bind_sparse_metadata",
+             "clear_sparse_metadata"]
+    for h in hooks:
+        assert callable(getattr(GSAOnDevice, h)), h
+    assert base.INVALID_SLOT == -1
+    assert {r.name for r in base.UcmSparseRole} == {"SCHEDULER", "WORKER"}
+    import inspect
+    sig = inspect.signature(GSAOnDevice.attention_begin)
+    assert list(sig.parameters)[1:] == ["query", "key", "value", "layer_name", "forward_context", "output", "phase",
+                                        "k_hash", "decode_ql_nope", "decode_q_pe"]
+
+
+def test_scheduler_role_needs_no_device_buffers():
+    from unified_cache_management_b200.gsa_on_device import GSAOnDevice
+    plugin = GSAOnDevice(F.make_vllm_config("Qwen/Qwen3-4B", max_model_len=32768), base.UcmSparseRole.SCHEDULER)
+    assert plugin.role == base.UcmSparseRole.SCHEDULER
+    assert plugin.estimate_num_slots_sparsed(None) == base.INVALID_SLOT
+    assert plugin.hash_topk_tokens == 2048 and plugin.seq_len_threshold == 2048
+    plugin.request_begin("r", [1, 2, 3])
+    plugin.request_finished_in_scheduler("r")
+    with pytest.raises(ValueError):
+        GSAOnDevice(F.make_vllm_config("Qwen/Qwen3-4B", device_type="npu"), base.UcmSparseRole.SCHEDULER)
+    with pytest.raises(AssertionError):   # top-k budget above the context limit
+        GSAOnDevice(F.make_vllm_config("Qwen/Qwen3-4B", max_model_len=1024), base.UcmSparseRole.SCHEDULER)

@@ -1,11 +1,13 @@
 // Hamming scan, staged variant (sm_100a): one persistent CTA per SM streams paged code blocks through
-// a shared-memory ring with the bulk-copy (TMA) engine and reduces them with eight consumer warps.
+// a shared-memory ring with the bulk-copy (TMA) engine and reduces them with six consumer warps.
 //
 //   producer warp   resolves the next 32 work items in parallel (request, logical block, block-table
 //                   lookup), then one lane issues cp.async.bulk global->shared for each item onto the
 //                   stage's mbarrier.  Up to kRingBytes of loads are in flight per SM at any time, so
 //                   the block-table -> code-block dependency never stalls the memory pipe.
-//   consumer warps  item i belongs to warp i % 8.
+//   consumer warps  item i belongs to warp i % 6; the stage count is a multiple of 6, so a stage is always
+//                   drained by the same warp and no waiter can be two barrier phases ahead (a parity
+//                   wait cannot tell phase n from phase n+2).
 //     sum mode: the distance sum over a block only depends on how many of its tokens have each code
 //       bit set.  A lane owns one 32-bit column (kv head, word) of the block and folds all its tokens
 //       into bit-sliced vertical counters with carry-save adders (about 2.4 LOP3 per code word, no
@@ -25,11 +27,13 @@
 //  ucm/sparse/gsa_on_device/hamming_topk.py:45-47).
 #include <limits.h>
 
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace ucmr {
 
-constexpr int kRingConsumerWarps = 8;
+constexpr int kRingConsumerWarps = 6;
 constexpr int kRingThreads = 32 * (1 + kRingConsumerWarps);
 constexpr int kRingBytes = 192 * 1024;
 constexpr int kRingMaxStages = 32;
@@ -53,10 +57,23 @@ struct RingParams {
     int RW;            // words per token row = Hkv * W
     int bps;           // blocks per stage
     int block_bytes;   // BS * RW * 4
-    int block_stride;  // block_bytes (+16 when several blocks share a stage: spreads them over banks)
+    int block_stride;  // = block_bytes (tensor copies land on 128-byte boundaries)
+    int rows128;       // 128-byte rows per block in the flat [bytes/128, 32 words] view of the cache
     int stage_bytes;   // bps * block_stride, rounded up to 128
     int n_stages;
 };
+
+// Tiled TMA load of one code block: the cache is viewed as a 2-D tensor [bytes/128, 32 words] and a
+// block is a box of rows128 rows.  (The untiled cp.async.bulk form of the same copy sustains a much
+// lower rate per SM.)
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+            "r"(smem_u32(smem_dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
 
 struct StageMeta {
     int b, j0, seq;
@@ -71,25 +88,13 @@ __device__ __forceinline__ void csa(uint32_t& h, uint32_t& l, uint32_t a, uint32
     l = u ^ c;
 }
 
-constexpr int kPlanes = 8;        // vertical counters hold up to 255 tokens between flushes
-constexpr int kFlushTokens = 192;  // multiple of 64, below 256
-
-// Adds a one-bit-per-position value of weight 2^LEVEL into the counters (ripple carry).
-template <int LEVEL>
-__device__ __forceinline__ void ripple_add(uint32_t (&pl)[kPlanes], uint32_t v)
-{
-#pragma unroll
-    for (int p = LEVEL; p < kPlanes; ++p) {
-        const uint32_t carry = pl[p] & v;
-        pl[p] ^= v;
-        v = carry;
-    }
-}
+constexpr int kPlanes = 8;     // vertical counters of one chunk: counts up to 128
+constexpr int kChunkTokens = 128;  // tokens a lane buffers in registers per chunk
 
 // Folds 16 words into planes 0..3 (carry-save) and returns the carry of weight 16.
-__device__ __forceinline__ uint32_t fold16(uint32_t (&pl)[kPlanes], const uint32_t (&x)[16])
+__device__ __forceinline__ uint32_t fold16(uint32_t& ones, uint32_t& twos, uint32_t& fours, uint32_t& eights,
+                                           const uint32_t* x)
 {
-    uint32_t ones = pl[0], twos = pl[1], fours = pl[2], eights = pl[3];
     uint32_t t2a, t2b, t4a, t4b, t8a, t8b, t16;
     csa(t2a, ones, ones, x[0], x[1]);
     csa(t2b, ones, ones, x[2], x[3]);
@@ -106,70 +111,85 @@ __device__ __forceinline__ uint32_t fold16(uint32_t (&pl)[kPlanes], const uint32
     csa(t4b, twos, twos, t2a, t2b);
     csa(t8b, fours, fours, t4a, t4b);
     csa(t16, eights, eights, t8a, t8b);
-    pl[0] = ones; pl[1] = twos; pl[2] = fours; pl[3] = eights;
     return t16;
 }
 
-// One column of a block: folds tokens [0, ntok) of the 32-bit column at colp (row stride RW words)
-// into vertical counters and returns sum_g sum_tokens popc(word ^ q[g]).
-// RW_T / G_T > 0 fix the stride / group size at compile time (immediate offsets, unrolled popcounts).
-template <int RW_T, int G_T>
-__device__ __forceinline__ int column_sum(const uint32_t* colp, int ntok, int rw_rt, int g_rt, const uint32_t* qw)
+// Counts, for every bit position, how many of the 128 buffered words have the bit set: eight
+// bit-sliced planes (plane p holds bit p of the 32 counters).  Pure carry-save adder tree.
+__device__ __forceinline__ void fold128(const uint32_t (&x)[kChunkTokens], uint32_t (&pl)[kPlanes])
 {
-    const int RW = RW_T > 0 ? RW_T : rw_rt;
+    uint32_t p0 = 0, p1 = 0, p2 = 0, p3 = 0, p4 = 0, p5 = 0, p6 = 0;
+    uint32_t c[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) c[u] = fold16(p0, p1, p2, p3, &x[u * 16]);
+    uint32_t t32a, t32b, t32c, t32d, t64a, t64b, t128;
+    csa(t32a, p4, p4, c[0], c[1]);
+    csa(t32b, p4, p4, c[2], c[3]);
+    csa(t32c, p4, p4, c[4], c[5]);
+    csa(t32d, p4, p4, c[6], c[7]);
+    csa(t64a, p5, p5, t32a, t32b);
+    csa(t64b, p5, p5, t32c, t32d);
+    csa(t128, p6, p6, t64a, t64b);
+    pl[0] = p0; pl[1] = p1; pl[2] = p2; pl[3] = p3; pl[4] = p4; pl[5] = p5; pl[6] = p6; pl[7] = t128;
+}
+
+// sum_g sum_tokens popc(word ^ q[g]) of one buffered chunk of n tokens (unused slots hold 0).
+template <int G_T>
+__device__ __forceinline__ int chunk_score(const uint32_t (&x)[kChunkTokens], int n, int g_rt, const uint32_t* qw)
+{
     const int G = G_T > 0 ? G_T : g_rt;
     constexpr int GMAX = G_T > 0 ? G_T : kRingMaxG;
+    uint32_t pl[kPlanes];
+    fold128(x, pl);
     int qpop = 0;
 #pragma unroll
     for (int g = 0; g < GMAX; ++g)
         if (g < G) qpop += __popc(qw[g]);
-    int acc = 0;
-    for (int t0 = 0; t0 < ntok; t0 += kFlushTokens) {
-        uint32_t pl[kPlanes];
+    int acc = n * qpop;
 #pragma unroll
-        for (int i = 0; i < kPlanes; ++i) pl[i] = 0u;
-        const int t1 = min(ntok, t0 + kFlushTokens);
-        const uint32_t* cp = colp + (size_t)t0 * RW;
-        int t = t0;
-        for (; t + 64 <= t1; t += 64, cp += 64 * RW) {
-            uint32_t c16[4];
+    for (int i = 0; i < kPlanes; ++i) {
+        int d = G * __popc(pl[i]);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                uint32_t x[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) x[i] = cp[(u * 16 + i) * RW];
-                c16[u] = fold16(pl, x);
-            }
-            uint32_t t32a, t32b, t64, p4 = pl[4], p5 = pl[5];
-            csa(t32a, p4, p4, c16[0], c16[1]);
-            csa(t32b, p4, p4, c16[2], c16[3]);
-            csa(t64, p5, p5, t32a, t32b);
-            pl[4] = p4; pl[5] = p5;
-            ripple_add<6>(pl, t64);
-        }
-        for (; t < t1; t += 16, cp += 16 * RW) {
-            uint32_t x[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) x[i] = (t + i < t1) ? cp[i * RW] : 0u;
-            ripple_add<4>(pl, fold16(pl, x));
-        }
-        acc += (t1 - t0) * qpop;
-#pragma unroll
-        for (int i = 0; i < kPlanes; ++i) {
-            int d = G * __popc(pl[i]);
-#pragma unroll
-            for (int g = 0; g < GMAX; ++g)
-                if (g < G) d -= 2 * __popc(pl[i] & qw[g]);
-            acc += d * (1 << i);
-        }
+        for (int g = 0; g < GMAX; ++g)
+            if (g < G) d -= 2 * __popc(pl[i] & qw[g]);
+        acc += d * (1 << i);
     }
     return acc;
+}
+
+// Copies tokens [t0, t0+128) of the lane's 32-bit column (row stride RW words) from the stage into
+// registers; slots at or past ntok read as 0.  `rot` > 0 (several blocks per stage, one per lane
+// group): block k starts its walk k tokens later, wrapping inside [0, bs), because the blocks sit on
+// 128-byte boundaries and the same token of every block would otherwise hit the same banks.
+template <int RW_T>
+__device__ __forceinline__ void load_chunk(uint32_t (&x)[kChunkTokens], const uint32_t* colp, int t0, int ntok, int rw_rt,
+                                           int rot, int bs)
+{
+    const int RW = RW_T > 0 ? RW_T : rw_rt;
+    constexpr bool kMaybeNarrow = (RW_T == 0 || RW_T < 32);
+    if (kMaybeNarrow && RW < 32) {
+#pragma unroll
+        for (int i = 0; i < kChunkTokens; ++i) {
+            int tt = t0 + i + rot;
+            if (tt >= bs) tt -= bs;
+            x[i] = (t0 + i < bs && tt < ntok) ? colp[tt * RW] : 0u;
+        }
+    } else if (t0 + kChunkTokens <= ntok) {
+        const uint32_t* cp = colp + (size_t)t0 * RW;
+#pragma unroll
+        for (int i = 0; i < kChunkTokens; ++i) x[i] = cp[i * RW];
+    } else {
+        const uint32_t* cp = colp + (size_t)t0 * RW;
+#pragma unroll
+        for (int i = 0; i < kChunkTokens; ++i) x[i] = (t0 + i < ntok) ? cp[i * RW] : 0u;
+    }
 }
 
 // MIN selects the per-token-minimum consumer; RW_T / G_T (sum mode only) are compile-time copies of
 // the row width and group size for the common shapes, 0 = read them from the parameters.
 template <bool MIN, int RW_T, int G_T>
-__global__ void __launch_bounds__(kRingThreads, 1) scan_ring_kernel(const RingParams p)
+__global__ void __launch_bounds__(kRingThreads, 1)
+scan_ring_kernel(const __grid_constant__ CUtensorMap cmap, const RingParams p)
 {
     extern __shared__ __align__(128) uint8_t s_ring[];
     __shared__ __align__(8) uint64_t s_full[kRingMaxStages];
@@ -183,6 +203,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) scan_ring_kernel(const RingPa
     if (tid == 0) {
         for (int s = 0; s < p.n_stages; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 1); }
         fence_mbar_init();
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&cmap) : "memory");
     }
     if (warp == 0) {  // prefix sum of items per request
         int run = 0;
@@ -275,8 +296,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) scan_ring_kernel(const RingPa
 #pragma unroll
                         for (int k = 0; k < kRingMaxBps; ++k)
                             if (ph[k] >= 0)
-                                bulk_g2s(dst + k * p.block_stride, p.codes + (int64_t)ph[k] * p.block_bytes,
-                                         (uint32_t)p.block_bytes, &s_full[s]);
+                                tma_load_2d(dst + k * p.block_stride, &cmap, 0, ph[k] * p.rows128, &s_full[s]);
                     }
                 }
             }
@@ -295,6 +315,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) scan_ring_kernel(const RingPa
             const int passes = RW / cols;
             const int blk = (RW < 32) ? lane / RW : 0;
             const int col0 = (RW < 32) ? lane % RW : lane;
+            const int rot = (RW < 32) ? blk % max(p.BS, 1) : 0;  // see column_sum
             uint32_t qw[GMAX];
             for (int it = cw; it < my_items; it += kRingConsumerWarps) {
                 const int s = it % p.n_stages;
@@ -306,6 +327,11 @@ __global__ void __launch_bounds__(kRingThreads, 1) scan_ring_kernel(const RingPa
                 const int ntok = have ? min(p.BS, m.seq - j * p.BS) : 0;
                 const uint8_t* sb = s_ring + (size_t)s * p.stage_bytes + blk * p.block_stride;
                 int total = 0;  // per-head (or all-head) score, complete in the lanes that write
+                // tokens are walked in 128-token chunks; with several blocks per stage every lane group walks
+                // the whole block capacity (rotated), else only the valid tokens
+                const int walk = (RW < 32) ? p.BS : ntok;
+                const int n_chunks = (__reduce_max_sync(0xffffffffu, walk) + kChunkTokens - 1) / kChunkTokens;
+                bool released = false;
                 for (int ps = 0; ps < passes; ++ps) {
                     const int col = col0 + ps * 32;
                     const int head = col / p.W, w = col - head * p.W;
@@ -315,7 +341,19 @@ __global__ void __launch_bounds__(kRingThreads, 1) scan_ring_kernel(const RingPa
                             if (g < G) qw[g] = __ldg(p.q + ((int64_t)m.b * p.Hq + head * G + g) * p.W + w);
                     }
                     const uint32_t* colp = reinterpret_cast<const uint32_t*>(sb) + col;
-                    int acc = column_sum<RW_T, G_T>(colp, ntok, RW, G, qw);
+                    int acc = 0;
+                    for (int c = 0; c < n_chunks; ++c) {
+                        uint32_t x[kChunkTokens];
+                        load_chunk<RW_T>(x, colp, c * kChunkTokens, ntok, RW, rot, p.BS);
+                        if (ps == passes - 1 && c == n_chunks - 1) {
+                            // the stage's last words are in registers: hand the buffer back before the math
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&s_empty[s]);
+                            released = true;
+                        }
+                        const int n_here = max(0, min(kChunkTokens, ntok - ((RW < 32) ? 0 : c * kChunkTokens)));
+                        acc += chunk_score<G_T>(x, (RW < 32) ? (c == 0 ? ntok : 0) : n_here, G, qw);
+                    }
                     // fold the words of a head; with reduce_kvhead also the heads of this pass
                     const int span = p.reduce_kvhead ? cols : p.W;
                     for (int off = 1; off < span && off < 32; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
@@ -331,8 +369,10 @@ __global__ void __launch_bounds__(kRingThreads, 1) scan_ring_kernel(const RingPa
                     // block inside the stage but not loaded: past the request's end or a bad id
                     for (int h = 0; h < Hout; ++h) p.out[((int64_t)m.b * Hout + h) * p.max_blocks + j] = -1;
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&s_empty[s]);
+                if (!released) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&s_empty[s]);
+                }
             }
         } else {
             // lane <-> (block in stage, 16-byte piece of a token row, token slot)
@@ -427,12 +467,46 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     p.q = q; p.bt = bt; p.max_blocks = max_blocks; p.bt_stride = bt_stride; p.seq_lens = seq_lens; p.B = B;
     p.reduce_kvhead = reduce_kvhead ? 1 : 0; p.out = out; p.status = status;
     p.RW = (int)RW; p.bps = bps; p.block_bytes = (int)block_bytes;
-    p.block_stride = (int)block_bytes + (bps > 1 ? 16 : 0);
-    p.stage_bytes = (bps * p.block_stride + 127) / 128 * 128;
+    if (block_bytes % 128 != 0) return UCMR_ERR_UNSUPPORTED;
+    if (!is_min && RW < 32 && BS > 240) return UCMR_ERR_UNSUPPORTED;
+    p.block_stride = (int)block_bytes;
+    p.rows128 = (int)(block_bytes / 128);
+    if (p.rows128 > 256) return UCMR_ERR_UNSUPPORTED;
+    p.stage_bytes = bps * p.block_stride;
     p.n_stages = kRingBytes / p.stage_bytes;
     if (p.n_stages > kRingMaxStages) p.n_stages = kRingMaxStages;
-    if (p.n_stages < 4) return UCMR_ERR_UNSUPPORTED;
+    p.n_stages = p.n_stages / kRingConsumerWarps * kRingConsumerWarps;  // fixed stage -> warp ownership
+    if (p.n_stages < kRingConsumerWarps) return UCMR_ERR_UNSUPPORTED;
     const size_t smem = (size_t)p.n_stages * p.stage_bytes;
+    const int64_t total_rows = NB * (int64_t)p.rows128;
+    if (total_rows > 0xFFFFFFFFll) return UCMR_ERR_UNSUPPORTED;
+
+    CUtensorMap cmap;
+    {
+        typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                          const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                          CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                          CUtensorMapFloatOOBfill);
+        static EncodeTiledFn encode = nullptr;  // resolving twice is harmless
+        if (!encode) {
+            void* ptr = nullptr;
+            cudaDriverEntryPointQueryResult qres;
+            cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+            if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !ptr) {
+                if (e != cudaSuccess) note_cuda_error(e);
+                return UCMR_ERR_LAUNCH;
+            }
+            encode = reinterpret_cast<EncodeTiledFn>(ptr);
+        }
+        const cuuint64_t dims[2] = {32, (cuuint64_t)total_rows};
+        const cuuint64_t strides[1] = {128};
+        const cuuint32_t box[2] = {32, (cuuint32_t)p.rows128};
+        const cuuint32_t estr[2] = {1, 1};
+        CUresult r = encode(&cmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(codes), dims, strides, box,
+                            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return UCMR_ERR_LAUNCH;
+    }
 
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -440,7 +514,7 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     const int64_t max_items = (int64_t)B * ((max_blocks + bps - 1) / bps);
     const int grid = (int)(max_items < sms ? (max_items > 0 ? max_items : 1) : sms);
 
-    void (*kernel)(const RingParams) = nullptr;
+    void (*kernel)(const CUtensorMap, const RingParams) = nullptr;
     if (is_min) {
         kernel = scan_ring_kernel<true, 0, 0>;
     } else {
@@ -455,7 +529,7 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     // idempotent attribute, set on every call: cheap, and correct on every device of a process
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
     if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
-    kernel<<<grid, kRingThreads, smem, st>>>(p);
+    kernel<<<grid, kRingThreads, smem, st>>>(cmap, p);
     return check_launch();
 }
 

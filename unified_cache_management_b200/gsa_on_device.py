@@ -1,0 +1,385 @@
+"""``GSAOnDevice`` sparse-attention plugin on the sm_100a retrieval kernels (CUDA, GQA models).
+
+Drop-in for the reference plugin of the same name
+(``ucm/sparse/gsa_on_device/gsa_on_device.py:99-1421``): same ``UcmSparseBase`` hooks with the same
+side effects on ``attn_metadata.block_table`` / ``.seq_lens``, same config keys, same per-request
+prefill/decode bookkeeping.  What changed is underneath:
+
+* ``attention_begin`` caches the new tokens' key codes with ONE fused launch
+  (encode + paged scatter on tcgen05; reference: Triton ``fused_hash_and_cache_kernel``);
+* a decode step hashes the queries (group mean + encode, one launch) and retrieves with two launches
+  (Hamming scan, exact top-k with block-table lookup; reference: scan kernel + torch min/topk/sort/
+  gather), into persistent buffers, so the step is CUDA-graph friendly;
+* nothing is imported from vLLM at module scope, and nothing else of the reference package is needed.
+
+MLA models (576-bit codes, FlashMLA metadata rebuild) are not served by this class yet.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Union
+
+import torch
+
+from . import ops
+from .base import INVALID_SLOT, UcmSparseBase, UcmSparseCpuGpuBuffer, UcmSparseMetadata, UcmSparseRole
+from .gsa_on_device_config import GSAOnDeviceConfig
+from .hamming_topk import update_seq_lens
+from .hash_encoder import HashEncoder
+
+ReqType = Union[str, int]
+_CONFIG_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "configs")
+
+
+def cdiv(a: int, b: int) -> int:
+    return -(-a // b)
+
+
+def gsa_on_device_config_path_for_model(vllm_config, search_dirs: Optional[List[str]] = None) -> str:
+    """Per-model JSON lookup by substrings of the model name (reference: gsa_on_device.py:46-96).
+    ``UCM_GSA_ON_DEVICE_CONFIG`` or the ``config_path`` override wins."""
+    env = os.environ.get("UCM_GSA_ON_DEVICE_CONFIG")
+    if env:
+        return env
+    model = str(vllm_config.model_config.model).lower()
+    rules = [
+        (("deepseek", "r1"), (), "gsa_on_device_deepseek_r1_awq_config.json"),
+        (("qwen3", "32b"), ("coder",), "gsa_on_device_qwen3_32B_config.json"),
+        (("qwen3", "30b", "coder"), (), "gsa_on_device_qwen3_coder_30B_A3B_config.json"),
+        (("qwen3", "4b"), (), "gsa_on_device_qwen3_4B_config.json"),
+        (("qwq", "32b"), (), "gsa_on_device_qwq_32B_config.json"),
+        (("deepseek", "v2"), (), "gsa_on_device_deepseek_v2_lite_config.json"),
+        (("llama", "70b"), (), "gsa_on_device_llama3_70B_config.json"),
+        (("llama", "8b"), (), "gsa_on_device_llama3_8B_config.json"),
+    ]
+    for must, must_not, fname in rules:
+        if all(m in model for m in must) and not any(m in model for m in must_not):
+            for d in (search_dirs or []) + [_CONFIG_DIR]:
+                p = os.path.join(d, fname)
+                if os.path.isfile(p):
+                    return p
+    raise ValueError(f"[GSAOnDevice] Unsupported model for gsa_on_device: {model}")
+
+
+def _plugin_overrides(vllm_config) -> Dict:
+    """Inline settings under kv_connector_extra_config['ucm_sparse_config']['GSAOnDevice']."""
+    ktc = getattr(vllm_config, "kv_transfer_config", None)
+    extra = getattr(ktc, "kv_connector_extra_config", None) if ktc is not None else None
+    if isinstance(extra, dict):
+        cfg = extra.get("ucm_sparse_config") or {}
+        if isinstance(cfg, dict):
+            return dict(cfg.get("GSAOnDevice") or {})
+    return {}
+
+
+class GSAOnDevice(UcmSparseBase):
+    def __init__(self, vllm_config, role: UcmSparseRole):
+        super().__init__(vllm_config, role)
+        self.rank = vllm_config.parallel_config.rank
+        self.is_mla = bool(getattr(vllm_config.model_config, "is_deepseek_mla", False))
+        self.gsa_enabled = False
+        if vllm_config.device_config.device_type != "cuda":
+            raise ValueError(f"Unsupported device type: {vllm_config.device_config.device_type}")
+        if self.is_mla:
+            raise NotImplementedError("MLA models are not served by the B200 GSAOnDevice plugin yet")
+        self.is_cuda = True
+        self.device = torch.device(f"cuda:{self.rank}")
+
+        # per tensor-parallel rank, as the reference reads them (gsa_on_device.py:118-123)
+        self.num_q_heads = vllm_config.model_config.get_num_attention_heads(vllm_config.parallel_config)
+        self.num_key_heads = vllm_config.model_config.get_num_kv_heads(vllm_config.parallel_config)
+        self.block_size = vllm_config.cache_config.block_size
+
+        overrides = _plugin_overrides(vllm_config)
+        path = overrides.pop("config_path", None) or gsa_on_device_config_path_for_model(vllm_config)
+        self.gsa_on_device_config = GSAOnDeviceConfig.from_json(path)
+        self.gsa_on_device_config.apply_overrides(overrides, self.block_size)
+        # the reference forces 1 sink block and 4 recent blocks (gsa_on_device.py:782-783); the config's
+        # must_select_blocks list is used instead when this switch is on
+        self.use_must_select_blocks = bool(overrides.get("use_must_select_blocks", False))
+
+        cfg = self.gsa_on_device_config
+        self.hash_topk_tokens = cfg.vllm_hash_attention_topk
+        self.hash_rollback_layers = cfg.vllm_hash_attention_rollback_layers
+        self.hash_skip_layers = cfg.vllm_hash_attention_skip_layers
+        self.seq_len_threshold = cfg.gpu_seq_len_threshold
+        self.concurrency_threshold = cfg.gpu_concurrency_threshold
+        assert self.seq_len_threshold >= self.hash_topk_tokens, \
+            "seq_len_threshold must be larger than or equal to vllm_hash_attention_topk"
+        assert self.hash_topk_tokens % self.block_size == 0, "vllm_hash_attention_topk must be divisible by block_size"
+        assert self.hash_topk_tokens <= vllm_config.model_config.max_model_len, \
+            "vllm_hash_attention_topk must be less than max_model_len"
+
+        if role != UcmSparseRole.WORKER:
+            return
+
+        self.ori_seq_lens_decode = None
+        self.ori_block_table_decode = None
+        self.topk_block_table = None
+        self.topk_seq_lens = None
+        self.topk_seq_lens_qwen = None
+        self.has_pc_hit = False
+        self.has_decode = False
+        self.decode_only = False
+        self.is_prefill_flag: Dict[ReqType, bool] = {}
+        self.num_reqs = 0
+
+        self.max_batch_size = vllm_config.scheduler_config.max_num_seqs
+        self.max_num_tokens = vllm_config.model_config.max_model_len
+        self.decode_req_ids_buf = UcmSparseCpuGpuBuffer(self.max_batch_size, dtype=torch.int64, device=self.device,
+                                                        pin_memory=True, with_numpy=True)
+        max_block_per_seq = cdiv(self.max_num_tokens, self.block_size)
+        self.max_block_per_seq = max_block_per_seq
+        dev = self.device
+        self.full_block_table = torch.zeros((self.max_batch_size, max_block_per_seq), dtype=torch.int32, device=dev)
+        self.full_seq_lens = torch.zeros((self.max_batch_size,), dtype=torch.int32, device=dev)
+        self.head_dim = vllm_config.model_config.get_head_size()
+        self.hash_encoder = HashEncoder(input_dim=self.head_dim, hash_bits=cfg.hash_bits or self.head_dim,
+                                        dtype=vllm_config.model_config.dtype, device=dev)
+        # persistent retrieval buffers (no allocation inside a step)
+        self.topk_blocks = self.hash_topk_tokens // self.block_size
+        self._workspace = ops.new_workspace(self.max_batch_size, self.num_key_heads, max_block_per_seq, dev, True)
+        kb = min(self.topk_blocks, max_block_per_seq)
+        self._retrieval = ops.Retrieval(
+            physical=torch.zeros((self.max_batch_size, 1, kb), dtype=torch.int32, device=dev),
+            logical=torch.zeros((self.max_batch_size, 1, kb), dtype=torch.int32, device=dev), scores=None,
+            valid_count=torch.zeros((self.max_batch_size,), dtype=torch.int32, device=dev),
+            new_seq_lens=torch.zeros((self.max_batch_size,), dtype=torch.int32, device=dev))
+        self.init_for_pc()
+
+    # ---- prefix-cache bookkeeping buffers (gsa_on_device.py:333-360) ------------------------------
+    def init_for_pc(self):
+        self.prefix_slot_mapping_buf = torch.empty(self.max_num_tokens * self.max_batch_size, device=self.device,
+                                                   dtype=torch.int64)
+        self.prefix_block_ids_buf = torch.empty(cdiv(self.max_num_tokens * self.max_batch_size, self.block_size),
+                                                device=self.device, dtype=torch.int32)
+        self.token_idx_buf = torch.arange(self.max_num_tokens, device=self.device, dtype=torch.int64)
+
+    # ---- hashing ---------------------------------------------------------------------------------
+    def hash_code(self, nope=None, rope=None, reduction_head_num: int = 1, query: Optional[torch.Tensor] = None):
+        """GQA branch of the reference (gsa_on_device.py:396-412): one code per kv head from the mean of
+        its query group.  Returns the packed codes viewed as bf16, like the reference."""
+        if query is None:
+            raise ValueError("GQA mode requires `query`.")
+        if self.num_q_heads > self.num_key_heads:
+            codes = self.hash_encoder.compute_hash_grouped(query, self.num_q_heads // self.num_key_heads)
+        elif self.num_q_heads < self.num_key_heads:
+            query = torch.repeat_interleave(query, self.num_key_heads // self.num_q_heads, dim=1)
+            codes = self.hash_encoder.compute_hash_grouped(query, 1)
+        else:
+            codes = self.hash_encoder.compute_hash_grouped(query, 1)
+        return codes.view(torch.bfloat16)
+
+    def get_layer_attn_metadata(self, forward_context, layer_name: str):
+        attn_meta = forward_context.attn_metadata
+        return attn_meta[layer_name] if isinstance(attn_meta, dict) else attn_meta
+
+    def get_layer_state(self, layer_name: str):
+        layer_id = int(layer_name.split(".")[2])
+        is_rollback_layer = layer_id in self.hash_rollback_layers
+        is_skip_hash_layer = layer_id < len(self.hash_skip_layers) and bool(self.hash_skip_layers[layer_id])
+        return is_rollback_layer, is_skip_hash_layer
+
+    def cache_k_hash_gqa_cuda(self, key, attn_metadata, k_hash, forward_context, layer_name):
+        slot_mapping = attn_metadata.slot_mapping.flatten()
+        n = slot_mapping.numel()
+        self.hash_encoder.compute_hash_and_cache(key[:n], slot_mapping, k_hash, block_size=self.block_size)
+        if self.has_pc_hit:
+            # keys of the prefix-cache hit are already in the KV cache: gather their blocks, hash, scatter
+            attn = forward_context.no_compile_layers[layer_name]
+            kv_cache = attn.kv_cache[forward_context.virtual_engine]
+            k_pool = kv_cache[0][0]
+            gathered, _ = ops.gather_kv(k_pool, None, self.prefix_block_ids.view(1, -1).contiguous())
+            k_rows = gathered.view(-1, k_pool.shape[2], k_pool.shape[3])
+            m = self.prefix_slot_mapping.numel()
+            self.hash_encoder.compute_hash_and_cache(k_rows[:m], self.prefix_slot_mapping.flatten(), k_hash,
+                                                     block_size=self.block_size)
+
+    # ---- retrieval ---------------------------------------------------------------------------------
+    def _forced(self):
+        if self.use_must_select_blocks:
+            return dict(must_select=tuple(self.gsa_on_device_config.must_select_blocks))
+        return dict(sink_tokens=self.block_size, recent_tokens=self.block_size * 4)
+
+    def update_decode_topk_gqa_cuda(self, query, k_hash, attn_metadata):
+        n = self.num_reqs
+        q_hash = self.hash_code(query=query[:n])
+        kb = self._retrieval.physical.shape[2]
+        out = ops.Retrieval(physical=self._retrieval.physical[:n], logical=self._retrieval.logical[:n], scores=None,
+                            valid_count=self._retrieval.valid_count[:n], new_seq_lens=self._retrieval.new_seq_lens[:n])
+        ops.hamming_topk(k_hash, q_hash, attn_metadata.block_table[:n], attn_metadata.seq_lens[:n], kb,
+                         reduce=self.gsa_on_device_config.reduce, reduce_kvhead=self.num_key_heads > 1,
+                         workspace=self._workspace, out=out, want_scores=False, **self._forced())
+        block_table_decode = out.physical[:, 0, :]
+        topk = kb
+        if self.decode_only:
+            self.new_block_table[:n, :topk] = block_table_decode
+            self.new_block_table[:n, topk:] = 0
+            attn_metadata.block_table = self.new_block_table
+            self.new_seq_lens[:n] = self.topk_seq_lens_qwen
+            attn_metadata.seq_lens = self.new_seq_lens
+        else:
+            ids = self.decode_req_ids
+            self.new_block_table[ids, :topk] = block_table_decode[ids, :topk]
+            self.new_block_table[ids, topk:] = 0
+            attn_metadata.block_table = self.new_block_table
+            self.new_seq_lens.index_copy_(0, ids, self.topk_seq_lens_qwen[ids])
+            attn_metadata.seq_lens = self.new_seq_lens
+        self.topk_block_table = attn_metadata.block_table
+        self.topk_seq_lens = attn_metadata.seq_lens
+
+    # ---- hooks ---------------------------------------------------------------------------------------
+    def attention_begin(self, query, key, value, layer_name, forward_context, output=None, phase=None, k_hash=None,
+                        decode_ql_nope=None, decode_q_pe=None):
+        attn_metadata = self.get_layer_attn_metadata(forward_context, layer_name)
+        is_rollback_layer, is_skip_hash_layer = self.get_layer_state(layer_name)
+        # key codes are cached even while retrieval is off, so that it can switch on later
+        if not is_rollback_layer and not is_skip_hash_layer:
+            self.cache_k_hash_gqa_cuda(key, attn_metadata, k_hash, forward_context, layer_name)
+        if not self.gsa_enabled:
+            return query, key, value, output
+        if self.has_decode and not is_rollback_layer:
+            if is_skip_hash_layer:
+                attn_metadata.block_table = self.topk_block_table  # reuse the previous layer's selection
+                attn_metadata.seq_lens = self.topk_seq_lens
+            else:
+                self.update_decode_topk_gqa_cuda(query, k_hash, attn_metadata)
+        return query, key, value, output
+
+    def attention_finished(self, query, key, value, attn_output, layer_name, forward_context, phase=None) -> None:
+        if not self.gsa_enabled:
+            return
+        attn_metadata = self.get_layer_attn_metadata(forward_context, layer_name)
+        if self.has_decode:
+            is_rollback_layer, _ = self.get_layer_state(layer_name)
+            if not is_rollback_layer:
+                attn_metadata.block_table = self.ori_block_table_decode
+                attn_metadata.seq_lens = self.ori_seq_lens_decode
+
+    def request_begin(self, request_id: ReqType, prompt_token_ids: List[int]):
+        pass
+
+    def request_finished_in_scheduler(self, request_id: ReqType):
+        pass
+
+    def execute_begin(self, scheduler_output):
+        pass
+
+    def execute_finished(self, logits_indices: torch.Tensor):
+        self.has_decode = False
+        self.gsa_enabled = False
+        self.decode_only = False
+        self.has_pc_hit = False
+        return logits_indices
+
+    def estimate_num_slots_sparsed(self, request) -> int:
+        return INVALID_SLOT
+
+    def initialize_kv_hash_cache_tensors(self, kv_caches, device):
+        """kv_caches[layer] becomes (kv_cache, khash_cache); the code cache has the K cache's shape with
+        the last dim divided by 16 (bf16 storage, one bit per key element) - gsa_on_device.py:1020-1032."""
+        dtype = torch.bfloat16
+        for layer_name, kv_cache in kv_caches.items():
+            is_rollback_layer, is_skip_hash_layer = self.get_layer_state(layer_name)
+            if not is_rollback_layer and not is_skip_hash_layer:
+                shape = list(kv_cache[0].shape)
+                shape[-1] //= dtype.itemsize * 8
+                khash_cache = torch.zeros(shape, dtype=dtype, device=device)
+            else:
+                khash_cache = None
+            kv_caches[layer_name] = (kv_cache, khash_cache)
+
+    # ---- per-step bookkeeping (host) -------------------------------------------------------------------
+    def rebuild_prefix_cache_info_for_req(self, block_table_row, num_prompt_tokens: int, qlen: int, block_size: int):
+        assert 0 <= qlen <= num_prompt_tokens
+        num_prefix_tokens = num_prompt_tokens - qlen
+        if num_prefix_tokens <= 0:
+            empty = block_table_row[:0]
+            return 0, 0, empty, empty
+        num_prefix_blocks = cdiv(num_prefix_tokens, block_size)
+        prefix_block_ids = block_table_row[:num_prefix_blocks]
+        token_idx = self.token_idx_buf[:num_prefix_tokens]
+        block_indices = token_idx // block_size
+        block_offsets = token_idx - block_indices * block_size
+        token_block_numbers = prefix_block_ids.index_select(0, block_indices)
+        return num_prefix_tokens, num_prefix_blocks, prefix_block_ids, token_block_numbers * block_size + block_offsets
+
+    def prepare_cuda_decode_sparse_meta(self, attn_metadata, num_decodes):
+        n = self.num_reqs
+        self.full_seq_lens[:n].copy_(attn_metadata.seq_lens[:n], True)
+        cols = attn_metadata.block_table.shape[1]
+        self.full_block_table[:n, :cols].copy_(attn_metadata.block_table[:n], True)
+        self.ori_seq_lens_decode = self.full_seq_lens[:n]
+        self.ori_block_table_decode = self.full_block_table[:n, :cols]
+        if not self.decode_only:
+            self.decode_req_ids_buf.copy_to_gpu(num_decodes)
+            self.decode_req_ids = self.decode_req_ids_buf.gpu[:num_decodes]
+        self.topk_seq_lens_qwen = update_seq_lens(attn_metadata.seq_lens, topk_token=self.hash_topk_tokens,
+                                                  block_size=self.block_size)
+        self.new_block_table = attn_metadata.block_table
+        self.new_seq_lens = attn_metadata.seq_lens
+
+    def build_sparse_meta(self, scheduler_output, requests, input_batch, attn_metadata) -> Optional[UcmSparseMetadata]:
+        self.num_reqs = len(scheduler_output.num_scheduled_tokens)
+        if isinstance(attn_metadata, dict):
+            attn_metadata = next(iter(attn_metadata.values()))
+        seq_lens = getattr(attn_metadata, "seq_lens", None)
+        if seq_lens is None:
+            return None
+        # retrieval is on only when enough long requests run together (one host sync per step)
+        num_long_reqs = int((seq_lens[: self.num_reqs] >= self.seq_len_threshold).sum().item())
+        self.gsa_enabled = num_long_reqs >= self.concurrency_threshold
+
+        num_decodes = num_pc_hit = all_prefix_tokens = all_prefix_blocks = 0
+        compute_q_lens = attn_metadata.query_start_loc[1:] - attn_metadata.query_start_loc[:-1]
+        self.decode_req_ids_buf.clear()
+        ext_tokens_map = getattr(scheduler_output, "num_external_computed_tokens_per_req", None) or {}
+        for req_id, num_scheduled_tokens in scheduler_output.num_scheduled_tokens.items():
+            req = requests[req_id]
+            is_decode = req_id in self.is_prefill_flag and not self.is_prefill_flag[req_id]
+            is_first_prefill = req_id not in self.is_prefill_flag
+            is_prefill = is_first_prefill or self.is_prefill_flag[req_id]
+            is_last_chunk = is_prefill and (req.num_computed_tokens + num_scheduled_tokens >= req.num_prompt_tokens)
+            if is_decode:
+                self.decode_req_ids_buf.np[num_decodes] = input_batch.req_id_to_index[req_id]
+                num_decodes += 1
+            if is_first_prefill:
+                self.is_prefill_flag[req_id] = True
+                req_row_id = input_batch.req_id_to_index[req_id]
+                ext_tokens = int(ext_tokens_map.get(req_id, 0))
+                if ext_tokens > 0:
+                    (n_tok, n_blk, blk_ids, slots) = self.rebuild_prefix_cache_info_for_req(
+                        block_table_row=attn_metadata.block_table[req_row_id], num_prompt_tokens=req.num_prompt_tokens,
+                        qlen=int(compute_q_lens[req_row_id]), block_size=self.block_size)
+                    self.prefix_slot_mapping_buf[all_prefix_tokens: all_prefix_tokens + n_tok] = slots
+                    self.prefix_block_ids_buf[all_prefix_blocks: all_prefix_blocks + n_blk] = blk_ids
+                    all_prefix_tokens += n_tok
+                    all_prefix_blocks += n_blk
+                    num_pc_hit += 1
+            if is_last_chunk:
+                self.is_prefill_flag[req_id] = False
+        self.has_pc_hit = num_pc_hit > 0
+        if self.has_pc_hit:
+            self.prefix_slot_mapping = self.prefix_slot_mapping_buf[:all_prefix_tokens]
+            self.prefix_block_ids = self.prefix_block_ids_buf[:all_prefix_blocks]
+        if not self.gsa_enabled:
+            return None
+        self.has_decode = num_decodes > 0
+        self.decode_only = self.has_decode and (num_decodes == self.num_reqs)
+        if self.has_decode:
+            self.prepare_cuda_decode_sparse_meta(attn_metadata, num_decodes)
+        return None
+
+    def _free_cached_request(self, request_id: ReqType) -> None:
+        self.is_prefill_flag.pop(request_id, None)
+
+    def update_states(self, scheduler_output) -> None:
+        for req_id in scheduler_output.finished_req_ids:
+            self._free_cached_request(req_id)
+        req_data = scheduler_output.scheduled_cached_reqs
+        for req_id, resumed in zip(req_data.req_ids, req_data.resumed_from_preemption):
+            if resumed:
+                self._free_cached_request(req_id)
+
+    def request_finished_in_worker(self, request_id: ReqType):
+        self._free_cached_request(request_id)
