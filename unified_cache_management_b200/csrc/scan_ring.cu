@@ -1,7 +1,7 @@
 // Hamming scan, staged variant (sm_100a): one persistent CTA per SM streams paged code blocks through
 // a shared-memory ring with the bulk-copy (TMA) engine and reduces them with six consumer warps.
 //
-//   producer warp   resolves the next 32 work items in parallel (request, logical block, block-table
+//   producer warps  (two, alternate items) each resolve their next 32 work items in parallel (request, logical block, block-table
 //                   lookup), then one lane issues cp.async.bulk global->shared for each item onto the
 //                   stage's mbarrier.  Up to kRingBytes of loads are in flight per SM at any time, so
 //                   the block-table -> code-block dependency never stalls the memory pipe.
@@ -34,7 +34,8 @@
 namespace ucmr {
 
 constexpr int kRingConsumerWarps = 6;
-constexpr int kRingThreads = 32 * (1 + kRingConsumerWarps);
+constexpr int kRingProducerWarps = 2;  // item i is issued by producer warp i % 2 (divides the stage count)
+constexpr int kRingThreads = 32 * (kRingProducerWarps + kRingConsumerWarps);
 constexpr int kRingBytes = 192 * 1024;
 constexpr int kRingMaxStages = 32;
 constexpr int kRingMaxBatch = 1024;  // requests per launch (prefix table in shared memory)
@@ -75,7 +76,7 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
-struct StageMeta {
+struct __align__(16) StageMeta {
     int b, j0, seq;
     uint32_t valid_mask;  // bit k: block j0+k was loaded
 };
@@ -240,15 +241,20 @@ scan_ring_kernel(const __grid_constant__ CUtensorMap cmap, const RingParams p)
     const int first = blockIdx.x, step = gridDim.x;
     const int my_items = first < total_items ? (total_items - first + step - 1) / step : 0;
 
-    if (warp == 0) {
-        // ------------------------------------------------------------------ producer
-        for (int base = 0; base < my_items; base += 32) {
-            const int it = base + lane;
+    if (warp < kRingProducerWarps) {
+        // ------------------------------------------------------------------ producers
+        // One thread's issue chain (wait for the stage, publish its descriptor, arm the barrier, start
+        // the copy) costs several hundred cycles per item, more than the 16 KiB it moves are worth at
+        // full bandwidth; two warps issue alternate items so that the chains overlap.
+        const int my_n = (my_items - warp + kRingProducerWarps - 1) / kRingProducerWarps;  // items of this producer
+        for (int base = 0; base < my_n; base += 32) {
+            const int mine = base + lane;                       // index among this producer's items
+            const int it = mine * kRingProducerWarps + warp;    // CTA-local item index
             int b = 0, j0 = 0, seq = 0;
             int phys[kRingMaxBps];
 #pragma unroll
             for (int k = 0; k < kRingMaxBps; ++k) phys[k] = -1;
-            if (it < my_items) {
+            if (mine < my_n) {
                 const int flat = first + it * step;
                 int lo = 0, hi = p.B - 1;  // last b with s_cum[b] <= flat
                 while (lo < hi) {
@@ -268,7 +274,7 @@ scan_ring_kernel(const __grid_constant__ CUtensorMap cmap, const RingParams p)
                     }
                 }
             }
-            const int n_here = min(32, my_items - base);
+            const int n_here = min(32, my_n - base);
             bool dead = false;
             for (int i = 0; i < n_here; ++i) {
                 const int bi = __shfl_sync(0xffffffffu, b, i);
@@ -276,9 +282,9 @@ scan_ring_kernel(const __grid_constant__ CUtensorMap cmap, const RingParams p)
                 const int si = __shfl_sync(0xffffffffu, seq, i);
                 int ph[kRingMaxBps];
 #pragma unroll
-                for (int k = 0; k < kRingMaxBps; ++k) ph[k] = __shfl_sync(0xffffffffu, phys[k], i);
+                for (int k = 0; k < kRingMaxBps; ++k) ph[k] = (k < p.bps) ? __shfl_sync(0xffffffffu, phys[k], i) : -1;
                 if (lane == 0 && !dead) {
-                    const int gi = base + i;
+                    const int gi = (base + i) * kRingProducerWarps + warp;
                     const int s = gi % p.n_stages;
                     const uint32_t phase = (uint32_t)((gi / p.n_stages) & 1);
                     if (!mbar_wait(&s_empty[s], phase ^ 1u)) {
@@ -304,7 +310,7 @@ scan_ring_kernel(const __grid_constant__ CUtensorMap cmap, const RingParams p)
         }
     } else {
         // ------------------------------------------------------------------ consumers
-        const int cw = warp - 1;
+        const int cw = warp - kRingProducerWarps;
         int cur_b = -1;
         if constexpr (!MIN) {
             // lane <-> (block in stage, column); a column is one 32-bit word of one kv head
