@@ -158,6 +158,8 @@ int ucmr_update_seq_lens(const int32_t* seq_lens, int B, int topk_tokens, int BS
  *     seq_lens_global) carry -1.0 so that they survive the merge.
  *     ucmr_merge_topk: cand_* [R, B, Hout, kl] gathered in ascending shard order -> first k under
  *     (score, id), written in ascending id order to out_* [B, Hout, k]; padding = (+inf, -1).
+ *     rank_stride = distance in elements between two shards' arrays (0 = dense, B*Hout*kl), so that
+ *     scores and ids may sit side by side in one all-gathered buffer.
  * ------------------------------------------------------------------------------------------ */
 int ucmr_topk_candidates(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
                          const uint32_t* q_codes, int Hq, const int32_t* block_table,
@@ -168,8 +170,8 @@ int ucmr_topk_candidates(const uint32_t* codes, int64_t NB, int BS, int Hkv, int
                          int sink_tokens, int recent_tokens, float* cand_scores,
                          int32_t* cand_ids, void* workspace, size_t workspace_bytes, void* stream);
 
-int ucmr_merge_topk(const float* cand_scores, const int32_t* cand_ids, int R, int B, int Hout,
-                    int kl, int k, float* out_scores, int32_t* out_ids, void* stream);
+int ucmr_merge_topk(const float* cand_scores, const int32_t* cand_ids, int64_t rank_stride, int R, int B,
+                    int Hout, int kl, int k, float* out_scores, int32_t* out_ids, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * (4) Paged-KV gather.  out[b, i*BS + t, h, :] = pool[sel[b,(h),i], t, h, :] for the K pool and

@@ -40,7 +40,7 @@ def test_host_argument_validation_needs_no_gpu():
     lib = L.load_library()
     null = ctypes.c_void_p(0)
     assert lib.ucmr_update_seq_lens(null, 4, 128, 128, null, null) == L.UCMR_ERR_BAD_ARG
-    assert lib.ucmr_merge_topk(null, null, 1, 1, 1, 1, 1, null, null, null) == L.UCMR_ERR_BAD_ARG
+    assert lib.ucmr_merge_topk(null, null, 0, 1, 1, 1, 1, 1, null, null, null) == L.UCMR_ERR_BAD_ARG
     assert lib.ucmr_gather_kv(null, null, 1, 16, null, 1, 1, 0, 1, 1, 16, null, null, null, null) == L.UCMR_ERR_BAD_ARG
     assert lib.ucmr_hash_encode(null, 1, 128, null, 128, 128, null, null, null) == L.UCMR_ERR_BAD_ARG
     assert lib.ucmr_workspace_init(null, 0, null) == L.UCMR_ERR_WORKSPACE

@@ -1,13 +1,16 @@
 // Hamming scan, staged variant (sm_100a): one persistent CTA per SM streams paged code blocks through
-// a shared-memory ring with the bulk-copy (TMA) engine and reduces them with six consumer warps.
+// shared memory with the TMA engine; twelve warps each own one 16 KiB stage.
 //
-//   producer warps  (two, alternate items) each resolve their next 32 work items in parallel (request, logical block, block-table
-//                   lookup), then one lane issues cp.async.bulk global->shared for each item onto the
-//                   stage's mbarrier.  Up to kRingBytes of loads are in flight per SM at any time, so
-//                   the block-table -> code-block dependency never stalls the memory pipe.
-//   consumer warps  item i belongs to warp i % 6; the stage count is a multiple of 6, so a stage is always
-//                   drained by the same warp and no waiter can be two barrier phases ahead (a parity
-//                   wait cannot tell phase n from phase n+2).
+//   Every warp runs the same loop over its share of the work items (an item = one code block, or a
+//   few small ones): wait for its stage's mbarrier, copy the block from shared memory into registers,
+//   start the TMA load of its NEXT item into the now free stage, then do the arithmetic on the
+//   registers while that load is in flight.  There is no producer warp and no "stage empty" barrier:
+//   the warp that frees a stage is the one that refills it, so the issue latency (resolve request and
+//   block-table entry, arm the barrier, launch the copy: several hundred cycles) is spread over twelve
+//   instruction streams and overlaps their math.  Up to 12 x 16 KiB are in flight per SM.  Each
+//   barrier has a single waiter that sees every phase in order, so a parity wait is never ambiguous.
+//   The lanes of a warp resolve the warp's next 32 items in parallel (one round of global loads).
+//
 //     sum mode: the distance sum over a block only depends on how many of its tokens have each code
 //       bit set.  A lane owns one 32-bit column (kv head, word) of the block and folds all its tokens
 //       into bit-sliced vertical counters with carry-save adders (about 2.4 LOP3 per code word, no
@@ -33,11 +36,9 @@
 
 namespace ucmr {
 
-constexpr int kRingConsumerWarps = 6;
-constexpr int kRingProducerWarps = 2;  // item i is issued by producer warp i % 2 (divides the stage count)
-constexpr int kRingThreads = 32 * (kRingProducerWarps + kRingConsumerWarps);
+constexpr int kRingWarps = 12;  // each warp owns one stage of the ring
+constexpr int kRingThreads = 32 * kRingWarps;
 constexpr int kRingBytes = 192 * 1024;
-constexpr int kRingMaxStages = 32;
 constexpr int kRingMaxBatch = 1024;  // requests per launch (prefix table in shared memory)
 constexpr int kRingMaxBps = 8;       // blocks per stage
 constexpr int kRingMaxG = 16;
@@ -55,13 +56,14 @@ struct RingParams {
     int reduce_kvhead;
     int32_t* out;
     int32_t* status;
+    int32_t* sched;    // optional zero-initialised work counter (dynamic item claiming); null = static split
     int RW;            // words per token row = Hkv * W
     int bps;           // blocks per stage
     int block_bytes;   // BS * RW * 4
     int block_stride;  // = block_bytes (tensor copies land on 128-byte boundaries)
     int rows128;       // 128-byte rows per block in the flat [bytes/128, 32 words] view of the cache
     int stage_bytes;   // bps * block_stride, rounded up to 128
-    int n_stages;
+    int n_active;      // warps (= stages) in use: min(kRingWarps, ring bytes / stage bytes)
 };
 
 // Tiled TMA load of one code block: the cache is viewed as a 2-D tensor [bytes/128, 32 words] and a
@@ -186,23 +188,23 @@ __device__ __forceinline__ void load_chunk(uint32_t (&x)[kChunkTokens], const ui
     }
 }
 
-// MIN selects the per-token-minimum consumer; RW_T / G_T (sum mode only) are compile-time copies of
-// the row width and group size for the common shapes, 0 = read them from the parameters.
+// MIN selects the per-token-minimum path; RW_T / G_T (sum mode only) are compile-time copies of the row
+// width and group size for the common shapes, 0 = read them from the parameters.
 template <bool MIN, int RW_T, int G_T>
 __global__ void __launch_bounds__(kRingThreads, 1)
 scan_ring_kernel(const __grid_constant__ CUtensorMap cmap, const RingParams p)
 {
     extern __shared__ __align__(128) uint8_t s_ring[];
-    __shared__ __align__(8) uint64_t s_full[kRingMaxStages];
-    __shared__ __align__(8) uint64_t s_empty[kRingMaxStages];
-    __shared__ StageMeta s_meta[kRingMaxStages];
+    __shared__ __align__(8) uint64_t s_full[kRingWarps];
+    __shared__ StageMeta s_meta[kRingWarps];
     __shared__ int s_cum[kRingMaxBatch + 1];  // s_cum[b] = work items before request b
+    __shared__ int s_seq[kRingMaxBatch];      // seq_lens[b]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int Hout = p.reduce_kvhead ? 1 : p.Hkv;
 
     if (tid == 0) {
-        for (int s = 0; s < p.n_stages; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 1); }
+        for (int s = 0; s < kRingWarps; ++s) mbar_init(&s_full[s], 1);
         fence_mbar_init();
         asm volatile("prefetch.tensormap [%0];" ::"l"(&cmap) : "memory");
     }
@@ -212,7 +214,9 @@ scan_ring_kernel(const __grid_constant__ CUtensorMap cmap, const RingParams p)
             const int b = b0 + lane;
             int n = 0;
             if (b < p.B) {
-                const int nb = min(p.max_blocks, (p.seq_lens[b] + p.BS - 1) / p.BS);
+                const int sl = p.seq_lens[b];
+                s_seq[b] = sl;
+                const int nb = min(p.max_blocks, (sl + p.BS - 1) / p.BS);
                 n = (max(nb, 0) + p.bps - 1) / p.bps;
             }
             int incl = n;
@@ -238,203 +242,202 @@ scan_ring_kernel(const __grid_constant__ CUtensorMap cmap, const RingParams p)
             for (int h = 0; h < Hout; ++h) p.out[((int64_t)b * Hout + h) * p.max_blocks + j] = -1;
     }
 
-    const int first = blockIdx.x, step = gridDim.x;
-    const int my_items = first < total_items ? (total_items - first + step - 1) / step : 0;
+    // Work split.  Static part: CTA c takes flat items c, c + grid, ... and warp w every n_active-th of
+    // those.  With a work counter (p.sched) only the first 7/8 of the items are split that way; the rest
+    // is claimed item by item with an atomic, so that all SMs finish together whatever their luck with
+    // the memory system (a fully dynamic split would serialise ~10^4 atomics on one address).
+    if (warp >= p.n_active) return;
+    uint8_t* const stage = s_ring + (size_t)warp * p.stage_bytes;
+    uint64_t* const full = &s_full[warp];
+    const int lanes_total = gridDim.x * p.n_active;
+    const int static_items = (p.sched != nullptr) ? (total_items - total_items / 8) / lanes_total * lanes_total
+                                                  : total_items;
+    int static_k = 0;
+    // claim_start returns a token (meaningful in lane 0); claim_finish turns it into a flat item index or
+    // -1.  They are called one item apart so that the atomic's latency is hidden.
+    auto claim_start = [&]() -> int {
+        const int flat = blockIdx.x + (static_k * p.n_active + warp) * gridDim.x;
+        if (flat < static_items || p.sched == nullptr) {
+            ++static_k;
+            return flat;
+        }
+        int t = 0;
+        if (lane == 0) t = static_items + atomicAdd(p.sched, 1);
+        return t;
+    };
+    auto claim_finish = [&](int token) -> int {
+        const int flat = __shfl_sync(0xffffffffu, token, 0);
+        return flat < total_items ? flat : -1;
+    };
+    // A claimed item resolved to (request, first block, length); lane i < bps holds the block-table entry
+    // of block j0 + i (-1: past the end or out of range).  The global load of the entry is started here
+    // and first needed one item later, so its latency is off the critical path.
+    struct Item { int valid, b, j0, seq, phys; };
+    auto resolve = [&](int flat) -> Item {
+        Item r{0, 0, 0, 0, -1};
+        if (flat < 0) return r;
+        int lo = 0, hi = p.B - 1;  // last b with s_cum[b] <= flat
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (s_cum[mid] <= flat) lo = mid; else hi = mid - 1;
+        }
+        r.valid = 1; r.b = lo; r.j0 = (flat - s_cum[lo]) * p.bps; r.seq = s_seq[lo];
+        const int nb = min(p.max_blocks, (r.seq + p.BS - 1) / p.BS);
+        if (lane < p.bps && r.j0 + lane < nb) r.phys = p.bt[(int64_t)lo * p.bt_stride + r.j0 + lane];
+        return r;
+    };
+    // Starts the copy of a resolved item into the warp's stage (which must be free).  All lanes call.
+    auto issue = [&](const Item& r) {
+        if (!r.valid) return;
+        int ph = r.phys;
+        if (lane < p.bps && ph != -1 && (ph < 0 || ph >= p.NB)) {
+            flag_status(p.status, UCMR_DEV_BAD_BLOCK_ID);
+            ph = -1;
+        }
+        const uint32_t mask = __ballot_sync(0xffffffffu, ph >= 0) & ((1u << p.bps) - 1u);
+        if (lane == 0) {
+            s_meta[warp] = StageMeta{r.b, r.j0, r.seq, mask};
+            mbar_expect_tx(full, (uint32_t)(__popc(mask) * p.block_bytes));
+        }
+        __syncwarp();
+        if (lane < p.bps && ph >= 0) tma_load_2d(stage + lane * p.block_stride, &cmap, 0, ph * p.rows128, full);
+        __syncwarp();
+    };
 
-    if (warp < kRingProducerWarps) {
-        // ------------------------------------------------------------------ producers
-        // One thread's issue chain (wait for the stage, publish its descriptor, arm the barrier, start
-        // the copy) costs several hundred cycles per item, more than the 16 KiB it moves are worth at
-        // full bandwidth; two warps issue alternate items so that the chains overlap.
-        const int my_n = (my_items - warp + kRingProducerWarps - 1) / kRingProducerWarps;  // items of this producer
-        for (int base = 0; base < my_n; base += 32) {
-            const int mine = base + lane;                       // index among this producer's items
-            const int it = mine * kRingProducerWarps + warp;    // CTA-local item index
-            int b = 0, j0 = 0, seq = 0;
-            int phys[kRingMaxBps];
+    Item cur = resolve(claim_finish(claim_start()));
+    int token = claim_start();
+    issue(cur);
+    Item nxt = resolve(claim_finish(token));
+    token = claim_start();
+    // refill the (free) stage with the next item and advance the two-deep claim/resolve pipeline
+    auto advance = [&]() {
+        issue(nxt);
+        cur = nxt;
+        nxt = resolve(claim_finish(token));
+        token = claim_start();
+    };
+    int cur_b = -1;
+    uint32_t phase = 0;
+    if constexpr (!MIN) {
+        // lane <-> (block in stage, column); a column is one 32-bit word of one kv head
+        const int RW = RW_T > 0 ? RW_T : p.RW;
+        const int G = G_T > 0 ? G_T : p.G;
+        constexpr int GMAX = G_T > 0 ? G_T : kRingMaxG;
+        const int cols = min(RW, 32);
+        const int passes = RW / cols;
+        const int blk = (RW < 32) ? lane / RW : 0;
+        const int col0 = (RW < 32) ? lane % RW : lane;
+        const int rot = (RW < 32) ? blk % max(p.BS, 1) : 0;  // see load_chunk
+        uint32_t qw[GMAX];
+        while (cur.valid) {
+            if (!mbar_wait(full, phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
+            phase ^= 1u;
+            const StageMeta m = s_meta[warp];
+            const int j = m.j0 + blk;
+            const bool have = blk < p.bps && ((m.valid_mask >> blk) & 1u);
+            const int ntok = have ? min(p.BS, m.seq - j * p.BS) : 0;
+            const uint8_t* sb = stage + blk * p.block_stride;
+            int total = 0;  // per-head (or all-head) score, complete in the lanes that write
+            // tokens are walked in 128-token chunks; with several blocks per stage every lane group walks
+            // the whole block capacity (rotated), else only the valid tokens
+            const int walk = (RW < 32) ? p.BS : ntok;
+            const int n_chunks = (__reduce_max_sync(0xffffffffu, walk) + kChunkTokens - 1) / kChunkTokens;
+            bool reissued = false;
+            for (int ps = 0; ps < passes; ++ps) {
+                const int col = col0 + ps * 32;
+                const int head = col / p.W, w = col - head * p.W;
+                if (m.b != cur_b || passes > 1) {
 #pragma unroll
-            for (int k = 0; k < kRingMaxBps; ++k) phys[k] = -1;
-            if (mine < my_n) {
-                const int flat = first + it * step;
-                int lo = 0, hi = p.B - 1;  // last b with s_cum[b] <= flat
-                while (lo < hi) {
-                    const int mid = (lo + hi + 1) >> 1;
-                    if (s_cum[mid] <= flat) lo = mid; else hi = mid - 1;
+                    for (int g = 0; g < GMAX; ++g)
+                        if (g < G) qw[g] = __ldg(p.q + ((int64_t)m.b * p.Hq + head * G + g) * p.W + w);
                 }
-                b = lo;
-                j0 = (flat - s_cum[b]) * p.bps;
-                seq = p.seq_lens[b];
-                const int nb = min(p.max_blocks, (seq + p.BS - 1) / p.BS);
-#pragma unroll
-                for (int k = 0; k < kRingMaxBps; ++k) {
-                    if (k < p.bps && j0 + k < nb) {
-                        const int v = p.bt[(int64_t)b * p.bt_stride + j0 + k];
-                        if (v >= 0 && v < p.NB) phys[k] = v;
-                        else flag_status(p.status, UCMR_DEV_BAD_BLOCK_ID);
+                const uint32_t* colp = reinterpret_cast<const uint32_t*>(sb) + col;
+                int acc = 0;
+                for (int c = 0; c < n_chunks; ++c) {
+                    uint32_t x[kChunkTokens];
+                    load_chunk<RW_T>(x, colp, c * kChunkTokens, ntok, RW, rot, p.BS);
+                    if (ps == passes - 1 && c == n_chunks - 1) {
+                        // the stage's last words are in registers: refill it before doing the math
+                        __syncwarp();
+                        advance();
+                        reissued = true;
                     }
+                    const int n_here = max(0, min(kChunkTokens, ntok - ((RW < 32) ? 0 : c * kChunkTokens)));
+                    acc += chunk_score<G_T>(x, (RW < 32) ? (c == 0 ? ntok : 0) : n_here, G, qw);
+                }
+                // fold the words of a head; with reduce_kvhead also the heads of this pass
+                const int span = p.reduce_kvhead ? cols : p.W;
+                for (int off = 1; off < span && off < 32; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+                if (p.reduce_kvhead) {
+                    total += acc;
+                } else if (have && w == 0) {
+                    p.out[((int64_t)m.b * Hout + head) * p.max_blocks + j] = acc;
                 }
             }
-            const int n_here = min(32, my_n - base);
-            bool dead = false;
-            for (int i = 0; i < n_here; ++i) {
-                const int bi = __shfl_sync(0xffffffffu, b, i);
-                const int ji = __shfl_sync(0xffffffffu, j0, i);
-                const int si = __shfl_sync(0xffffffffu, seq, i);
-                int ph[kRingMaxBps];
-#pragma unroll
-                for (int k = 0; k < kRingMaxBps; ++k) ph[k] = (k < p.bps) ? __shfl_sync(0xffffffffu, phys[k], i) : -1;
-                if (lane == 0 && !dead) {
-                    const int gi = (base + i) * kRingProducerWarps + warp;
-                    const int s = gi % p.n_stages;
-                    const uint32_t phase = (uint32_t)((gi / p.n_stages) & 1);
-                    if (!mbar_wait(&s_empty[s], phase ^ 1u)) {
-                        flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT);
-                        dead = true;
-                    } else {
-                        uint32_t mask = 0;
-                        int n_valid = 0;
-#pragma unroll
-                        for (int k = 0; k < kRingMaxBps; ++k)
-                            if (ph[k] >= 0) { mask |= 1u << k; ++n_valid; }
-                        s_meta[s] = StageMeta{bi, ji, si, mask};
-                        mbar_expect_tx(&s_full[s], (uint32_t)(n_valid * p.block_bytes));
-                        uint8_t* dst = s_ring + (size_t)s * p.stage_bytes;
-#pragma unroll
-                        for (int k = 0; k < kRingMaxBps; ++k)
-                            if (ph[k] >= 0)
-                                tma_load_2d(dst + k * p.block_stride, &cmap, 0, ph[k] * p.rows128, &s_full[s]);
-                    }
-                }
+            cur_b = m.b;
+            if (p.reduce_kvhead && have && col0 == 0) p.out[(int64_t)m.b * p.max_blocks + j] = total;
+            if (!have && blk < p.bps && col0 == 0 && j < p.max_blocks) {
+                // block inside the stage but not loaded: past the request's end or a bad id
+                for (int h = 0; h < Hout; ++h) p.out[((int64_t)m.b * Hout + h) * p.max_blocks + j] = -1;
             }
-            if (__shfl_sync(0xffffffffu, (int)dead, 0)) break;
+            if (!reissued) {
+                __syncwarp();
+                advance();
+            }
         }
     } else {
-        // ------------------------------------------------------------------ consumers
-        const int cw = warp - kRingProducerWarps;
-        int cur_b = -1;
-        if constexpr (!MIN) {
-            // lane <-> (block in stage, column); a column is one 32-bit word of one kv head
-            const int RW = RW_T > 0 ? RW_T : p.RW;
-            const int G = G_T > 0 ? G_T : p.G;
-            constexpr int GMAX = G_T > 0 ? G_T : kRingMaxG;
-            const int cols = min(RW, 32);
-            const int passes = RW / cols;
-            const int blk = (RW < 32) ? lane / RW : 0;
-            const int col0 = (RW < 32) ? lane % RW : lane;
-            const int rot = (RW < 32) ? blk % max(p.BS, 1) : 0;  // see column_sum
-            uint32_t qw[GMAX];
-            for (int it = cw; it < my_items; it += kRingConsumerWarps) {
-                const int s = it % p.n_stages;
-                const uint32_t phase = (uint32_t)((it / p.n_stages) & 1);
-                if (!mbar_wait(&s_full[s], phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
-                const StageMeta m = s_meta[s];
-                const int j = m.j0 + blk;
-                const bool have = blk < p.bps && ((m.valid_mask >> blk) & 1u);
-                const int ntok = have ? min(p.BS, m.seq - j * p.BS) : 0;
-                const uint8_t* sb = s_ring + (size_t)s * p.stage_bytes + blk * p.block_stride;
-                int total = 0;  // per-head (or all-head) score, complete in the lanes that write
-                // tokens are walked in 128-token chunks; with several blocks per stage every lane group walks
-                // the whole block capacity (rotated), else only the valid tokens
-                const int walk = (RW < 32) ? p.BS : ntok;
-                const int n_chunks = (__reduce_max_sync(0xffffffffu, walk) + kChunkTokens - 1) / kChunkTokens;
-                bool released = false;
-                for (int ps = 0; ps < passes; ++ps) {
-                    const int col = col0 + ps * 32;
-                    const int head = col / p.W, w = col - head * p.W;
-                    if (m.b != cur_b || passes > 1) {
+        // lane <-> (block in stage, 16-byte piece of a token row, token slot)
+        const int PW = p.W / 4, P = p.Hkv * PW;
+        const int LG = 32 / p.bps;     // lanes per block
+        const int TS = LG / P;         // token slots per block (>= 1 by construction)
+        const int blk = lane / LG, lam = lane % LG;
+        const int hp = lam % P, slot = lam / P;
+        const int head = hp / PW, part = hp % PW;
+        uint4 qv[kRingMaxG];
+        while (cur.valid) {
+            if (!mbar_wait(full, phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
+            phase ^= 1u;
+            const StageMeta m = s_meta[warp];
+            const int j = m.j0 + blk;
+            const bool have = (m.valid_mask >> blk) & 1u;
+            const int ntok = have ? min(p.BS, m.seq - j * p.BS) : 0;
+            if (m.b != cur_b) {
+                const uint4* q4 = reinterpret_cast<const uint4*>(p.q) + ((int64_t)m.b * p.Hq + head * p.G) * PW + part;
 #pragma unroll
-                        for (int g = 0; g < GMAX; ++g)
-                            if (g < G) qw[g] = __ldg(p.q + ((int64_t)m.b * p.Hq + head * G + g) * p.W + w);
-                    }
-                    const uint32_t* colp = reinterpret_cast<const uint32_t*>(sb) + col;
-                    int acc = 0;
-                    for (int c = 0; c < n_chunks; ++c) {
-                        uint32_t x[kChunkTokens];
-                        load_chunk<RW_T>(x, colp, c * kChunkTokens, ntok, RW, rot, p.BS);
-                        if (ps == passes - 1 && c == n_chunks - 1) {
-                            // the stage's last words are in registers: hand the buffer back before the math
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(&s_empty[s]);
-                            released = true;
-                        }
-                        const int n_here = max(0, min(kChunkTokens, ntok - ((RW < 32) ? 0 : c * kChunkTokens)));
-                        acc += chunk_score<G_T>(x, (RW < 32) ? (c == 0 ? ntok : 0) : n_here, G, qw);
-                    }
-                    // fold the words of a head; with reduce_kvhead also the heads of this pass
-                    const int span = p.reduce_kvhead ? cols : p.W;
-                    for (int off = 1; off < span && off < 32; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-                    if (p.reduce_kvhead) {
-                        total += acc;
-                    } else if (have && w == 0) {
-                        p.out[((int64_t)m.b * Hout + head) * p.max_blocks + j] = acc;
-                    }
-                }
+                for (int g = 0; g < kRingMaxG; ++g)
+                    if (g < p.G) qv[g] = __ldg(q4 + g * PW);
                 cur_b = m.b;
-                if (p.reduce_kvhead && have && col0 == 0) p.out[(int64_t)m.b * p.max_blocks + j] = total;
-                if (!have && blk < p.bps && col0 == 0 && j < p.max_blocks) {
-                    // block inside the stage but not loaded: past the request's end or a bad id
-                    for (int h = 0; h < Hout; ++h) p.out[((int64_t)m.b * Hout + h) * p.max_blocks + j] = -1;
-                }
-                if (!released) {
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&s_empty[s]);
-                }
             }
-        } else {
-            // lane <-> (block in stage, 16-byte piece of a token row, token slot)
-            const int PW = p.W / 4, P = p.Hkv * PW;
-            const int LG = 32 / p.bps;     // lanes per block
-            const int TS = LG / P;         // token slots per block (>= 1 by construction)
-            const int blk = lane / LG, lam = lane % LG;
-            const int hp = lam % P, slot = lam / P;
-            const int head = hp / PW, part = hp % PW;
-            uint4 qv[kRingMaxG];
-            for (int it = cw; it < my_items; it += kRingConsumerWarps) {
-                const int s = it % p.n_stages;
-                const uint32_t phase = (uint32_t)((it / p.n_stages) & 1);
-                if (!mbar_wait(&s_full[s], phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
-                const StageMeta m = s_meta[s];
-                const int j = m.j0 + blk;
-                const bool have = (m.valid_mask >> blk) & 1u;
-                const int ntok = have ? min(p.BS, m.seq - j * p.BS) : 0;
-                if (m.b != cur_b) {
-                    const uint4* q4 = reinterpret_cast<const uint4*>(p.q) + ((int64_t)m.b * p.Hq + head * p.G) * PW + part;
+            const uint4* sb = reinterpret_cast<const uint4*>(stage + blk * p.block_stride);
+            int best = INT_MAX;
+            const int rounds = (p.BS + TS - 1) / TS;  // same trip count in every lane (shuffles inside)
+            for (int r = 0; r < rounds; ++r) {
+                const int tok = r * TS + slot;
+                const bool ok = tok < ntok;
+                int d = 0;
+                if (ok) {
+                    const uint4 kv = sb[tok * P + hp];
 #pragma unroll
                     for (int g = 0; g < kRingMaxG; ++g)
-                        if (g < p.G) qv[g] = __ldg(q4 + g * PW);
-                    cur_b = m.b;
+                        if (g < p.G)
+                            d += __popc(kv.x ^ qv[g].x) + __popc(kv.y ^ qv[g].y) + __popc(kv.z ^ qv[g].z) +
+                                 __popc(kv.w ^ qv[g].w);
                 }
-                const uint4* sb = reinterpret_cast<const uint4*>(s_ring + (size_t)s * p.stage_bytes + blk * p.block_stride);
-                int best = INT_MAX;
-                const int rounds = (p.BS + TS - 1) / TS;  // same trip count in every lane (shuffles inside)
-                for (int r = 0; r < rounds; ++r) {
-                    const int tok = r * TS + slot;
-                    const bool ok = tok < ntok;
-                    int d = 0;
-                    if (ok) {
-                        const uint4 kv = sb[tok * P + hp];
-#pragma unroll
-                        for (int g = 0; g < kRingMaxG; ++g)
-                            if (g < p.G)
-                                d += __popc(kv.x ^ qv[g].x) + __popc(kv.y ^ qv[g].y) + __popc(kv.z ^ qv[g].z) +
-                                     __popc(kv.w ^ qv[g].w);
-                    }
-                    for (int off = 1; off < PW; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
-                    best = min(best, ok ? d : INT_MAX);
+                for (int off = 1; off < PW; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+                best = min(best, ok ? d : INT_MAX);
+            }
+            __syncwarp();
+            advance();  // every lane has read its last word of the stage
+            // lanes of the same block that differ in the token slot (>= P), or with reduce_kvhead in
+            // the head bits as well, fold by min
+            for (int off = p.reduce_kvhead ? PW : P; off < LG; off <<= 1)
+                best = min(best, __shfl_xor_sync(0xffffffffu, best, off));
+            if (j < p.max_blocks) {
+                if (p.reduce_kvhead) {
+                    if (lam == 0) p.out[(int64_t)m.b * p.max_blocks + j] = have ? best : -1;
+                } else if (slot == 0 && part == 0) {
+                    p.out[((int64_t)m.b * Hout + head) * p.max_blocks + j] = have ? best : -1;
                 }
-                // lanes of the same block that differ in the token slot (>= P), or with reduce_kvhead in
-                // the head bits as well, fold by min
-                for (int off = p.reduce_kvhead ? PW : P; off < LG; off <<= 1)
-                    best = min(best, __shfl_xor_sync(0xffffffffu, best, off));
-                if (j < p.max_blocks) {
-                    if (p.reduce_kvhead) {
-                        if (lam == 0) p.out[(int64_t)m.b * p.max_blocks + j] = have ? best : -1;
-                    } else if (slot == 0 && part == 0) {
-                        p.out[((int64_t)m.b * Hout + head) * p.max_blocks + j] = have ? best : -1;
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&s_empty[s]);
             }
         }
     }
@@ -444,7 +447,7 @@ scan_ring_kernel(const __grid_constant__ CUtensorMap cmap, const RingParams p)
 // then uses the register kernel).
 int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const uint32_t* q, int Hq,
                   const int32_t* bt, int max_blocks, int64_t bt_stride, const int32_t* seq_lens, int B,
-                  int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, cudaStream_t st)
+                  int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, int32_t* sched, cudaStream_t st)
 {
     const int G = Hq / Hkv;
     const int64_t RW = (int64_t)Hkv * W;
@@ -471,7 +474,7 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     p.codes = reinterpret_cast<const char*>(codes);
     p.NB = NB; p.BS = BS; p.Hkv = Hkv; p.W = W; p.G = G; p.Hq = Hq;
     p.q = q; p.bt = bt; p.max_blocks = max_blocks; p.bt_stride = bt_stride; p.seq_lens = seq_lens; p.B = B;
-    p.reduce_kvhead = reduce_kvhead ? 1 : 0; p.out = out; p.status = status;
+    p.reduce_kvhead = reduce_kvhead ? 1 : 0; p.out = out; p.status = status; p.sched = sched;
     p.RW = (int)RW; p.bps = bps; p.block_bytes = (int)block_bytes;
     if (block_bytes % 128 != 0) return UCMR_ERR_UNSUPPORTED;
     if (!is_min && RW < 32 && BS > 240) return UCMR_ERR_UNSUPPORTED;
@@ -479,11 +482,10 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     p.rows128 = (int)(block_bytes / 128);
     if (p.rows128 > 256) return UCMR_ERR_UNSUPPORTED;
     p.stage_bytes = bps * p.block_stride;
-    p.n_stages = kRingBytes / p.stage_bytes;
-    if (p.n_stages > kRingMaxStages) p.n_stages = kRingMaxStages;
-    p.n_stages = p.n_stages / kRingConsumerWarps * kRingConsumerWarps;  // fixed stage -> warp ownership
-    if (p.n_stages < kRingConsumerWarps) return UCMR_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)p.n_stages * p.stage_bytes;
+    p.n_active = kRingBytes / p.stage_bytes;
+    if (p.n_active > kRingWarps) p.n_active = kRingWarps;
+    if (p.n_active < 4) return UCMR_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)p.n_active * p.stage_bytes;
     const int64_t total_rows = NB * (int64_t)p.rows128;
     if (total_rows > 0xFFFFFFFFll) return UCMR_ERR_UNSUPPORTED;
 

@@ -19,7 +19,7 @@ namespace ucmr {
 
 int run_scan(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const uint32_t* q, int Hq,
              const int32_t* bt, int max_blocks, int64_t bt_stride, const int32_t* seq_lens, int B,
-             int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, cudaStream_t st);
+             int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, int32_t* sched, cudaStream_t st);
 
 constexpr int kSelThreads = 512;
 constexpr int kSelWarps = kSelThreads / 32;
@@ -166,6 +166,7 @@ struct SelectParams {
     float* cand_scores;
     int32_t* cand_ids;
     float scale;
+    int32_t* sched;  // the scan's work counter, cleared here for the next launch
 };
 
 template <bool CANDIDATES>
@@ -175,6 +176,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     __shared__ SelScratch sc;
     const int tid = threadIdx.x;
     const int row = blockIdx.x;
+    if (row == 0 && tid == 0 && p.sched != nullptr) *p.sched = 0;
     const int b = row / p.Hout;
     const int n = p.max_blocks;
     const int seq_l = p.seq_local[b];
@@ -247,6 +249,7 @@ __device__ __forceinline__ uint32_t f32_order_key(float x)
 struct MergeParams {
     const float* cand_scores;  // [R, B, H, kl]
     const int32_t* cand_ids;
+    int64_t rank_stride;
     int R, B, H, kl, k, n_cached;
     float* out_scores;  // [B, H, k]
     int32_t* out_ids;
@@ -259,7 +262,6 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
     const int tid = threadIdx.x;
     const int row = blockIdx.x;  // b*H + h
     const int n = p.R * p.kl;
-    const int64_t rows = (int64_t)p.B * p.H;
     const int64_t obase = (int64_t)row * p.k;
     for (int i = tid; i < p.k; i += kSelThreads) {
         p.out_scores[obase + i] = INFINITY;
@@ -268,7 +270,7 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
     __syncthreads();
     auto at = [&](int i) -> int64_t {
         const int r = i / p.kl, c = i - r * p.kl;
-        return ((int64_t)r * rows + row) * p.kl + c;
+        return (int64_t)r * p.rank_stride + (int64_t)row * p.kl + c;
     };
     auto key_of = [&](int i) -> uint32_t {
         const int64_t a = at(i);
@@ -366,9 +368,15 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
     if (rc != UCMR_OK) return rc;
     int32_t* status = static_cast<int32_t*>(workspace);
     int32_t* scores = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + UCMR_WORKSPACE_HEADER_BYTES);
+    int32_t* sched = status + 2;  // work counter of the scan; zero between launches
     rc = run_scan(codes, NB, BS, Hkv, W, q_codes, Hq, bt, max_blocks, bt_stride, seq_local, B, reduce_mode,
-                  reduce_kvhead, scores, status, st);
-    if (rc != UCMR_OK || B == 0 || k == 0) return rc;
+                  reduce_kvhead, scores, status, sched, st);
+    if (rc != UCMR_OK || B == 0) return rc;
+    if (k == 0) {  // no selection kernel will run: clear the counter here
+        cudaError_t e = cudaMemsetAsync(sched, 0, sizeof(int32_t), st);
+        if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
+        return UCMR_OK;
+    }
 
     p.scores = scores;
     p.Hout = reduce_kvhead ? 1 : Hkv; p.max_blocks = max_blocks; p.BS = BS;
@@ -379,7 +387,7 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
     p.n_cached = max_blocks < kSelMaxCachedKeys ? max_blocks : kSelMaxCachedKeys;
     p.out_phys = out_phys; p.out_logical = out_logical; p.out_scores = out_scores;
     p.out_valid = out_valid; p.out_newseq = out_newseq;
-    p.cand_scores = cand_scores; p.cand_ids = cand_ids; p.scale = scale;
+    p.cand_scores = cand_scores; p.cand_ids = cand_ids; p.scale = scale; p.sched = sched;
     const size_t smem = (size_t)p.n_cached * sizeof(uint32_t);
     const int rows = B * p.Hout;
     if (candidates) {
@@ -427,14 +435,16 @@ extern "C" int ucmr_topk_candidates(const uint32_t* codes, int64_t NB, int BS, i
                       static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int ucmr_merge_topk(const float* cand_scores, const int32_t* cand_ids, int R, int B, int Hout,
-                               int kl, int k, float* out_scores, int32_t* out_ids, void* stream)
+extern "C" int ucmr_merge_topk(const float* cand_scores, const int32_t* cand_ids, int64_t rank_stride, int R,
+                               int B, int Hout, int kl, int k, float* out_scores, int32_t* out_ids, void* stream)
 {
+    if (rank_stride == 0) rank_stride = (int64_t)B * Hout * kl;
+    if (rank_stride < (int64_t)B * Hout * kl) return UCMR_ERR_BAD_ARG;
     if (!cand_scores || !cand_ids || !out_scores || !out_ids) return UCMR_ERR_BAD_ARG;
     if (R <= 0 || B < 0 || Hout <= 0 || kl <= 0 || k < 0) return UCMR_ERR_BAD_ARG;
     if ((int64_t)R * kl > INT_MAX) return UCMR_ERR_UNSUPPORTED;
     if (B == 0 || k == 0) return UCMR_OK;
-    MergeParams p{cand_scores, cand_ids, R, B, Hout, kl, k, 0, out_scores, out_ids};
+    MergeParams p{cand_scores, cand_ids, rank_stride, R, B, Hout, kl, k, 0, out_scores, out_ids};
     const int n = R * kl;
     p.n_cached = n < kSelMaxCachedKeys ? n : kSelMaxCachedKeys;
     const size_t smem = (size_t)p.n_cached * sizeof(uint32_t);

@@ -323,18 +323,25 @@ def topk_candidates(codes, q_codes, block_table, seq_lens_local, seq_lens_global
 
 
 def merge_topk(cand_scores: torch.Tensor, cand_ids: torch.Tensor, k: int, out_scores=None, out_ids=None):
-    """cand_* [R, B, Hout, kl] (ascending shard order) -> global top-k [B, Hout, k], ascending id."""
-    _need_cuda("cand_scores", cand_scores, torch.float32)
-    _need_cuda("cand_ids", cand_ids, torch.int32)
-    if cand_scores.dim() != 4 or cand_scores.shape != cand_ids.shape:
+    """cand_* [R, B, Hout, kl] (ascending shard order) -> global top-k [B, Hout, k], ascending id.
+    The two tensors may be strided views of one gathered buffer as long as each shard's [B,Hout,kl]
+    slab is dense and both use the same shard stride."""
+    for name, t, dt in (("cand_scores", cand_scores, torch.float32), ("cand_ids", cand_ids, torch.int32)):
+        _need_cuda(name, t, dt, contiguous=False)
+        if t.dim() != 4 or not t[0].is_contiguous():
+            raise ValueError(f"{name} must be [R, B, Hout, kl] with dense per-shard slabs")
+    if cand_scores.shape != cand_ids.shape:
         raise ValueError("candidates must be [R, B, Hout, kl]")
     r, b, h, kl = cand_scores.shape
+    stride = cand_scores.stride(0) if r > 1 else b * h * kl
+    if r > 1 and cand_ids.stride(0) != stride:
+        raise ValueError("scores and ids must use the same shard stride")
     dev = cand_scores.device
     if out_scores is None:
         out_scores = torch.empty((b, h, k), dtype=torch.float32, device=dev)
     if out_ids is None:
         out_ids = torch.empty((b, h, k), dtype=torch.int32, device=dev)
-    _l.check(_l.load_library().ucmr_merge_topk(_ptr(cand_scores), _ptr(cand_ids), r, b, h, kl, int(k),
+    _l.check(_l.load_library().ucmr_merge_topk(_ptr(cand_scores), _ptr(cand_ids), stride, r, b, h, kl, int(k),
                                                _ptr(out_scores), _ptr(out_ids), _stream(cand_scores)),
              "ucmr_merge_topk")
     return out_scores, out_ids

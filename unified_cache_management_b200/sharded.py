@@ -1,0 +1,73 @@
+"""Sequence-sharded retrieval for very long contexts: every rank scans its contiguous range of
+logical blocks, emits its best k blocks as (score, global id) records, one all-gather brings the
+records of all ranks into each GPU's own memory, and a merge kernel picks the global top-k.
+
+The reference plugin has no context-parallel retrieval; the per-shard computation is the same scan
+and selection as the unsharded path, and the result is identical to it (any member of the global
+top-k is in its shard's local top-k; forced blocks carry score -1 so they survive the merge).
+
+The collective is `torch.distributed.all_gather_into_tensor` (NCCL on GPUs): one message of
+`B*Hout*k*8` bytes per rank, latency-bound.  The compute functions are parameters so that the plumbing
+can be exercised with CPU ranks.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class ShardPlan:
+    block_offset: int            # first logical block this rank holds
+    blocks_per_rank: int
+    seq_lens_local: torch.Tensor  # int32 [B]: tokens of each request inside this rank's range
+
+
+def shard_plan(seq_lens_global: torch.Tensor, block_size: int, max_blocks_global: int, world: int, rank: int) -> ShardPlan:
+    """Contiguous split of the logical block range [0, max_blocks_global) into `world` equal parts."""
+    if max_blocks_global % world != 0:
+        raise ValueError("max_blocks_global must be a multiple of the world size")
+    per = max_blocks_global // world
+    off = rank * per
+    local = (seq_lens_global.to(torch.int64) - off * block_size).clamp(min=0, max=per * block_size).to(torch.int32)
+    return ShardPlan(block_offset=off, blocks_per_rank=per, seq_lens_local=local)
+
+
+def _default_candidates(*args, **kw):
+    from . import ops
+    return ops.topk_candidates(*args, **kw)
+
+
+def _default_merge(*args, **kw):
+    from . import ops
+    return ops.merge_topk(*args, **kw)
+
+
+def sharded_hamming_topk(codes_local, q_codes, block_table_local, seq_lens_global, k: int, block_size: int,
+                         max_blocks_global: int, score_scale: float, *, group=None, reduce="sum",
+                         reduce_kvhead: bool = False, must_select: Sequence[int] = (), sink_tokens: int = 0,
+                         recent_tokens: int = 0, workspace=None, gather_buffer: Optional[torch.Tensor] = None,
+                         candidates_fn: Callable = _default_candidates, merge_fn: Callable = _default_merge):
+    """Returns (scores float32 [B,Hout,k], global logical block ids int32 [B,Hout,k]), identical on
+    every rank.  block_table_local is this rank's slice [B, max_blocks_global/world] of the table."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    plan = shard_plan(seq_lens_global, block_size, max_blocks_global, world, rank)
+    kl = min(k, plan.blocks_per_rank)
+    sc, ids = candidates_fn(codes_local, q_codes, block_table_local, plan.seq_lens_local, seq_lens_global, kl,
+                            plan.block_offset, score_scale, reduce=reduce, reduce_kvhead=reduce_kvhead,
+                            must_select=must_select, sink_tokens=sink_tokens, recent_tokens=recent_tokens,
+                            workspace=workspace)
+    b, h, _ = sc.shape
+    # one message per rank: [2, B, H, kl] int32 (float bits, then ids)
+    send = torch.stack((sc.view(torch.int32), ids))
+    if gather_buffer is None:
+        gather_buffer = torch.empty((world * 2,) + tuple(send.shape[1:]), dtype=torch.int32, device=send.device)
+    dist.all_gather_into_tensor(gather_buffer, send, group=group)   # concatenation along dim 0
+    gathered = gather_buffer.view((world, 2) + tuple(send.shape[1:]))
+    cand_scores = gathered[:, 0].view(torch.float32)
+    cand_ids = gathered[:, 1]
+    return merge_fn(cand_scores, cand_ids, k)
