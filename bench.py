@@ -3,8 +3,8 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 One "step" is one decode-step retrieval of ONE decoder layer for a whole batch:
-    encode the new K token of every request into the paged code cache   (ucmr_hash_encode_and_cache)
-    encode the query heads                                               (ucmr_hash_encode_query)
+    encode the query heads and the new K token of every request (into the paged code cache), one launch
+                                                                         (ucmr_hash_encode_decode_step)
     Hamming scan of every cached token + exact top-k per (request, kv head)   (ucmr_hamming_topk)
 on synthetic data of the shapes the workload names.  "Tokens scored" = cached KV positions scanned.
 
@@ -162,8 +162,7 @@ def make_step(cfg, wl, dev):
     def step(layer, q=None, k_new=None):
         qq = wl["q"][layer] if q is None else q
         kk = wl["k_new"][layer] if k_new is None else k_new
-        ops.hash_encode_and_cache(kk, wl["last_slot"], wl["caches"][layer], wl["R"])
-        ops.hash_encode_query(qq, wl["R"], out=q_codes)
+        ops.hash_encode_decode_step(qq, kk, wl["last_slot"], wl["caches"][layer], wl["R"], q_codes_out=q_codes)
         ops.hamming_topk(wl["caches"][layer], q_codes, wl["bt"], wl["seq_lens"], k, reduce="sum",
                          must_select=MUST_SELECT, workspace=ws, out=out, want_scores=False)
         return out
@@ -410,7 +409,7 @@ def main():
                                "frac_hbm": prefill["gbs"] / peaks["hbm_gbs"]},
             "e2e": {"value": world * tokens_per_step * K / (e2e_ms * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / K},
-            "gpu_launches": 4 * K, "device_status_word": status, "clocks": clocks,
+            "gpu_launches": 3 * K, "device_status_word": status, "clocks": clocks,
         }
         if not args.no_cpu_baseline:
             base, _, _ = time_cpu(cfg, host_copies(cfg, wl))

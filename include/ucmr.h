@@ -83,6 +83,16 @@ int ucmr_hash_encode_and_cache(const void* x, int64_t T, int H, int64_t stride_t
                                int slot_is_int64, uint32_t* cache, int64_t NB, int BS,
                                int32_t* status_word, void* stream);
 
+/*     The two encodes of one decode step in a single launch: the step's queries (as
+ *     ucmr_hash_encode_query, hash_code at gsa_on_device.py:396-412) and its new key rows (as
+ *     ucmr_hash_encode_and_cache, cache_k_hash_gqa_cuda at gsa_on_device.py:564-573).              */
+int ucmr_hash_encode_decode_step(const void* q, int64_t Tq, int Hq, int64_t q_stride_t,
+                                 int64_t q_stride_h, int group_mean, uint32_t* q_codes_out,
+                                 const void* k, int64_t Tk, int Hk, int64_t k_stride_t,
+                                 int64_t k_stride_h, const void* slot_mapping, int slot_is_int64,
+                                 uint32_t* cache, int64_t NB, int BS, const void* R, int in_dim,
+                                 int hash_bits, int32_t* status_word, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Workspace.  Holds the device status word and the block scores between the scan and the
  * selection kernel.  Clear it once with ucmr_workspace_init after allocating it; the status word

@@ -151,3 +151,31 @@ def test_tensor_core_and_cuda_core_paths_agree(cuda_device):
     _, p64 = O.hash_encode(x.reshape(-1, 128), r)
     diff = O.unpack_bits_u32(H.dev_to_u32(a)) != O.unpack_bits_u32(H.dev_to_u32(b).reshape(-1, 4))
     assert (np.abs(p64[diff]) < TOL).all()
+
+
+@pytest.mark.parametrize("G", [1, 4])
+def test_decode_step_fused_encode(cuda_device, G):
+    """Queries and new key rows of one decode step in one launch (group mean on the query side)."""
+    import torch
+    from unified_cache_management_b200 import ops
+    rng = np.random.default_rng(50 + G)
+    B, Hkv, NB, BS = 16, 8, 64, 128
+    q = H.bf16_normal(rng, (B, Hkv * 4, 128))
+    kn = H.bf16_normal(rng, (B, Hkv, 128))
+    r = _r_matrix(1)
+    slots = rng.permutation(NB * BS)[:B].astype(np.int64)
+    cache0 = H.rand_codes(rng, (NB, BS, Hkv, 4))
+    cache = H.to_dev_i32(cache0, cuda_device)
+    qc = ops.hash_encode_decode_step(H.bf16_to_dev(q, cuda_device), H.bf16_to_dev(kn, cuda_device),
+                                     torch.from_numpy(slots).to(cuda_device), cache, H.bf16_to_dev(r, cuda_device),
+                                     group_mean=G)
+    torch.cuda.synchronize()
+    qm = O.group_mean_bf16(q, Hkv * 4 // G) if G > 1 else q
+    _check(H.dev_to_u32(qc), qm, r)
+    got = H.dev_to_u32(cache).reshape(NB * BS, Hkv, 4)
+    _, p64 = O.hash_encode(kn, r)
+    hard, soft = O.count_code_mismatches(got[slots], p64, TOL)
+    assert hard == 0 and soft <= 2
+    untouched = np.ones(NB * BS, dtype=bool)
+    untouched[slots] = False
+    assert np.array_equal(got[untouched], cache0.reshape(NB * BS, Hkv, 4)[untouched])

@@ -119,6 +119,34 @@ __device__ __forceinline__ uint32_t pack_signs(const uint32_t (&r)[32])
     return w;
 }
 
+
+// R[k][n] (row-major bf16) -> B[n][k], K-major with the 128-byte swizzle the MMA descriptors expect:
+// row n holds 64 k-values (128 bytes) per K half, and its 16-byte chunk c lives at chunk c ^ (n & 7).
+// Each thread transposes 8x8 blocks in registers: eight 16-byte loads in, eight 16-byte stores out.
+__device__ __forceinline__ void build_rt_swizzled(uint8_t* s_b, const __nv_bfloat16* R, int tid, int nthreads)
+{
+    for (int blk = tid; blk < (kEncD / 8) * (kEncBits / 8); blk += nthreads) {
+        const int kc = blk / (kEncBits / 8), nc = blk % (kEncBits / 8);
+        uint4 v[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            v[r] = __ldg(reinterpret_cast<const uint4*>(R + (size_t)(kc * 8 + r) * kEncBits + nc * 8));
+        const int half = kc >> 3, chunk = kc & 7;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+            uint4 o;
+            o.x = __byte_perm(reinterpret_cast<const uint32_t*>(&v[0])[j >> 1], reinterpret_cast<const uint32_t*>(&v[1])[j >> 1], sel);
+            o.y = __byte_perm(reinterpret_cast<const uint32_t*>(&v[2])[j >> 1], reinterpret_cast<const uint32_t*>(&v[3])[j >> 1], sel);
+            o.z = __byte_perm(reinterpret_cast<const uint32_t*>(&v[4])[j >> 1], reinterpret_cast<const uint32_t*>(&v[5])[j >> 1], sel);
+            o.w = __byte_perm(reinterpret_cast<const uint32_t*>(&v[6])[j >> 1], reinterpret_cast<const uint32_t*>(&v[7])[j >> 1], sel);
+            const int n = nc * 8 + j;
+            const uint32_t off = (uint32_t)half * kEncHalfBytes + (uint32_t)n * 128u + ((uint32_t)(chunk ^ (n & 7)) << 4);
+            *reinterpret_cast<uint4*>(s_b + off) = o;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kEncThreads, 1)
 encode_tc_kernel(const __grid_constant__ CUtensorMap x_map, const EncParams p)
 {
@@ -148,21 +176,7 @@ encode_tc_kernel(const __grid_constant__ CUtensorMap x_map, const EncParams p)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // R[k][n] (row-major) -> B[n][k] K-major with the 128-byte swizzle: 16-byte chunk c of row n
-    // lives at chunk c ^ (n & 7) of that row.
-    for (int i = tid; i < kEncD * (kEncBits / 8); i += kEncThreads) {
-        const int k = i / (kEncBits / 8), n0 = (i % (kEncBits / 8)) * 8;
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.R + (size_t)k * kEncBits + n0));
-        const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
-        const int half = k >> 6, kk = k & 63, chunk = kk >> 3;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int n = n0 + j;
-            const uint32_t off = (uint32_t)half * kEncHalfBytes + (uint32_t)n * 128u +
-                                 ((uint32_t)(chunk ^ (n & 7)) << 4) + (uint32_t)(kk & 7) * 2u;
-            *reinterpret_cast<uint16_t*>(s_b + off) = e[j];
-        }
-    }
+    build_rt_swizzled(s_b, p.R, tid, kEncThreads);
     fence_proxy_async();  // generic-proxy writes of R^T become visible to the MMA's async-proxy reads
     tc_fence_before();
     __syncthreads();
@@ -253,6 +267,142 @@ encode_tc_kernel(const __grid_constant__ CUtensorMap x_map, const EncParams p)
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kEncTmemCols)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// tensor-core path for small row counts: one 128-row tile per CTA, up to two jobs per launch
+// ---------------------------------------------------------------------------------------------
+// A decode step encodes a few hundred rows (the batch's query heads and its new key rows).  The persistent
+// kernel above would spend its time on set-up, and two launches cost more than the math.  Here every CTA
+// builds its A tile with plain 16-byte loads (optionally averaging G consecutive heads with one rounding
+// to bf16, which is how the plugin hashes a GQA query group), writes it swizzled next to R^T, issues the
+// eight MMAs and packs the signs.  Both jobs of a step (queries -> code array, new keys -> paged cache)
+// share one launch.
+constexpr int kTileThreads = 128;
+constexpr size_t kTileSmemBytes = 1024 + 2 * kEncHalfBytes + kEncStageBytes + 64;
+
+struct TileJob {
+    const __nv_bfloat16* x;
+    int64_t T;
+    int H_in, G;
+    int64_t stride_t, stride_h;
+    uint32_t* out;
+    const void* slot_mapping;  // null = write row r of the job to out[r]
+    int slot_is_int64;
+    int64_t n_slots;
+    int64_t tiles;  // 128-row tiles of this job
+};
+
+struct TileParams {
+    TileJob job[2];
+    const __nv_bfloat16* R;
+    int32_t* status;
+};
+
+__global__ void __launch_bounds__(kTileThreads) encode_tile_kernel(const TileParams p)
+{
+    extern __shared__ uint8_t s_raw[];
+    uint8_t* s_base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(s_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* s_b = s_base;
+    uint8_t* s_a = s_base + 2 * kEncHalfBytes;
+    uint64_t* done = reinterpret_cast<uint64_t*>(s_a + kEncStageBytes);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    const bool second = (int64_t)blockIdx.x >= p.job[0].tiles;
+    const TileJob& jb = p.job[second ? 1 : 0];
+    const int64_t tile = (int64_t)blockIdx.x - (second ? p.job[0].tiles : 0);
+    const int H_out = jb.H_in / jb.G;
+    const int64_t rows = jb.T * H_out;
+    const int64_t row0 = tile * kEncTileM;
+
+    if (tid == 0) { mbar_init(done, 1); fence_mbar_init(); }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)kEncBits)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // A tile: row r of the tile, 16-byte chunk c (8 elements) -> K half c >> 3, chunk (c & 7) ^ (r & 7)
+    for (int i = tid; i < kEncTileM * (kEncD / 8); i += kTileThreads) {
+        const int r = i >> 4, c = i & 15;
+        const int64_t row = row0 + r;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < rows) {
+            const int64_t t = row / H_out;
+            const int ho = (int)(row - t * H_out);
+            const __nv_bfloat16* src = jb.x + t * jb.stride_t + (int64_t)ho * jb.G * jb.stride_h + c * 8;
+            if (jb.G == 1) {
+                v = __ldg(reinterpret_cast<const uint4*>(src));
+            } else {
+                float acc[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+                for (int g = 0; g < jb.G; ++g) {
+                    const uint4 u = __ldg(reinterpret_cast<const uint4*>(src + (int64_t)g * jb.stride_h));
+                    const __nv_bfloat16* ue = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[e] += __bfloat162float(ue[e]);
+                }
+                __nv_bfloat16* ve = reinterpret_cast<__nv_bfloat16*>(&v);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ve[e] = __float2bfloat16_rn(acc[e] / (float)jb.G);
+            }
+        }
+        const uint32_t off = (uint32_t)(c >> 3) * kEncHalfBytes + (uint32_t)r * 128u + ((uint32_t)((c & 7) ^ (r & 7)) << 4);
+        *reinterpret_cast<uint4*>(s_a + off) = v;
+    }
+    build_rt_swizzled(s_b, p.R, tid, kTileThreads);
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (tid == 0) {
+        const uint32_t a_addr = smem_u32(s_a), b_addr = smem_u32(s_b);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                const uint32_t off = (uint32_t)half * kEncHalfBytes + (uint32_t)ks * 32u;
+                tc_mma_bf16(tmem_base, make_smem_desc_sw128(a_addr + off), make_smem_desc_sw128(b_addr + off), kEncIdesc,
+                            (half | ks) ? 1u : 0u);
+            }
+        }
+        tc_commit(done);
+    }
+    bool ok = mbar_wait(done, 0);
+    if (!ok) flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT);
+    tc_fence_after();
+    if (ok) {
+        const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
+        uint4 code;
+        uint32_t r[32];
+        tc_ld32(taddr + 0, r);  tc_wait_ld(); code.x = pack_signs(r);
+        tc_ld32(taddr + 32, r); tc_wait_ld(); code.y = pack_signs(r);
+        tc_ld32(taddr + 64, r); tc_wait_ld(); code.z = pack_signs(r);
+        tc_ld32(taddr + 96, r); tc_wait_ld(); code.w = pack_signs(r);
+        const int64_t row = row0 + warp * 32 + lane;
+        if (row < rows) {
+            if (jb.slot_mapping == nullptr) {
+                *reinterpret_cast<uint4*>(jb.out + row * 4) = code;
+            } else {
+                const int64_t tok = row / H_out;
+                const int h = (int)(row - tok * H_out);
+                const int64_t slot = jb.slot_is_int64 ? static_cast<const int64_t*>(jb.slot_mapping)[tok]
+                                                      : (int64_t) static_cast<const int32_t*>(jb.slot_mapping)[tok];
+                if (slot >= 0 && slot < jb.n_slots) *reinterpret_cast<uint4*>(jb.out + (slot * H_out + h) * 4) = code;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kEncBits)
                      : "memory");
     }
 }
@@ -418,6 +568,49 @@ static int launch_tc(const void* x, int64_t T, int H, int64_t stride_t, int64_t 
     return check_launch();
 }
 
+// Shapes the one-tile-per-CTA tensor-core kernel accepts (any head count; 16-byte aligned rows).
+static bool tile_path_ok(const void* x, int64_t T, int H_in, int G, int64_t stride_t, int64_t stride_h, int in_dim,
+                         int bits, const void* out, const void* R)
+{
+    if (in_dim != kEncD || bits != kEncBits) return false;
+    if (H_in <= 0 || G <= 0 || H_in % G != 0 || T <= 0) return false;
+    if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || reinterpret_cast<uintptr_t>(out) % 16 != 0 ||
+        reinterpret_cast<uintptr_t>(R) % 16 != 0)
+        return false;
+    if (stride_t % 8 != 0 || (H_in > 1 && stride_h % 8 != 0)) return false;
+    return true;
+}
+
+static TileJob make_job(const void* x, int64_t T, int H_in, int G, int64_t stride_t, int64_t stride_h, uint32_t* out,
+                        const void* slot_mapping, int slot_is_int64, int64_t n_slots)
+{
+    TileJob j{};
+    j.x = static_cast<const __nv_bfloat16*>(x); j.T = T; j.H_in = H_in; j.G = G;
+    j.stride_t = stride_t; j.stride_h = stride_h; j.out = out;
+    j.slot_mapping = slot_mapping; j.slot_is_int64 = slot_is_int64; j.n_slots = n_slots;
+    j.tiles = (T * (H_in / G) + kEncTileM - 1) / kEncTileM;
+    return j;
+}
+
+static int launch_tiles(const TileJob& j0, const TileJob* j1, const void* R, int32_t* status, cudaStream_t st)
+{
+    TileParams p{};
+    p.job[0] = j0;
+    if (j1) p.job[1] = *j1; else p.job[1].tiles = 0, p.job[1].H_in = 1, p.job[1].G = 1;
+    p.R = static_cast<const __nv_bfloat16*>(R); p.status = status;
+    const int64_t grid = p.job[0].tiles + p.job[1].tiles;
+    if (grid <= 0) return UCMR_OK;
+    if (grid > 0x7FFFFFFF) return UCMR_ERR_UNSUPPORTED;
+    cudaError_t e = cudaFuncSetAttribute(encode_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTileSmemBytes);
+    if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
+    encode_tile_kernel<<<(int)grid, kTileThreads, kTileSmemBytes, st>>>(p);
+    return check_launch();
+}
+
+// Row counts up to this many tiles go to the one-tile-per-CTA kernel (two waves of CTAs at most); above it the
+// persistent TMA-pipelined kernel amortises its set-up.
+constexpr int64_t kSmallTiles = 296;
+
 static int launch_simt(const void* x, int64_t T, int H_in, int G, int64_t stride_t, int64_t stride_h, const void* R,
                        int in_dim, int bits, uint32_t* out, const void* slot_mapping, int slot_is_int64,
                        int64_t n_slots, cudaStream_t st)
@@ -469,9 +662,14 @@ extern "C" int ucmr_hash_encode(const void* x, int64_t rows, int64_t row_stride,
     if (rc != UCMR_OK) return rc;
     if (rows == 0) return UCMR_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool tile_ok = !force_simt() && tile_path_ok(x, rows, 1, 1, row_stride, in_dim, in_dim, hash_bits, codes_out, R);
+    if (tile_ok && (rows + kEncTileM - 1) / kEncTileM <= kSmallTiles)
+        return launch_tiles(make_job(x, rows, 1, 1, row_stride, in_dim, codes_out, nullptr, 0, 0), nullptr, R, status_word, st);
     if (!force_simt() && tc_path_ok(x, rows, 1, row_stride, in_dim, in_dim, hash_bits) &&
         reinterpret_cast<uintptr_t>(codes_out) % 16 == 0 && reinterpret_cast<uintptr_t>(R) % 16 == 0)
         return launch_tc(x, rows, 1, row_stride, in_dim, R, codes_out, nullptr, 0, 0, status_word, st);
+    if (tile_ok)
+        return launch_tiles(make_job(x, rows, 1, 1, row_stride, in_dim, codes_out, nullptr, 0, 0), nullptr, R, status_word, st);
     return launch_simt(x, rows, 1, 1, row_stride, in_dim, R, in_dim, hash_bits, codes_out, nullptr, 0, 0, st);
 }
 
@@ -485,9 +683,15 @@ extern "C" int ucmr_hash_encode_query(const void* q, int64_t T, int Hq, int64_t 
     if (rc != UCMR_OK) return rc;
     if (T == 0) return UCMR_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool tile_ok = !force_simt() && tile_path_ok(q, T, Hq, group_mean, stride_t, stride_h, in_dim, hash_bits, codes_out, R);
+    const int64_t tiles = (T * (Hq / group_mean) + kEncTileM - 1) / kEncTileM;
+    if (tile_ok && (group_mean > 1 || tiles <= kSmallTiles))
+        return launch_tiles(make_job(q, T, Hq, group_mean, stride_t, stride_h, codes_out, nullptr, 0, 0), nullptr, R, status_word, st);
     if (group_mean == 1 && !force_simt() && tc_path_ok(q, T, Hq, stride_t, stride_h, in_dim, hash_bits) &&
         reinterpret_cast<uintptr_t>(codes_out) % 16 == 0 && reinterpret_cast<uintptr_t>(R) % 16 == 0)
         return launch_tc(q, T, Hq, stride_t, stride_h, R, codes_out, nullptr, 0, 0, status_word, st);
+    if (tile_ok)
+        return launch_tiles(make_job(q, T, Hq, group_mean, stride_t, stride_h, codes_out, nullptr, 0, 0), nullptr, R, status_word, st);
     return launch_simt(q, T, Hq, group_mean, stride_t, stride_h, R, in_dim, hash_bits, codes_out, nullptr, 0, 0, st);
 }
 
@@ -503,9 +707,42 @@ extern "C" int ucmr_hash_encode_and_cache(const void* x, int64_t T, int H, int64
     if (T == 0) return UCMR_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int64_t n_slots = NB * BS;
+    const bool tile_ok = !force_simt() && tile_path_ok(x, T, H, 1, stride_t, stride_h, in_dim, hash_bits, cache, R);
+    const bool tc_ok = !force_simt() && tc_path_ok(x, T, H, stride_t, stride_h, in_dim, hash_bits) &&
+                       reinterpret_cast<uintptr_t>(cache) % 16 == 0 && reinterpret_cast<uintptr_t>(R) % 16 == 0;
+    if (tile_ok && ((T * H + kEncTileM - 1) / kEncTileM <= kSmallTiles || !tc_ok))
+        return launch_tiles(make_job(x, T, H, 1, stride_t, stride_h, cache, slot_mapping, slot_is_int64 ? 1 : 0, n_slots),
+                            nullptr, R, status_word, st);
     if (!force_simt() && tc_path_ok(x, T, H, stride_t, stride_h, in_dim, hash_bits) &&
         reinterpret_cast<uintptr_t>(cache) % 16 == 0 && reinterpret_cast<uintptr_t>(R) % 16 == 0)
         return launch_tc(x, T, H, stride_t, stride_h, R, cache, slot_mapping, slot_is_int64 ? 1 : 0, n_slots, status_word, st);
     return launch_simt(x, T, H, 1, stride_t, stride_h, R, in_dim, hash_bits, cache, slot_mapping,
                        slot_is_int64 ? 1 : 0, n_slots, st);
+}
+
+extern "C" int ucmr_hash_encode_decode_step(const void* q, int64_t Tq, int Hq, int64_t q_stride_t, int64_t q_stride_h,
+                                            int group_mean, uint32_t* q_codes_out, const void* k, int64_t Tk, int Hk,
+                                            int64_t k_stride_t, int64_t k_stride_h, const void* slot_mapping,
+                                            int slot_is_int64, uint32_t* cache, int64_t NB, int BS, const void* R,
+                                            int in_dim, int hash_bits, int32_t* status_word, void* stream)
+{
+    if (!q || !k || !R || !q_codes_out || !slot_mapping || !cache) return UCMR_ERR_BAD_ARG;
+    if (Tq < 0 || Tk < 0 || Hq <= 0 || Hk <= 0 || group_mean <= 0 || Hq % group_mean != 0 || NB <= 0 || BS <= 0)
+        return UCMR_ERR_BAD_ARG;
+    int rc = check_dims(in_dim, hash_bits);
+    if (rc != UCMR_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool fused = !force_simt() && Tq > 0 && Tk > 0 &&
+                       tile_path_ok(q, Tq, Hq, group_mean, q_stride_t, q_stride_h, in_dim, hash_bits, q_codes_out, R) &&
+                       tile_path_ok(k, Tk, Hk, 1, k_stride_t, k_stride_h, in_dim, hash_bits, cache, R);
+    if (fused) {
+        const TileJob jq = make_job(q, Tq, Hq, group_mean, q_stride_t, q_stride_h, q_codes_out, nullptr, 0, 0);
+        const TileJob jk = make_job(k, Tk, Hk, 1, k_stride_t, k_stride_h, cache, slot_mapping, slot_is_int64 ? 1 : 0, NB * BS);
+        return launch_tiles(jq, &jk, R, status_word, st);
+    }
+    rc = ucmr_hash_encode_and_cache(k, Tk, Hk, k_stride_t, k_stride_h, R, in_dim, hash_bits, slot_mapping, slot_is_int64,
+                                    cache, NB, BS, status_word, stream);
+    if (rc != UCMR_OK) return rc;
+    return ucmr_hash_encode_query(q, Tq, Hq, q_stride_t, q_stride_h, group_mean, R, in_dim, hash_bits, q_codes_out,
+                                  status_word, stream);
 }

@@ -1,11 +1,11 @@
 // Exact per-row top-k over block scores (sm_100a): radix select in shared memory + ordered
 // compaction.  One CTA per (request, kv head) row.
 //
-// Each candidate j has a 32-bit key (forced block -> 0, valid block -> score + 1, past the
-// request's length -> 0xFFFFFFFF).  Four 8-bit histogram passes find the k-th smallest key T and how
-// many keys equal to T are still needed; a single ordered pass then emits every j with key < T and
-// the first `need` j with key == T, which is exactly "first k under (key, id)", already in ascending
-// id order.  No sort is involved.
+// Each candidate j has a key (forced block -> 0, valid block -> score + 1, past the request's length ->
+// all ones).  Two or three 11-bit histogram passes find the k-th smallest key T and how many keys equal
+// to T are still needed; a single ordered pass then emits every j with key < T and the first `need` j
+// with key == T, which is exactly "first k under (key, id)", already in ascending id order.  No sort
+// is involved.
 //
 // Stands in for torch.topk + torch.sort + torch.gather of the reference
 // (ucm/sparse/gsa_on_device/hamming_topk.py:49-54) and for update_seq_lens (:7-12), with the
@@ -23,7 +23,7 @@ int run_scan(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const ui
 
 constexpr int kSelThreads = 512;
 constexpr int kSelWarps = kSelThreads / 32;
-constexpr int kSelMaxCachedKeys = 48 * 1024;  // 192 KiB of keys in shared memory at most
+constexpr int kSelMaxCachedKeys = 40 * 1024;  // 160 KiB of keys in shared memory at most
 constexpr uint32_t kKeyInvalid = 0xFFFFFFFFu;
 
 struct ForcedSpec {
@@ -45,18 +45,27 @@ __device__ __forceinline__ bool block_is_forced(const ForcedSpec& f, int j, int 
     return false;
 }
 
+constexpr int kDigitBits = 11;
+constexpr int kBins = 1 << kDigitBits;
+constexpr int kBinsPerThread = kBins / kSelThreads;
+
 struct SelScratch {
-    int hist[256];
+    int hist[3][kBins];  // one histogram per radix pass (keys have at most 32 bits: 3 passes of <= 11)
     int warp_a[kSelWarps], warp_b[kSelWarps];
     uint32_t prefix;
     int remaining;
 };
 
 // Finds the first kb entries of keys[0..n) under (key, position) and calls emit(pos, j) for each,
-// pos = rank of j among the chosen in ascending j.  key_of(j) must be pure.  s_keys caches the
-// first n_cached keys.  All threads of the CTA must call this.
+// pos = rank of j among the chosen in ascending j.  Keys are below 2^key_bits; key_of(j) must be pure.
+// s_keys caches the first n_cached keys.  All threads of the CTA must call this.
+//
+// Radix select from the most significant digit: ceil(key_bits / 11) histogram passes over 2048 bins
+// each (a block score needs 17-20 bits, so two passes), every pass narrowing the candidates to the bin
+// that holds the kb-th smallest key.  Then one ordered pass emits every j with key < T and the first
+// `need` j with key == T: that is "first kb under (key, id)", already in ascending id order.
 template <typename KeyFn, typename EmitFn>
-__device__ void select_row(int n, int kb, KeyFn key_of, EmitFn emit, uint32_t* s_keys, int n_cached,
+__device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emit, uint32_t* s_keys, int n_cached,
                            SelScratch& sc)
 {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -64,52 +73,62 @@ __device__ void select_row(int n, int kb, KeyFn key_of, EmitFn emit, uint32_t* s
     if (kb > n) kb = n;
 
     for (int j = tid; j < n_cached; j += kSelThreads) s_keys[j] = key_of(j);
+    for (int i = tid; i < 3 * kBins; i += kSelThreads) (&sc.hist[0][0])[i] = 0;
     if (tid == 0) { sc.prefix = 0u; sc.remaining = kb; }
     __syncthreads();
     auto get = [&](int j) -> uint32_t { return j < n_cached ? s_keys[j] : key_of(j); };
 
-    uint32_t known = 0u;  // mask of the key bits fixed so far
-    for (int shift = 24; shift >= 0; shift -= 8) {
-        for (int i = tid; i < 256; i += kSelThreads) sc.hist[i] = 0;
-        __syncthreads();
+    int hi = key_bits;  // bits [hi, key_bits) of the k-th key are known (= prefix >> hi)
+    for (int pass = 0; hi > 0; ++pass) {
+        const int width = min(kDigitBits, hi);
+        const int shift = hi - width;
+        const uint32_t dmask = (1u << width) - 1u;
         const uint32_t prefix = sc.prefix;
+        int* hist = sc.hist[pass];
         const int n_round = (n + kSelThreads - 1) / kSelThreads * kSelThreads;
         for (int j = tid; j < n_round; j += kSelThreads) {
             const bool in = j < n;
             const uint32_t key = in ? get(j) : 0u;
-            const bool hit = in && ((key & known) == prefix);
-            const uint32_t digit = hit ? ((key >> shift) & 255u) : 256u;
-            // one atomic per distinct digit in the warp
-            const uint32_t peers = __match_any_sync(0xffffffffu, digit);
-            if (hit && lane == (__ffs(peers) - 1)) atomicAdd(&sc.hist[digit], __popc(peers));
+            const bool hit = in && (hi >= 32 || (key >> hi) == (prefix >> hi));
+            const uint32_t digit = (key >> shift) & dmask;
+            // block scores cluster, so whole warps often agree on the digit: one atomic for the warp then
+            int same;
+            __match_all_sync(0xffffffffu, hit ? digit : 0xFFFFFFFFu, &same);
+            if (same) {
+                if (hit && lane == 0) atomicAdd(&hist[digit], 32);
+            } else if (hit) {
+                atomicAdd(&hist[digit], 1);
+            }
         }
         __syncthreads();
-        if (warp == 0) {
-            int loc[8];
-            int sum = 0;
+        // exclusive scan over the bins, kBinsPerThread consecutive bins per thread
+        int loc[kBinsPerThread];
+        int sum = 0;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) { loc[i] = sc.hist[lane * 8 + i]; sum += loc[i]; }
-            int incl = sum;
+        for (int i = 0; i < kBinsPerThread; ++i) { loc[i] = hist[tid * kBinsPerThread + i]; sum += loc[i]; }
+        int incl = sum;
 #pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                const int o = __shfl_up_sync(0xffffffffu, incl, off);
-                if (lane >= off) incl += o;
-            }
-            const int excl = incl - sum;
-            const int rem = sc.remaining;
-            if (rem > excl && rem <= incl) {  // exactly one lane
-                int run = excl;
+        for (int off = 1; off < 32; off <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) incl += o;
+        }
+        if (lane == 31) sc.warp_a[warp] = incl;
+        const int rem = sc.remaining;
+        __syncthreads();
+        int excl = incl - sum;
+        for (int w = 0; w < warp; ++w) excl += sc.warp_a[w];
+        if (rem > excl && rem <= excl + sum) {  // exactly one thread
+            int run = excl;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    if (rem > run && rem <= run + loc[i]) {
-                        sc.prefix = prefix | ((uint32_t)(lane * 8 + i) << shift);
-                        sc.remaining = rem - run;
-                    }
-                    run += loc[i];
+            for (int i = 0; i < kBinsPerThread; ++i) {
+                if (rem > run && rem <= run + loc[i]) {
+                    sc.prefix = prefix | ((uint32_t)(tid * kBinsPerThread + i) << shift);
+                    sc.remaining = rem - run;
                 }
+                run += loc[i];
             }
         }
-        known |= 255u << shift;
+        hi = shift;
         __syncthreads();
     }
     const uint32_t T = sc.prefix;
@@ -160,6 +179,7 @@ struct SelectParams {
     ForcedSpec forced;
     int id_offset;
     int n_cached;
+    int key_bits;  // valid keys (score + 1) are below 2^key_bits - 1, which marks blocks past the end
     // block-id outputs
     int32_t *out_phys, *out_logical, *out_scores, *out_valid, *out_newseq;
     // candidate-record outputs
@@ -216,10 +236,11 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     if (masked) return;
     __syncthreads();  // padding stores precede the emits of the same CTA
 
+    const uint32_t key_invalid = p.key_bits >= 32 ? kKeyInvalid : (1u << p.key_bits) - 1u;
     auto key_of = [&](int j) -> uint32_t {
-        if (j >= nb_l) return kKeyInvalid;
+        if (j >= nb_l) return key_invalid;
         const int s = srow[j];
-        if (s < 0) return kKeyInvalid;
+        if (s < 0) return key_invalid;
         if (block_is_forced(p.forced, j + p.id_offset, nb_g, seq_g, p.BS)) return 0u;
         return (uint32_t)s + 1u;
     };
@@ -237,7 +258,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
             if (p.out_scores) p.out_scores[obase + pos] = valid ? srow[j] : -1;
         }
     };
-    select_row(n, kb, key_of, emit, s_keys, p.n_cached, sc);
+    select_row(n, kb, p.key_bits, key_of, emit, s_keys, p.n_cached, sc);
 }
 
 __device__ __forceinline__ uint32_t f32_order_key(float x)
@@ -285,7 +306,7 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
             p.out_ids[obase + pos] = p.cand_ids[a];
         }
     };
-    select_row(n, min(p.k, n), key_of, emit, s_keys, p.n_cached, sc);
+    select_row(n, min(p.k, n), 32, key_of, emit, s_keys, p.n_cached, sc);
 }
 
 __global__ void update_seq_lens_kernel(const int32_t* seq, int B, int topk_tokens, int BS, int32_t* out)
@@ -385,6 +406,13 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
     p.k = k; p.k_per_request = k_per_request; p.mask = mask;
     p.id_offset = id_offset;
     p.n_cached = max_blocks < kSelMaxCachedKeys ? max_blocks : kSelMaxCachedKeys;
+    {
+        const int G = Hq / Hkv;
+        int64_t max_score = (int64_t)G * W * 32;
+        if (reduce_mode == UCMR_REDUCE_SUM) max_score *= (int64_t)BS * (reduce_kvhead ? Hkv : 1);
+        p.key_bits = 1;
+        while (p.key_bits < 32 && ((int64_t)1 << p.key_bits) - 1 <= max_score + 1) ++p.key_bits;
+    }
     p.out_phys = out_phys; p.out_logical = out_logical; p.out_scores = out_scores;
     p.out_valid = out_valid; p.out_newseq = out_newseq;
     p.cand_scores = cand_scores; p.cand_ids = cand_ids; p.scale = scale; p.sched = sched;

@@ -46,6 +46,8 @@ SIGNATURES = {
     "ucmr_hash_encode": (_i, [_vp, _i64, _i64, _vp, _i, _i, _vp, _vp, _vp]),
     "ucmr_hash_encode_query": (_i, [_vp, _i64, _i, _i64, _i64, _i, _vp, _i, _i, _vp, _vp, _vp]),
     "ucmr_hash_encode_and_cache": (_i, [_vp, _i64, _i, _i64, _i64, _vp, _i, _i, _vp, _i, _vp, _i64, _i, _vp, _vp]),
+    "ucmr_hash_encode_decode_step": (_i, [_vp, _i64, _i, _i64, _i64, _i, _vp, _vp, _i64, _i, _i64, _i64, _vp, _i, _vp, _i64,
+                                          _i, _vp, _i, _i, _vp, _vp]),
     "ucmr_hamming_topk_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "ucmr_workspace_init": (_i, [_vp, _sz, _vp]),
     "ucmr_workspace_status": (_i, [_vp, C.POINTER(C.c_int), _vp]),

@@ -134,6 +134,37 @@ def hash_encode_and_cache(x: torch.Tensor, slot_mapping: torch.Tensor, cache: to
     return cache
 
 
+def hash_encode_decode_step(q: torch.Tensor, k_new: torch.Tensor, slot_mapping: torch.Tensor, cache: torch.Tensor,
+                            r: torch.Tensor, group_mean: int = 1, q_codes_out: Optional[torch.Tensor] = None,
+                            status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One launch for a decode step's two encodes: q [T,Hq,D] -> codes [T,Hq/group_mean,W] (returned) and
+    k_new [T,Hkv,D] -> slot ``slot_mapping[t]`` of the paged cache."""
+    _need_cuda("q", q, torch.bfloat16, contiguous=False)
+    _need_cuda("k_new", k_new, torch.bfloat16, contiguous=False)
+    if q.dim() != 3 or k_new.dim() != 3 or q.stride(2) != 1 or k_new.stride(2) != 1:
+        raise ValueError("q and k_new must be [T, H, in_dim] with a unit inner stride")
+    _need_cuda("slot_mapping", slot_mapping, (torch.int64, torch.int32))
+    if slot_mapping.dim() != 1 or slot_mapping.shape[0] != k_new.shape[0]:
+        raise ValueError("slot_mapping must have one entry per new key token")
+    _need_cuda("cache", cache)
+    cw = as_words(cache)
+    tq, hq, in_dim = q.shape
+    tk, hk, _ = k_new.shape
+    bits = _check_r(r, in_dim)
+    if k_new.shape[2] != in_dim or cw.dim() != 4 or cw.shape[2] != hk or cw.shape[3] != bits // 32:
+        raise ValueError("k_new / cache shapes do not match")
+    if group_mean <= 0 or hq % group_mean != 0:
+        raise ValueError("group_mean must divide the number of query heads")
+    if q_codes_out is None:
+        q_codes_out = torch.empty((tq, hq // group_mean, bits // 32), dtype=torch.int32, device=q.device)
+    lib = _l.load_library()
+    _l.check(lib.ucmr_hash_encode_decode_step(
+        _ptr(q), tq, hq, q.stride(0), q.stride(1), group_mean, _ptr(q_codes_out), _ptr(k_new), tk, hk, k_new.stride(0),
+        k_new.stride(1), _ptr(slot_mapping), int(slot_mapping.dtype == torch.int64), _ptr(cw), cw.shape[0], cw.shape[1],
+        _ptr(r), in_dim, bits, _ptr(status), _stream(q)), "ucmr_hash_encode_decode_step")
+    return q_codes_out
+
+
 # ----------------------------------------------------------------------------------------------
 # (2)+(3) scan + top-k
 # ----------------------------------------------------------------------------------------------
