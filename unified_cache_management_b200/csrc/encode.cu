@@ -325,34 +325,75 @@ __global__ void __launch_bounds__(kTileThreads) encode_tile_kernel(const TilePar
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // A tile: row r of the tile, 16-byte chunk c (8 elements) -> K half c >> 3, chunk (c & 7) ^ (r & 7)
-    for (int i = tid; i < kEncTileM * (kEncD / 8); i += kTileThreads) {
-        const int r = i >> 4, c = i & 15;
-        const int64_t row = row0 + r;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (row < rows) {
-            const int64_t t = row / H_out;
-            const int ho = (int)(row - t * H_out);
-            const __nv_bfloat16* src = jb.x + t * jb.stride_t + (int64_t)ho * jb.G * jb.stride_h + c * 8;
-            if (jb.G == 1) {
-                v = __ldg(reinterpret_cast<const uint4*>(src));
-            } else {
-                float acc[8];
+    // A tile: row r of the tile, 16-byte chunk c (8 elements) -> K half c >> 3, chunk (c & 7) ^ (r & 7).
+    // All of a thread's global loads are issued before the first shared-memory store, so the tile costs
+    // one memory round trip, not sixteen.
+    const int64_t t_base = row0 / H_out;
+    const int h_base = (int)(row0 - t_base * H_out);
+    constexpr int kChunksPerThread = kEncTileM * (kEncD / 8) / kTileThreads;  // 16
+    auto src_of = [&](int r, int c) -> const __nv_bfloat16* {
+        const int hh = h_base + r;
+        const int64_t t = t_base + hh / H_out;
+        const int ho = hh % H_out;
+        return jb.x + t * jb.stride_t + (int64_t)ho * jb.G * jb.stride_h + c * 8;
+    };
+    auto dst_of = [&](int r, int c) -> uint4* {
+        return reinterpret_cast<uint4*>(s_a + (uint32_t)(c >> 3) * kEncHalfBytes + (uint32_t)r * 128u +
+                                        ((uint32_t)((c & 7) ^ (r & 7)) << 4));
+    };
+    if (jb.G == 1) {
+        uint4 v[kChunksPerThread];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-                for (int g = 0; g < jb.G; ++g) {
-                    const uint4 u = __ldg(reinterpret_cast<const uint4*>(src + (int64_t)g * jb.stride_h));
-                    const __nv_bfloat16* ue = reinterpret_cast<const __nv_bfloat16*>(&u);
+        for (int u = 0; u < kChunksPerThread; ++u) {
+            const int i = tid + u * kTileThreads, r = i >> 4, c = i & 15;
+            v[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (row0 + r < rows) v[u] = __ldg(reinterpret_cast<const uint4*>(src_of(r, c)));
+        }
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[e] += __bfloat162float(ue[e]);
+        for (int u = 0; u < kChunksPerThread; ++u) {
+            const int i = tid + u * kTileThreads;
+            *dst_of(i >> 4, i & 15) = v[u];
+        }
+    } else {
+        constexpr int kBatch = 4;  // chunks whose G loads are in flight together
+        for (int u0 = 0; u0 < kChunksPerThread; u0 += kBatch) {
+            float acc[kBatch][8];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+            for (int g0 = 0; g0 < jb.G; g0 += 4) {
+                uint4 ld[kBatch][4];
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+                    const int i = tid + (u0 + u) * kTileThreads, r = i >> 4, c = i & 15;
+                    const __nv_bfloat16* src = src_of(r, c);
+#pragma unroll
+                    for (int gg = 0; gg < 4; ++gg) {
+                        ld[u][gg] = make_uint4(0u, 0u, 0u, 0u);
+                        if (row0 + r < rows && g0 + gg < jb.G)
+                            ld[u][gg] = __ldg(reinterpret_cast<const uint4*>(src + (int64_t)(g0 + gg) * jb.stride_h));
+                    }
                 }
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u)
+#pragma unroll
+                    for (int gg = 0; gg < 4; ++gg) {
+                        const __nv_bfloat16* ue = reinterpret_cast<const __nv_bfloat16*>(&ld[u][gg]);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[u][e] += __bfloat162float(ue[e]);  // + 0 past G
+                    }
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int i = tid + (u0 + u) * kTileThreads;
+                uint4 v;
                 __nv_bfloat16* ve = reinterpret_cast<__nv_bfloat16*>(&v);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) ve[e] = __float2bfloat16_rn(acc[e] / (float)jb.G);
+                for (int e = 0; e < 8; ++e) ve[e] = __float2bfloat16_rn(acc[u][e] / (float)jb.G);
+                *dst_of(i >> 4, i & 15) = v;
             }
         }
-        const uint32_t off = (uint32_t)(c >> 3) * kEncHalfBytes + (uint32_t)r * 128u + ((uint32_t)((c & 7) ^ (r & 7)) << 4);
-        *reinterpret_cast<uint4*>(s_a + off) = v;
     }
     build_rt_swizzled(s_b, p.R, tid, kTileThreads);
     fence_proxy_async();
