@@ -136,6 +136,32 @@ int ucmr_hamming_topk(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
                       int32_t* out_scores, int32_t* out_valid_count, int32_t* out_new_seq_lens,
                       void* workspace, size_t workspace_bytes, void* stream);
 
+/*     Same retrieval for callers that cannot provide a workspace (no counterpart in the reference:
+ *     its op allocates its output with torch on every call).  An engine that has already handed all free
+ *     GPU memory to its KV-cache pool, or a hook running inside its forward pass, has nowhere to
+ *     allocate from; this variant keeps the scan -> selection scores in a fixed device array that is
+ *     part of the library image, so it calls no cudaMalloc / cudaFree and no allocating library routine.
+ *     Limits and rules:
+ *       - the array is ucmr_static_workspace_capacity() bytes (4 MiB) on every GPU that loads the
+ *         library, held until the process exits; shapes whose workspace (see
+ *         ucmr_hamming_topk_workspace_bytes) is larger are refused with UCMR_ERR_WORKSPACE;
+ *       - the first call on each device resolves the array's device address (with that device current);
+ *         make that first call outside any stream capture;
+ *       - all calls on a device share the one array: calls that may overlap on the GPU (different
+ *         streams, no ordering between them) race on it and must be serialised by the caller;
+ *       - the array keeps the previous call's contents; each call clears the header it needs to start at
+ *         zero.  The status word is therefore not sticky here and cannot be read back.
+ *     Arguments and outputs are those of ucmr_hamming_topk without the workspace pair.              */
+size_t ucmr_static_workspace_capacity(void);
+int ucmr_hamming_topk_static(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
+                             const uint32_t* q_codes, int Hq, const int32_t* block_table,
+                             int max_blocks, int64_t block_table_stride, const int32_t* seq_lens, int B,
+                             int k, const int32_t* k_per_request, const uint8_t* request_mask,
+                             int reduce_mode, int reduce_kvhead, const int32_t* must_select, int n_must,
+                             int sink_tokens, int recent_tokens, int32_t* out_physical,
+                             int32_t* out_logical, int32_t* out_scores, int32_t* out_valid_count,
+                             int32_t* out_new_seq_lens, void* stream);
+
 /*     Scan only: block scores int32 [B, Hout, max_blocks] (-1 past the request's length).
  *     Same kernel as the first half of ucmr_hamming_topk.  status_word (device int32*, may be
  *     NULL) receives UCMR_DEV_* bits.                                                             */

@@ -53,6 +53,9 @@ SIGNATURES = {
     "ucmr_workspace_status": (_i, [_vp, C.POINTER(C.c_int), _vp]),
     "ucmr_hamming_topk": (_i, [_vp, _i64, _i, _i, _i, _vp, _i, _vp, _i, _i64, _vp, _i, _i, _vp, _vp, _i, _i,
                                C.POINTER(C.c_int32), _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "ucmr_static_workspace_capacity": (_sz, []),
+    "ucmr_hamming_topk_static": (_i, [_vp, _i64, _i, _i, _i, _vp, _i, _vp, _i, _i64, _vp, _i, _i, _vp, _vp, _i, _i,
+                                      C.POINTER(C.c_int32), _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "ucmr_block_scores": (_i, [_vp, _i64, _i, _i, _i, _vp, _i, _vp, _i, _i64, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "ucmr_hamming_score": (_i, [_vp, _i64, _i, _i, _i, _vp, _i, _vp, _i, _i64, _vp, _i, _i, _i, _i, _vp, _vp]),
     "ucmr_update_seq_lens": (_i, [_vp, _i, _i, _i, _vp, _vp]),

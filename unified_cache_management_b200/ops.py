@@ -272,6 +272,33 @@ def hamming_topk(codes: torch.Tensor, q_codes: torch.Tensor, block_table: torch.
     return out
 
 
+def hamming_topk_static(codes: torch.Tensor, q_codes: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
+                        k: int, *, out: Retrieval, reduce="sum", reduce_kvhead: bool = False,
+                        must_select: Sequence[int] = (), sink_tokens: int = 0, recent_tokens: int = 0,
+                        k_per_request: Optional[torch.Tensor] = None,
+                        request_mask: Optional[torch.Tensor] = None) -> Retrieval:
+    """``hamming_topk`` for callers that cannot allocate device memory: the scores between the two kernels
+    live in a fixed 4 MiB array inside the library, and the caller passes every output buffer (``out``),
+    so nothing here allocates.  Calls that may overlap on the GPU share that array and must be serialised;
+    shapes needing more than the array are refused (``UcmrError`` with the workspace status)."""
+    codes, q_codes, bt_stride = _scan_args(codes, q_codes, block_table, seq_lens)
+    nb, bs, hkv, w = codes.shape
+    b, hq, _ = q_codes.shape
+    mb = block_table.shape[1]
+    if k < 0 or k > mb:
+        raise ValueError(f"k={k} outside [0, max_blocks={mb}]")
+    if b == 0:
+        return out
+    must, n_must = _must_array(must_select)
+    lib = _l.load_library()
+    _l.check(lib.ucmr_hamming_topk_static(
+        _ptr(codes), nb, bs, hkv, w, _ptr(q_codes), hq, _ptr(block_table), mb, bt_stride, _ptr(seq_lens), b, k,
+        _ptr(k_per_request), _ptr(request_mask), reduce_mode(reduce), int(bool(reduce_kvhead)), must, n_must,
+        int(sink_tokens), int(recent_tokens), _ptr(out.physical), _ptr(out.logical), _ptr(out.scores),
+        _ptr(out.valid_count), _ptr(out.new_seq_lens), _stream(codes)), "ucmr_hamming_topk_static")
+    return out
+
+
 def block_scores(codes, q_codes, block_table, seq_lens, *, reduce="sum", reduce_kvhead=False,
                  out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """int32 [B, Hout, max_blocks] block scores (-1 past each request's length)."""
