@@ -24,6 +24,26 @@ inline int check_launch()
 
 inline bool is_pow2(int64_t v) { return v > 0 && (v & (v - 1)) == 0; }
 
+// Launches `kernel` on `st` and turns a refused launch into UCMR_ERR_LAUNCH.
+template <typename... KArgs, typename... Args>
+inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cfg.attrs = nullptr;
+    cfg.numAttrs = 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e != cudaSuccess) {
+        note_cuda_error(e);
+        (void)cudaGetLastError();
+        return UCMR_ERR_LAUNCH;
+    }
+    return UCMR_OK;
+}
+
 // Time bound of every spin-wait in this library.  A wait that runs out sets UCMR_DEV_WAIT_TIMEOUT in
 // the status word and the kernel winds down without touching the data.
 constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s

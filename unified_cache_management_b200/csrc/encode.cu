@@ -605,8 +605,7 @@ static int launch_tc(const void* x, int64_t T, int H, int64_t stride_t, int64_t 
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = (int)(p.n_tiles < sms ? p.n_tiles : sms);
-    encode_tc_kernel<<<grid, kEncThreads, kEncSmemBytes, st>>>(map, p);
-    return check_launch();
+    return launch_kernel(encode_tc_kernel, dim3(grid), dim3(kEncThreads), kEncSmemBytes, st, map, p);
 }
 
 // Shapes the one-tile-per-CTA tensor-core kernel accepts (any head count; 16-byte aligned rows).
@@ -644,8 +643,7 @@ static int launch_tiles(const TileJob& j0, const TileJob* j1, const void* R, int
     if (grid > 0x7FFFFFFF) return UCMR_ERR_UNSUPPORTED;
     cudaError_t e = cudaFuncSetAttribute(encode_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTileSmemBytes);
     if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
-    encode_tile_kernel<<<(int)grid, kTileThreads, kTileSmemBytes, st>>>(p);
-    return check_launch();
+    return launch_kernel(encode_tile_kernel, dim3((unsigned)grid), dim3(kTileThreads), kTileSmemBytes, st, p);
 }
 
 // Row counts up to this many tiles go to the one-tile-per-CTA kernel (two waves of CTAs at most); above it the

@@ -30,8 +30,6 @@
 //  ucm/sparse/gsa_on_device/hamming_topk.py:45-47).
 #include <limits.h>
 
-#include <cuda.h>
-
 #include "common.cuh"
 
 namespace ucmr {
@@ -60,23 +58,10 @@ struct RingParams {
     int RW;            // words per token row = Hkv * W
     int bps;           // blocks per stage
     int block_bytes;   // BS * RW * 4
-    int block_stride;  // = block_bytes (tensor copies land on 128-byte boundaries)
-    int rows128;       // 128-byte rows per block in the flat [bytes/128, 32 words] view of the cache
+    int block_stride;  // = block_bytes (blocks of a stage sit back to back on 128-byte boundaries)
     int stage_bytes;   // bps * block_stride, rounded up to 128
     int n_active;      // warps (= stages) in use: min(kRingWarps, ring bytes / stage bytes)
 };
-
-// Tiled TMA load of one code block: the cache is viewed as a 2-D tensor [bytes/128, 32 words] and a
-// block is a box of rows128 rows.  (The untiled cp.async.bulk form of the same copy sustains a much
-// lower rate per SM.)
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
-            "r"(smem_u32(smem_dst)),
-        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
-        : "memory");
-}
 
 struct __align__(16) StageMeta {
     int b, j0, seq;
@@ -117,23 +102,41 @@ __device__ __forceinline__ uint32_t fold16(uint32_t& ones, uint32_t& twos, uint3
     return t16;
 }
 
+// Bit-sliced ripple add of two counters of NP planes; the result has NP + 1 planes.
+template <int NP>
+__device__ __forceinline__ void add_planes(const uint32_t (&a)[NP], const uint32_t (&b)[NP], uint32_t (&out)[NP + 1])
+{
+    uint32_t carry = 0u;
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+        uint32_t h, l;
+        csa(h, l, a[p], b[p], carry);
+        out[p] = l;
+        carry = h;
+    }
+    out[NP] = carry;
+}
+
 // Counts, for every bit position, how many of the 128 buffered words have the bit set: eight
-// bit-sliced planes (plane p holds bit p of the 32 counters).  Pure carry-save adder tree.
+// bit-sliced planes (plane p holds bit p of the 32 counters).  Four independent carry-save chains of
+// 32 words each (instruction-level parallelism: a single chain is one long dependency), then two
+// levels of bit-sliced adds.
 __device__ __forceinline__ void fold128(const uint32_t (&x)[kChunkTokens], uint32_t (&pl)[kPlanes])
 {
-    uint32_t p0 = 0, p1 = 0, p2 = 0, p3 = 0, p4 = 0, p5 = 0, p6 = 0;
-    uint32_t c[8];
+    uint32_t q6[4][6];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) c[u] = fold16(p0, p1, p2, p3, &x[u * 16]);
-    uint32_t t32a, t32b, t32c, t32d, t64a, t64b, t128;
-    csa(t32a, p4, p4, c[0], c[1]);
-    csa(t32b, p4, p4, c[2], c[3]);
-    csa(t32c, p4, p4, c[4], c[5]);
-    csa(t32d, p4, p4, c[6], c[7]);
-    csa(t64a, p5, p5, t32a, t32b);
-    csa(t64b, p5, p5, t32c, t32d);
-    csa(t128, p6, p6, t64a, t64b);
-    pl[0] = p0; pl[1] = p1; pl[2] = p2; pl[3] = p3; pl[4] = p4; pl[5] = p5; pl[6] = p6; pl[7] = t128;
+    for (int c = 0; c < 4; ++c) {
+        uint32_t p0 = 0, p1 = 0, p2 = 0, p3 = 0;
+        const uint32_t c0 = fold16(p0, p1, p2, p3, &x[c * 32]);
+        const uint32_t c1 = fold16(p0, p1, p2, p3, &x[c * 32 + 16]);
+        q6[c][0] = p0; q6[c][1] = p1; q6[c][2] = p2; q6[c][3] = p3;
+        q6[c][4] = c0 ^ c1;
+        q6[c][5] = c0 & c1;
+    }
+    uint32_t h7a[7], h7b[7];
+    add_planes<6>(q6[0], q6[1], h7a);
+    add_planes<6>(q6[2], q6[3], h7b);
+    add_planes<7>(h7a, h7b, pl);
 }
 
 // sum_g sum_tokens popc(word ^ q[g]) of one buffered chunk of n tokens (unused slots hold 0).
@@ -192,7 +195,7 @@ __device__ __forceinline__ void load_chunk(uint32_t (&x)[kChunkTokens], const ui
 // width and group size for the common shapes, 0 = read them from the parameters.
 template <bool MIN, int RW_T, int G_T>
 __global__ void __launch_bounds__(kRingThreads, 1)
-scan_ring_kernel(const __grid_constant__ CUtensorMap cmap, const RingParams p)
+scan_ring_kernel(const RingParams p)
 {
     extern __shared__ __align__(128) uint8_t s_ring[];
     __shared__ __align__(8) uint64_t s_full[kRingWarps];
@@ -206,7 +209,6 @@ scan_ring_kernel(const __grid_constant__ CUtensorMap cmap, const RingParams p)
     if (tid == 0) {
         for (int s = 0; s < kRingWarps; ++s) mbar_init(&s_full[s], 1);
         fence_mbar_init();
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&cmap) : "memory");
     }
     if (warp == 0) {  // prefix sum of items per request
         int run = 0;
@@ -233,20 +235,23 @@ scan_ring_kernel(const __grid_constant__ CUtensorMap cmap, const RingParams p)
     __syncthreads();
     const int total_items = s_cum[p.B];
 
-    // scores of blocks past each request's length
-    for (int64_t i = (int64_t)blockIdx.x * kRingThreads + tid; i < (int64_t)p.B * p.max_blocks;
-         i += (int64_t)gridDim.x * kRingThreads) {
-        const int b = (int)(i / p.max_blocks), j = (int)(i - (int64_t)b * p.max_blocks);
-        const int nb = (p.seq_lens[b] + p.BS - 1) / p.BS;
-        if (j >= nb)
-            for (int h = 0; h < Hout; ++h) p.out[((int64_t)b * Hout + h) * p.max_blocks + j] = -1;
-    }
-
     // Work split.  Static part: CTA c takes flat items c, c + grid, ... and warp w every n_active-th of
     // those.  With a work counter (p.sched) only the first 7/8 of the items are split that way; the rest
     // is claimed item by item with an atomic, so that all SMs finish together whatever their luck with
     // the memory system (a fully dynamic split would serialise ~10^4 atomics on one address).
-    if (warp >= p.n_active) return;
+    auto mark_past_end = [&]() {  // scores of blocks past each request's length
+        for (int64_t i = (int64_t)blockIdx.x * kRingThreads + tid; i < (int64_t)p.B * p.max_blocks;
+             i += (int64_t)gridDim.x * kRingThreads) {
+            const int b = (int)(i / p.max_blocks), j = (int)(i - (int64_t)b * p.max_blocks);
+            const int nb = (s_seq[b] + p.BS - 1) / p.BS;
+            if (j >= nb)
+                for (int h = 0; h < Hout; ++h) p.out[((int64_t)b * Hout + h) * p.max_blocks + j] = -1;
+        }
+    };
+    if (warp >= p.n_active) {
+        mark_past_end();
+        return;
+    }
     uint8_t* const stage = s_ring + (size_t)warp * p.stage_bytes;
     uint64_t* const full = &s_full[warp];
     const int lanes_total = gridDim.x * p.n_active;
@@ -300,13 +305,15 @@ scan_ring_kernel(const __grid_constant__ CUtensorMap cmap, const RingParams p)
             mbar_expect_tx(full, (uint32_t)(__popc(mask) * p.block_bytes));
         }
         __syncwarp();
-        if (lane < p.bps && ph >= 0) tma_load_2d(stage + lane * p.block_stride, &cmap, 0, ph * p.rows128, full);
+        if (lane < p.bps && ph >= 0)
+            bulk_g2s(stage + lane * p.block_stride, p.codes + (int64_t)ph * p.block_bytes, (uint32_t)p.block_bytes, full);
         __syncwarp();
     };
 
     Item cur = resolve(claim_finish(claim_start()));
     int token = claim_start();
     issue(cur);
+    mark_past_end();  // while the first block is on its way
     Item nxt = resolve(claim_finish(token));
     token = claim_start();
     // refill the (free) stage with the next item and advance the two-deep claim/resolve pipeline
@@ -479,42 +486,11 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     if (block_bytes % 128 != 0) return UCMR_ERR_UNSUPPORTED;
     if (!is_min && RW < 32 && BS > 240) return UCMR_ERR_UNSUPPORTED;
     p.block_stride = (int)block_bytes;
-    p.rows128 = (int)(block_bytes / 128);
-    if (p.rows128 > 256) return UCMR_ERR_UNSUPPORTED;
     p.stage_bytes = bps * p.block_stride;
     p.n_active = kRingBytes / p.stage_bytes;
     if (p.n_active > kRingWarps) p.n_active = kRingWarps;
     if (p.n_active < 4) return UCMR_ERR_UNSUPPORTED;
     const size_t smem = (size_t)p.n_active * p.stage_bytes;
-    const int64_t total_rows = NB * (int64_t)p.rows128;
-    if (total_rows > 0xFFFFFFFFll) return UCMR_ERR_UNSUPPORTED;
-
-    CUtensorMap cmap;
-    {
-        typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                          const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                          CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                          CUtensorMapFloatOOBfill);
-        static EncodeTiledFn encode = nullptr;  // resolving twice is harmless
-        if (!encode) {
-            void* ptr = nullptr;
-            cudaDriverEntryPointQueryResult qres;
-            cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
-            if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !ptr) {
-                if (e != cudaSuccess) note_cuda_error(e);
-                return UCMR_ERR_LAUNCH;
-            }
-            encode = reinterpret_cast<EncodeTiledFn>(ptr);
-        }
-        const cuuint64_t dims[2] = {32, (cuuint64_t)total_rows};
-        const cuuint64_t strides[1] = {128};
-        const cuuint32_t box[2] = {32, (cuuint32_t)p.rows128};
-        const cuuint32_t estr[2] = {1, 1};
-        CUresult r = encode(&cmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(codes), dims, strides, box,
-                            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return UCMR_ERR_LAUNCH;
-    }
 
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -522,7 +498,7 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     const int64_t max_items = (int64_t)B * ((max_blocks + bps - 1) / bps);
     const int grid = (int)(max_items < sms ? (max_items > 0 ? max_items : 1) : sms);
 
-    void (*kernel)(const CUtensorMap, const RingParams) = nullptr;
+    void (*kernel)(const RingParams) = nullptr;
     if (is_min) {
         kernel = scan_ring_kernel<true, 0, 0>;
     } else {
@@ -537,8 +513,7 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     // idempotent attribute, set on every call: cheap, and correct on every device of a process
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
     if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
-    kernel<<<grid, kRingThreads, smem, st>>>(cmap, p);
-    return check_launch();
+    return launch_kernel(kernel, dim3(grid), dim3(kRingThreads), smem, st, p);
 }
 
 }  // namespace ucmr

@@ -421,13 +421,12 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
     if (candidates) {
         rc = set_dyn_smem(select_kernel<true>, smem);
         if (rc != UCMR_OK) return rc;
-        select_kernel<true><<<rows, kSelThreads, smem, st>>>(p);
+        return launch_kernel(select_kernel<true>, dim3(rows), dim3(kSelThreads), smem, st, p);
     } else {
         rc = set_dyn_smem(select_kernel<false>, smem);
         if (rc != UCMR_OK) return rc;
-        select_kernel<false><<<rows, kSelThreads, smem, st>>>(p);
+        return launch_kernel(select_kernel<false>, dim3(rows), dim3(kSelThreads), smem, st, p);
     }
-    return check_launch();
 }
 
 extern "C" int ucmr_hamming_topk(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
@@ -478,8 +477,7 @@ extern "C" int ucmr_merge_topk(const float* cand_scores, const int32_t* cand_ids
     const size_t smem = (size_t)p.n_cached * sizeof(uint32_t);
     int rc = set_dyn_smem(merge_kernel, smem);
     if (rc != UCMR_OK) return rc;
-    merge_kernel<<<B * Hout, kSelThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
-    return check_launch();
+    return launch_kernel(merge_kernel, dim3(B * Hout), dim3(kSelThreads), smem, static_cast<cudaStream_t>(stream), p);
 }
 
 extern "C" int ucmr_update_seq_lens(const int32_t* seq_lens, int B, int topk_tokens, int BS, int32_t* out,
