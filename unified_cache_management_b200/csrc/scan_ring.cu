@@ -191,7 +191,7 @@ __device__ __forceinline__ void load_chunk(uint32_t (&x)[kChunkTokens], const ui
     }
 }
 
-// MIN selects the per-token-minimum path; RW_T / G_T (sum mode only) are compile-time copies of the row
+// MIN selects the per-token-minimum path; RW_T (sum mode only) and G_T are compile-time copies of the row
 // width and group size for the common shapes, 0 = read them from the parameters.
 template <bool MIN, int RW_T, int G_T>
 __global__ void __launch_bounds__(kRingThreads, 1)
@@ -202,6 +202,7 @@ scan_ring_kernel(const RingParams p)
     __shared__ StageMeta s_meta[kRingWarps];
     __shared__ int s_cum[kRingMaxBatch + 1];  // s_cum[b] = work items before request b
     __shared__ int s_seq[kRingMaxBatch];      // seq_lens[b]
+    __shared__ volatile int s_pool_empty;     // a warp of this CTA found the dynamic item pool exhausted
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int Hout = p.reduce_kvhead ? 1 : p.Hkv;
@@ -209,6 +210,7 @@ scan_ring_kernel(const RingParams p)
     if (tid == 0) {
         for (int s = 0; s < kRingWarps; ++s) mbar_init(&s_full[s], 1);
         fence_mbar_init();
+        s_pool_empty = 0;
     }
     if (warp == 0) {  // prefix sum of items per request
         int run = 0;
@@ -255,19 +257,23 @@ scan_ring_kernel(const RingParams p)
     uint8_t* const stage = s_ring + (size_t)warp * p.stage_bytes;
     uint64_t* const full = &s_full[warp];
     const int lanes_total = gridDim.x * p.n_active;
-    const int static_items = (p.sched != nullptr) ? (total_items - total_items / 8) / lanes_total * lanes_total
-                                                  : total_items;
+    // (small launches stay static: every warp pays at least one atomic to learn that the pool is empty)
+    const bool dynamic = p.sched != nullptr && total_items >= 4 * lanes_total;
+    const int static_items = dynamic ? (total_items - total_items / 8) / lanes_total * lanes_total : total_items;
     int static_k = 0;
     // claim_start returns a token (meaningful in lane 0); claim_finish turns it into a flat item index or
     // -1.  They are called one item apart so that the atomic's latency is hidden.
     auto claim_start = [&]() -> int {
         const int flat = blockIdx.x + (static_k * p.n_active + warp) * gridDim.x;
-        if (flat < static_items || p.sched == nullptr) {
+        if (flat < static_items || !dynamic) {
             ++static_k;
             return flat;
         }
-        int t = 0;
-        if (lane == 0) t = static_items + atomicAdd(p.sched, 1);
+        int t = total_items;
+        if (lane == 0 && !s_pool_empty) {
+            t = static_items + atomicAdd(p.sched, 1);
+            if (t >= total_items) s_pool_empty = 1;  // spares the CTA's other warps their failing claim
+        }
         return t;
     };
     auto claim_finish = [&](int token) -> int {
@@ -400,7 +406,10 @@ scan_ring_kernel(const RingParams p)
         const int blk = lane / LG, lam = lane % LG;
         const int hp = lam % P, slot = lam / P;
         const int head = hp / PW, part = hp % PW;
-        uint4 qv[kRingMaxG];
+        const int G = G_T > 0 ? G_T : p.G;
+        constexpr int GMAX = G_T > 0 ? G_T : kRingMaxG;
+        constexpr int kMinRounds = 16;  // 16-byte pieces a lane buffers in registers at a time
+        uint4 qv[GMAX];
         while (cur.valid) {
             if (!mbar_wait(full, phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
             phase ^= 1u;
@@ -409,32 +418,40 @@ scan_ring_kernel(const RingParams p)
             const bool have = (m.valid_mask >> blk) & 1u;
             const int ntok = have ? min(p.BS, m.seq - j * p.BS) : 0;
             if (m.b != cur_b) {
-                const uint4* q4 = reinterpret_cast<const uint4*>(p.q) + ((int64_t)m.b * p.Hq + head * p.G) * PW + part;
+                const uint4* q4 = reinterpret_cast<const uint4*>(p.q) + ((int64_t)m.b * p.Hq + head * G) * PW + part;
 #pragma unroll
-                for (int g = 0; g < kRingMaxG; ++g)
-                    if (g < p.G) qv[g] = __ldg(q4 + g * PW);
+                for (int g = 0; g < GMAX; ++g)
+                    if (g < G) qv[g] = __ldg(q4 + g * PW);
                 cur_b = m.b;
             }
             const uint4* sb = reinterpret_cast<const uint4*>(stage + blk * p.block_stride);
             int best = INT_MAX;
             const int rounds = (p.BS + TS - 1) / TS;  // same trip count in every lane (shuffles inside)
-            for (int r = 0; r < rounds; ++r) {
-                const int tok = r * TS + slot;
-                const bool ok = tok < ntok;
-                int d = 0;
-                if (ok) {
-                    const uint4 kv = sb[tok * P + hp];
+            for (int r0 = 0; r0 < rounds; r0 += kMinRounds) {
+                uint4 kb[kMinRounds];
 #pragma unroll
-                    for (int g = 0; g < kRingMaxG; ++g)
-                        if (g < p.G)
-                            d += __popc(kv.x ^ qv[g].x) + __popc(kv.y ^ qv[g].y) + __popc(kv.z ^ qv[g].z) +
-                                 __popc(kv.w ^ qv[g].w);
+                for (int i = 0; i < kMinRounds; ++i) {
+                    const int tok = (r0 + i) * TS + slot;
+                    kb[i] = make_uint4(0u, 0u, 0u, 0u);
+                    if (tok < ntok) kb[i] = sb[tok * P + hp];
                 }
-                for (int off = 1; off < PW; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
-                best = min(best, ok ? d : INT_MAX);
+                if (r0 + kMinRounds >= rounds) {
+                    __syncwarp();
+                    advance();  // the stage's last words are in registers: refill it before the math
+                }
+#pragma unroll
+                for (int i = 0; i < kMinRounds; ++i) {
+                    const int tok = (r0 + i) * TS + slot;
+                    int d = 0;
+#pragma unroll
+                    for (int g = 0; g < GMAX; ++g)
+                        if (g < G)
+                            d += __popc(kb[i].x ^ qv[g].x) + __popc(kb[i].y ^ qv[g].y) + __popc(kb[i].z ^ qv[g].z) +
+                                 __popc(kb[i].w ^ qv[g].w);
+                    for (int off = 1; off < PW; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+                    best = min(best, tok < ntok ? d : INT_MAX);
+                }
             }
-            __syncwarp();
-            advance();  // every lane has read its last word of the stage
             // lanes of the same block that differ in the token slot (>= P), or with reduce_kvhead in
             // the head bits as well, fold by min
             for (int off = p.reduce_kvhead ? PW : P; off < LG; off <<= 1)
@@ -500,7 +517,13 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
 
     void (*kernel)(const RingParams) = nullptr;
     if (is_min) {
-        kernel = scan_ring_kernel<true, 0, 0>;
+        switch (G) {
+            case 1: kernel = scan_ring_kernel<true, 0, 1>; break;
+            case 2: kernel = scan_ring_kernel<true, 0, 2>; break;
+            case 4: kernel = scan_ring_kernel<true, 0, 4>; break;
+            case 8: kernel = scan_ring_kernel<true, 0, 8>; break;
+            default: kernel = scan_ring_kernel<true, 0, 0>;
+        }
     } else {
 #define UCMR_RING_CASE(RWV, GV) \
     if (p.RW == RWV && G == GV) kernel = scan_ring_kernel<false, RWV, GV>;

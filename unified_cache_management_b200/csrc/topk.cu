@@ -54,10 +54,13 @@ struct SelScratch {
     int warp_a[kSelWarps], warp_b[kSelWarps];
     uint32_t prefix;
     int remaining;
+    uint32_t kmin, kmax;  // range of the ordinary keys
+    int n_zero, n_normal;  // forced keys, ordinary keys
 };
 
 // Finds the first kb entries of keys[0..n) under (key, position) and calls emit(pos, j) for each,
-// pos = rank of j among the chosen in ascending j.  Keys are below 2^key_bits; key_of(j) must be pure.
+// pos = rank of j among the chosen in ascending j.  Keys are below 2^key_bits.  key_of has two pure members:
+// raw(j) does the global loads of entry j, key(j, raw) turns them into the key.
 // s_keys caches the first n_cached keys.  All threads of the CTA must call this.
 //
 // Radix select from the most significant digit: ceil(key_bits / 11) histogram passes over 2048 bins
@@ -72,67 +75,121 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
     if (kb <= 0 || n <= 0) return;
     if (kb > n) kb = n;
 
-    for (int j = tid; j < n_cached; j += kSelThreads) s_keys[j] = key_of(j);
-    for (int i = tid; i < 3 * kBins; i += kSelThreads) (&sc.hist[0][0])[i] = 0;
-    if (tid == 0) { sc.prefix = 0u; sc.remaining = kb; }
-    __syncthreads();
-    auto get = [&](int j) -> uint32_t { return j < n_cached ? s_keys[j] : key_of(j); };
-
-    int hi = key_bits;  // bits [hi, key_bits) of the k-th key are known (= prefix >> hi)
-    for (int pass = 0; hi > 0; ++pass) {
-        const int width = min(kDigitBits, hi);
-        const int shift = hi - width;
-        const uint32_t dmask = (1u << width) - 1u;
-        const uint32_t prefix = sc.prefix;
-        int* hist = sc.hist[pass];
-        const int n_round = (n + kSelThreads - 1) / kSelThreads * kSelThreads;
-        for (int j = tid; j < n_round; j += kSelThreads) {
-            const bool in = j < n;
-            const uint32_t key = in ? get(j) : 0u;
-            const bool hit = in && (hi >= 32 || (key >> hi) == (prefix >> hi));
-            const uint32_t digit = (key >> shift) & dmask;
-            // block scores cluster, so whole warps often agree on the digit: one atomic for the warp then
-            int same;
-            __match_all_sync(0xffffffffu, hit ? digit : 0xFFFFFFFFu, &same);
-            if (same) {
-                if (hit && lane == 0) atomicAdd(&hist[digit], 32);
-            } else if (hit) {
-                atomicAdd(&hist[digit], 1);
-            }
-        }
-        __syncthreads();
-        // exclusive scan over the bins, kBinsPerThread consecutive bins per thread
-        int loc[kBinsPerThread];
-        int sum = 0;
+    // keys into shared memory; the global loads of several entries are in flight together
+    constexpr int kU = 8;
+    for (int j0 = tid; j0 < n_cached; j0 += kSelThreads * kU) {
+        decltype(key_of.raw(0)) raw[kU];
 #pragma unroll
-        for (int i = 0; i < kBinsPerThread; ++i) { loc[i] = hist[tid * kBinsPerThread + i]; sum += loc[i]; }
-        int incl = sum;
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-            const int o = __shfl_up_sync(0xffffffffu, incl, off);
-            if (lane >= off) incl += o;
+        for (int u = 0; u < kU; ++u) {
+            const int j = j0 + u * kSelThreads;
+            if (j < n_cached) raw[u] = key_of.raw(j);
         }
-        if (lane == 31) sc.warp_a[warp] = incl;
-        const int rem = sc.remaining;
-        __syncthreads();
-        int excl = incl - sum;
-        for (int w = 0; w < warp; ++w) excl += sc.warp_a[w];
-        if (rem > excl && rem <= excl + sum) {  // exactly one thread
-            int run = excl;
 #pragma unroll
-            for (int i = 0; i < kBinsPerThread; ++i) {
-                if (rem > run && rem <= run + loc[i]) {
-                    sc.prefix = prefix | ((uint32_t)(tid * kBinsPerThread + i) << shift);
-                    sc.remaining = rem - run;
-                }
-                run += loc[i];
-            }
+        for (int u = 0; u < kU; ++u) {
+            const int j = j0 + u * kSelThreads;
+            if (j < n_cached) s_keys[j] = key_of.key(j, raw[u]);
         }
-        hi = shift;
-        __syncthreads();
     }
-    const uint32_t T = sc.prefix;
-    const int need = sc.remaining;  // how many keys equal to T are taken, lowest positions first
+    for (int i = tid; i < 3 * kBins; i += kSelThreads) (&sc.hist[0][0])[i] = 0;
+    if (tid == 0) { sc.kmin = 0xFFFFFFFFu; sc.kmax = 0u; sc.n_zero = 0; sc.n_normal = 0; }
+    __syncthreads();
+    auto get = [&](int j) -> uint32_t { return j < n_cached ? s_keys[j] : key_of.key(j, key_of.raw(j)); };
+    const uint32_t key_top = key_bits >= 32 ? 0xFFFFFFFFu : (1u << key_bits) - 1u;  // "past the end" marker
+
+    // Range of the ordinary keys (neither 0 = forced nor key_top).  Block scores cluster in a narrow band,
+    // so radix digits are taken from (key - kmin): the histogram spreads over the band instead of piling
+    // onto a few bins of the top digit, and one pass usually pins the k-th key.
+    {
+        uint32_t lo = 0xFFFFFFFFu, hi = 0u;
+        int zeros = 0, normals = 0;
+        for (int j = tid; j < n; j += kSelThreads) {
+            const uint32_t key = get(j);
+            if (key == 0u) ++zeros;
+            else if (key != key_top) { ++normals; lo = min(lo, key); hi = max(hi, key); }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, off));
+            hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+            zeros += __shfl_xor_sync(0xffffffffu, zeros, off);
+            normals += __shfl_xor_sync(0xffffffffu, normals, off);
+        }
+        if (lane == 0) {
+            atomicMin(&sc.kmin, lo);
+            atomicMax(&sc.kmax, hi);
+            atomicAdd(&sc.n_zero, zeros);
+            atomicAdd(&sc.n_normal, normals);
+        }
+    }
+    __syncthreads();
+    const int n_zero = sc.n_zero, n_normal = sc.n_normal;
+    const uint32_t kmin = sc.kmin;
+    uint32_t T;
+    int need;
+    if (kb <= n_zero) {
+        T = 0u; need = kb;
+    } else if (kb > n_zero + n_normal) {
+        T = key_top; need = kb - n_zero - n_normal;
+    } else {
+        const uint32_t range = sc.kmax - kmin;
+        int hi = 32 - __clz(range | 1u);  // bits of (key - kmin) still undecided
+        if (tid == 0) { sc.prefix = 0u; sc.remaining = kb - n_zero; }
+        __syncthreads();
+        for (int pass = 0; hi > 0; ++pass) {
+            const int width = min(kDigitBits, hi);
+            const int shift = hi - width;
+            const uint32_t dmask = (1u << width) - 1u;
+            const uint32_t prefix = sc.prefix;
+            int* hist = sc.hist[pass];
+            const int n_round = (n + kSelThreads - 1) / kSelThreads * kSelThreads;
+            for (int j = tid; j < n_round; j += kSelThreads) {
+                const uint32_t key = j < n ? get(j) : 0u;
+                const uint32_t rel = key - kmin;
+                const bool hit = key != 0u && key != key_top && (hi >= 32 || (rel >> hi) == (prefix >> hi));
+                const uint32_t digit = (rel >> shift) & dmask;
+                int same;
+                __match_all_sync(0xffffffffu, hit ? digit : 0xFFFFFFFFu, &same);
+                if (same) {
+                    if (hit && lane == 0) atomicAdd(&hist[digit], 32);
+                } else if (hit) {
+                    atomicAdd(&hist[digit], 1);
+                }
+            }
+            __syncthreads();
+            // exclusive scan over the bins, kBinsPerThread consecutive bins per thread
+            int loc[kBinsPerThread];
+            int sum = 0;
+#pragma unroll
+            for (int i = 0; i < kBinsPerThread; ++i) { loc[i] = hist[tid * kBinsPerThread + i]; sum += loc[i]; }
+            int incl = sum;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, incl, off);
+                if (lane >= off) incl += o;
+            }
+            if (lane == 31) sc.warp_a[warp] = incl;
+            const int rem = sc.remaining;
+            __syncthreads();
+            int excl = incl - sum;
+            for (int w = 0; w < warp; ++w) excl += sc.warp_a[w];
+            if (rem > excl && rem <= excl + sum) {  // exactly one thread
+                int run = excl;
+#pragma unroll
+                for (int i = 0; i < kBinsPerThread; ++i) {
+                    if (rem > run && rem <= run + loc[i]) {
+                        sc.prefix = prefix | ((uint32_t)(tid * kBinsPerThread + i) << shift);
+                        sc.remaining = rem - run;
+                    }
+                    run += loc[i];
+                }
+            }
+            hi = shift;
+            __syncthreads();
+        }
+        T = kmin + sc.prefix;
+        need = sc.remaining;  // how many keys equal to T are taken, lowest positions first
+    }
+
 
     const int ipt = (n + kSelThreads - 1) / kSelThreads;
     const int j_begin = min(n, tid * ipt), j_end = min(n, j_begin + ipt);
@@ -153,16 +210,28 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
     __syncthreads();
     int lt_before = lt_incl - lt, eq_before = eq_incl - eq;
     for (int w = 0; w < warp; ++w) { lt_before += sc.warp_a[w]; eq_before += sc.warp_b[w]; }
+    // The chosen entries are first listed in shared memory (the histograms are free by now) and then emitted
+    // one per thread, so that the global loads and stores of an emit are not chained inside one thread's walk.
+    int* const sel = &sc.hist[0][0];
+    const bool listed = kb <= 3 * kBins;
     for (int j = j_begin; j < j_end; ++j) {
         const uint32_t key = get(j);
+        int pos = -1;
         if (key < T) {
-            emit(lt_before + min(eq_before, need), j);
+            pos = lt_before + min(eq_before, need);
             ++lt_before;
         } else if (key == T) {
-            if (eq_before < need) emit(lt_before + eq_before, j);
+            if (eq_before < need) pos = lt_before + eq_before;
             ++eq_before;
         }
+        if (pos >= 0) {
+            if (listed) sel[pos] = j;
+            else emit(pos, j);
+        }
     }
+    __syncthreads();
+    if (listed)
+        for (int pos = tid; pos < kb; pos += kSelThreads) emit(pos, sel[pos]);
     __syncthreads();
 }
 
@@ -237,13 +306,20 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     __syncthreads();  // padding stores precede the emits of the same CTA
 
     const uint32_t key_invalid = p.key_bits >= 32 ? kKeyInvalid : (1u << p.key_bits) - 1u;
-    auto key_of = [&](int j) -> uint32_t {
-        if (j >= nb_l) return key_invalid;
-        const int s = srow[j];
-        if (s < 0) return key_invalid;
-        if (block_is_forced(p.forced, j + p.id_offset, nb_g, seq_g, p.BS)) return 0u;
-        return (uint32_t)s + 1u;
+    struct KeyOf {
+        const SelectParams& p;
+        const int32_t* srow;
+        int nb_l, nb_g, seq_g;
+        uint32_t key_invalid;
+        __device__ int raw(int j) const { return j < nb_l ? srow[j] : -1; }
+        __device__ uint32_t key(int j, int s) const
+        {
+            if (j >= nb_l || s < 0) return key_invalid;
+            if (block_is_forced(p.forced, j + p.id_offset, nb_g, seq_g, p.BS)) return 0u;
+            return (uint32_t)s + 1u;
+        }
     };
+    const KeyOf key_of{p, srow, nb_l, nb_g, seq_g, key_invalid};
     auto emit = [&](int pos, int j) {
         const bool valid = j < nb_l && srow[j] >= 0;
         if (CANDIDATES) {
@@ -293,12 +369,28 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
         const int r = i / p.kl, c = i - r * p.kl;
         return (int64_t)r * p.rank_stride + (int64_t)row * p.kl + c;
     };
-    auto key_of = [&](int i) -> uint32_t {
-        const int64_t a = at(i);
-        if (p.cand_ids[a] < 0) return kKeyInvalid;
-        const uint32_t key = f32_order_key(p.cand_scores[a]);
-        return key == kKeyInvalid ? kKeyInvalid - 1u : key;
+    struct Rec { int32_t id; float score; };
+    struct KeyOf {
+        const MergeParams& p;
+        int row;
+        __device__ int64_t at(int i) const
+        {
+            const int r = i / p.kl, c = i - r * p.kl;
+            return (int64_t)r * p.rank_stride + (int64_t)row * p.kl + c;
+        }
+        __device__ Rec raw(int i) const
+        {
+            const int64_t a = at(i);
+            return Rec{p.cand_ids[a], p.cand_scores[a]};
+        }
+        __device__ uint32_t key(int, Rec r) const
+        {
+            if (r.id < 0) return kKeyInvalid;
+            const uint32_t k = f32_order_key(r.score);
+            return k == kKeyInvalid ? kKeyInvalid - 1u : k;
+        }
     };
+    const KeyOf key_of{p, row};
     auto emit = [&](int pos, int i) {
         const int64_t a = at(i);
         if (p.cand_ids[a] >= 0) {
@@ -330,7 +422,8 @@ static int fill_forced(ForcedSpec& f, const int32_t* must, int n_must, int sink,
 template <typename K>
 static int set_dyn_smem(K kernel, size_t bytes)
 {
-    if (bytes > 48 * 1024) {
+    // static + dynamic shared memory above 48 KiB needs the opt-in; the kernels hold ~25 KiB statically
+    if (bytes > 16 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
         if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
     }
