@@ -60,7 +60,8 @@ struct SelScratch {
 
 // Finds the first kb entries of keys[0..n) under (key, position) and calls emit(pos, j) for each,
 // pos = rank of j among the chosen in ascending j.  Keys are below 2^key_bits.  key_of has two pure members:
-// raw(j) does the global loads of entry j, key(j, raw) turns them into the key.
+// raw(j) does the global loads of entry j, key(j, raw) turns them into the key; key_fast may skip rules that
+// fixup(s_keys, n_cached) (called by all threads, between two barriers) applies to the cached keys afterwards.
 // s_keys caches the first n_cached keys.  All threads of the CTA must call this.
 //
 // Radix select from the most significant digit: ceil(key_bits / 11) histogram passes over 2048 bins
@@ -75,7 +76,10 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
     if (kb <= 0 || n <= 0) return;
     if (kb > n) kb = n;
 
-    // keys into shared memory; the global loads of several entries are in flight together
+    for (int i = tid; i < 3 * kBins; i += kSelThreads) (&sc.hist[0][0])[i] = 0;
+    if (tid == 0) { sc.kmin = 0xFFFFFFFFu; sc.kmax = 0u; sc.n_zero = 0; sc.n_normal = 0; }
+    // keys into shared memory; the global loads of several entries are in flight together.  key_fast leaves
+    // out the forced-block rule, which fixup() then applies to the few entries it concerns.
     constexpr int kU = 8;
     for (int j0 = tid; j0 < n_cached; j0 += kSelThreads * kU) {
         decltype(key_of.raw(0)) raw[kU];
@@ -87,11 +91,11 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
             const int j = j0 + u * kSelThreads;
-            if (j < n_cached) s_keys[j] = key_of.key(j, raw[u]);
+            if (j < n_cached) s_keys[j] = key_of.key_fast(j, raw[u]);
         }
     }
-    for (int i = tid; i < 3 * kBins; i += kSelThreads) (&sc.hist[0][0])[i] = 0;
-    if (tid == 0) { sc.kmin = 0xFFFFFFFFu; sc.kmax = 0u; sc.n_zero = 0; sc.n_normal = 0; }
+    __syncthreads();
+    key_of.fixup(s_keys, n_cached);
     __syncthreads();
     auto get = [&](int j) -> uint32_t { return j < n_cached ? s_keys[j] : key_of.key(j, key_of.raw(j)); };
     const uint32_t key_top = key_bits >= 32 ? 0xFFFFFFFFu : (1u << key_bits) - 1u;  // "past the end" marker
@@ -312,11 +316,31 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         int nb_l, nb_g, seq_g;
         uint32_t key_invalid;
         __device__ int raw(int j) const { return j < nb_l ? srow[j] : -1; }
+        __device__ uint32_t key_fast(int j, int s) const { return (j >= nb_l || s < 0) ? key_invalid : (uint32_t)s + 1u; }
         __device__ uint32_t key(int j, int s) const
         {
             if (j >= nb_l || s < 0) return key_invalid;
             if (block_is_forced(p.forced, j + p.id_offset, nb_g, seq_g, p.BS)) return 0u;
             return (uint32_t)s + 1u;
+        }
+        // Forced blocks are few: the listed ones, the first blocks (sink) and the last ones (recent window).
+        __device__ void fixup(uint32_t* s_keys, int n_cached) const
+        {
+            const ForcedSpec& f = p.forced;
+            const int n_sink = f.sink > 0 ? min(nb_g, (f.sink + p.BS - 1) / p.BS) : 0;
+            const int first_recent = f.recent > 0 ? max(0, (seq_g - f.recent) / p.BS) : nb_g;
+            const int n_recent = max(0, nb_g - first_recent);
+            const int total = f.n_must + n_sink + n_recent;
+            for (int i = threadIdx.x; i < total; i += blockDim.x) {
+                int jg;  // global block index
+                if (i < f.n_must) jg = f.must[i] >= 0 ? f.must[i] : nb_g + f.must[i];
+                else if (i < f.n_must + n_sink) jg = i - f.n_must;
+                else jg = first_recent + (i - f.n_must - n_sink);
+                const int j = jg - p.id_offset;
+                if (jg >= 0 && jg < nb_g && j >= 0 && j < nb_l && j < n_cached && s_keys[j] != key_invalid &&
+                    block_is_forced(f, jg, nb_g, seq_g, p.BS))
+                    s_keys[j] = 0u;
+            }
         }
     };
     const KeyOf key_of{p, srow, nb_l, nb_g, seq_g, key_invalid};
@@ -389,6 +413,8 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
             const uint32_t k = f32_order_key(r.score);
             return k == kKeyInvalid ? kKeyInvalid - 1u : k;
         }
+        __device__ uint32_t key_fast(int i, Rec r) const { return key(i, r); }
+        __device__ void fixup(uint32_t*, int) const {}
     };
     const KeyOf key_of{p, row};
     auto emit = [&](int pos, int i) {
