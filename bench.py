@@ -235,6 +235,63 @@ def time_cpu(cfg, host, budget_s=12.0, max_steps=5):
 
 
 # ----------------------------------------------------------------------------------------------
+# small single-kernel cases for profiler captures (inputs above L2 size, a few hundred MB on the device)
+# ----------------------------------------------------------------------------------------------
+def run_profile_case(what: str) -> None:
+    """Three launches of one kernel on a small case: `ncu -k regex:<kernel> -s 1 -c 1 python bench.py --ncu-case X`."""
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+
+    def rnd_codes(shape):
+        return torch.randint(-2**31, 2**31 - 1, shape, dtype=torch.int32, device=dev, generator=g)
+
+    if what in ("scan", "scan_min", "select", "scan_256bit"):
+        if what == "scan_256bit":
+            B, Hkv, Hq, W, BS, seq, k = 2, 8, 32, 8, 64, 262144, 256     # million-token shard shape
+        else:
+            B, Hkv, Hq, W, BS, seq, k = 8, 8, 32, 4, 128, 131072, 16     # half of the benchmark batch: 134 MB
+        mb = seq // BS
+        codes = rnd_codes((B * mb, BS, Hkv, W))
+        q = rnd_codes((B, Hq, W))
+        bt = torch.randperm(B * mb, device=dev, generator=g).to(torch.int32).view(B, mb)
+        sl = torch.full((B,), seq, dtype=torch.int32, device=dev)
+        ws = ops.new_workspace(B, Hkv, mb, dev)
+        for _ in range(3):
+            ops.hamming_topk(codes, q, bt, sl, k, reduce="min" if what == "scan_min" else "sum",
+                             must_select=MUST_SELECT, workspace=ws)
+    elif what == "encode":
+        x = torch.randn((65536, 8, 128), device=dev, dtype=torch.bfloat16)          # 134 MB of keys
+        r = (torch.randn((128, 128), device=dev) / 128 ** 0.5).to(torch.bfloat16)
+        out = torch.empty((65536, 8, 4), dtype=torch.int32, device=dev)
+        for _ in range(3):
+            ops.hash_encode(x, r, out=out)
+    elif what == "encode_step":
+        xq = torch.randn((16, 32, 128), device=dev, dtype=torch.bfloat16)
+        xk = torch.randn((16, 8, 128), device=dev, dtype=torch.bfloat16)
+        r = (torch.randn((128, 128), device=dev) / 128 ** 0.5).to(torch.bfloat16)
+        cache = torch.zeros((64, 128, 8, 4), dtype=torch.int32, device=dev)
+        slots = torch.arange(16, device=dev, dtype=torch.int64) * 128
+        for _ in range(3):
+            ops.hash_encode_decode_step(xq, xk, slots, cache, r)
+    elif what == "gather":
+        nbp = 2000                                                                   # 2 x 524 MB pools
+        kp = torch.randn((nbp, 128, 8, 128), device=dev, dtype=torch.bfloat16)
+        vp = torch.randn((nbp, 128, 8, 128), device=dev, dtype=torch.bfloat16)
+        sel = torch.randperm(nbp, device=dev, generator=g)[:16 * 32].to(torch.int32).view(16, 32)
+        ok = torch.empty((16, 32 * 128, 8, 128), device=dev, dtype=torch.bfloat16)
+        ov = torch.empty_like(ok)
+        for _ in range(3):
+            ops.gather_kv(kp, vp, sel, ok, ov)
+    else:
+        raise SystemExit(f"unknown --ncu-case {what}")
+    torch.cuda.synchronize()
+    print("ok", what)
+
+
+# ----------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -243,7 +300,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama3_8b_decode16", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ncu-case", default=None,
+                    help="run a small single-kernel case for a profiler capture and exit "
+                         "(scan, scan_min, scan_256bit, select, encode, encode_step, gather)")
     args = ap.parse_args()
+
+    if args.ncu_case:
+        run_profile_case(args.ncu_case)
+        return
 
     import torch
     import torch.distributed as dist
