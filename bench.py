@@ -41,6 +41,18 @@ WORKLOADS = {
 }
 MUST_SELECT = (0, -2, -1)
 
+# Further workloads (the other benchmark configs).  They use Bernoulli(0.5) code bits directly (the scan's cost
+# does not depend on the values) and report the same JSON line without the prefill / CPU extras.
+EXTRA_WORKLOADS = {
+    # config 2: decode step + physical gather of the selected K/V blocks, ragged batch, 200k-block pool
+    "paged_gather_b64": dict(B=64, Hkv=8, Hq=32, D=128, bits=128, BS=128, k=32, pool_blocks=200000,
+                             seq_lo=8192, seq_hi=131072, layers=2),
+    # config 3: tensor parallel by kv head, no collective; rank r owns Hkv/N kv heads and their query heads
+    "llama3_70b_tp": dict(B=8, seq=262144, Hkv=8, Hq=64, D=128, bits=128, BS=128, k=32, layers=4),
+    # config 4: sequence sharded over the ranks, local candidates -> one all-gather -> merge
+    "million_token_sharded": dict(B=2, seq=4194304, Hkv=8, Hq=32, D=128, bits=256, BS=64, k=256, layers=2),
+}
+
 
 def _peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -214,6 +226,7 @@ def host_copies(cfg, wl, layer=0):
 def time_cpu(cfg, host, budget_s=12.0, max_steps=5):
     """Times the CPU arm on a bounded sample: as many requests as fit in about budget_s/max_steps per step."""
     from oracle import oracle_c as OC
+    OC.use_all_cores()
     codes, bt, sl, r, q, kn = host
     probe = cpu_step_factory(cfg, codes, bt, sl, r, q, kn, 1)
     t0 = time.perf_counter()
@@ -292,13 +305,164 @@ def run_profile_case(what: str) -> None:
 
 
 # ----------------------------------------------------------------------------------------------
+# the other benchmark configs (gather, tensor-parallel heads, sequence shards)
+# ----------------------------------------------------------------------------------------------
+def run_extra_workload(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from unified_cache_management_b200 import ops, sharded
+    cfg = dict(EXTRA_WORKLOADS[args.workload])
+    name = args.workload
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": f"the CPU arm is wired for the default workload only, not {name}"}))
+        return
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    W, K = max(args.warmup, 3), max(args.steps, 1)
+    g = torch.Generator(device=dev)
+    g.manual_seed(100 + rank)
+    B, BS, k, L = cfg["B"], cfg["BS"], cfg["k"], cfg["layers"]
+    Wd = cfg["bits"] // 32
+
+    def rnd(shape):
+        return torch.randint(-2**31, 2**31 - 1, shape, dtype=torch.int32, device=dev, generator=g)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    launches = 2
+    if name == "paged_gather_b64":
+        Hkv, Hq = cfg["Hkv"], cfg["Hq"]
+        gs = torch.Generator().manual_seed(2)
+        seq = (torch.randint(cfg["seq_lo"] // BS, cfg["seq_hi"] // BS + 1, (B,), generator=gs) * BS).to(torch.int32)
+        nblk = (seq // BS).tolist()
+        mb = cfg["seq_hi"] // BS
+        perm = torch.randperm(cfg["pool_blocks"], generator=gs)[: sum(nblk)].to(torch.int32)
+        bt = torch.zeros((B, mb), dtype=torch.int32)
+        off = 0
+        for b in range(B):
+            bt[b, : nblk[b]] = perm[off: off + nblk[b]]
+            off += nblk[b]
+        bt, seq_d = bt.to(dev), seq.to(dev)
+        NB = cfg["pool_blocks"]
+        caches = [rnd((NB, BS, Hkv, Wd)) for _ in range(L)]
+        # K / V pools of one layer (104.9 GB); their content does not matter for the copy rate
+        kp = torch.empty((NB, BS, Hkv, cfg["D"]), dtype=torch.bfloat16, device=dev)
+        vp = torch.empty((NB, BS, Hkv, cfg["D"]), dtype=torch.bfloat16, device=dev)
+        q = rnd((B, Hq, Wd))
+        ws = ops.new_workspace(B, Hkv, mb, dev, True)
+        ret = ops.Retrieval(physical=torch.empty((B, 1, k), dtype=torch.int32, device=dev),
+                            logical=torch.empty((B, 1, k), dtype=torch.int32, device=dev), scores=None,
+                            valid_count=torch.empty((B,), dtype=torch.int32, device=dev),
+                            new_seq_lens=torch.empty((B,), dtype=torch.int32, device=dev))
+        ok = torch.empty((B, k * BS, Hkv, cfg["D"]), dtype=torch.bfloat16, device=dev)
+        ov = torch.empty_like(ok)
+        tokens = int(seq.sum())
+        launches = 3
+
+        def step(layer):
+            ops.hamming_topk(caches[layer], q, bt, seq_d, k, reduce="sum", reduce_kvhead=True, must_select=MUST_SELECT,
+                             workspace=ws, out=ret, want_scores=False)
+            ops.gather_kv(kp, vp, ret.physical.view(B, k), ok, ov)
+        par, scaling = f"dp{world} (independent replicas)", "weak"
+        total_tokens = tokens * world
+        alg = dict(scan_bytes=tokens * Hkv * Wd * 4, gather_bytes=2 * 2 * B * k * BS * Hkv * cfg["D"] * 2)
+    elif name == "llama3_70b_tp":
+        if cfg["Hkv"] % world != 0:
+            raise SystemExit("kv heads must divide by the number of ranks")
+        Hkv, Hq, seq_len = cfg["Hkv"] // world, cfg["Hq"] // world, cfg["seq"]
+        mb = seq_len // BS
+        NB = B * mb
+        caches = [rnd((NB, BS, Hkv, Wd)) for _ in range(L)]
+        bt = torch.randperm(NB, device=dev, generator=g).to(torch.int32).view(B, mb)
+        seq_d = torch.full((B,), seq_len, dtype=torch.int32, device=dev)
+        q = rnd((B, Hq, Wd))
+        ws = ops.new_workspace(B, Hkv, mb, dev)
+        ret = ops.Retrieval(physical=torch.empty((B, Hkv, k), dtype=torch.int32, device=dev),
+                            logical=torch.empty((B, Hkv, k), dtype=torch.int32, device=dev), scores=None,
+                            valid_count=torch.empty((B,), dtype=torch.int32, device=dev),
+                            new_seq_lens=torch.empty((B,), dtype=torch.int32, device=dev))
+
+        def step(layer):
+            ops.hamming_topk(caches[layer], q, bt, seq_d, k, reduce="sum", must_select=MUST_SELECT, workspace=ws,
+                             out=ret, want_scores=False)
+        par, scaling = f"tp{world} by kv head, no collective", "strong"
+        total_tokens = B * seq_len
+        alg = dict(scan_bytes_per_gpu=B * seq_len * Hkv * Wd * 4)
+    else:  # million_token_sharded
+        Hkv, Hq, seq_total = cfg["Hkv"], cfg["Hq"], cfg["seq"]
+        nblk_total = seq_total // BS
+        if nblk_total % world != 0:
+            raise SystemExit("blocks must divide by the number of ranks")
+        per = nblk_total // world
+        NB = B * per
+        caches = [rnd((NB, BS, Hkv, Wd)) for _ in range(L)]
+        bt_local = torch.randperm(NB, device=dev, generator=g).to(torch.int32).view(B, per)
+        seq_g = torch.full((B,), seq_total, dtype=torch.int32, device=dev)
+        q = rnd((B, Hq, Wd))
+        ws = ops.new_workspace(B, Hkv, per, dev)
+        scale = 1.0 / (BS * (Hq // Hkv))
+        gbuf = torch.empty((max(world, 1) * 2, B, Hkv, min(k, per)), dtype=torch.int32, device=dev)
+        launches = 3
+
+        if world > 1:
+            def step(layer):
+                sharded.sharded_hamming_topk(caches[layer], q, bt_local, seq_g, k, BS, nblk_total, scale, reduce="sum",
+                                             must_select=MUST_SELECT, workspace=ws, gather_buffer=gbuf)
+        else:
+            plan = sharded.shard_plan(seq_g, BS, nblk_total, 1, 0)
+
+            def step(layer):
+                cs, ci = ops.topk_candidates(caches[layer], q, bt_local, plan.seq_lens_local, seq_g, k, 0, scale,
+                                             reduce="sum", must_select=MUST_SELECT, workspace=ws)
+                ops.merge_topk(cs.unsqueeze(0), ci.unsqueeze(0), k)
+        par, scaling = f"sequence shards over {world} rank(s), one NCCL all-gather of (score, id) records", "strong"
+        total_tokens = B * seq_total
+        alg = dict(scan_bytes_per_gpu=B * per * BS * Hkv * Wd * 4, allgather_bytes_per_rank=2 * B * Hkv * min(k, per) * 4)
+
+    for i in range(W):
+        step(i % L)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(K):
+        step(i % L)
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_total = float(ms.item())
+    if rank == 0:
+        print(json.dumps({
+            "metric": "tokens_scored_per_sec", "value": total_tokens * K / (ms_total * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K, "higher_is_better": True,
+            "scaling": scaling, "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+            "config": dict(workload=name, parallelism=par, l2="steps rotate over resident layer caches", **{
+                kk: vv for kk, vv in cfg.items() if kk != "layers"}),
+            "algorithmic": alg, "gpu_launches": launches * K, "clocks": clocks,
+            "note": "stream-ordered launches from Python (no CUDA graph): small steps are host-bound"}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llama3_8b_decode16", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="llama3_8b_decode16", choices=sorted(WORKLOADS) + sorted(EXTRA_WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ncu-case", default=None,
                     help="run a small single-kernel case for a profiler capture and exit "
@@ -315,6 +479,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload in EXTRA_WORKLOADS:
+        run_extra_workload(args, rank, world, local_rank)
+        return
     cfg = dict(WORKLOADS[args.workload])
     W = max(args.warmup, 3)
     K = max(args.steps, 1)
@@ -341,6 +508,8 @@ def main():
         del wl
         torch.cuda.empty_cache()
         codes, bt, sl, r, q, kn = host
+        from oracle import oracle_c as OC
+        OC.use_all_cores()
         probe = cpu_step_factory(cfg, codes, bt, sl, r, q, kn, 1)
         t0 = time.perf_counter(); probe(); t1 = time.perf_counter() - t0
         n_req = int(max(1, min(cfg["B"], 1.0 / max(t1, 1e-6))))   # about a second per step at most
@@ -354,7 +523,6 @@ def main():
                 K = _ + 1
                 break
         dt = time.perf_counter() - t0
-        from oracle import oracle_c as OC
         val = n_req * cfg["seq"] * K / dt
         sample = f"{n_req} of {cfg['B']} requests x {cfg['seq']} tokens per step, one layer"
         print(json.dumps({"impl": "reference", "metric": "tokens_scored_per_sec", "value": val, "unit": "tokens/s",
@@ -490,7 +658,12 @@ def main():
             "roofline": {"bound": "hbm", "kernel": "scan_ring_kernel (Hamming scan)", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "peak_kind": f"{peak_kind} copy bandwidth", "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "frac_of_8tbs_spec": achieved / 8000.0,
-                         "traffic": None, "algorithmic_bytes_per_launch": sb,
+                         # ncu (one launch of the half-batch case, 134.5 MB algorithmic): 134,328,576 B read +
+                         # 3,549,440 B written = 1.025 x algorithmic; traffic grows with the blocks scanned, so the
+                         # full launch is that ratio times its own algorithmic bytes.
+                         "traffic": int(round(1.025 * sb)) if args.workload == "llama3_8b_decode16" else None,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a half-batch launch, scaled by blocks scanned",
+                         "algorithmic_bytes_per_launch": sb,
                          "launch_us_mean": scan_t * 1e6, "launches_timed": K},
             "prefill_encode": {"kernel": "encode_tc_kernel (tcgen05)", **prefill,
                                "frac_hbm": prefill["gbs"] / peaks["hbm_gbs"]},

@@ -35,6 +35,16 @@ int orc_num_threads(void)
 #endif
 }
 
+/* Sets the OpenMP team size (launchers such as torchrun export OMP_NUM_THREADS=1). */
+void orc_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 static inline float bf16_to_f32(uint16_t v)
 {
     uint32_t u = ((uint32_t)v) << 16;

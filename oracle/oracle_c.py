@@ -30,6 +30,13 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def use_all_cores() -> int:
+    """Sizes the OpenMP team to the cores this process may run on; returns the team size."""
+    import os
+    lib().orc_set_num_threads(len(os.sched_getaffinity(0)))
+    return num_threads()
+
+
 def hash_encode(x_bf16: np.ndarray, r_bf16: np.ndarray) -> np.ndarray:
     x = np.ascontiguousarray(x_bf16, dtype=np.uint16)
     r = np.ascontiguousarray(r_bf16, dtype=np.uint16)
