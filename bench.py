@@ -187,6 +187,53 @@ def make_step(cfg, wl, dev):
     return step, ws, q_codes, out
 
 
+def time_reference_gpu(cfg, wl, dev, iters=30):
+    """Times the reference project's own CUDA path for the same shape, compiled unmodified for this GPU (the
+    prebuilt module under oracle/_ref/hamming_cuda, if present): HammingScoreContiCUDA, then the torch tail
+    min -> topk -> sort -> gather of its cuda_hamming_topk.  Scan and selection only, no encode.  The codes are
+    handed over permuted into that kernel's [Hkv][BS][W] block indexing.  Returns None when the module is absent."""
+    import torch
+    from oracle import build_oracle
+    mod = build_oracle.load_ref_cuda()
+    if mod is None:
+        return None
+    B, Hkv, Hq, BS, k, L = cfg["B"], cfg["Hkv"], cfg["Hq"], cfg["BS"], cfg["k"], cfg["layers"]
+    W, mb = wl["W"], wl["mb"]
+    refs = [c.permute(0, 2, 1, 3).contiguous().view(c.shape) for c in wl["caches"]]
+    q = torch.randint(-2**31, 2**31 - 1, (B, 1, Hq, W), dtype=torch.int32, device=dev)
+
+    def run(layer):
+        out = mod.hamming_score(refs[layer], q, wl["bt"], wl["seq_lens"], mb * BS, BS, 2 * BS, True)
+        blk = torch.min(out.view(out.shape[0], out.shape[-1] // BS, BS), dim=-1)[0]
+        ind = torch.topk(blk, k=k, dim=-1, largest=False)[1]
+        ind = torch.sort(ind, dim=-1, descending=False)[0]
+        return torch.gather(wl["bt"], dim=-1, index=ind)
+
+    for i in range(5):
+        run(i % L)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        run(i % L)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    # the kernel alone
+    e0.record()
+    for i in range(iters):
+        mod.hamming_score(refs[i % L], q, wl["bt"], wl["seq_lens"], mb * BS, BS, 2 * BS, True)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_k = e0.elapsed_time(e1) / iters
+    del refs
+    return {"what": "reference HammingScoreContiKernel (unmodified, compiled for sm_100) + torch min/topk/sort/gather, "
+                    "same shape, block-min selection over all kv heads, no encode",
+            "ms_per_step": ms, "value": B * cfg["seq"] / (ms * 1e-3), "unit": "tokens/s",
+            "scan_kernel_ms": ms_k, "scan_kernel_gbs": B * cfg["seq"] * Hkv * W * 4 / (ms_k * 1e-3) / 1e9,
+            "iters": iters}
+
+
 def scan_bytes(cfg, wl):
     """Algorithmic bytes of one scan launch: codes + query codes + block table + block scores out."""
     B, seq, Hkv, Hq = cfg["B"], cfg["seq"], cfg["Hkv"], cfg["Hq"]
@@ -672,6 +719,9 @@ def main():
             "gpu_launches": 3 * K, "device_status_word": status, "clocks": clocks,
         }
         if not args.no_cpu_baseline:
+            ref_gpu = time_reference_gpu(cfg, wl, dev)
+            if ref_gpu is not None:
+                line["reference_gpu_kernel"] = ref_gpu
             base, _, _ = time_cpu(cfg, host_copies(cfg, wl))
             line["cpu_baseline"] = base
         print(json.dumps(line))

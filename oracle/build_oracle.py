@@ -8,7 +8,13 @@
   source is copied.  It is skipped when the checkout is not present (the
   prebuilt module, if any, is used as is).
 
-Run ``python oracle/build_oracle.py`` to build both.
+* ``build_ref_cuda()`` compiles the reference project's CUDA Hamming-score
+  extension (``.../csrc/cuda/ham_dist/paged_ham_dist_mla.cu`` + ``cpy/hamming.cpp``,
+  unmodified, for sm_100) with ``torch.utils.cpp_extension`` into
+  ``oracle/_ref/hamming_cuda/``: the GPU-side checker and the "reference kernel
+  recompiled for B200" timing leg.  About two minutes of nvcc.
+
+Run ``python oracle/build_oracle.py`` to build the CPU pair; add ``--cuda-ref`` for the third.
 """
 from __future__ import annotations
 
@@ -65,6 +71,52 @@ def build_ref(reference_root: str | None = None, force: bool = False) -> str | N
     return out
 
 
+REF_CUDA_DIR_REL = "ucm/sparse/gsa_on_device/csrc/cuda/ham_dist"
+REF_CUDA_BUILD = os.path.join(REF_DIR, "hamming_cuda")
+REF_CUDA_NAME = "ucm_ref_hamming"
+
+
+# torch's extension builder defines these; the reference's own CMake build does not, and its kernel
+# relies on the implicit __half conversions and operators.
+_UNDEF_HALF = ["-U__CUDA_NO_HALF_OPERATORS__", "-U__CUDA_NO_HALF_CONVERSIONS__", "-U__CUDA_NO_HALF2_OPERATORS__"]
+
+
+def ref_cuda_module_path() -> str:
+    return os.path.join(REF_CUDA_BUILD, REF_CUDA_NAME + ".so")
+
+
+def build_ref_cuda(reference_root: str | None = None, force: bool = False) -> str | None:
+    """Returns the module path, or None when neither source nor prebuilt module exists."""
+    reference_root = reference_root or os.environ.get("UCM_REFERENCE_ROOT", "/root/reference")
+    src_dir = os.path.join(reference_root, REF_CUDA_DIR_REL)
+    sources = [os.path.join(src_dir, "paged_ham_dist_mla.cu"), os.path.join(src_dir, "cpy", "hamming.cpp")]
+    out = ref_cuda_module_path()
+    if not all(os.path.exists(s) for s in sources):
+        return out if os.path.exists(out) else None
+    if not force and _newer(out, *sources):
+        return out
+    os.makedirs(REF_CUDA_BUILD, exist_ok=True)
+    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0")
+    from torch.utils import cpp_extension
+    cpp_extension.load(name=REF_CUDA_NAME, sources=sources, extra_include_paths=[src_dir],
+                       extra_cflags=["-O3"], extra_cuda_cflags=["-O3", "--use_fast_math"] + _UNDEF_HALF,
+                       build_directory=REF_CUDA_BUILD, is_python_module=True, verbose=False)
+    return out if os.path.exists(out) else None
+
+
+def load_ref_cuda():
+    """Import the compiled reference CUDA extension (needs torch), or return None if it was never built."""
+    path = ref_cuda_module_path()
+    if not os.path.exists(path):
+        return None
+    import importlib.util
+    import torch  # noqa: F401  (the extension links against libtorch)
+    spec = importlib.util.spec_from_file_location(REF_CUDA_NAME, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def load_ref():
     """Import the compiled reference backend, or return None if it was never built."""
     path = ref_module_path()
@@ -80,3 +132,5 @@ def load_ref():
 if __name__ == "__main__":
     print(build_oracle_c(force="--force" in sys.argv))
     print(build_ref(force="--force" in sys.argv))
+    if "--cuda-ref" in sys.argv:
+        print(build_ref_cuda(force="--force" in sys.argv))
