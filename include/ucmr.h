@@ -85,7 +85,10 @@ int ucmr_hash_encode_and_cache(const void* x, int64_t T, int H, int64_t stride_t
 
 /*     The two encodes of one decode step in a single launch: the step's queries (as
  *     ucmr_hash_encode_query, hash_code at gsa_on_device.py:396-412) and its new key rows (as
- *     ucmr_hash_encode_and_cache, cache_k_hash_gqa_cuda at gsa_on_device.py:564-573).              */
+ *     ucmr_hash_encode_and_cache, cache_k_hash_gqa_cuda at gsa_on_device.py:564-573).
+ *     q and k (a few hundred KB per step) may also point to page-locked host memory that the
+ *     device can address: the kernel then fetches them across the bus itself, which saves the
+ *     caller a separate host-to-device copy per step.                                              */
 int ucmr_hash_encode_decode_step(const void* q, int64_t Tq, int Hq, int64_t q_stride_t,
                                  int64_t q_stride_h, int group_mean, uint32_t* q_codes_out,
                                  const void* k, int64_t Tk, int Hk, int64_t k_stride_t,
@@ -126,6 +129,8 @@ int ucmr_workspace_status(const void* workspace, int* host_status, void* stream)
  *     Outputs (device; any of out_logical / out_scores / out_valid_count / out_new_seq_lens may
  *     be NULL): out_physical, out_logical, out_scores int32 [B, Hout, k]; out_valid_count,
  *     out_new_seq_lens int32 [B].  out_scores holds the raw block score (-1 for padding).
+ *     out_physical may be page-locked host memory (the ids are then on the host when the stream
+ *     has drained, without a separate device-to-host copy).
  * ------------------------------------------------------------------------------------------ */
 int ucmr_hamming_topk(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
                       const uint32_t* q_codes, int Hq, const int32_t* block_table, int max_blocks,

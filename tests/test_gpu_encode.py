@@ -179,3 +179,34 @@ def test_decode_step_fused_encode(cuda_device, G):
     untouched = np.ones(NB * BS, dtype=bool)
     untouched[slots] = False
     assert np.array_equal(got[untouched], cache0.reshape(NB * BS, Hkv, 4)[untouched])
+
+
+def test_decode_step_reads_pinned_host_inputs_and_writes_pinned_result(cuda_device):
+    """q / new keys in page-locked host memory and the id output in page-locked host memory give the same
+    codes, cache rows and selection as device-resident operands."""
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    g = torch.Generator(device=dev).manual_seed(5)
+    B, Hq, Hkv, D, BS, mb, k = 6, 32, 8, 128, 128, 12, 4
+    R = (torch.randn((D, 128), device=dev, generator=g) / D ** 0.5).to(torch.bfloat16)
+    q = torch.randn((B, Hq, D), device=dev, generator=g).to(torch.bfloat16)
+    kn = torch.randn((B, Hkv, D), device=dev, generator=g).to(torch.bfloat16)
+    NB = B * mb
+    cache_a = torch.randint(-2**31, 2**31 - 1, (NB, BS, Hkv, 4), dtype=torch.int32, device=dev, generator=g)
+    cache_b = cache_a.clone()
+    bt = torch.randperm(NB, device=dev, generator=g).to(torch.int32).view(B, mb)
+    seq = torch.full((B,), mb * BS, dtype=torch.int32, device=dev)
+    slots = bt[:, -1].to(torch.int64) * BS + BS - 1
+    qa = ops.hash_encode_decode_step(q, kn, slots, cache_a, R)
+    qb = ops.hash_encode_decode_step(q.cpu().pin_memory(), kn.cpu().pin_memory(), slots, cache_b, R)
+    assert qb.is_cuda and torch.equal(qa, qb) and torch.equal(cache_a, cache_b)
+    ra = ops.hamming_topk(cache_a, qa, bt, seq, k, must_select=(0, -1))
+    host_ids = torch.empty((B, Hkv, k), dtype=torch.int32).pin_memory()
+    rb = ops.Retrieval(physical=host_ids, logical=torch.empty_like(ra.logical), scores=None,
+                       valid_count=torch.empty_like(ra.valid_count), new_seq_lens=torch.empty_like(ra.new_seq_lens))
+    ops.hamming_topk(cache_b, qb, bt, seq, k, must_select=(0, -1), out=rb, want_scores=False)
+    torch.cuda.synchronize()
+    assert torch.equal(ra.physical.cpu(), host_ids) and torch.equal(ra.logical, rb.logical)
+    with pytest.raises(ValueError):
+        ops.hash_encode_decode_step(q.cpu(), kn, slots, cache_b, R)   # pageable host memory is refused

@@ -76,8 +76,9 @@ __device__ __forceinline__ void csa(uint32_t& h, uint32_t& l, uint32_t a, uint32
     l = u ^ c;
 }
 
-constexpr int kPlanes = 8;     // vertical counters of one chunk: counts up to 128
-constexpr int kChunkTokens = 128;  // tokens a lane buffers in registers per chunk
+// A lane buffers CH tokens of its column in registers per chunk: 128, or 64 for blocks of at most 64 tokens
+// (half the carry-save work per chunk).  The vertical counters of a chunk then need log2(CH) + 1 planes.
+__host__ __device__ constexpr int planes_of(int ch) { return ch == 128 ? 8 : 7; }
 
 // Folds 16 words into planes 0..3 (carry-save) and returns the carry of weight 16.
 __device__ __forceinline__ uint32_t fold16(uint32_t& ones, uint32_t& twos, uint32_t& fours, uint32_t& eights,
@@ -117,15 +118,16 @@ __device__ __forceinline__ void add_planes(const uint32_t (&a)[NP], const uint32
     out[NP] = carry;
 }
 
-// Counts, for every bit position, how many of the 128 buffered words have the bit set: eight
-// bit-sliced planes (plane p holds bit p of the 32 counters).  Four independent carry-save chains of
-// 32 words each (instruction-level parallelism: a single chain is one long dependency), then two
-// levels of bit-sliced adds.
-__device__ __forceinline__ void fold128(const uint32_t (&x)[kChunkTokens], uint32_t (&pl)[kPlanes])
+// Counts, for every bit position, how many of the CH buffered words have the bit set: bit-sliced
+// planes (plane p holds bit p of the 32 counters).  Independent carry-save chains of 32 words each
+// (instruction-level parallelism: a single chain is one long dependency), then bit-sliced adds.
+template <int CH>
+__device__ __forceinline__ void fold_chunk(const uint32_t (&x)[CH], uint32_t (&pl)[planes_of(CH)])
 {
-    uint32_t q6[4][6];
+    static_assert(CH == 128 || CH == 64, "chunk size");
+    uint32_t q6[CH / 32][6];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < CH / 32; ++c) {
         uint32_t p0 = 0, p1 = 0, p2 = 0, p3 = 0;
         const uint32_t c0 = fold16(p0, p1, p2, p3, &x[c * 32]);
         const uint32_t c1 = fold16(p0, p1, p2, p3, &x[c * 32 + 16]);
@@ -133,20 +135,25 @@ __device__ __forceinline__ void fold128(const uint32_t (&x)[kChunkTokens], uint3
         q6[c][4] = c0 ^ c1;
         q6[c][5] = c0 & c1;
     }
-    uint32_t h7a[7], h7b[7];
-    add_planes<6>(q6[0], q6[1], h7a);
-    add_planes<6>(q6[2], q6[3], h7b);
-    add_planes<7>(h7a, h7b, pl);
+    if constexpr (CH == 128) {
+        uint32_t h7a[7], h7b[7];
+        add_planes<6>(q6[0], q6[1], h7a);
+        add_planes<6>(q6[2], q6[3], h7b);
+        add_planes<7>(h7a, h7b, pl);
+    } else {
+        add_planes<6>(q6[0], q6[1], pl);
+    }
 }
 
 // sum_g sum_tokens popc(word ^ q[g]) of one buffered chunk of n tokens (unused slots hold 0).
-template <int G_T>
-__device__ __forceinline__ int chunk_score(const uint32_t (&x)[kChunkTokens], int n, int g_rt, const uint32_t* qw)
+template <int G_T, int CH>
+__device__ __forceinline__ int chunk_score(const uint32_t (&x)[CH], int n, int g_rt, const uint32_t* qw)
 {
     const int G = G_T > 0 ? G_T : g_rt;
     constexpr int GMAX = G_T > 0 ? G_T : kRingMaxG;
+    constexpr int kPlanes = planes_of(CH);
     uint32_t pl[kPlanes];
-    fold128(x, pl);
+    fold_chunk<CH>(x, pl);
     int qpop = 0;
 #pragma unroll
     for (int g = 0; g < GMAX; ++g)
@@ -163,37 +170,38 @@ __device__ __forceinline__ int chunk_score(const uint32_t (&x)[kChunkTokens], in
     return acc;
 }
 
-// Copies tokens [t0, t0+128) of the lane's 32-bit column (row stride RW words) from the stage into
+// Copies tokens [t0, t0+CH) of the lane's 32-bit column (row stride RW words) from the stage into
 // registers; slots at or past ntok read as 0.  `rot` > 0 (several blocks per stage, one per lane
 // group): block k starts its walk k tokens later, wrapping inside [0, bs), because the blocks sit on
 // 128-byte boundaries and the same token of every block would otherwise hit the same banks.
-template <int RW_T>
-__device__ __forceinline__ void load_chunk(uint32_t (&x)[kChunkTokens], const uint32_t* colp, int t0, int ntok, int rw_rt,
+template <int RW_T, int CH>
+__device__ __forceinline__ void load_chunk(uint32_t (&x)[CH], const uint32_t* colp, int t0, int ntok, int rw_rt,
                                            int rot, int bs)
 {
     const int RW = RW_T > 0 ? RW_T : rw_rt;
     constexpr bool kMaybeNarrow = (RW_T == 0 || RW_T < 32);
     if (kMaybeNarrow && RW < 32) {
 #pragma unroll
-        for (int i = 0; i < kChunkTokens; ++i) {
+        for (int i = 0; i < CH; ++i) {
             int tt = t0 + i + rot;
             if (tt >= bs) tt -= bs;
             x[i] = (t0 + i < bs && tt < ntok) ? colp[tt * RW] : 0u;
         }
-    } else if (t0 + kChunkTokens <= ntok) {
+    } else if (t0 + CH <= ntok) {
         const uint32_t* cp = colp + (size_t)t0 * RW;
 #pragma unroll
-        for (int i = 0; i < kChunkTokens; ++i) x[i] = cp[i * RW];
+        for (int i = 0; i < CH; ++i) x[i] = cp[i * RW];
     } else {
         const uint32_t* cp = colp + (size_t)t0 * RW;
 #pragma unroll
-        for (int i = 0; i < kChunkTokens; ++i) x[i] = (t0 + i < ntok) ? cp[i * RW] : 0u;
+        for (int i = 0; i < CH; ++i) x[i] = (t0 + i < ntok) ? cp[i * RW] : 0u;
     }
 }
 
 // MIN selects the per-token-minimum path; RW_T (sum mode only) and G_T are compile-time copies of the row
-// width and group size for the common shapes, 0 = read them from the parameters.
-template <bool MIN, int RW_T, int G_T>
+// width and group size for the common shapes, 0 = read them from the parameters; CH is the sum mode's
+// chunk size.
+template <bool MIN, int RW_T, int G_T, int CH>
 __global__ void __launch_bounds__(kRingThreads, 1)
 scan_ring_kernel(const RingParams p)
 {
@@ -341,7 +349,10 @@ scan_ring_kernel(const RingParams p)
         const int blk = (RW < 32) ? lane / RW : 0;
         const int col0 = (RW < 32) ? lane % RW : lane;
         const int rot = (RW < 32) ? blk % max(p.BS, 1) : 0;  // see load_chunk
-        uint32_t qw[GMAX];
+        // query words of the lane's column(s): kept across items of one request; rows of 64 words keep both
+        // passes' sets, wider rows reload per pass
+        constexpr int QP = (RW_T == 64) ? 2 : 1;
+        uint32_t qw[QP][GMAX];
         while (cur.valid) {
             if (!mbar_wait(full, phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
             phase ^= 1u;
@@ -354,29 +365,30 @@ scan_ring_kernel(const RingParams p)
             // tokens are walked in 128-token chunks; with several blocks per stage every lane group walks
             // the whole block capacity (rotated), else only the valid tokens
             const int walk = (RW < 32) ? p.BS : ntok;
-            const int n_chunks = (__reduce_max_sync(0xffffffffu, walk) + kChunkTokens - 1) / kChunkTokens;
+            const int n_chunks = (__reduce_max_sync(0xffffffffu, walk) + CH - 1) / CH;
             bool reissued = false;
             for (int ps = 0; ps < passes; ++ps) {
                 const int col = col0 + ps * 32;
                 const int head = col / p.W, w = col - head * p.W;
-                if (m.b != cur_b || passes > 1) {
+                const int qs = (QP == 2) ? ps : 0;
+                if (m.b != cur_b || passes > QP) {
 #pragma unroll
                     for (int g = 0; g < GMAX; ++g)
-                        if (g < G) qw[g] = __ldg(p.q + ((int64_t)m.b * p.Hq + head * G + g) * p.W + w);
+                        if (g < G) qw[qs][g] = __ldg(p.q + ((int64_t)m.b * p.Hq + head * G + g) * p.W + w);
                 }
                 const uint32_t* colp = reinterpret_cast<const uint32_t*>(sb) + col;
                 int acc = 0;
                 for (int c = 0; c < n_chunks; ++c) {
-                    uint32_t x[kChunkTokens];
-                    load_chunk<RW_T>(x, colp, c * kChunkTokens, ntok, RW, rot, p.BS);
+                    uint32_t x[CH];
+                    load_chunk<RW_T, CH>(x, colp, c * CH, ntok, RW, rot, p.BS);
                     if (ps == passes - 1 && c == n_chunks - 1) {
                         // the stage's last words are in registers: refill it before doing the math
                         __syncwarp();
                         advance();
                         reissued = true;
                     }
-                    const int n_here = max(0, min(kChunkTokens, ntok - ((RW < 32) ? 0 : c * kChunkTokens)));
-                    acc += chunk_score<G_T>(x, (RW < 32) ? (c == 0 ? ntok : 0) : n_here, G, qw);
+                    const int n_here = max(0, min(CH, ntok - ((RW < 32) ? 0 : c * CH)));
+                    acc += chunk_score<G_T, CH>(x, (RW < 32) ? (c == 0 ? ntok : 0) : n_here, G, qw[qs]);
                 }
                 // fold the words of a head; with reduce_kvhead also the heads of this pass
                 const int span = p.reduce_kvhead ? cols : p.W;
@@ -518,20 +530,27 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     void (*kernel)(const RingParams) = nullptr;
     if (is_min) {
         switch (G) {
-            case 1: kernel = scan_ring_kernel<true, 0, 1>; break;
-            case 2: kernel = scan_ring_kernel<true, 0, 2>; break;
-            case 4: kernel = scan_ring_kernel<true, 0, 4>; break;
-            case 8: kernel = scan_ring_kernel<true, 0, 8>; break;
-            default: kernel = scan_ring_kernel<true, 0, 0>;
+            case 1: kernel = scan_ring_kernel<true, 0, 1, 128>; break;
+            case 2: kernel = scan_ring_kernel<true, 0, 2, 128>; break;
+            case 4: kernel = scan_ring_kernel<true, 0, 4, 128>; break;
+            case 8: kernel = scan_ring_kernel<true, 0, 8, 128>; break;
+            default: kernel = scan_ring_kernel<true, 0, 0, 128>;
         }
     } else {
-#define UCMR_RING_CASE(RWV, GV) \
-    if (p.RW == RWV && G == GV) kernel = scan_ring_kernel<false, RWV, GV>;
-#define UCMR_RING_ROW(RWV) UCMR_RING_CASE(RWV, 1) UCMR_RING_CASE(RWV, 2) UCMR_RING_CASE(RWV, 4) UCMR_RING_CASE(RWV, 8)
-        UCMR_RING_ROW(4) UCMR_RING_ROW(8) UCMR_RING_ROW(16) UCMR_RING_ROW(32) UCMR_RING_ROW(64)
+        const bool short_blocks = BS <= 64;  // half-size register chunks (wide rows only)
+#define UCMR_RING_CASE(RWV, GV, CHV) \
+    if (p.RW == RWV && G == GV) kernel = scan_ring_kernel<false, RWV, GV, CHV>;
+#define UCMR_RING_ROW(RWV, CHV) \
+    UCMR_RING_CASE(RWV, 1, CHV) UCMR_RING_CASE(RWV, 2, CHV) UCMR_RING_CASE(RWV, 4, CHV) UCMR_RING_CASE(RWV, 8, CHV)
+        if (short_blocks) {
+            UCMR_RING_ROW(32, 64) UCMR_RING_ROW(64, 64)
+        }
+        if (!kernel) {
+            UCMR_RING_ROW(4, 128) UCMR_RING_ROW(8, 128) UCMR_RING_ROW(16, 128) UCMR_RING_ROW(32, 128) UCMR_RING_ROW(64, 128)
+        }
 #undef UCMR_RING_ROW
 #undef UCMR_RING_CASE
-        if (!kernel) kernel = scan_ring_kernel<false, 0, 0>;
+        if (!kernel) kernel = scan_ring_kernel<false, 0, 0, 128>;
     }
     // idempotent attribute, set on every call: cheap, and correct on every device of a process
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);

@@ -47,6 +47,18 @@ def _need_cuda(name: str, t: torch.Tensor, dtype=None, contiguous=True) -> None:
         raise ValueError(f"{name} must be contiguous")
 
 
+def _need_cuda_or_pinned(name: str, t: torch.Tensor, dtype=None, contiguous=True) -> None:
+    """Small per-step operands may also live in page-locked host memory: under unified addressing the
+    kernels read (or write) it across the bus themselves, which saves a separate copy."""
+    if isinstance(t, torch.Tensor) and not t.is_cuda and t.is_pinned():
+        if dtype is not None and t.dtype not in (dtype if isinstance(dtype, tuple) else (dtype,)):
+            raise ValueError(f"{name} must have dtype {dtype}, got {t.dtype}")
+        if contiguous and not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+        return
+    _need_cuda(name, t, dtype, contiguous)
+
+
 def as_words(t: torch.Tensor) -> torch.Tensor:
     """Reinterpret a packed-code tensor (uint8 / bf16 / int32 ...) as int32 words, last dim = W."""
     if t.dtype == torch.int32:
@@ -139,8 +151,8 @@ def hash_encode_decode_step(q: torch.Tensor, k_new: torch.Tensor, slot_mapping: 
                             status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One launch for a decode step's two encodes: q [T,Hq,D] -> codes [T,Hq/group_mean,W] (returned) and
     k_new [T,Hkv,D] -> slot ``slot_mapping[t]`` of the paged cache."""
-    _need_cuda("q", q, torch.bfloat16, contiguous=False)
-    _need_cuda("k_new", k_new, torch.bfloat16, contiguous=False)
+    _need_cuda_or_pinned("q", q, torch.bfloat16, contiguous=False)
+    _need_cuda_or_pinned("k_new", k_new, torch.bfloat16, contiguous=False)
     if q.dim() != 3 or k_new.dim() != 3 or q.stride(2) != 1 or k_new.stride(2) != 1:
         raise ValueError("q and k_new must be [T, H, in_dim] with a unit inner stride")
     _need_cuda("slot_mapping", slot_mapping, (torch.int64, torch.int32))
@@ -156,12 +168,12 @@ def hash_encode_decode_step(q: torch.Tensor, k_new: torch.Tensor, slot_mapping: 
     if group_mean <= 0 or hq % group_mean != 0:
         raise ValueError("group_mean must divide the number of query heads")
     if q_codes_out is None:
-        q_codes_out = torch.empty((tq, hq // group_mean, bits // 32), dtype=torch.int32, device=q.device)
+        q_codes_out = torch.empty((tq, hq // group_mean, bits // 32), dtype=torch.int32, device=cache.device)
     lib = _l.load_library()
     _l.check(lib.ucmr_hash_encode_decode_step(
         _ptr(q), tq, hq, q.stride(0), q.stride(1), group_mean, _ptr(q_codes_out), _ptr(k_new), tk, hk, k_new.stride(0),
         k_new.stride(1), _ptr(slot_mapping), int(slot_mapping.dtype == torch.int64), _ptr(cw), cw.shape[0], cw.shape[1],
-        _ptr(r), in_dim, bits, _ptr(status), _stream(q)), "ucmr_hash_encode_decode_step")
+        _ptr(r), in_dim, bits, _ptr(status), _stream(cache)), "ucmr_hash_encode_decode_step")
     return q_codes_out
 
 
@@ -261,6 +273,7 @@ def hamming_topk(codes: torch.Tensor, q_codes: torch.Tensor, block_table: torch.
             new_seq_lens=torch.empty((b,), dtype=torch.int32, device=dev))
     if b == 0:
         return out
+    _need_cuda_or_pinned("out.physical", out.physical, torch.int32)  # may be written straight to pinned host memory
     must, n_must = _must_array(must_select)
     lib = _l.load_library()
     _l.check(lib.ucmr_hamming_topk(
