@@ -199,3 +199,42 @@ def test_large_row_select(cuda_device):
     ref = OC.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], 256, O.REDUCE_SUM, False,
                           must_select=(0, -2, -1))
     _cmp(out, ref)
+
+
+@pytest.mark.parametrize("mode", ["min", "sum"])
+@pytest.mark.parametrize("reduce_kvhead", [False, True])
+def test_few_long_rows_cluster_select(cuda_device, mode, reduce_kvhead):
+    """Few rows of thousands of blocks: the selection splits each row over a thread-block cluster.  Small codes
+    give many equal scores, so ties cross the slice boundaries; lengths are ragged and sink / recent windows set."""
+    B, Hkv, G, W, BS, mb = 2, 2, 1, 4, 16, 3000
+    seq = [mb * BS - 5, 1000 * BS + 3]
+    case = H.make_paged_case(77, B, Hkv, G, W, BS, mb, seq_lens=seq)
+    kw = dict(must_select=(0, 7, -3), sink_tokens=40, recent_tokens=100)
+    for k in (1, 100, 1500):
+        out = _run_dev(case, cuda_device, k, reduce=mode, reduce_kvhead=reduce_kvhead, **kw)
+        ref = OC.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], k, MODES[mode],
+                              reduce_kvhead, **kw)
+        _cmp(out, ref)
+
+
+def test_cluster_select_k_per_request_and_mask(cuda_device):
+    import torch
+    B, Hkv, G, W, BS, mb = 3, 1, 2, 4, 16, 2100
+    case = H.make_paged_case(78, B, Hkv, G, W, BS, mb, seq_lens=[mb * BS, 50 * BS, 1300 * BS + 1])
+    kpr = np.array([600, 64, 0], dtype=np.int32)
+    mask = np.array([1, 1, 0], dtype=np.uint8)
+    out = _run_dev(case, cuda_device, 600, reduce="sum", k_per_request=torch.from_numpy(kpr).to(cuda_device),
+                   request_mask=torch.from_numpy(mask).to(cuda_device))
+    ref = OC.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], 600, O.REDUCE_SUM, False,
+                          k_per_request=kpr, request_mask=mask)
+    _cmp(out, ref)
+
+
+def test_many_long_rows_uncached_keys(cuda_device):
+    """More rows than a cluster split is used for, each longer than the shared-memory key cache."""
+    B, Hkv, G, W, BS, mb = 84, 1, 1, 4, 2, 41500
+    case = H.make_paged_case(79, B, Hkv, G, W, BS, mb, identity=True)
+    out = _run_dev(case, cuda_device, 300, reduce="sum", must_select=(0, -1))
+    ref = OC.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], 300, O.REDUCE_SUM, False,
+                          must_select=(0, -1))
+    _cmp(out, ref)

@@ -71,3 +71,35 @@ def test_merge_with_short_shards(cuda_device):
     ws, wi = O.merge_topk(sc, ids, k)
     assert np.array_equal(mi.cpu().numpy(), wi)
     assert np.array_equal(ms.cpu().numpy().view(np.uint32), ws.view(np.uint32))
+
+
+def test_long_shards_cluster_candidates(cuda_device):
+    """Shards of 4500 blocks each: the candidate selection runs split over thread-block clusters."""
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    B, Hkv, G, W, BS, R, per, k = 2, 2, 2, 4, 16, 2, 4500, 256
+    nblk = R * per
+    seq = np.array([nblk * BS, nblk * BS - 700 * BS - 9], dtype=np.int32)
+    case = H.make_paged_case(91, B, Hkv, G, W, BS, nblk, seq_lens=seq)
+    must = (0, 1, -1)
+    scale = 1.0 / (BS * G)
+    codes, q = H.to_dev_i32(case["codes"], dev), H.to_dev_i32(case["q"], dev)
+    cs, ci = [], []
+    for r in range(R):
+        bt_local = np.ascontiguousarray(case["block_table"][:, r * per:(r + 1) * per])
+        seq_local = np.clip(seq - r * per * BS, 0, per * BS).astype(np.int32)
+        s, i = ops.topk_candidates(codes, q, H.to_dev_i32(bt_local, dev), H.to_dev_i32(seq_local, dev),
+                                   H.to_dev_i32(seq, dev), k, r * per, scale, reduce="sum", must_select=must)
+        forced = np.stack([O.forced_blocks(seq[b], BS, nblk, must)[r * per:(r + 1) * per] for b in range(B)])
+        ws, wi = O.topk_candidates(case["codes"], case["q"], bt_local, seq_local, k, r * per, scale, forced,
+                                   O.REDUCE_SUM, False)
+        torch.cuda.synchronize()
+        assert np.array_equal(i.cpu().numpy(), wi)
+        assert np.array_equal(s.cpu().numpy().view(np.uint32), ws.view(np.uint32))
+        cs.append(s)
+        ci.append(i)
+    ms, mi = ops.merge_topk(torch.stack(cs), torch.stack(ci), k)
+    torch.cuda.synchronize()
+    full = O.hamming_topk(case["codes"], case["q"], case["block_table"], seq, k, O.REDUCE_SUM, False, must_select=must)
+    assert np.array_equal(mi.cpu().numpy(), full["logical"])

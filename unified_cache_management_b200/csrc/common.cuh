@@ -44,6 +44,32 @@ inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t
     return UCMR_OK;
 }
 
+// Same, with `cluster_x` consecutive CTAs of the grid forming a thread-block cluster (grid.x % cluster_x == 0).
+template <typename... KArgs, typename... Args>
+inline int launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                 int cluster_x, Args... args)
+{
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster_x;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e != cudaSuccess) {
+        note_cuda_error(e);
+        (void)cudaGetLastError();
+        return UCMR_ERR_LAUNCH;
+    }
+    return UCMR_OK;
+}
+
 // Time bound of every spin-wait in this library.  A wait that runs out sets UCMR_DEV_WAIT_TIMEOUT in
 // the status word and the kernel winds down without touching the data.
 constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s

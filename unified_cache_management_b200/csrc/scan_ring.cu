@@ -176,11 +176,22 @@ __device__ __forceinline__ int chunk_score(const uint32_t (&x)[CH], int n, int g
 // 128-byte boundaries and the same token of every block would otherwise hit the same banks.
 template <int RW_T, int CH>
 __device__ __forceinline__ void load_chunk(uint32_t (&x)[CH], const uint32_t* colp, int t0, int ntok, int rw_rt,
-                                           int rot, int bs)
+                                           int rot, int bs, bool full_narrow)
 {
     const int RW = RW_T > 0 ? RW_T : rw_rt;
     constexpr bool kMaybeNarrow = (RW_T == 0 || RW_T < 32);
     if (kMaybeNarrow && RW < 32) {
+        if (full_narrow) {
+            // every block of the stage is full and exactly one chunk long: the rotated walk only wraps in
+            // its last kRingMaxBps slots (rot < kRingMaxBps), the rest are plain strided loads
+            const uint32_t* cp = colp + rot * RW;
+#pragma unroll
+            for (int i = 0; i < CH; ++i) {
+                if (i < CH - kRingMaxBps) x[i] = cp[i * RW];
+                else x[i] = (i + rot >= CH) ? cp[(i - CH) * RW] : cp[i * RW];
+            }
+            return;
+        }
 #pragma unroll
         for (int i = 0; i < CH; ++i) {
             int tt = t0 + i + rot;
@@ -367,6 +378,7 @@ scan_ring_kernel(const RingParams p)
             const int walk = (RW < 32) ? p.BS : ntok;
             const int n_chunks = (__reduce_max_sync(0xffffffffu, walk) + CH - 1) / CH;
             bool reissued = false;
+            const bool full_narrow = RW < 32 && p.BS == CH && __all_sync(0xffffffffu, ntok == CH);
             for (int ps = 0; ps < passes; ++ps) {
                 const int col = col0 + ps * 32;
                 const int head = col / p.W, w = col - head * p.W;
@@ -380,7 +392,7 @@ scan_ring_kernel(const RingParams p)
                 int acc = 0;
                 for (int c = 0; c < n_chunks; ++c) {
                     uint32_t x[CH];
-                    load_chunk<RW_T, CH>(x, colp, c * CH, ntok, RW, rot, p.BS);
+                    load_chunk<RW_T, CH>(x, colp, c * CH, ntok, RW, rot, p.BS, full_narrow);
                     if (ps == passes - 1 && c == n_chunks - 1) {
                         // the stage's last words are in registers: refill it before doing the math
                         __syncwarp();

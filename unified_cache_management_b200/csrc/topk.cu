@@ -12,6 +12,9 @@
 // (score, id) total order the reference leaves unspecified.
 #include <limits.h>
 #include <math.h>
+#include <stdlib.h>
+
+#include <cooperative_groups.h>
 
 #include "common.cuh"
 
@@ -25,6 +28,10 @@ constexpr int kSelThreads = 512;
 constexpr int kSelWarps = kSelThreads / 32;
 constexpr int kSelMaxCachedKeys = 40 * 1024;  // 160 KiB of keys in shared memory at most
 constexpr uint32_t kKeyInvalid = 0xFFFFFFFFu;
+// Rows longer than this are split over a thread-block cluster (2, 4 or 8 CTAs) when there are few enough rows.
+// Measured: a cluster launch costs about 2 us more than a plain one and large grids of clusters schedule
+// slowly, so shorter rows and launches of many rows stay with one CTA per row.
+constexpr int kSelClusterSlice = 2048;
 
 struct ForcedSpec {
     int must[UCMR_MAX_MUST_SELECT];
@@ -56,48 +63,79 @@ struct SelScratch {
     int remaining;
     uint32_t kmin, kmax;  // range of the ordinary keys
     int n_zero, n_normal;  // forced keys, ordinary keys
+    int cta_lt, cta_eq;    // this CTA's slice: keys below / equal to the threshold
+    // cluster-wide values, gathered by warp 0 from the other CTAs' scratch
+    int g_zero, g_normal;
+    uint32_t g_kmin, g_kmax;
+    int base_lt, base_eq;
 };
 
 // Finds the first kb entries of keys[0..n) under (key, position) and calls emit(pos, j) for each,
 // pos = rank of j among the chosen in ascending j.  Keys are below 2^key_bits.  key_of has two pure members:
 // raw(j) does the global loads of entry j, key(j, raw) turns them into the key; key_fast may skip rules that
-// fixup(s_keys, n_cached) (called by all threads, between two barriers) applies to the cached keys afterwards.
-// s_keys caches the first n_cached keys.  All threads of the CTA must call this.
+// fixup(s_keys, j_lo, n_cached) (called by all threads, between two barriers) applies to the cached keys
+// afterwards.  All threads of the CTA must call this.
 //
 // Radix select from the most significant digit: ceil(key_bits / 11) histogram passes over 2048 bins
 // each (a block score needs 17-20 bits, so two passes), every pass narrowing the candidates to the bin
 // that holds the kb-th smallest key.  Then one ordered pass emits every j with key < T and the first
 // `need` j with key == T: that is "first kb under (key, id)", already in ascending id order.
-template <typename KeyFn, typename EmitFn>
+//
+// CL = true: the CTAs of a thread-block cluster share one row.  CTA r works on the r-th slice of the row
+// (its keys cached in its own shared memory).  Key range and emit offsets are combined by warp 0 reading the
+// other CTAs' scratch through distributed shared memory after a cluster barrier (lane r reads CTA r: one
+// remote latency); histograms are summed in CTA 0's shared memory with remote atomics on the non-empty bins,
+// and every CTA derives the same threshold from that sum, so no result has to be broadcast.  A few very long
+// rows (sequence shards) would otherwise leave most SMs idle during the selection.
+// s_keys caches the first n_cached keys of the CTA's slice.
+template <bool CL, typename KeyFn, typename EmitFn>
 __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emit, uint32_t* s_keys, int n_cached,
                            SelScratch& sc)
 {
+    namespace cg = cooperative_groups;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (kb <= 0 || n <= 0) return;
+    if (kb <= 0 || n <= 0) return;  // (the same for every CTA of a cluster)
     if (kb > n) kb = n;
+    int crank = 0, csize = 1;
+    if constexpr (CL) {
+        crank = (int)cg::this_cluster().block_rank();
+        csize = (int)cg::this_cluster().num_blocks();
+    }
+    auto cluster_sync = [&]() {
+        if constexpr (CL) cg::this_cluster().sync();
+    };
+    auto remote = [&](int r) -> SelScratch* {
+        if constexpr (CL) return cg::this_cluster().map_shared_rank(&sc, r);
+        return &sc;
+    };
+    // slice of this CTA
+    const int slice = CL ? ((n + csize - 1) / csize + 3) / 4 * 4 : n;
+    const int j_lo = min(n, crank * slice), j_hi = min(n, j_lo + slice);
+    const int len = j_hi - j_lo;
+    n_cached = min(n_cached, len);
 
     for (int i = tid; i < 3 * kBins; i += kSelThreads) (&sc.hist[0][0])[i] = 0;
     if (tid == 0) { sc.kmin = 0xFFFFFFFFu; sc.kmax = 0u; sc.n_zero = 0; sc.n_normal = 0; }
     // keys into shared memory; the global loads of several entries are in flight together.  key_fast leaves
     // out the forced-block rule, which fixup() then applies to the few entries it concerns.
     constexpr int kU = 8;
-    for (int j0 = tid; j0 < n_cached; j0 += kSelThreads * kU) {
+    for (int i0 = tid; i0 < n_cached; i0 += kSelThreads * kU) {
         decltype(key_of.raw(0)) raw[kU];
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
-            const int j = j0 + u * kSelThreads;
-            if (j < n_cached) raw[u] = key_of.raw(j);
+            const int i = i0 + u * kSelThreads;
+            if (i < n_cached) raw[u] = key_of.raw(j_lo + i);
         }
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
-            const int j = j0 + u * kSelThreads;
-            if (j < n_cached) s_keys[j] = key_of.key_fast(j, raw[u]);
+            const int i = i0 + u * kSelThreads;
+            if (i < n_cached) s_keys[i] = key_of.key_fast(j_lo + i, raw[u]);
         }
     }
     __syncthreads();
-    key_of.fixup(s_keys, n_cached);
+    key_of.fixup(s_keys, j_lo, n_cached);
     __syncthreads();
-    auto get = [&](int j) -> uint32_t { return j < n_cached ? s_keys[j] : key_of.key(j, key_of.raw(j)); };
+    auto get = [&](int j) -> uint32_t { return j - j_lo < n_cached ? s_keys[j - j_lo] : key_of.key(j, key_of.raw(j)); };
     const uint32_t key_top = key_bits >= 32 ? 0xFFFFFFFFu : (1u << key_bits) - 1u;  // "past the end" marker
 
     // Range of the ordinary keys (neither 0 = forced nor key_top).  Block scores cluster in a narrow band,
@@ -106,7 +144,7 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
     {
         uint32_t lo = 0xFFFFFFFFu, hi = 0u;
         int zeros = 0, normals = 0;
-        for (int j = tid; j < n; j += kSelThreads) {
+        for (int j = j_lo + tid; j < j_hi; j += kSelThreads) {
             const uint32_t key = get(j);
             if (key == 0u) ++zeros;
             else if (key != key_top) { ++normals; lo = min(lo, key); hi = max(hi, key); }
@@ -126,8 +164,29 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
         }
     }
     __syncthreads();
-    const int n_zero = sc.n_zero, n_normal = sc.n_normal;
-    const uint32_t kmin = sc.kmin;
+    int n_zero = sc.n_zero, n_normal = sc.n_normal;
+    uint32_t kmin = sc.kmin, kmax = sc.kmax;
+    if constexpr (CL) {
+        cluster_sync();
+        if (warp == 0) {
+            int z = 0, nn = 0;
+            uint32_t lo = 0xFFFFFFFFu, hi = 0u;
+            if (lane < csize) {
+                const SelScratch* o = remote(lane);
+                z = o->n_zero; nn = o->n_normal; lo = o->kmin; hi = o->kmax;
+            }
+#pragma unroll
+            for (int off = 4; off > 0; off >>= 1) {  // clusters have at most 8 CTAs
+                z += __shfl_xor_sync(0xffffffffu, z, off);
+                nn += __shfl_xor_sync(0xffffffffu, nn, off);
+                lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, off));
+                hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+            }
+            if (lane == 0) { sc.g_zero = z; sc.g_normal = nn; sc.g_kmin = lo; sc.g_kmax = hi; }
+        }
+        __syncthreads();
+        n_zero = sc.g_zero; n_normal = sc.g_normal; kmin = sc.g_kmin; kmax = sc.g_kmax;
+    }
     uint32_t T;
     int need;
     if (kb <= n_zero) {
@@ -135,7 +194,7 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
     } else if (kb > n_zero + n_normal) {
         T = key_top; need = kb - n_zero - n_normal;
     } else {
-        const uint32_t range = sc.kmax - kmin;
+        const uint32_t range = kmax - kmin;
         int hi = 32 - __clz(range | 1u);  // bits of (key - kmin) still undecided
         if (tid == 0) { sc.prefix = 0u; sc.remaining = kb - n_zero; }
         __syncthreads();
@@ -145,9 +204,9 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
             const uint32_t dmask = (1u << width) - 1u;
             const uint32_t prefix = sc.prefix;
             int* hist = sc.hist[pass];
-            const int n_round = (n + kSelThreads - 1) / kSelThreads * kSelThreads;
-            for (int j = tid; j < n_round; j += kSelThreads) {
-                const uint32_t key = j < n ? get(j) : 0u;
+            const int len_round = (len + kSelThreads - 1) / kSelThreads * kSelThreads;
+            for (int i = tid; i < len_round; i += kSelThreads) {
+                const uint32_t key = i < len ? get(j_lo + i) : 0u;
                 const uint32_t rel = key - kmin;
                 const bool hit = key != 0u && key != key_top && (hi >= 32 || (rel >> hi) == (prefix >> hi));
                 const uint32_t digit = (rel >> shift) & dmask;
@@ -160,11 +219,27 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
                 }
             }
             __syncthreads();
-            // exclusive scan over the bins, kBinsPerThread consecutive bins per thread
+            // exclusive scan over the (cluster-wide) bins, kBinsPerThread consecutive bins per thread
             int loc[kBinsPerThread];
             int sum = 0;
+            if constexpr (CL) {
+                int* const h0 = remote(0)->hist[pass];
+                if (crank != 0) {
 #pragma unroll
-            for (int i = 0; i < kBinsPerThread; ++i) { loc[i] = hist[tid * kBinsPerThread + i]; sum += loc[i]; }
+                    for (int i = 0; i < kBinsPerThread; ++i) {
+                        const int v = hist[tid * kBinsPerThread + i];
+                        if (v != 0) atomicAdd(&h0[tid * kBinsPerThread + i], v);
+                    }
+                }
+                cluster_sync();
+#pragma unroll
+                for (int i = 0; i < kBinsPerThread; ++i) loc[i] = h0[tid * kBinsPerThread + i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < kBinsPerThread; ++i) loc[i] = hist[tid * kBinsPerThread + i];
+            }
+#pragma unroll
+            for (int i = 0; i < kBinsPerThread; ++i) sum += loc[i];
             int incl = sum;
 #pragma unroll
             for (int off = 1; off < 32; off <<= 1) {
@@ -194,9 +269,8 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
         need = sc.remaining;  // how many keys equal to T are taken, lowest positions first
     }
 
-
-    const int ipt = (n + kSelThreads - 1) / kSelThreads;
-    const int j_begin = min(n, tid * ipt), j_end = min(n, j_begin + ipt);
+    const int ipt = (len + kSelThreads - 1) / kSelThreads;
+    const int j_begin = min(j_hi, j_lo + tid * ipt), j_end = min(j_hi, j_begin + ipt);
     int lt = 0, eq = 0;
     for (int j = j_begin; j < j_end; ++j) {
         const uint32_t key = get(j);
@@ -213,11 +287,41 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
     if (lane == 31) { sc.warp_a[warp] = lt_incl; sc.warp_b[warp] = eq_incl; }
     __syncthreads();
     int lt_before = lt_incl - lt, eq_before = eq_incl - eq;
-    for (int w = 0; w < warp; ++w) { lt_before += sc.warp_a[w]; eq_before += sc.warp_b[w]; }
+    int cta_lt = 0, cta_eq = 0;
+    for (int w = 0; w < kSelWarps; ++w) {
+        if (w < warp) { lt_before += sc.warp_a[w]; eq_before += sc.warp_b[w]; }
+        cta_lt += sc.warp_a[w]; cta_eq += sc.warp_b[w];
+    }
+    // entries of the row that precede this CTA's slice
+    int base_lt = 0, base_eq = 0;
+    if constexpr (CL) {
+        if (tid == 0) { sc.cta_lt = cta_lt; sc.cta_eq = cta_eq; }
+        __syncthreads();
+        cluster_sync();  // also: every CTA is done reading CTA 0's histograms
+        if (warp == 0) {
+            int a = 0, b = 0;
+            if (lane < crank) {
+                const SelScratch* o = remote(lane);
+                a = o->cta_lt; b = o->cta_eq;
+            }
+#pragma unroll
+            for (int off = 4; off > 0; off >>= 1) {
+                a += __shfl_xor_sync(0xffffffffu, a, off);
+                b += __shfl_xor_sync(0xffffffffu, b, off);
+            }
+            if (lane == 0) { sc.base_lt = a; sc.base_eq = b; }
+        }
+        __syncthreads();
+        base_lt = sc.base_lt; base_eq = sc.base_eq;
+        cg::this_cluster().barrier_arrive();  // last remote access of this CTA is done; waited for at the end
+    }
+    lt_before += base_lt; eq_before += base_eq;
     // The chosen entries are first listed in shared memory (the histograms are free by now) and then emitted
     // one per thread, so that the global loads and stores of an emit are not chained inside one thread's walk.
     int* const sel = &sc.hist[0][0];
-    const bool listed = kb <= 3 * kBins;
+    const int pos_base = base_lt + min(base_eq, need);                           // first position this CTA emits
+    const int n_mine = cta_lt + max(0, min(cta_eq, need - base_eq));             // how many it emits
+    const bool listed = n_mine <= 3 * kBins;
     for (int j = j_begin; j < j_end; ++j) {
         const uint32_t key = get(j);
         int pos = -1;
@@ -229,14 +333,15 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
             ++eq_before;
         }
         if (pos >= 0) {
-            if (listed) sel[pos] = j;
+            if (listed) sel[pos - pos_base] = j;
             else emit(pos, j);
         }
     }
     __syncthreads();
     if (listed)
-        for (int pos = tid; pos < kb; pos += kSelThreads) emit(pos, sel[pos]);
+        for (int i = tid; i < n_mine; i += kSelThreads) emit(pos_base + i, sel[i]);
     __syncthreads();
+    if constexpr (CL) cg::this_cluster().barrier_wait();  // no CTA leaves while another may still read its scratch
 }
 
 struct SelectParams {
@@ -260,16 +365,19 @@ struct SelectParams {
     int32_t* cand_ids;
     float scale;
     int32_t* sched;  // the scan's work counter, cleared here for the next launch
+    int cluster;     // CTAs per row (thread-block cluster size), 1 = one CTA per row
 };
 
-template <bool CANDIDATES>
+// CL: p.cluster consecutive CTAs (one thread-block cluster) share a row.
+template <bool CANDIDATES, bool CL>
 __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams p)
 {
     extern __shared__ uint32_t s_keys[];
     __shared__ SelScratch sc;
     const int tid = threadIdx.x;
-    const int row = blockIdx.x;
-    if (row == 0 && tid == 0 && p.sched != nullptr) *p.sched = 0;
+    const int row = CL ? blockIdx.x / p.cluster : blockIdx.x;
+    const bool lead = !CL || blockIdx.x % p.cluster == 0;  // the CTA that writes the row's padding and scalars
+    if (blockIdx.x == 0 && tid == 0 && p.sched != nullptr) *p.sched = 0;
     const int b = row / p.Hout;
     const int n = p.max_blocks;
     const int seq_l = p.seq_local[b];
@@ -283,8 +391,8 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     const bool masked = p.mask != nullptr && p.mask[b] == 0;
     const int64_t obase = (int64_t)row * p.k;
 
-    // padding first; the chosen entries overwrite positions [0, kb)
-    for (int i = tid; i < p.k; i += kSelThreads) {
+    // padding first; the chosen entries overwrite positions [0, kb) (in a cluster: after its first barrier)
+    for (int i = tid; lead && i < p.k; i += kSelThreads) {
         if (CANDIDATES) {
             p.cand_scores[obase + i] = INFINITY;
             p.cand_ids[obase + i] = -1;
@@ -295,7 +403,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
             if (p.out_scores) p.out_scores[obase + i] = pass ? (i < nb_l ? srow[i] : -1) : -1;
         }
     }
-    if (!CANDIDATES && tid == 0 && row % p.Hout == 0) {
+    if (!CANDIDATES && lead && tid == 0 && row % p.Hout == 0) {
         if (p.out_valid) p.out_valid[b] = min(kb, nb_l);
         if (p.out_newseq) {
             int ns = seq_l;
@@ -324,7 +432,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
             return (uint32_t)s + 1u;
         }
         // Forced blocks are few: the listed ones, the first blocks (sink) and the last ones (recent window).
-        __device__ void fixup(uint32_t* s_keys, int n_cached) const
+        __device__ void fixup(uint32_t* s_keys, int j_lo, int n_cached) const
         {
             const ForcedSpec& f = p.forced;
             const int n_sink = f.sink > 0 ? min(nb_g, (f.sink + p.BS - 1) / p.BS) : 0;
@@ -337,9 +445,10 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
                 else if (i < f.n_must + n_sink) jg = i - f.n_must;
                 else jg = first_recent + (i - f.n_must - n_sink);
                 const int j = jg - p.id_offset;
-                if (jg >= 0 && jg < nb_g && j >= 0 && j < nb_l && j < n_cached && s_keys[j] != key_invalid &&
+                const int c = j - j_lo;  // index in this CTA's cached slice
+                if (jg >= 0 && jg < nb_g && j >= 0 && j < nb_l && c >= 0 && c < n_cached && s_keys[c] != key_invalid &&
                     block_is_forced(f, jg, nb_g, seq_g, p.BS))
-                    s_keys[j] = 0u;
+                    s_keys[c] = 0u;
             }
         }
     };
@@ -358,7 +467,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
             if (p.out_scores) p.out_scores[obase + pos] = valid ? srow[j] : -1;
         }
     };
-    select_row(n, kb, p.key_bits, key_of, emit, s_keys, p.n_cached, sc);
+    select_row<CL>(n, kb, p.key_bits, key_of, emit, s_keys, p.n_cached, sc);
 }
 
 __device__ __forceinline__ uint32_t f32_order_key(float x)
@@ -414,7 +523,7 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
             return k == kKeyInvalid ? kKeyInvalid - 1u : k;
         }
         __device__ uint32_t key_fast(int i, Rec r) const { return key(i, r); }
-        __device__ void fixup(uint32_t*, int) const {}
+        __device__ void fixup(uint32_t*, int, int) const {}
     };
     const KeyOf key_of{p, row};
     auto emit = [&](int pos, int i) {
@@ -424,7 +533,7 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
             p.out_ids[obase + pos] = p.cand_ids[a];
         }
     };
-    select_row(n, min(p.k, n), 32, key_of, emit, s_keys, p.n_cached, sc);
+    select_row<false>(n, min(p.k, n), 32, key_of, emit, s_keys, p.n_cached, sc);
 }
 
 __global__ void update_seq_lens_kernel(const int32_t* seq, int B, int topk_tokens, int BS, int32_t* out)
@@ -535,17 +644,29 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
     p.out_phys = out_phys; p.out_logical = out_logical; p.out_scores = out_scores;
     p.out_valid = out_valid; p.out_newseq = out_newseq;
     p.cand_scores = cand_scores; p.cand_ids = cand_ids; p.scale = scale; p.sched = sched;
-    const size_t smem = (size_t)p.n_cached * sizeof(uint32_t);
     const int rows = B * p.Hout;
-    if (candidates) {
-        rc = set_dyn_smem(select_kernel<true>, smem);
-        if (rc != UCMR_OK) return rc;
-        return launch_kernel(select_kernel<true>, dim3(rows), dim3(kSelThreads), smem, st, p);
-    } else {
-        rc = set_dyn_smem(select_kernel<false>, smem);
-        if (rc != UCMR_OK) return rc;
-        return launch_kernel(select_kernel<false>, dim3(rows), dim3(kSelThreads), smem, st, p);
+    // Few long rows: split each over a thread-block cluster so that the selection uses more than `rows` SMs.
+    p.cluster = 1;
+    while (p.cluster < 8 && rows * p.cluster * 2 <= 160 && max_blocks > p.cluster * kSelClusterSlice) p.cluster *= 2;
+    bool use_cluster = p.cluster > 1;
+    if (const char* env = getenv("UCMR_SEL_CLUSTER")) {  // tuning aid: 0 = never split, 1/2/4/8 = force that size
+        const int v = atoi(env);
+        if (v == 0) { p.cluster = 1; use_cluster = false; }
+        else if (v == 1 || v == 2 || v == 4 || v == 8) { p.cluster = v; use_cluster = true; }
     }
+    if (use_cluster) {
+        const int slice = ((max_blocks + p.cluster - 1) / p.cluster + 3) / 4 * 4;
+        p.n_cached = slice < kSelMaxCachedKeys ? slice : kSelMaxCachedKeys;
+    }
+    const size_t smem = (size_t)p.n_cached * sizeof(uint32_t);
+    void (*kernel)(const SelectParams) =
+        candidates ? (use_cluster ? select_kernel<true, true> : select_kernel<true, false>)
+                   : (use_cluster ? select_kernel<false, true> : select_kernel<false, false>);
+    rc = set_dyn_smem(kernel, smem);
+    if (rc != UCMR_OK) return rc;
+    if (use_cluster)
+        return launch_kernel_cluster(kernel, dim3(rows * p.cluster), dim3(kSelThreads), smem, st, p.cluster, p);
+    return launch_kernel(kernel, dim3(rows), dim3(kSelThreads), smem, st, p);
 }
 
 extern "C" int ucmr_hamming_topk(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
