@@ -83,6 +83,20 @@ int ucmr_hash_encode_and_cache(const void* x, int64_t T, int H, int64_t stride_t
                                int slot_is_int64, uint32_t* cache, int64_t NB, int BS,
                                int32_t* status_word, void* stream);
 
+/*     Re-hash of key blocks that already sit in the paged K cache (a prefix-cache hit): stands in for
+ *     the torch gather kv_cache[0][0][prefix_block_ids] followed by compute_hash_and_cache with the
+ *     prefix slot mapping (ucm/sparse/gsa_on_device/gsa_on_device.py:574-588), without the gathered
+ *     copy.  k_cache is bf16 [NB, BS, H, in_dim] with strides in elements (stride_block between
+ *     blocks, stride_t between tokens, stride_h between heads).  For every listed block i the codes of
+ *     its first block_tokens[i] tokens (all BS when block_tokens is NULL) are written to block
+ *     block_ids[i] of cache [NB_codes, BS, H, W] - the code cache uses the K cache's block ids.  Ids
+ *     outside [0, NB) are flagged in status_word and skipped.                                        */
+int ucmr_hash_encode_blocks(const void* k_cache, int64_t NB, int BS, int H, int64_t stride_block,
+                            int64_t stride_t, int64_t stride_h, const int32_t* block_ids,
+                            const int32_t* block_tokens, int64_t n_blocks, const void* R, int in_dim,
+                            int hash_bits, uint32_t* cache, int64_t NB_codes, int32_t* status_word,
+                            void* stream);
+
 /*     The two encodes of one decode step in a single launch: the step's queries (as
  *     ucmr_hash_encode_query, hash_code at gsa_on_device.py:396-412) and its new key rows (as
  *     ucmr_hash_encode_and_cache, cache_k_hash_gqa_cuda at gsa_on_device.py:564-573).

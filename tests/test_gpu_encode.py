@@ -210,3 +210,59 @@ def test_decode_step_reads_pinned_host_inputs_and_writes_pinned_result(cuda_devi
     assert torch.equal(ra.physical.cpu(), host_ids) and torch.equal(ra.logical, rb.logical)
     with pytest.raises(ValueError):
         ops.hash_encode_decode_step(q.cpu(), kn, slots, cache_b, R)   # pageable host memory is refused
+
+
+@pytest.mark.parametrize("BS,Hh,dims,strided", [
+    (128, 8, (128, 128), False),  # eight tiles per block
+    (16, 8, (128, 128), False),   # one tile per block (vLLM block 16)
+    (16, 1, (128, 128), False),   # eight blocks per tile (one kv head per GPU)
+    (16, 2, (128, 128), True),    # four blocks per tile, K sliced out of a [NB, 2, BS, H, D] cache
+    (64, 4, (128, 128), True),
+    (32, 2, (64, 64), False),     # other code sizes: CUDA-core kernel
+    (24, 3, (128, 128), False),   # rows per block not a tile divisor: CUDA-core kernel
+])
+def test_rehash_blocks_in_place(cuda_device, BS, Hh, dims, strided):
+    """Prefix-hit re-hash: codes of listed K-cache blocks written to the same blocks of the code cache; the
+    last block of each request is partial; unlisted blocks and the tails of partial blocks keep their content;
+    ids outside the cache are flagged and skipped."""
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    D, bits = dims
+    rng = np.random.default_rng(BS * 100 + Hh)
+    NB = 40
+    kv = H.bf16_normal(rng, (NB, 2, BS, Hh, D)) if strided else H.bf16_normal(rng, (NB, BS, Hh, D))
+    r = _r_matrix(3, D, bits)
+    kv_d = H.bf16_to_dev(kv, dev)
+    k_d = kv_d[:, 0] if strided else kv_d
+    k_host = kv[:, 0] if strided else kv
+    ids = np.array([7, 3, 39, 0, 12, 21, 5, 30, 8, 17, 2], dtype=np.int32)
+    toks = np.full(ids.shape, BS, dtype=np.int32)
+    toks[4] = 1
+    toks[-1] = BS - 3
+    W = bits // 32
+    sentinel = np.uint32(0xDEADBEEF)
+    cache = torch.full((NB, BS, Hh, W), int(np.int32(sentinel.view(np.int32))), dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.hash_encode_blocks(k_d, torch.from_numpy(ids).to(dev), cache, H.bf16_to_dev(r, dev),
+                           block_tokens=torch.from_numpy(toks).to(dev), status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    got = H.dev_to_u32(cache)
+    listed = np.zeros((NB, BS), dtype=bool)
+    for i, n in zip(ids, toks):
+        listed[i, :n] = True
+    assert (got[~listed] == sentinel).all()
+    _check(got[listed], k_host[listed], r)
+    # all tokens when block_tokens is omitted; a bad id is flagged, the others still land
+    cache.fill_(0)
+    ids2 = np.array([4, -1, 9, NB, 1], dtype=np.int32)
+    ops.hash_encode_blocks(k_d, torch.from_numpy(ids2).to(dev), cache, H.bf16_to_dev(r, dev), status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) & 1
+    got = H.dev_to_u32(cache)
+    good = [4, 9, 1]
+    _check(got[good], k_host[good], r)
+    rest = np.ones(NB, dtype=bool)
+    rest[good] = False
+    assert (got[rest] == 0).all()

@@ -130,6 +130,74 @@ def test_prefill_then_decode_rewrites_and_restores_block_table(cuda_device):
     assert "r0" not in plugin.is_prefill_flag and "r1" not in plugin.is_prefill_flag and "r2" in plugin.is_prefill_flag
 
 
+def test_prefix_cache_hit_rehashes_blocks_in_place(cuda_device):
+    """First prefill of requests whose prefix is already in the K cache: the plugin hashes those blocks straight
+    from the paged K cache (one request ends its prefix inside a block) and the scheduled tokens from `key`."""
+    import torch
+    from unified_cache_management_b200.base import UcmSparseRole
+    from unified_cache_management_b200.gsa_on_device import GSAOnDevice
+    dev = cuda_device
+    BS, Hq, Hkv, D = 16, 8, 2, 128
+    cfg = F.make_vllm_config(block_size=BS, num_q_heads=Hq, num_kv_heads=Hkv, max_model_len=32 * BS, max_num_seqs=4,
+                             overrides=dict(vllm_hash_attention_topk=4 * BS, gpu_seq_len_threshold=4 * BS,
+                                            gpu_concurrency_threshold=1, vllm_hash_attention_rollback_layers=[0],
+                                            vllm_hash_attention_skip_layers=[False, False]))
+    plugin = GSAOnDevice(cfg, UcmSparseRole.WORKER)
+    NB, mb = 64, 32
+    prompt = [5 * BS + 7, 4 * BS]
+    prefix = [3 * BS + 4, 2 * BS]
+    rng = np.random.default_rng(3)
+    perm = rng.permutation(NB)
+    bt = np.zeros((2, mb), dtype=np.int32)
+    off = 0
+    for b, ln in enumerate(prompt):
+        n = -(-ln // BS)
+        bt[b, :n] = perm[off:off + n]
+        off += n
+    layer = "model.layers.1.self_attn.attn"
+    kv_bits = H.bf16_normal(rng, (2, NB, BS, Hkv, D))
+    kv = H.bf16_to_dev(kv_bits, dev)
+    kv_caches = {"model.layers.0.self_attn.attn": torch.zeros_like(kv), layer: kv}
+    plugin.initialize_kv_hash_cache_tensors(kv_caches, dev)
+    k_hash = kv_caches[layer][1]
+    requests = {f"r{b}": F.FakeRequest(num_computed_tokens=prefix[b], num_prompt_tokens=prompt[b]) for b in range(2)}
+    input_batch = SimpleNamespace(req_id_to_index={"r0": 0, "r1": 1})
+    qlens = [prompt[b] - prefix[b] for b in range(2)]
+    keys = [H.bf16_normal(rng, (q, Hkv, D)) for q in qlens]
+    key_all = torch.cat([H.bf16_to_dev(k, dev) for k in keys])
+    slots = np.concatenate([bt[b, np.arange(prefix[b], prompt[b]) // BS].astype(np.int64) * BS
+                            + np.arange(prefix[b], prompt[b]) % BS for b in range(2)])
+    qsl = np.concatenate([[0], np.cumsum(qlens)]).astype(np.int32)
+    meta = SimpleNamespace(seq_lens=torch.tensor(prompt, dtype=torch.int32, device=dev),
+                           block_table=torch.from_numpy(bt).to(dev), slot_mapping=torch.from_numpy(slots).to(dev),
+                           query_start_loc=torch.from_numpy(qsl).to(dev))
+    fc = SimpleNamespace(attn_metadata={layer: meta}, virtual_engine=0,
+                         no_compile_layers={layer: SimpleNamespace(kv_cache=[kv_caches[layer]])})
+    so = F.scheduler_output({"r0": qlens[0], "r1": qlens[1]})
+    so.num_external_computed_tokens_per_req = {"r0": prefix[0], "r1": prefix[1]}
+    plugin.update_states(so)
+    plugin.build_sparse_meta(so, requests, input_batch, {layer: meta})
+    assert plugin.has_pc_hit
+    assert plugin.prefix_block_ids.cpu().tolist() == bt[0, :4].tolist() + bt[1, :2].tolist()
+    assert plugin.prefix_block_tokens.cpu().tolist() == [BS, BS, BS, 4, BS, BS]
+    q_dummy = torch.zeros((sum(qlens), Hq, D), dtype=torch.bfloat16, device=dev)
+    plugin.attention_begin(q_dummy, key_all, key_all, layer, fc, k_hash=k_hash)
+    torch.cuda.synchronize()
+    r_bits = _bf16_bits(plugin.hash_encoder.hash_weights_bf16)
+    codes = k_hash.view(torch.int32).cpu().numpy().view(np.uint32).reshape(NB * BS, Hkv, 4)
+    k_rows = kv_bits[0].reshape(NB * BS, Hkv, D)
+    touched = np.zeros(NB * BS, dtype=bool)
+    for b in range(2):
+        pos = np.arange(prompt[b])
+        slot = bt[b, pos // BS].astype(np.int64) * BS + pos % BS
+        src = np.concatenate([k_rows[slot[:prefix[b]]], keys[b]])
+        _, p64 = O.hash_encode(src, r_bits)
+        hard, _ = O.count_code_mismatches(codes[slot], p64)
+        assert hard == 0
+        touched[slot] = True
+    assert (codes[~touched] == 0).all()     # nothing else was written (the code cache starts zeroed)
+
+
 def test_reference_hamming_topk_module_interface(cuda_device):
     """cuda_hamming_topk / update_seq_lens with the reference's argument list."""
     import torch

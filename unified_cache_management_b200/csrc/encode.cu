@@ -54,6 +54,14 @@ struct EncParams {
     int64_t n_slots;           // NB * BS
     const __nv_bfloat16* R;    // [128, 128] row-major
     int32_t* status;           // may be null
+    // Paged source (re-hash of blocks that already sit in the K cache): the tiles walk the rows of the listed
+    // blocks, block i of the list being block src_blocks[i] of the source AND of the code cache.
+    const int32_t* src_blocks;    // null = x is one run of consecutive tokens
+    const int32_t* block_tokens;  // valid tokens per listed block, null = all BS
+    int64_t n_src_blocks;
+    int64_t NB_src;
+    int BS;                       // tokens per block
+    int rpb;                      // rows per block = BS * H (a multiple of 8; divides or is a multiple of 128)
 };
 
 __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr)
@@ -73,6 +81,16 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
             "r"(smem_u32(smem_dst)),
         "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, int x, int y, int z, int w,
+                                            uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::
+            "r"(smem_u32(smem_dst)),
+        "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
         : "memory");
 }
 
@@ -194,11 +212,33 @@ encode_tc_kernel(const __grid_constant__ CUtensorMap x_map, const EncParams p)
                 const uint32_t ph = (uint32_t)((it / kEncStages) & 1);
                 if (!mbar_wait(&empty[s], ph ^ 1u)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
                 const int64_t tile = first + it * step;
-                const int t0 = (int)(tile * tok_per_tile);
                 uint8_t* dst = s_a + (size_t)s * kEncStageBytes;
                 mbar_expect_tx(&full[s], kEncStageBytes);
-                tma_load_3d(dst, &x_map, 0, 0, t0, &full[s]);
-                tma_load_3d(dst + kEncHalfBytes, &x_map, 64, 0, t0, &full[s]);
+                if (p.src_blocks == nullptr) {
+                    const int t0 = (int)(tile * tok_per_tile);
+                    tma_load_3d(dst, &x_map, 0, 0, t0, &full[s]);
+                    tma_load_3d(dst + kEncHalfBytes, &x_map, 64, 0, t0, &full[s]);
+                } else if (p.rpb >= kEncTileM) {
+                    // the tile is one slice of one listed block
+                    const int parts = p.rpb / kEncTileM;
+                    const int64_t bi = tile / parts;
+                    int id = p.src_blocks[bi];
+                    if (id < 0 || id >= p.NB_src) id = 0;  // rows of a bad id are dropped by the epilogue
+                    const int tok0 = (int)(tile - bi * parts) * tok_per_tile;
+                    tma_load_4d(dst, &x_map, 0, 0, tok0, id, &full[s]);
+                    tma_load_4d(dst + kEncHalfBytes, &x_map, 64, 0, tok0, id, &full[s]);
+                } else {
+                    // the tile holds several whole blocks, each a box of rpb rows
+                    const int sub = kEncTileM / p.rpb;
+                    for (int u = 0; u < sub; ++u) {
+                        const int64_t bi = tile * sub + u;
+                        int id = bi < p.n_src_blocks ? p.src_blocks[bi] : 0;
+                        if (id < 0 || id >= p.NB_src) id = 0;
+                        uint8_t* d = dst + (size_t)u * p.rpb * 128;
+                        tma_load_4d(d, &x_map, 0, 0, 0, id, &full[s]);
+                        tma_load_4d(d + kEncHalfBytes, &x_map, 64, 0, 0, id, &full[s]);
+                    }
+                }
             }
         }
     } else if (warp == 1) {
@@ -248,7 +288,21 @@ encode_tc_kernel(const __grid_constant__ CUtensorMap x_map, const EncParams p)
             if (lane == 0) mbar_arrive(&acc_empty[a]);
             const int64_t tile = first + it * step;
             const int64_t row = tile * kEncTileM + q * 32 + lane;
-            if (row < p.rows) {
+            if (p.src_blocks != nullptr) {
+                const int64_t bi = row / p.rpb;
+                if (bi < p.n_src_blocks) {
+                    const int within = (int)(row - bi * p.rpb);
+                    const int tok = within / p.H, h = within - tok * p.H;
+                    const int id = p.src_blocks[bi];
+                    const int ntok = p.block_tokens ? p.block_tokens[bi] : p.BS;
+                    if (id < 0 || id >= p.NB_src) {
+                        if (within == 0) flag_status(p.status, UCMR_DEV_BAD_BLOCK_ID);
+                    } else if (tok < ntok) {
+                        const int64_t slot = (int64_t)id * p.BS + tok;
+                        if (slot < p.n_slots) *reinterpret_cast<uint4*>(p.out + (slot * p.H + h) * 4) = code;
+                    }
+                }
+            } else if (row < p.rows) {
                 if (p.slot_mapping == nullptr) {
                     *reinterpret_cast<uint4*>(p.out + row * 4) = code;
                 } else {
@@ -466,7 +520,27 @@ struct SimtParams {
     const void* slot_mapping;
     int slot_is_int64;
     int64_t n_slots;
+    // paged source (see EncParams): token t of the walk is token t % BS of listed block t / BS
+    const int32_t* src_blocks;
+    const int32_t* block_tokens;
+    int64_t stride_block, NB_src;
+    int BS;
+    int32_t* status;
 };
+
+// Source token and destination slot of walk position t of a paged-source job; false = skip.
+__device__ __forceinline__ bool paged_token(const SimtParams& p, int64_t t, int64_t& src_off, int64_t& slot, bool& bad)
+{
+    const int64_t bi = t / p.BS;
+    const int tok = (int)(t - bi * p.BS);
+    const int id = p.src_blocks[bi];
+    bad = id < 0 || id >= p.NB_src;
+    if (bad) return false;
+    if (tok >= (p.block_tokens ? p.block_tokens[bi] : p.BS)) return false;
+    src_off = (int64_t)id * p.stride_block + (int64_t)tok * p.stride_t;
+    slot = (int64_t)id * p.BS + tok;
+    return true;
+}
 
 __global__ void __launch_bounds__(kSimtThreads) encode_simt_kernel(const SimtParams p)
 {
@@ -484,8 +558,13 @@ __global__ void __launch_bounds__(kSimtThreads) encode_simt_kernel(const SimtPar
         if (row < rows) {
             const int64_t t = row / H_out;
             const int ho = (int)(row - t * H_out);
-            const __nv_bfloat16* src = p.x + t * p.stride_t + (int64_t)ho * p.G * p.stride_h + k;
-            if (p.G == 1) {
+            int64_t src_off = t * p.stride_t, slot_unused;
+            bool bad = false;
+            const bool live = p.src_blocks == nullptr || paged_token(p, t, src_off, slot_unused, bad);
+            const __nv_bfloat16* src = p.x + (live ? src_off : 0) + (int64_t)ho * p.G * p.stride_h + k;
+            if (!live) {
+                v = 0.f;
+            } else if (p.G == 1) {
                 v = __bfloat162float(*src);
             } else {
                 float acc = 0.f;
@@ -525,7 +604,15 @@ __global__ void __launch_bounds__(kSimtThreads) encode_simt_kernel(const SimtPar
                 const uint32_t word = __ballot_sync(0xffffffffu, acc[r][c] > 0.f);
                 if (lane == 0 && c < wn && row < rows) {
                     int64_t dst_row = row;
-                    if (p.slot_mapping != nullptr) {
+                    if (p.src_blocks != nullptr) {
+                        const int64_t t = row / H_out;
+                        const int ho = (int)(row - t * H_out);
+                        int64_t src_off, slot;
+                        bool bad = false;
+                        const bool live = paged_token(p, t, src_off, slot, bad);
+                        if (bad && ho == 0 && t % p.BS == 0) flag_status(p.status, UCMR_DEV_BAD_BLOCK_ID);
+                        dst_row = (live && slot < p.n_slots) ? slot * H_out + ho : -1;
+                    } else if (p.slot_mapping != nullptr) {
                         const int64_t t = row / H_out;
                         const int ho = (int)(row - t * H_out);
                         const int64_t slot = p.slot_is_int64 ? static_cast<const int64_t*>(p.slot_mapping)[t]
@@ -608,6 +695,52 @@ static int launch_tc(const void* x, int64_t T, int H, int64_t stride_t, int64_t 
     return launch_kernel(encode_tc_kernel, dim3(grid), dim3(kEncThreads), kEncSmemBytes, st, map, p);
 }
 
+// Paged-source form of launch_tc: a 4-D map {in_dim, H, BS, NB} over the K cache, one box per (block, slice).
+static bool tc_blocks_path_ok(const void* x, int64_t NB, int BS, int H, int64_t stride_block, int64_t stride_t,
+                              int64_t stride_h, int in_dim, int bits)
+{
+    if (!tc_path_ok(x, BS, H, stride_t, stride_h, in_dim, bits)) return false;
+    const int64_t rpb = (int64_t)BS * H;
+    if (rpb % 8 != 0 || (rpb < kEncTileM ? kEncTileM % rpb != 0 : rpb % kEncTileM != 0)) return false;
+    if (stride_block % 8 != 0 || (uint64_t)stride_block * 2 >= (1ull << 40)) return false;
+    if (NB <= 0 || NB > 0x7FFFFFFF || BS > 256) return false;
+    return true;
+}
+
+static int launch_tc_blocks(const void* x, int64_t NB, int BS, int H, int64_t stride_block, int64_t stride_t,
+                            int64_t stride_h, const int32_t* block_ids, const int32_t* block_tokens, int64_t n_blocks,
+                            const void* R, uint32_t* out, int64_t n_slots, int32_t* status, cudaStream_t st)
+{
+    EncodeTiledFn encode = get_encode_tiled();
+    if (!encode) return UCMR_ERR_LAUNCH;
+    const int tok_per_tile = kEncTileM / H;
+    const int box_tok = BS < tok_per_tile ? BS : tok_per_tile;
+    CUtensorMap map;
+    const cuuint64_t dims[4] = {(cuuint64_t)kEncD, (cuuint64_t)H, (cuuint64_t)BS, (cuuint64_t)NB};
+    const cuuint64_t strides[3] = {(cuuint64_t)(H > 1 ? stride_h : kEncD) * 2, (cuuint64_t)stride_t * 2,
+                                   (cuuint64_t)stride_block * 2};
+    const cuuint32_t box[4] = {64, (cuuint32_t)H, (cuuint32_t)box_tok, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(x), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return UCMR_ERR_LAUNCH;
+
+    EncParams p{};
+    p.H = H; p.BS = BS; p.rpb = BS * H;
+    p.rows = n_blocks * p.rpb;
+    p.n_tiles = (p.rows + kEncTileM - 1) / kEncTileM;
+    p.out = out; p.n_slots = n_slots;
+    p.src_blocks = block_ids; p.block_tokens = block_tokens; p.n_src_blocks = n_blocks; p.NB_src = NB;
+    p.R = static_cast<const __nv_bfloat16*>(R); p.status = status;
+    cudaError_t e = cudaFuncSetAttribute(encode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kEncSmemBytes);
+    if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = (int)(p.n_tiles < sms ? p.n_tiles : sms);
+    return launch_kernel(encode_tc_kernel, dim3(grid), dim3(kEncThreads), kEncSmemBytes, st, map, p);
+}
+
 // Shapes the one-tile-per-CTA tensor-core kernel accepts (any head count; 16-byte aligned rows).
 static bool tile_path_ok(const void* x, int64_t T, int H_in, int G, int64_t stride_t, int64_t stride_h, int in_dim,
                          int bits, const void* out, const void* R)
@@ -650,6 +783,8 @@ static int launch_tiles(const TileJob& j0, const TileJob* j1, const void* R, int
 // persistent TMA-pipelined kernel amortises its set-up.
 constexpr int64_t kSmallTiles = 296;
 
+static int launch_simt_params(const SimtParams& p, cudaStream_t st);
+
 static int launch_simt(const void* x, int64_t T, int H_in, int G, int64_t stride_t, int64_t stride_h, const void* R,
                        int in_dim, int bits, uint32_t* out, const void* slot_mapping, int slot_is_int64,
                        int64_t n_slots, cudaStream_t st)
@@ -659,10 +794,15 @@ static int launch_simt(const void* x, int64_t T, int H_in, int G, int64_t stride
     p.stride_t = stride_t; p.stride_h = stride_h;
     p.R = static_cast<const __nv_bfloat16*>(R); p.in_dim = in_dim; p.bits = bits;
     p.out = out; p.slot_mapping = slot_mapping; p.slot_is_int64 = slot_is_int64; p.n_slots = n_slots;
-    const int64_t rows = T * (H_in / G);
+    return launch_simt_params(p, st);
+}
+
+static int launch_simt_params(const SimtParams& p, cudaStream_t st)
+{
+    const int64_t rows = p.T * (p.H_in / p.G);
     const int64_t grid = (rows + kSimtRowsPerCta - 1) / kSimtRowsPerCta;
     if (grid > 0x7FFFFFFF) return UCMR_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)kSimtRowsPerCta * in_dim * sizeof(float);
+    const size_t smem = (size_t)kSimtRowsPerCta * p.in_dim * sizeof(float);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(encode_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
@@ -784,4 +924,32 @@ extern "C" int ucmr_hash_encode_decode_step(const void* q, int64_t Tq, int Hq, i
     if (rc != UCMR_OK) return rc;
     return ucmr_hash_encode_query(q, Tq, Hq, q_stride_t, q_stride_h, group_mean, R, in_dim, hash_bits, q_codes_out,
                                   status_word, stream);
+}
+
+extern "C" int ucmr_hash_encode_blocks(const void* k_cache, int64_t NB, int BS, int H, int64_t stride_block,
+                                       int64_t stride_t, int64_t stride_h, const int32_t* block_ids,
+                                       const int32_t* block_tokens, int64_t n_blocks, const void* R, int in_dim,
+                                       int hash_bits, uint32_t* cache, int64_t NB_codes, int32_t* status_word,
+                                       void* stream)
+{
+    if (!k_cache || !R || !cache || NB <= 0 || BS <= 0 || H <= 0 || NB_codes <= 0 || n_blocks < 0) return UCMR_ERR_BAD_ARG;
+    if (n_blocks > 0 && !block_ids) return UCMR_ERR_BAD_ARG;
+    if (stride_h < in_dim || stride_t < in_dim || stride_block < stride_t) return UCMR_ERR_BAD_ARG;
+    int rc = check_dims(in_dim, hash_bits);
+    if (rc != UCMR_OK) return rc;
+    if (n_blocks == 0) return UCMR_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t n_slots = NB_codes * BS;
+    if (!force_simt() && tc_blocks_path_ok(k_cache, NB, BS, H, stride_block, stride_t, stride_h, in_dim, hash_bits) &&
+        reinterpret_cast<uintptr_t>(cache) % 16 == 0 && reinterpret_cast<uintptr_t>(R) % 16 == 0)
+        return launch_tc_blocks(k_cache, NB, BS, H, stride_block, stride_t, stride_h, block_ids, block_tokens, n_blocks,
+                                R, cache, n_slots, status_word, st);
+    SimtParams p{};
+    p.x = static_cast<const __nv_bfloat16*>(k_cache); p.T = n_blocks * BS; p.H_in = H; p.G = 1;
+    p.stride_t = stride_t; p.stride_h = stride_h;
+    p.R = static_cast<const __nv_bfloat16*>(R); p.in_dim = in_dim; p.bits = hash_bits;
+    p.out = cache; p.n_slots = n_slots;
+    p.src_blocks = block_ids; p.block_tokens = block_tokens; p.stride_block = stride_block; p.NB_src = NB; p.BS = BS;
+    p.status = status_word;
+    return launch_simt_params(p, st);
 }

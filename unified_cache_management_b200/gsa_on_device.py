@@ -153,6 +153,7 @@ class GSAOnDevice(UcmSparseBase):
                                                    dtype=torch.int64)
         self.prefix_block_ids_buf = torch.empty(cdiv(self.max_num_tokens * self.max_batch_size, self.block_size),
                                                 device=self.device, dtype=torch.int32)
+        self.prefix_block_tokens_buf = torch.empty_like(self.prefix_block_ids_buf)  # valid tokens per listed block
         self.token_idx_buf = torch.arange(self.max_num_tokens, device=self.device, dtype=torch.int64)
 
     # ---- hashing ---------------------------------------------------------------------------------
@@ -185,15 +186,14 @@ class GSAOnDevice(UcmSparseBase):
         n = slot_mapping.numel()
         self.hash_encoder.compute_hash_and_cache(key[:n], slot_mapping, k_hash, block_size=self.block_size)
         if self.has_pc_hit:
-            # keys of the prefix-cache hit are already in the KV cache: gather their blocks, hash, scatter
+            # keys of the prefix-cache hit are already in the KV cache: hash those blocks into the code cache
             attn = forward_context.no_compile_layers[layer_name]
             kv_cache = attn.kv_cache[forward_context.virtual_engine]
             k_pool = kv_cache[0][0]
-            gathered, _ = ops.gather_kv(k_pool, None, self.prefix_block_ids.view(1, -1).contiguous())
-            k_rows = gathered.view(-1, k_pool.shape[2], k_pool.shape[3])
-            m = self.prefix_slot_mapping.numel()
-            self.hash_encoder.compute_hash_and_cache(k_rows[:m], self.prefix_slot_mapping.flatten(), k_hash,
-                                                     block_size=self.block_size)
+            # (reference: torch gather of the blocks, then compute_hash_and_cache with the prefix slot mapping,
+            # gsa_on_device.py:574-588; here one kernel reads the blocks where they lie)
+            self.hash_encoder.compute_hash_of_blocks(k_pool, self.prefix_block_ids, k_hash,
+                                                     block_tokens=self.prefix_block_tokens)
 
     # ---- retrieval ---------------------------------------------------------------------------------
     def _forced(self):
@@ -353,6 +353,8 @@ class GSAOnDevice(UcmSparseBase):
                         qlen=int(compute_q_lens[req_row_id]), block_size=self.block_size)
                     self.prefix_slot_mapping_buf[all_prefix_tokens: all_prefix_tokens + n_tok] = slots
                     self.prefix_block_ids_buf[all_prefix_blocks: all_prefix_blocks + n_blk] = blk_ids
+                    self.prefix_block_tokens_buf[all_prefix_blocks: all_prefix_blocks + n_blk] = self.block_size
+                    self.prefix_block_tokens_buf[all_prefix_blocks + n_blk - 1] = n_tok - (n_blk - 1) * self.block_size
                     all_prefix_tokens += n_tok
                     all_prefix_blocks += n_blk
                     num_pc_hit += 1
@@ -362,6 +364,7 @@ class GSAOnDevice(UcmSparseBase):
         if self.has_pc_hit:
             self.prefix_slot_mapping = self.prefix_slot_mapping_buf[:all_prefix_tokens]
             self.prefix_block_ids = self.prefix_block_ids_buf[:all_prefix_blocks]
+            self.prefix_block_tokens = self.prefix_block_tokens_buf[:all_prefix_blocks]
         if not self.gsa_enabled:
             return None
         self.has_decode = num_decodes > 0

@@ -11,6 +11,8 @@ are served: there is no Triton, NPU or CPU branch here.
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from . import ops
@@ -117,6 +119,25 @@ class HashEncoder:
             raise ValueError(f"k_hash_cache.shape[2]={k_hash_cache.shape[2]} != H={h}")
         cache_u8 = self._reinterpret_cache_as_u8(k_hash_cache)
         ops.hash_encode_and_cache(self._as_bf16(x), slot_mapping, cache_u8, self.hash_weights_bf16)
+        return k_hash_cache
+
+    def compute_hash_of_blocks(self, k_cache: torch.Tensor, block_ids: torch.Tensor, k_hash_cache: torch.Tensor,
+                               block_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Encode the keys of the listed blocks of the paged K cache [NB, BS, H, K] into the same blocks of the
+        code cache, reading the blocks where they lie.  Same result as gathering the blocks and calling
+        ``compute_hash_and_cache`` with their slot mapping (what the reference does on a prefix-cache hit,
+        gsa_on_device.py:574-588); ``block_tokens[i]`` limits block i to its first tokens."""
+        if k_cache.ndim != 4 or k_hash_cache.ndim != 4:
+            raise ValueError("k_cache and k_hash_cache must be rank-4")
+        if k_cache.shape[-1] != self.input_dim:
+            raise ValueError(f"k_cache last dim must be {self.input_dim}, got {k_cache.shape[-1]}")
+        if k_cache.dtype != torch.bfloat16:
+            raise ValueError("the paged K cache must be bf16 (it is read in place)")
+        if k_hash_cache.shape[1] != k_cache.shape[1] or k_hash_cache.shape[2] != k_cache.shape[2]:
+            raise ValueError("k_hash_cache and k_cache disagree on block size or head count")
+        cache_u8 = self._reinterpret_cache_as_u8(k_hash_cache)
+        ops.hash_encode_blocks(k_cache, block_ids.to(torch.int32), cache_u8, self.hash_weights_bf16,
+                               block_tokens=None if block_tokens is None else block_tokens.to(torch.int32))
         return k_hash_cache
 
     def _unpack_hash(self, packed_codes: torch.Tensor) -> torch.Tensor:

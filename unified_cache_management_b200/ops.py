@@ -146,6 +146,35 @@ def hash_encode_and_cache(x: torch.Tensor, slot_mapping: torch.Tensor, cache: to
     return cache
 
 
+def hash_encode_blocks(k_cache: torch.Tensor, block_ids: torch.Tensor, cache: torch.Tensor, r: torch.Tensor,
+                       block_tokens: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Re-hash key blocks in place of the paged K cache: for every listed block id, encode its first
+    ``block_tokens[i]`` tokens (all of them when None) of k_cache bf16 [NB, BS, H, in_dim] into the same block of the
+    code cache [NB_codes, BS, H, W].  No gathered copy of the keys is made."""
+    _need_cuda("k_cache", k_cache, torch.bfloat16, contiguous=False)
+    if k_cache.dim() != 4 or k_cache.stride(3) != 1:
+        raise ValueError(f"k_cache must be [NB,BS,H,K] with a unit inner stride, got {tuple(k_cache.shape)}")
+    _need_cuda("block_ids", block_ids, torch.int32)
+    if block_ids.dim() != 1:
+        raise ValueError("block_ids must be one-dimensional")
+    if block_tokens is not None:
+        _need_cuda("block_tokens", block_tokens, torch.int32)
+        if block_tokens.shape != block_ids.shape:
+            raise ValueError("block_tokens must have one entry per listed block")
+    _need_cuda("cache", cache)
+    cw = as_words(cache)
+    nb, bs, h, in_dim = k_cache.shape
+    bits = _check_r(r, in_dim)
+    if cw.dim() != 4 or cw.shape[1] != bs or cw.shape[2] != h or cw.shape[3] != bits // 32:
+        raise ValueError(f"cache shape {tuple(cw.shape)} does not match [*, {bs}, {h}, {bits // 32}]")
+    lib = _l.load_library()
+    _l.check(lib.ucmr_hash_encode_blocks(_ptr(k_cache), nb, bs, h, k_cache.stride(0), k_cache.stride(1),
+                                         k_cache.stride(2), _ptr(block_ids), _ptr(block_tokens), block_ids.numel(),
+                                         _ptr(r), in_dim, bits, _ptr(cw), cw.shape[0], _ptr(status), _stream(k_cache)),
+             "ucmr_hash_encode_blocks")
+    return cache
+
+
 def hash_encode_decode_step(q: torch.Tensor, k_new: torch.Tensor, slot_mapping: torch.Tensor, cache: torch.Tensor,
                             r: torch.Tensor, group_mean: int = 1, q_codes_out: Optional[torch.Tensor] = None,
                             status: Optional[torch.Tensor] = None) -> torch.Tensor:
