@@ -38,7 +38,10 @@ def _cmp(out, ref):
     (2, 4, 1, 4, 16, 33),    # plugin path: one code per kv head, vLLM block 16
     (2, 8, 1, 16, 32, 9),    # 512-bit codes
     (1, 2, 3, 4, 128, 6),    # G outside {1,2,4,8}: query codes in shared memory
-    (2, 1, 16, 18, 64, 7),   # 576-bit MLA codes, W=18: generic kernel
+    (2, 1, 16, 18, 64, 7),   # 576-bit MLA codes, W=18: token-row path of the staged kernel
+    (3, 1, 64, 18, 64, 9),   # MLA, 64 query codes per request (128 heads, reduction 2)
+    (2, 1, 128, 18, 128, 5), # MLA, 128 query codes, block 128
+    (2, 1, 5, 18, 16, 21),   # MLA, odd group size, block 16 (several blocks per stage)
     (2, 3, 2, 4, 128, 5),    # non power-of-two kv heads: generic kernel
 ])
 def test_topk_matches_oracle(cuda_device, shape, mode, reduce_kvhead):

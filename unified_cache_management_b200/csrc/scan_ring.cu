@@ -76,6 +76,30 @@ __device__ __forceinline__ void csa(uint32_t& h, uint32_t& l, uint32_t a, uint32
     l = u ^ c;
 }
 
+// sum_i popc(v[i]) with carry-save adders (Harley-Seal): N words of weight 1 become one word of weight 1 and
+// N/2 words of weight 2, recursively, so only about log2(N) + 1 popcounts are issued.  POPC runs at a
+// quarter of the rate of the logic instructions, which is what bounds the per-token distance forms.
+template <int N>
+__device__ __forceinline__ int hs_popc(const uint32_t (&v)[N])
+{
+    if constexpr (N == 1) {
+        return __popc(v[0]);
+    } else if constexpr (N == 2) {
+        return __popc(v[0]) + __popc(v[1]);
+    } else {
+        constexpr int K = N / 2;  // words of weight 2 produced
+        uint32_t carry[K];
+        uint32_t ones = v[0];
+#pragma unroll
+        for (int i = 0; i < (N - 1) / 2; ++i) csa(carry[i], ones, ones, v[1 + 2 * i], v[2 + 2 * i]);
+        if constexpr (N % 2 == 0) {  // one word left: half adder
+            carry[K - 1] = ones & v[N - 1];
+            ones ^= v[N - 1];
+        }
+        return __popc(ones) + 2 * hs_popc<K>(carry);
+    }
+}
+
 // A lane buffers CH tokens of its column in registers per chunk: 128, or 64 for blocks of at most 64 tokens
 // (half the carry-save work per chunk).  The vertical counters of a chunk then need log2(CH) + 1 planes.
 __host__ __device__ constexpr int planes_of(int ch) { return ch == 128 ? 8 : 7; }
@@ -211,8 +235,8 @@ __device__ __forceinline__ void load_chunk(uint32_t (&x)[CH], const uint32_t* co
 
 // MIN selects the per-token-minimum path; RW_T (sum mode only) and G_T are compile-time copies of the row
 // width and group size for the common shapes, 0 = read them from the parameters; CH is the sum mode's
-// chunk size.
-template <bool MIN, int RW_T, int G_T, int CH>
+// chunk size.  ROW > 0 selects the token-row path for one kv head with ROW words per token (any group size).
+template <bool MIN, int RW_T, int G_T, int CH, int ROW>
 __global__ void __launch_bounds__(kRingThreads, 1)
 scan_ring_kernel(const RingParams p)
 {
@@ -350,7 +374,153 @@ scan_ring_kernel(const RingParams p)
     };
     int cur_b = -1;
     uint32_t phase = 0;
-    if constexpr (!MIN) {
+    if constexpr (ROW > 0) {
+        // One kv head, ROW words per token (MLA: 512 + 64 bits = 18 words), up to 255 query codes per request.
+        // A lane owns a token.  sum_g popc(k ^ q_g) only depends on c[i] = how many of the G query codes have
+        // bit i set:  d = sum_i c[i] + G * popc(k) - 2 * sum_p 2^p * popc(k & Q_p),  Q_p = bit p of the counts
+        // (bit-sliced), so a token costs (1 + log2 G) popcount sums instead of G, each taken over its ROW words
+        // with carry-save adders.  The planes Q_p of the warp's current request live in shared memory.
+        constexpr int W = ROW;
+        constexpr int kQPlanes = 8;
+        __shared__ uint32_t s_qp[kRingWarps][kQPlanes][ROW];
+        uint32_t* const qp = &s_qp[warp][0][0];
+        const int G = p.G;
+        const int nq = 32 - __clz(G);  // planes needed for counts 0..G
+        int ctot = 0;
+        while (cur.valid) {
+            if (!mbar_wait(full, phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
+            phase ^= 1u;
+            const StageMeta m = s_meta[warp];
+            if (m.b != cur_b) {
+                uint32_t P[kQPlanes];
+#pragma unroll
+                for (int pl = 0; pl < kQPlanes; ++pl) P[pl] = 0u;
+                int cpop = 0;
+                if (lane < W) {
+                    const uint32_t* qb = p.q + (int64_t)m.b * p.Hq * W + lane;
+                    for (int g0 = 0; g0 < G; g0 += 8) {
+                        uint32_t wv[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) wv[u] = (g0 + u < G) ? __ldg(qb + (int64_t)(g0 + u) * W) : 0u;
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            uint32_t carry = wv[u];
+                            cpop += __popc(carry);
+#pragma unroll
+                            for (int pl = 0; pl < kQPlanes; ++pl) {  // bit-sliced increment
+                                const uint32_t t = P[pl] & carry;
+                                P[pl] ^= carry;
+                                carry = t;
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int pl = 0; pl < kQPlanes; ++pl) qp[pl * W + lane] = P[pl];
+                }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) cpop += __shfl_xor_sync(0xffffffffu, cpop, off);
+                ctot = cpop;
+                cur_b = m.b;
+                __syncwarp();
+            }
+            // The blocks of a stage sit back to back, so the stage is one array of bps * BS token rows.  It is
+            // walked 64 rows at a time, two rows per lane (two independent dependency chains, and every plane
+            // word read from shared memory serves both).  BS is a power of two below 32 or a multiple of 32
+            // (checked on the host), so each half of a step lies in one block or covers whole blocks.
+            const uint32_t* sb = reinterpret_cast<const uint32_t*>(stage);
+            const int n_rows = p.bps * p.BS;
+            const int seg = min(p.BS, 32);  // lanes that share a block within a half step
+            int agg = MIN ? INT_MAX : 0;    // running result of the block in progress (BS >= 32)
+            bool reissued = false;
+            for (int r0 = 0; r0 < n_rows; r0 += 64) {
+                uint32_t k[2][W];
+                int blk[2], within[2];
+                bool ok[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int tt = r0 + 32 * h + lane;
+                    blk[h] = tt / p.BS;
+                    within[h] = tt - blk[h] * p.BS;
+                    const bool have = tt < n_rows && ((m.valid_mask >> blk[h]) & 1u);
+                    const int ntok = have ? min(p.BS, m.seq - (m.j0 + blk[h]) * p.BS) : 0;
+                    ok[h] = within[h] < ntok;
+                    if (ok[h]) {
+                        if constexpr (W % 2 == 0) {
+                            const uint2* rp = reinterpret_cast<const uint2*>(sb + (size_t)tt * W);
+#pragma unroll
+                            for (int i = 0; i < W / 2; ++i) { const uint2 v = rp[i]; k[h][2 * i] = v.x; k[h][2 * i + 1] = v.y; }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < W; ++i) k[h][i] = sb[(size_t)tt * W + i];
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < W; ++i) k[h][i] = 0u;
+                    }
+                }
+                if (r0 + 64 >= n_rows) {
+                    __syncwarp();
+                    advance();  // the stage's last words are in registers: refill it before the math
+                    reissued = true;
+                }
+                int d[2], masked[2] = {0, 0};
+                if (G == 1) {
+                    // a single query code: plane 0 is the code itself, so the distance is popc(k ^ q) directly
+                    uint32_t v0[W], v1[W];
+#pragma unroll
+                    for (int i = 0; i < W; ++i) {
+                        const uint32_t qw = qp[i];
+                        v0[i] = k[0][i] ^ qw;
+                        v1[i] = k[1][i] ^ qw;
+                    }
+                    d[0] = hs_popc<W>(v0);
+                    d[1] = hs_popc<W>(v1);
+                } else {
+                    d[0] = ctot + G * hs_popc<W>(k[0]);
+                    d[1] = ctot + G * hs_popc<W>(k[1]);
+                }
+                for (int pl = 0; pl < (G == 1 ? 0 : nq); ++pl) {
+                    uint32_t v0[W], v1[W];
+#pragma unroll
+                    for (int i = 0; i < W; ++i) {
+                        const uint32_t qw = qp[pl * W + i];
+                        v0[i] = k[0][i] & qw;
+                        v1[i] = k[1][i] & qw;
+                    }
+                    masked[0] += hs_popc<W>(v0) << pl;
+                    masked[1] += hs_popc<W>(v1) << pl;
+                }
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    int v = ok[h] ? d[h] - 2 * masked[h] : (MIN ? INT_MAX : 0);
+                    for (int off = 1; off < seg; off <<= 1) {
+                        const int o = __shfl_xor_sync(0xffffffffu, v, off);
+                        v = MIN ? min(v, o) : v + o;
+                    }
+                    const int tt0 = r0 + 32 * h;  // first row of this half step
+                    if (tt0 >= n_rows) continue;
+                    if (p.BS < 32) {
+                        // whole blocks inside the half step: the first lane of each writes
+                        const int j = m.j0 + blk[h];
+                        if (within[h] == 0 && blk[h] < p.bps && j < p.max_blocks)
+                            p.out[(int64_t)m.b * p.max_blocks + j] = ((m.valid_mask >> blk[h]) & 1u) ? v : -1;
+                    } else {
+                        agg = MIN ? min(agg, v) : agg + v;
+                        if ((tt0 + 32) % p.BS == 0) {  // the block ends with this half step
+                            const int bk = tt0 / p.BS, j = m.j0 + bk;
+                            if (lane == 0 && j < p.max_blocks)
+                                p.out[(int64_t)m.b * p.max_blocks + j] = ((m.valid_mask >> bk) & 1u) ? agg : -1;
+                            agg = MIN ? INT_MAX : 0;
+                        }
+                    }
+                }
+            }
+            if (!reissued) {
+                __syncwarp();
+                advance();
+            }
+        }
+    } else if constexpr (!MIN) {
         // lane <-> (block in stage, column); a column is one 32-bit word of one kv head
         const int RW = RW_T > 0 ? RW_T : p.RW;
         const int G = G_T > 0 ? G_T : p.G;
@@ -467,11 +637,21 @@ scan_ring_kernel(const RingParams p)
                 for (int i = 0; i < kMinRounds; ++i) {
                     const int tok = (r0 + i) * TS + slot;
                     int d = 0;
+                    if constexpr (G_T >= 2) {
+                        uint32_t v[4 * G_T];
 #pragma unroll
-                    for (int g = 0; g < GMAX; ++g)
-                        if (g < G)
-                            d += __popc(kb[i].x ^ qv[g].x) + __popc(kb[i].y ^ qv[g].y) + __popc(kb[i].z ^ qv[g].z) +
-                                 __popc(kb[i].w ^ qv[g].w);
+                        for (int g = 0; g < G_T; ++g) {
+                            v[4 * g + 0] = kb[i].x ^ qv[g].x; v[4 * g + 1] = kb[i].y ^ qv[g].y;
+                            v[4 * g + 2] = kb[i].z ^ qv[g].z; v[4 * g + 3] = kb[i].w ^ qv[g].w;
+                        }
+                        d = hs_popc<4 * G_T>(v);
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < GMAX; ++g)
+                            if (g < G)
+                                d += __popc(kb[i].x ^ qv[g].x) + __popc(kb[i].y ^ qv[g].y) + __popc(kb[i].z ^ qv[g].z) +
+                                     __popc(kb[i].w ^ qv[g].w);
+                    }
                     for (int off = 1; off < PW; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
                     best = min(best, tok < ntok ? d : INT_MAX);
                 }
@@ -499,14 +679,19 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
 {
     const int G = Hq / Hkv;
     const int64_t RW = (int64_t)Hkv * W;
-    if (!is_pow2(W) || !is_pow2(Hkv) || W > 32 || RW < 4 || RW > 1024) return UCMR_ERR_UNSUPPORTED;
-    if (G > kRingMaxG || B > kRingMaxBatch) return UCMR_ERR_UNSUPPORTED;
+    // MLA codes: one latent "head" of 576 bits; blocks of 8, 16 or a multiple of 32 tokens
+    const bool row_mode = Hkv == 1 && W == 18 && (BS % 32 == 0 || BS == 16 || BS == 8);
+    if (!row_mode && (!is_pow2(W) || !is_pow2(Hkv) || W > 32 || RW < 4 || RW > 1024)) return UCMR_ERR_UNSUPPORTED;
+    if ((row_mode ? G > 255 : G > kRingMaxG) || G < 1 || B > kRingMaxBatch) return UCMR_ERR_UNSUPPORTED;
     if (reinterpret_cast<uintptr_t>(codes) % 16 != 0) return UCMR_ERR_UNSUPPORTED;
     const int64_t block_bytes = (int64_t)BS * RW * 4;
     if (block_bytes % 16 != 0 || block_bytes > 32 * 1024) return UCMR_ERR_UNSUPPORTED;
     const bool is_min = reduce_mode == UCMR_REDUCE_MIN;
     int bps = 1;
-    if (is_min) {
+    if (row_mode) {
+        // several blocks per stage, scanned one after the other
+        while (bps < kRingMaxBps && block_bytes * (bps + 1) <= 16 * 1024) ++bps;
+    } else if (is_min) {
         if (W % 4 != 0 || reinterpret_cast<uintptr_t>(q) % 16 != 0) return UCMR_ERR_UNSUPPORTED;
         const int P = Hkv * (W / 4);
         if (P > 32) return UCMR_ERR_UNSUPPORTED;
@@ -524,7 +709,7 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     p.q = q; p.bt = bt; p.max_blocks = max_blocks; p.bt_stride = bt_stride; p.seq_lens = seq_lens; p.B = B;
     p.reduce_kvhead = reduce_kvhead ? 1 : 0; p.out = out; p.status = status; p.sched = sched;
     p.RW = (int)RW; p.bps = bps; p.block_bytes = (int)block_bytes;
-    if (block_bytes % 128 != 0) return UCMR_ERR_UNSUPPORTED;
+    if (block_bytes % (row_mode ? 16 : 128) != 0) return UCMR_ERR_UNSUPPORTED;
     if (!is_min && RW < 32 && BS > 240) return UCMR_ERR_UNSUPPORTED;
     p.block_stride = (int)block_bytes;
     p.stage_bytes = bps * p.block_stride;
@@ -540,18 +725,20 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     const int grid = (int)(max_items < sms ? (max_items > 0 ? max_items : 1) : sms);
 
     void (*kernel)(const RingParams) = nullptr;
-    if (is_min) {
+    if (row_mode) {
+        kernel = is_min ? scan_ring_kernel<true, 0, 0, 128, 18> : scan_ring_kernel<false, 0, 0, 128, 18>;
+    } else if (is_min) {
         switch (G) {
-            case 1: kernel = scan_ring_kernel<true, 0, 1, 128>; break;
-            case 2: kernel = scan_ring_kernel<true, 0, 2, 128>; break;
-            case 4: kernel = scan_ring_kernel<true, 0, 4, 128>; break;
-            case 8: kernel = scan_ring_kernel<true, 0, 8, 128>; break;
-            default: kernel = scan_ring_kernel<true, 0, 0, 128>;
+            case 1: kernel = scan_ring_kernel<true, 0, 1, 128, 0>; break;
+            case 2: kernel = scan_ring_kernel<true, 0, 2, 128, 0>; break;
+            case 4: kernel = scan_ring_kernel<true, 0, 4, 128, 0>; break;
+            case 8: kernel = scan_ring_kernel<true, 0, 8, 128, 0>; break;
+            default: kernel = scan_ring_kernel<true, 0, 0, 128, 0>;
         }
     } else {
         const bool short_blocks = BS <= 64;  // half-size register chunks (wide rows only)
 #define UCMR_RING_CASE(RWV, GV, CHV) \
-    if (p.RW == RWV && G == GV) kernel = scan_ring_kernel<false, RWV, GV, CHV>;
+    if (p.RW == RWV && G == GV) kernel = scan_ring_kernel<false, RWV, GV, CHV, 0>;
 #define UCMR_RING_ROW(RWV, CHV) \
     UCMR_RING_CASE(RWV, 1, CHV) UCMR_RING_CASE(RWV, 2, CHV) UCMR_RING_CASE(RWV, 4, CHV) UCMR_RING_CASE(RWV, 8, CHV)
         if (short_blocks) {
@@ -562,7 +749,7 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
         }
 #undef UCMR_RING_ROW
 #undef UCMR_RING_CASE
-        if (!kernel) kernel = scan_ring_kernel<false, 0, 0, 128>;
+        if (!kernel) kernel = scan_ring_kernel<false, 0, 0, 128, 0>;
     }
     // idempotent attribute, set on every call: cheap, and correct on every device of a process
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
