@@ -97,6 +97,21 @@ int ucmr_hash_encode_blocks(const void* k_cache, int64_t NB, int BS, int H, int6
                             int hash_bits, uint32_t* cache, int64_t NB_codes, int32_t* status_word,
                             void* stream);
 
+/*     Variants for code caches whose (token, head) row holds more than one code: the row has
+ *     row_words 32-bit words and this call's code goes to words [word_offset, word_offset +
+ *     hash_bits/32).  MLA keeps a 512-bit code of the latent vector and a 64-bit code of the rope part
+ *     side by side in rows of 18 words (the reference hashes them with two encoders and joins them with
+ *     vLLM's concat_and_cache_mla, gsa_on_device.py:426-455): two calls, word_offset 0 and 16.        */
+int ucmr_hash_encode_and_cache_at(const void* x, int64_t T, int H, int64_t stride_t, int64_t stride_h,
+                                  const void* R, int in_dim, int hash_bits, const void* slot_mapping,
+                                  int slot_is_int64, uint32_t* cache, int64_t NB, int BS, int row_words,
+                                  int word_offset, int32_t* status_word, void* stream);
+int ucmr_hash_encode_blocks_at(const void* k_cache, int64_t NB, int BS, int H, int64_t stride_block,
+                               int64_t stride_t, int64_t stride_h, const int32_t* block_ids,
+                               const int32_t* block_tokens, int64_t n_blocks, const void* R, int in_dim,
+                               int hash_bits, uint32_t* cache, int64_t NB_codes, int row_words,
+                               int word_offset, int32_t* status_word, void* stream);
+
 /*     The two encodes of one decode step in a single launch: the step's queries (as
  *     ucmr_hash_encode_query, hash_code at gsa_on_device.py:396-412) and its new key rows (as
  *     ucmr_hash_encode_and_cache, cache_k_hash_gqa_cuda at gsa_on_device.py:564-573).

@@ -5,12 +5,14 @@ from types import SimpleNamespace
 
 
 def make_vllm_config(model="meta-llama/Meta-Llama-3-8B", num_q_heads=32, num_kv_heads=8, head_size=128, block_size=128,
-                     max_model_len=8192, max_num_seqs=8, rank=0, overrides=None, dtype=None, device_type="cuda"):
+                     max_model_len=8192, max_num_seqs=8, rank=0, overrides=None, dtype=None, device_type="cuda",
+                     mla=False, enforce_eager=True):
     import torch
     model_config = SimpleNamespace(
-        model=model, is_deepseek_mla=False, max_model_len=max_model_len, dtype=dtype or torch.bfloat16,
-        enforce_eager=True, get_num_attention_heads=lambda pc: num_q_heads, get_num_kv_heads=lambda pc: num_kv_heads,
-        get_head_size=lambda: head_size)
+        model=model, is_deepseek_mla=mla, max_model_len=max_model_len, dtype=dtype or torch.bfloat16,
+        enforce_eager=enforce_eager, get_num_attention_heads=lambda pc: num_q_heads,
+        get_num_kv_heads=lambda pc: num_kv_heads, get_head_size=lambda: head_size,
+        hf_text_config=SimpleNamespace(kv_lora_rank=512, qk_rope_head_dim=64) if mla else SimpleNamespace())
     extra = {"ucm_sparse_config": {"GSAOnDevice": dict(overrides or {})}}
     return SimpleNamespace(
         model_config=model_config, parallel_config=SimpleNamespace(rank=rank),

@@ -266,3 +266,48 @@ def test_rehash_blocks_in_place(cuda_device, BS, Hh, dims, strided):
     rest = np.ones(NB, dtype=bool)
     rest[good] = False
     assert (got[rest] == 0).all()
+
+
+@pytest.mark.parametrize("in_dim,bits", [(512, 512), (256, 384), (128, 256), (384, 128)])
+def test_wide_projection_tensor_core_path(cuda_device, in_dim, bits):
+    """Projections wider than 128 x 128 with enough rows take the chunked tensor-core kernel (each CTA holds a
+    128-column chunk of R); rows with a stride, and a ragged last tile."""
+    import torch
+    from unified_cache_management_b200 import ops
+    rng = np.random.default_rng(in_dim + bits)
+    rows = 128 * 37 + 53
+    x = H.bf16_normal(rng, (rows, in_dim + 64))
+    r = _r_matrix(5, in_dim, bits)
+    xd = H.bf16_to_dev(x, cuda_device)[:, :in_dim]          # row stride in_dim + 64
+    out = ops.hash_encode(xd, H.bf16_to_dev(r, cuda_device))
+    torch.cuda.synchronize()
+    _check(H.dev_to_u32(out), x[:, :in_dim], r)
+
+
+def test_mla_rows_latent_and_rope_codes_side_by_side(cuda_device):
+    """512-bit and 64-bit codes written at words 0 and 16 of 18-word cache rows, through the slot mapping; enough
+    tokens for the tensor-core kernel on the latent part.  Skipped slots and the other rows stay untouched."""
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    rng = np.random.default_rng(99)
+    T, NB, BS = 3000, 64, 64
+    nope, rope = H.bf16_normal(rng, (T, 1, 512)), H.bf16_normal(rng, (T, 1, 64))
+    rn, rr = _r_matrix(6, 512, 512), _r_matrix(7, 64, 64)
+    slots = rng.permutation(NB * BS)[:T].astype(np.int64)
+    slots[5] = -1
+    slots[77] = NB * BS + 3
+    cache = torch.full((NB, BS, 1, 18), 0x5A5A5A5A, dtype=torch.int32, device=dev)
+    sd = torch.from_numpy(slots).to(dev)
+    ops.hash_encode_and_cache(H.bf16_to_dev(nope, dev), sd, cache, H.bf16_to_dev(rn, dev), word_offset=0)
+    ops.hash_encode_and_cache(H.bf16_to_dev(rope, dev), sd, cache, H.bf16_to_dev(rr, dev), word_offset=16)
+    torch.cuda.synchronize()
+    got = H.dev_to_u32(cache).reshape(NB * BS, 18)
+    ok = (slots >= 0) & (slots < NB * BS)
+    _check(got[slots[ok], :16], nope[ok, 0], rn)
+    _check(got[slots[ok], 16:], rope[ok, 0], rr)
+    rest = np.ones(NB * BS, dtype=bool)
+    rest[slots[ok]] = False
+    assert (got[rest] == 0x5A5A5A5A).all()
+    with pytest.raises(ValueError):
+        ops.hash_encode_and_cache(H.bf16_to_dev(rope, dev), sd, cache, H.bf16_to_dev(rr, dev), word_offset=17)

@@ -198,6 +198,125 @@ def test_prefix_cache_hit_rehashes_blocks_in_place(cuda_device):
     assert (codes[~touched] == 0).all()     # nothing else was written (the code cache starts zeroed)
 
 
+def test_mla_prefill_then_decode(cuda_device):
+    """MLA (DeepSeek) branch: latent + rope codes side by side in 18-word rows; the decode step swaps in the selected
+    block table, the shortened lengths and their scheduling metadata, and attention_finished swaps them back."""
+    import torch
+    from unified_cache_management_b200.base import UcmSparseRole
+    from unified_cache_management_b200.gsa_on_device import GSAOnDevice
+    dev = cuda_device
+    BS, Hq, red = 64, 16, 2
+    topk_tokens = 8 * BS
+    cfg = F.make_vllm_config(model="deepseek-ai/DeepSeek-V2-Lite-Chat", mla=True, block_size=BS, num_q_heads=Hq,
+                             num_kv_heads=1, head_size=576, max_model_len=64 * BS, max_num_seqs=4, enforce_eager=False,
+                             overrides=dict(vllm_hash_attention_topk=topk_tokens, gpu_seq_len_threshold=topk_tokens,
+                                            gpu_concurrency_threshold=1, vllm_hash_attention_rollback_layers=[0],
+                                            vllm_hash_attention_skip_layers=[False, False, True]))
+    plugin = GSAOnDevice(cfg, UcmSparseRole.WORKER)
+    assert plugin.is_mla and plugin.hash_reduction_head_num == red
+    n_req, NB, mb = 2, 120, 64
+    lens = [30 * BS + 5, 17 * BS]
+    rng = np.random.default_rng(11)
+    perm = rng.permutation(NB)
+    bt = np.zeros((n_req, mb), dtype=np.int32)
+    off = 0
+    for b, ln in enumerate(lens):
+        n = -(-(ln + 1) // BS)
+        bt[b, :n] = perm[off:off + n]
+        off += n
+    layers = [f"model.layers.{i}.self_attn.attn" for i in range(3)]
+    kv_caches = {name: torch.zeros((NB, BS, 576), dtype=torch.bfloat16, device=dev) for name in layers}
+    plugin.initialize_kv_hash_cache_tensors(kv_caches, dev)
+    layer = layers[1]
+    k_hash = kv_caches[layer][1]
+    assert kv_caches[layers[0]][1] is None and k_hash.shape == (NB, BS, 36) and k_hash.dtype == torch.bfloat16
+    requests = {f"r{b}": F.FakeRequest(num_computed_tokens=0, num_prompt_tokens=lens[b]) for b in range(n_req)}
+    input_batch = SimpleNamespace(req_id_to_index={f"r{b}": b for b in range(n_req)})
+
+    # ---- prefill ----------------------------------------------------------------------------------------
+    T = sum(lens)
+    nope = H.bf16_normal(rng, (T, 512))
+    rope = H.bf16_normal(rng, (T, 1, 64))
+    slots = np.concatenate([bt[b, np.arange(ln) // BS].astype(np.int64) * BS + np.arange(ln) % BS
+                            for b, ln in enumerate(lens)])
+    qsl = torch.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)).to(dev)
+    bt_dev = torch.from_numpy(bt).to(dev)
+    meta = SimpleNamespace(decode=None, prefill=SimpleNamespace(query_start_loc=qsl, block_table=bt_dev, chunked_context=None),
+                           slot_mapping=torch.from_numpy(slots).to(dev), query_start_loc=qsl)
+    fc = SimpleNamespace(attn_metadata={layer: meta}, no_compile_layers={}, virtual_engine=0)
+    so = F.scheduler_output({f"r{b}": lens[b] for b in range(n_req)})
+    plugin.update_states(so)
+    plugin.build_sparse_meta(so, requests, input_batch, {layer: meta})
+    plugin.attention_begin(None, H.bf16_to_dev(nope, dev), H.bf16_to_dev(rope, dev), layer, fc, phase="prefill",
+                           k_hash=k_hash)
+    plugin.attention_finished(None, None, None, None, layer, fc, phase="prefill")
+    plugin.execute_finished(None)
+    torch.cuda.synchronize()
+    rn = _bf16_bits(plugin.hash_encoder_nope.hash_weights_bf16)
+    rr = _bf16_bits(plugin.hash_encoder_rope.hash_weights_bf16)
+    codes = k_hash.view(torch.int32).cpu().numpy().view(np.uint32).reshape(NB * BS, 18)
+    _, p64 = O.hash_encode(nope, rn)
+    assert O.count_code_mismatches(codes[slots, :16], p64)[0] == 0
+    _, p64 = O.hash_encode(rope[:, 0], rr)
+    assert O.count_code_mismatches(codes[slots, 16:], p64)[0] == 0
+    untouched = np.ones(NB * BS, dtype=bool)
+    untouched[slots] = False
+    assert (codes[untouched] == 0).all()
+
+    # ---- decode -------------------------------------------------------------------------------------------
+    for r in requests.values():
+        r.num_computed_tokens = r.num_prompt_tokens
+    new_lens = np.array([ln + 1 for ln in lens], dtype=np.int32)
+    new_slots = np.array([bt[b, lens[b] // BS].astype(np.int64) * BS + lens[b] % BS for b in range(n_req)])
+    new_nope, new_rope = H.bf16_normal(rng, (n_req, 512)), H.bf16_normal(rng, (n_req, 1, 64))
+    q_nope, q_rope = H.bf16_normal(rng, (n_req, Hq, 512)), H.bf16_normal(rng, (n_req, Hq, 64))
+    seq_dev = torch.from_numpy(new_lens).to(dev)
+    plugin.mla_metadata_fn = lambda s, hq, hkv: (torch.full((4, 8), 7, dtype=torch.int32, device=dev),
+                                                 torch.arange(s.numel() + 1, dtype=torch.int32, device=dev))
+    topk_seq, topk_tiles, topk_splits = plugin.build_decode_hash(seq_dev)
+    assert np.array_equal(topk_seq.cpu().numpy(), O.update_seq_lens(new_lens, topk_tokens, BS))
+    tiles0 = torch.zeros((4, 8), dtype=torch.int32, device=dev)
+    splits0 = torch.zeros((n_req + 1,), dtype=torch.int32, device=dev)
+    topk_tiles, topk_splits, topk_seq = plugin.maybe_init_cudagraph_buffers_for_topk(n_req + 1, tiles0, topk_tiles,
+                                                                                     topk_splits, topk_seq)
+    dec = SimpleNamespace(block_table=bt_dev, seq_lens=seq_dev, topk_block_table=None, topk_seq_lens=topk_seq,
+                          topk_tile_scheduler_metadata=topk_tiles, topk_num_splits=topk_splits,
+                          tile_scheduler_metadata=tiles0, num_splits=splits0)
+    meta = SimpleNamespace(decode=dec, prefill=None, slot_mapping=torch.from_numpy(new_slots).to(dev),
+                           query_start_loc=torch.arange(n_req + 1, dtype=torch.int32, device=dev))
+    fc = SimpleNamespace(attn_metadata={layer: meta}, no_compile_layers={}, virtual_engine=0)
+    so = F.scheduler_output({f"r{b}": 1 for b in range(n_req)})
+    plugin.build_sparse_meta(so, requests, input_batch, {layer: meta})
+    assert plugin.gsa_enabled
+    plugin.attention_begin(None, H.bf16_to_dev(new_nope, dev), H.bf16_to_dev(new_rope, dev), layer, fc, phase="decode",
+                           k_hash=k_hash, decode_ql_nope=H.bf16_to_dev(q_nope, dev), decode_q_pe=H.bf16_to_dev(q_rope, dev))
+    torch.cuda.synchronize()
+    k = topk_tokens // BS
+    assert dec.seq_lens is topk_seq and dec.tile_scheduler_metadata is topk_tiles and dec.num_splits is topk_splits
+    sel = dec.block_table.cpu().numpy()
+    assert sel.shape == (n_req, k)
+
+    def pair_mean(x):   # heads h and h + Hq/red averaged: float32 sum, one rounding to bf16
+        f = O.bf16_bits_to_f32(x).reshape(n_req, red, Hq // red, -1)
+        return O.f32_to_bf16_bits((f.sum(axis=1, dtype=np.float32) / np.float32(red)).astype(np.float32))
+    qn, _ = O.hash_encode(pair_mean(q_nope), rn)
+    qr, _ = O.hash_encode(pair_mean(q_rope), rr)
+    q_codes = np.concatenate([qn, qr], axis=-1)                             # [B, 8, 18]
+    codes_now = k_hash.view(torch.int32).cpu().numpy().view(np.uint32).reshape(NB, BS, 1, 18)
+    ref = O.hamming_topk(codes_now, q_codes, bt, new_lens, k, O.REDUCE_MIN, False, sink_tokens=BS,
+                         recent_tokens=4 * BS)
+    assert np.array_equal(sel, ref["physical"][:, 0, :])
+    # the skip layer reuses the selection; attention_finished restores everything
+    plugin.attention_finished(None, None, None, None, layer, fc, phase="decode")
+    assert dec.block_table is bt_dev and dec.seq_lens is seq_dev and dec.tile_scheduler_metadata is tiles0
+    assert dec.num_splits is splits0
+    fc2 = SimpleNamespace(attn_metadata={layers[2]: meta}, no_compile_layers={}, virtual_engine=0)
+    plugin.attention_begin(None, None, None, layers[2], fc2, phase="decode", k_hash=None)
+    assert np.array_equal(dec.block_table.cpu().numpy(), sel)
+    plugin.attention_finished(None, None, None, None, layers[2], fc2, phase="decode")
+    assert dec.block_table is bt_dev
+
+
 def test_reference_hamming_topk_module_interface(cuda_device):
     """cuda_hamming_topk / update_seq_lens with the reference's argument list."""
     import torch

@@ -326,6 +326,194 @@ encode_tc_kernel(const __grid_constant__ CUtensorMap x_map, const EncParams p)
 }
 
 // ---------------------------------------------------------------------------------------------
+// tensor-core path for wide projections (in_dim and hash_bits multiples of 128, up to 512 x 512)
+// ---------------------------------------------------------------------------------------------
+// The MLA latent encoder is 512 -> 512 bits: 480 flop per byte of input, i.e. tensor-bound, and its R (512 KiB)
+// does not fit in shared memory.  Each CTA keeps one 128-column chunk of R^T resident (in_dim x 128, K-major,
+// swizzled: 128 KiB at in_dim 512) and streams token tiles through a ring of 128-row x 128-k stages,
+// accumulating the in_dim/128 slices of a tile in TMEM; the hash_bits/128 CTAs with consecutive block ids work
+// on the same token tile at about the same time, so the tile is fetched from HBM once and re-read from L2.
+// Same warp roles and barriers as encode_tc_kernel.  Output rows may be wider than the code (row_words,
+// word_offset): the chunk's four words go to words [word_offset + 4*chunk, +4) of the row.
+constexpr int kWideStages = 3;
+constexpr int kWideMaxK = 512;
+constexpr size_t kWideSmemBytes = 1024 + (size_t)(kWideMaxK / 64) * kEncHalfBytes + (size_t)kWideStages * kEncStageBytes + 256;
+
+struct WideParams {
+    int64_t rows;      // tokens (one row per token)
+    int64_t n_tiles;   // token tiles of 128
+    int K, N;          // in_dim, hash_bits
+    int n_chunks;      // N / 128
+    uint32_t* out;
+    int row_words, word_offset;
+    const void* slot_mapping;  // null = row t of out is token t
+    int slot_is_int64;
+    int64_t n_slots;
+    const __nv_bfloat16* R;    // [K, N] row-major
+    int32_t* status;
+};
+
+// Columns [n0, n0 + 128) of R[k][n] -> B[n][k], K-major, one 128-byte-swizzled [128 n][64 k] block per 64 k.
+__device__ __forceinline__ void build_rt_chunk_swizzled(uint8_t* s_b, const __nv_bfloat16* R, int K, int N, int n0,
+                                                        int tid, int nthreads)
+{
+    for (int blk = tid; blk < (K / 8) * (kEncBits / 8); blk += nthreads) {
+        const int kc = blk / (kEncBits / 8), nc = blk % (kEncBits / 8);
+        uint4 v[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            v[r] = __ldg(reinterpret_cast<const uint4*>(R + (size_t)(kc * 8 + r) * N + n0 + nc * 8));
+        const int half = kc >> 3, chunk = kc & 7;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+            uint4 o;
+            o.x = __byte_perm(reinterpret_cast<const uint32_t*>(&v[0])[j >> 1], reinterpret_cast<const uint32_t*>(&v[1])[j >> 1], sel);
+            o.y = __byte_perm(reinterpret_cast<const uint32_t*>(&v[2])[j >> 1], reinterpret_cast<const uint32_t*>(&v[3])[j >> 1], sel);
+            o.z = __byte_perm(reinterpret_cast<const uint32_t*>(&v[4])[j >> 1], reinterpret_cast<const uint32_t*>(&v[5])[j >> 1], sel);
+            o.w = __byte_perm(reinterpret_cast<const uint32_t*>(&v[6])[j >> 1], reinterpret_cast<const uint32_t*>(&v[7])[j >> 1], sel);
+            const int n = nc * 8 + j;
+            const uint32_t off = (uint32_t)half * kEncHalfBytes + (uint32_t)n * 128u + ((uint32_t)(chunk ^ (n & 7)) << 4);
+            *reinterpret_cast<uint4*>(s_b + off) = o;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kEncThreads, 1)
+encode_wide_kernel(const __grid_constant__ CUtensorMap x_map, const WideParams p)
+{
+    extern __shared__ uint8_t s_raw[];
+    uint8_t* s_base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(s_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* s_b = s_base;                                            // R^T chunk: K/64 blocks of [128 n][64 k]
+    uint8_t* s_a = s_base + (size_t)(kWideMaxK / 64) * kEncHalfBytes; // stages: 128 rows x 128 k
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_a + (size_t)kWideStages * kEncStageBytes);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + kWideStages;
+    uint64_t* acc_full = bars + 2 * kWideStages;
+    uint64_t* acc_empty = acc_full + kEncAccs;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kEncAccs);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int chunk = blockIdx.x % p.n_chunks;
+    const int k_slices = p.K / 128;
+
+    if (tid == 0) {
+        for (int s = 0; s < kWideStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < kEncAccs; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+        fence_mbar_init();
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&x_map) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)kEncTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    build_rt_chunk_swizzled(s_b, p.R, p.K, p.N, chunk * kEncBits, tid, kEncThreads);
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int64_t first = blockIdx.x / p.n_chunks, step = gridDim.x / p.n_chunks;
+    const int64_t my_tiles = first < p.n_tiles ? (p.n_tiles - first + step - 1) / step : 0;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int64_t slot_it = 0;
+            bool ok = true;
+            for (int64_t it = 0; it < my_tiles && ok; ++it) {
+                const int t0 = (int)((first + it * step) * kEncTileM);
+                for (int ks = 0; ks < k_slices; ++ks, ++slot_it) {
+                    const int s = (int)(slot_it % kWideStages);
+                    const uint32_t ph = (uint32_t)((slot_it / kWideStages) & 1);
+                    if (!mbar_wait(&empty[s], ph ^ 1u)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); ok = false; break; }
+                    uint8_t* dst = s_a + (size_t)s * kEncStageBytes;
+                    mbar_expect_tx(&full[s], kEncStageBytes);
+                    tma_load_3d(dst, &x_map, ks * 128, 0, t0, &full[s]);
+                    tma_load_3d(dst + kEncHalfBytes, &x_map, ks * 128 + 64, 0, t0, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t b_addr = smem_u32(s_b);
+            int64_t slot_it = 0;
+            bool ok = true;
+            for (int64_t it = 0; it < my_tiles && ok; ++it) {
+                const int a = (int)(it % kEncAccs);
+                const uint32_t aph = (uint32_t)((it / kEncAccs) & 1);
+                if (!mbar_wait(&acc_empty[a], aph ^ 1u)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
+                const uint32_t d_tmem = tmem_base + (uint32_t)(a * kEncBits);
+                for (int ks = 0; ks < k_slices; ++ks, ++slot_it) {
+                    const int s = (int)(slot_it % kWideStages);
+                    const uint32_t ph = (uint32_t)((slot_it / kWideStages) & 1);
+                    if (!mbar_wait(&full[s], ph)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(s_a + (size_t)s * kEncStageBytes);
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            const uint32_t a_off = (uint32_t)half * kEncHalfBytes + (uint32_t)kk * 32u;
+                            const uint32_t b_off = (uint32_t)(ks * 2 + half) * kEncHalfBytes + (uint32_t)kk * 32u;
+                            tc_mma_bf16(d_tmem, make_smem_desc_sw128(a_addr + a_off), make_smem_desc_sw128(b_addr + b_off),
+                                        kEncIdesc, (ks | half | kk) ? 1u : 0u);
+                        }
+                    }
+                    tc_commit(&empty[s]);
+                }
+                if (ok) tc_commit(&acc_full[a]);
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        for (int64_t it = 0; it < my_tiles; ++it) {
+            const int a = (int)(it % kEncAccs);
+            const uint32_t aph = (uint32_t)((it / kEncAccs) & 1);
+            if (!mbar_wait(&acc_full[a], aph)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kEncBits);
+            uint32_t code[4];
+            uint32_t r[32];
+            tc_ld32(taddr + 0, r);  tc_wait_ld(); code[0] = pack_signs(r);
+            tc_ld32(taddr + 32, r); tc_wait_ld(); code[1] = pack_signs(r);
+            tc_ld32(taddr + 64, r); tc_wait_ld(); code[2] = pack_signs(r);
+            tc_ld32(taddr + 96, r); tc_wait_ld(); code[3] = pack_signs(r);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[a]);
+            const int64_t row = (first + it * step) * kEncTileM + q * 32 + lane;
+            if (row < p.rows) {
+                int64_t dst = row;
+                if (p.slot_mapping != nullptr) {
+                    const int64_t slot = p.slot_is_int64 ? static_cast<const int64_t*>(p.slot_mapping)[row]
+                                                         : (int64_t) static_cast<const int32_t*>(p.slot_mapping)[row];
+                    dst = (slot >= 0 && slot < p.n_slots) ? slot : -1;
+                }
+                if (dst >= 0) {
+                    uint32_t* o = p.out + dst * p.row_words + p.word_offset + chunk * 4;
+                    if ((reinterpret_cast<uintptr_t>(o) & 7u) == 0) {
+                        reinterpret_cast<uint2*>(o)[0] = make_uint2(code[0], code[1]);
+                        reinterpret_cast<uint2*>(o)[1] = make_uint2(code[2], code[3]);
+                    } else {
+                        o[0] = code[0]; o[1] = code[1]; o[2] = code[2]; o[3] = code[3];
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kEncTmemCols)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // tensor-core path for small row counts: one 128-row tile per CTA, up to two jobs per launch
 // ---------------------------------------------------------------------------------------------
 // A decode step encodes a few hundred rows (the batch's query heads and its new key rows).  The persistent
@@ -526,6 +714,9 @@ struct SimtParams {
     int64_t stride_block, NB_src;
     int BS;
     int32_t* status;
+    // Output row layout: a (token, head) row of `out` has row_words words and this job's code goes to words
+    // [word_offset, word_offset + bits/32).  0 = rows of exactly bits/32 words (the plain layout).
+    int row_words, word_offset;
 };
 
 // Source token and destination slot of walk position t of a paged-source job; false = skip.
@@ -619,7 +810,7 @@ __global__ void __launch_bounds__(kSimtThreads) encode_simt_kernel(const SimtPar
                                                              : (int64_t) static_cast<const int32_t*>(p.slot_mapping)[t];
                         dst_row = (slot >= 0 && slot < p.n_slots) ? slot * H_out + ho : -1;
                     }
-                    if (dst_row >= 0) p.out[dst_row * W + w0 + c] = word;
+                    if (dst_row >= 0) p.out[dst_row * (p.row_words > 0 ? p.row_words : W) + p.word_offset + w0 + c] = word;
                 }
             }
         }
@@ -741,6 +932,50 @@ static int launch_tc_blocks(const void* x, int64_t NB, int BS, int H, int64_t st
     return launch_kernel(encode_tc_kernel, dim3(grid), dim3(kEncThreads), kEncSmemBytes, st, map, p);
 }
 
+// Wide tensor-core path: one row per token (H = 1), in_dim and hash_bits multiples of 128 up to 512, enough rows
+// to fill the GPU.  out rows have row_words words (0 = hash_bits/32), the code starts at word_offset.
+static bool wide_path_ok(const void* x, int64_t T, int H, int64_t stride_t, int in_dim, int bits, const void* R)
+{
+    if (H != 1 || in_dim % 128 != 0 || bits % 128 != 0 || in_dim > kWideMaxK || bits > 512) return false;
+    if (in_dim == kEncD && bits == kEncBits) return false;  // the 128 x 128 kernels are better there
+    if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || reinterpret_cast<uintptr_t>(R) % 16 != 0) return false;
+    if (stride_t % 8 != 0 || stride_t < in_dim || (uint64_t)stride_t * 2 >= (1ull << 40)) return false;
+    if (T < 2048 || T > 0x7FFFFFFF) return false;  // small jobs: the CUDA-core kernel has no set-up cost
+    return true;
+}
+
+static int launch_wide(const void* x, int64_t T, int64_t stride_t, const void* R, int in_dim, int bits, uint32_t* out,
+                       int row_words, int word_offset, const void* slot_mapping, int slot_is_int64, int64_t n_slots,
+                       int32_t* status, cudaStream_t st)
+{
+    EncodeTiledFn encode = get_encode_tiled();
+    if (!encode) return UCMR_ERR_LAUNCH;
+    CUtensorMap map;
+    const cuuint64_t dims[3] = {(cuuint64_t)in_dim, 1, (cuuint64_t)T};
+    const cuuint64_t strides[2] = {(cuuint64_t)in_dim * 2, (cuuint64_t)stride_t * 2};
+    const cuuint32_t box[3] = {64, 1, (cuuint32_t)kEncTileM};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(x), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return UCMR_ERR_LAUNCH;
+    WideParams p{};
+    p.rows = T; p.n_tiles = (T + kEncTileM - 1) / kEncTileM;
+    p.K = in_dim; p.N = bits; p.n_chunks = bits / kEncBits;
+    p.out = out; p.row_words = row_words > 0 ? row_words : bits / 32; p.word_offset = word_offset;
+    p.slot_mapping = slot_mapping; p.slot_is_int64 = slot_is_int64; p.n_slots = n_slots;
+    p.R = static_cast<const __nv_bfloat16*>(R); p.status = status;
+    cudaError_t e = cudaFuncSetAttribute(encode_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWideSmemBytes);
+    if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int64_t groups = sms / p.n_chunks;  // CTAs of a group share a token tile
+    if (groups > p.n_tiles) groups = p.n_tiles;
+    if (groups < 1) return UCMR_ERR_UNSUPPORTED;
+    const int grid = (int)(groups * p.n_chunks);
+    return launch_kernel(encode_wide_kernel, dim3(grid), dim3(kEncThreads), kWideSmemBytes, st, map, p);
+}
+
 // Shapes the one-tile-per-CTA tensor-core kernel accepts (any head count; 16-byte aligned rows).
 static bool tile_path_ok(const void* x, int64_t T, int H_in, int G, int64_t stride_t, int64_t stride_h, int in_dim,
                          int bits, const void* out, const void* R)
@@ -787,9 +1022,10 @@ static int launch_simt_params(const SimtParams& p, cudaStream_t st);
 
 static int launch_simt(const void* x, int64_t T, int H_in, int G, int64_t stride_t, int64_t stride_h, const void* R,
                        int in_dim, int bits, uint32_t* out, const void* slot_mapping, int slot_is_int64,
-                       int64_t n_slots, cudaStream_t st)
+                       int64_t n_slots, cudaStream_t st, int row_words = 0, int word_offset = 0)
 {
     SimtParams p{};
+    p.row_words = row_words; p.word_offset = word_offset;
     p.x = static_cast<const __nv_bfloat16*>(x); p.T = T; p.H_in = H_in; p.G = G;
     p.stride_t = stride_t; p.stride_h = stride_h;
     p.R = static_cast<const __nv_bfloat16*>(R); p.in_dim = in_dim; p.bits = bits;
@@ -849,6 +1085,8 @@ extern "C" int ucmr_hash_encode(const void* x, int64_t rows, int64_t row_stride,
         return launch_tc(x, rows, 1, row_stride, in_dim, R, codes_out, nullptr, 0, 0, status_word, st);
     if (tile_ok)
         return launch_tiles(make_job(x, rows, 1, 1, row_stride, in_dim, codes_out, nullptr, 0, 0), nullptr, R, status_word, st);
+    if (!force_simt() && wide_path_ok(x, rows, 1, row_stride, in_dim, hash_bits, R))
+        return launch_wide(x, rows, row_stride, R, in_dim, hash_bits, codes_out, 0, 0, nullptr, 0, 0, status_word, st);
     return launch_simt(x, rows, 1, 1, row_stride, in_dim, R, in_dim, hash_bits, codes_out, nullptr, 0, 0, st);
 }
 
@@ -874,18 +1112,29 @@ extern "C" int ucmr_hash_encode_query(const void* q, int64_t T, int Hq, int64_t 
     return launch_simt(q, T, Hq, group_mean, stride_t, stride_h, R, in_dim, hash_bits, codes_out, nullptr, 0, 0, st);
 }
 
-extern "C" int ucmr_hash_encode_and_cache(const void* x, int64_t T, int H, int64_t stride_t, int64_t stride_h,
-                                          const void* R, int in_dim, int hash_bits, const void* slot_mapping,
-                                          int slot_is_int64, uint32_t* cache, int64_t NB, int BS,
-                                          int32_t* status_word, void* stream)
+// row_words = 0: cache rows of exactly hash_bits/32 words.  Otherwise the code lands at words
+// [word_offset, word_offset + hash_bits/32) of rows of row_words words (CUDA-core kernel only).
+static int encode_and_cache_impl(const void* x, int64_t T, int H, int64_t stride_t, int64_t stride_h, const void* R,
+                                 int in_dim, int hash_bits, const void* slot_mapping, int slot_is_int64,
+                                 uint32_t* cache, int64_t NB, int BS, int row_words, int word_offset,
+                                 int32_t* status_word, void* stream)
 {
     if (!x || !R || !slot_mapping || !cache || T < 0 || H <= 0 || NB <= 0 || BS <= 0) return UCMR_ERR_BAD_ARG;
     if (stride_h < in_dim || stride_t < in_dim) return UCMR_ERR_BAD_ARG;
     int rc = check_dims(in_dim, hash_bits);
     if (rc != UCMR_OK) return rc;
+    if (row_words < 0 || word_offset < 0 || (row_words > 0 && word_offset + hash_bits / 32 > row_words) ||
+        (row_words == 0 && word_offset != 0))
+        return UCMR_ERR_BAD_ARG;
     if (T == 0) return UCMR_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int64_t n_slots = NB * BS;
+    if (!force_simt() && wide_path_ok(x, T, H, stride_t, in_dim, hash_bits, R))
+        return launch_wide(x, T, stride_t, R, in_dim, hash_bits, cache, row_words, word_offset, slot_mapping,
+                           slot_is_int64 ? 1 : 0, n_slots, status_word, st);
+    if (row_words > 0 && !(row_words == hash_bits / 32 && word_offset == 0))
+        return launch_simt(x, T, H, 1, stride_t, stride_h, R, in_dim, hash_bits, cache, slot_mapping,
+                           slot_is_int64 ? 1 : 0, n_slots, st, row_words, word_offset);
     const bool tile_ok = !force_simt() && tile_path_ok(x, T, H, 1, stride_t, stride_h, in_dim, hash_bits, cache, R);
     const bool tc_ok = !force_simt() && tc_path_ok(x, T, H, stride_t, stride_h, in_dim, hash_bits) &&
                        reinterpret_cast<uintptr_t>(cache) % 16 == 0 && reinterpret_cast<uintptr_t>(R) % 16 == 0;
@@ -897,6 +1146,25 @@ extern "C" int ucmr_hash_encode_and_cache(const void* x, int64_t T, int H, int64
         return launch_tc(x, T, H, stride_t, stride_h, R, cache, slot_mapping, slot_is_int64 ? 1 : 0, n_slots, status_word, st);
     return launch_simt(x, T, H, 1, stride_t, stride_h, R, in_dim, hash_bits, cache, slot_mapping,
                        slot_is_int64 ? 1 : 0, n_slots, st);
+}
+
+extern "C" int ucmr_hash_encode_and_cache(const void* x, int64_t T, int H, int64_t stride_t, int64_t stride_h,
+                                          const void* R, int in_dim, int hash_bits, const void* slot_mapping,
+                                          int slot_is_int64, uint32_t* cache, int64_t NB, int BS,
+                                          int32_t* status_word, void* stream)
+{
+    return encode_and_cache_impl(x, T, H, stride_t, stride_h, R, in_dim, hash_bits, slot_mapping, slot_is_int64, cache,
+                                 NB, BS, 0, 0, status_word, stream);
+}
+
+extern "C" int ucmr_hash_encode_and_cache_at(const void* x, int64_t T, int H, int64_t stride_t, int64_t stride_h,
+                                             const void* R, int in_dim, int hash_bits, const void* slot_mapping,
+                                             int slot_is_int64, uint32_t* cache, int64_t NB, int BS, int row_words,
+                                             int word_offset, int32_t* status_word, void* stream)
+{
+    if (row_words <= 0) return UCMR_ERR_BAD_ARG;
+    return encode_and_cache_impl(x, T, H, stride_t, stride_h, R, in_dim, hash_bits, slot_mapping, slot_is_int64, cache,
+                                 NB, BS, row_words, word_offset, status_word, stream);
 }
 
 extern "C" int ucmr_hash_encode_decode_step(const void* q, int64_t Tq, int Hq, int64_t q_stride_t, int64_t q_stride_h,
@@ -926,13 +1194,16 @@ extern "C" int ucmr_hash_encode_decode_step(const void* q, int64_t Tq, int Hq, i
                                   status_word, stream);
 }
 
-extern "C" int ucmr_hash_encode_blocks(const void* k_cache, int64_t NB, int BS, int H, int64_t stride_block,
-                                       int64_t stride_t, int64_t stride_h, const int32_t* block_ids,
-                                       const int32_t* block_tokens, int64_t n_blocks, const void* R, int in_dim,
-                                       int hash_bits, uint32_t* cache, int64_t NB_codes, int32_t* status_word,
-                                       void* stream)
+static int encode_blocks_impl(const void* k_cache, int64_t NB, int BS, int H, int64_t stride_block, int64_t stride_t,
+                              int64_t stride_h, const int32_t* block_ids, const int32_t* block_tokens, int64_t n_blocks,
+                              const void* R, int in_dim, int hash_bits, uint32_t* cache, int64_t NB_codes, int row_words,
+                              int word_offset, int32_t* status_word, void* stream)
 {
     if (!k_cache || !R || !cache || NB <= 0 || BS <= 0 || H <= 0 || NB_codes <= 0 || n_blocks < 0) return UCMR_ERR_BAD_ARG;
+    if (row_words < 0 || word_offset < 0 || (row_words > 0 && word_offset + hash_bits / 32 > row_words) ||
+        (row_words == 0 && word_offset != 0))
+        return UCMR_ERR_BAD_ARG;
+    const bool plain_rows = row_words == 0 || (row_words == hash_bits / 32 && word_offset == 0);
     if (n_blocks > 0 && !block_ids) return UCMR_ERR_BAD_ARG;
     if (stride_h < in_dim || stride_t < in_dim || stride_block < stride_t) return UCMR_ERR_BAD_ARG;
     int rc = check_dims(in_dim, hash_bits);
@@ -940,7 +1211,7 @@ extern "C" int ucmr_hash_encode_blocks(const void* k_cache, int64_t NB, int BS, 
     if (n_blocks == 0) return UCMR_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int64_t n_slots = NB_codes * BS;
-    if (!force_simt() && tc_blocks_path_ok(k_cache, NB, BS, H, stride_block, stride_t, stride_h, in_dim, hash_bits) &&
+    if (plain_rows && !force_simt() && tc_blocks_path_ok(k_cache, NB, BS, H, stride_block, stride_t, stride_h, in_dim, hash_bits) &&
         reinterpret_cast<uintptr_t>(cache) % 16 == 0 && reinterpret_cast<uintptr_t>(R) % 16 == 0)
         return launch_tc_blocks(k_cache, NB, BS, H, stride_block, stride_t, stride_h, block_ids, block_tokens, n_blocks,
                                 R, cache, n_slots, status_word, st);
@@ -951,5 +1222,27 @@ extern "C" int ucmr_hash_encode_blocks(const void* k_cache, int64_t NB, int BS, 
     p.out = cache; p.n_slots = n_slots;
     p.src_blocks = block_ids; p.block_tokens = block_tokens; p.stride_block = stride_block; p.NB_src = NB; p.BS = BS;
     p.status = status_word;
+    p.row_words = plain_rows ? 0 : row_words; p.word_offset = plain_rows ? 0 : word_offset;
     return launch_simt_params(p, st);
+}
+
+extern "C" int ucmr_hash_encode_blocks(const void* k_cache, int64_t NB, int BS, int H, int64_t stride_block,
+                                       int64_t stride_t, int64_t stride_h, const int32_t* block_ids,
+                                       const int32_t* block_tokens, int64_t n_blocks, const void* R, int in_dim,
+                                       int hash_bits, uint32_t* cache, int64_t NB_codes, int32_t* status_word,
+                                       void* stream)
+{
+    return encode_blocks_impl(k_cache, NB, BS, H, stride_block, stride_t, stride_h, block_ids, block_tokens, n_blocks, R,
+                              in_dim, hash_bits, cache, NB_codes, 0, 0, status_word, stream);
+}
+
+extern "C" int ucmr_hash_encode_blocks_at(const void* k_cache, int64_t NB, int BS, int H, int64_t stride_block,
+                                          int64_t stride_t, int64_t stride_h, const int32_t* block_ids,
+                                          const int32_t* block_tokens, int64_t n_blocks, const void* R, int in_dim,
+                                          int hash_bits, uint32_t* cache, int64_t NB_codes, int row_words,
+                                          int word_offset, int32_t* status_word, void* stream)
+{
+    if (row_words <= 0) return UCMR_ERR_BAD_ARG;
+    return encode_blocks_impl(k_cache, NB, BS, H, stride_block, stride_t, stride_h, block_ids, block_tokens, n_blocks, R,
+                              in_dim, hash_bits, cache, NB_codes, row_words, word_offset, status_word, stream);
 }

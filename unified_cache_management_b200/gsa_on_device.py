@@ -1,4 +1,4 @@
-"""``GSAOnDevice`` sparse-attention plugin on the sm_100a retrieval kernels (CUDA, GQA models).
+"""``GSAOnDevice`` sparse-attention plugin on the sm_100a retrieval kernels (CUDA; GQA and MLA models).
 
 Drop-in for the reference plugin of the same name
 (``ucm/sparse/gsa_on_device/gsa_on_device.py:99-1421``): same ``UcmSparseBase`` hooks with the same
@@ -12,7 +12,11 @@ prefill/decode bookkeeping.  What changed is underneath:
   gather), into persistent buffers, so the step is CUDA-graph friendly;
 * nothing is imported from vLLM at module scope, and nothing else of the reference package is needed.
 
-MLA models (576-bit codes, FlashMLA metadata rebuild) are not served by this class yet.
+MLA models (DeepSeek: one latent kv head, 512-bit code of the latent + 64-bit code of the rope part per token)
+follow the reference's CUDA MLA branch (gsa_on_device.py:221-233, 375-394, 426-455, 667-714, 1083-1096): two
+encoders write side by side into 18-word cache rows, the decode step retrieves with the token-row scan, and the
+FlashMLA scheduling metadata of the shortened sequences comes from vLLM's ``get_mla_metadata`` (imported when
+first needed; ``mla_metadata_fn`` can be set instead).
 """
 from __future__ import annotations
 
@@ -80,8 +84,6 @@ class GSAOnDevice(UcmSparseBase):
         self.gsa_enabled = False
         if vllm_config.device_config.device_type != "cuda":
             raise ValueError(f"Unsupported device type: {vllm_config.device_config.device_type}")
-        if self.is_mla:
-            raise NotImplementedError("MLA models are not served by the B200 GSAOnDevice plugin yet")
         self.is_cuda = True
         self.device = torch.device(f"cuda:{self.rank}")
 
@@ -131,6 +133,13 @@ class GSAOnDevice(UcmSparseBase):
         max_block_per_seq = cdiv(self.max_num_tokens, self.block_size)
         self.max_block_per_seq = max_block_per_seq
         dev = self.device
+        self.origin_tile_scheduler_metadata = None
+        self.origin_num_splits = None
+        self.mla_metadata_fn = None  # get_mla_metadata(seq_lens, num_q_heads, num_kv_heads); vLLM's when None
+        if self.is_mla:
+            self._init_mla(vllm_config, cfg, max_block_per_seq)
+            self.init_for_pc()
+            return
         self.full_block_table = torch.zeros((self.max_batch_size, max_block_per_seq), dtype=torch.int32, device=dev)
         self.full_seq_lens = torch.zeros((self.max_batch_size,), dtype=torch.int32, device=dev)
         self.head_dim = vllm_config.model_config.get_head_size()
@@ -147,6 +156,37 @@ class GSAOnDevice(UcmSparseBase):
             new_seq_lens=torch.zeros((self.max_batch_size,), dtype=torch.int32, device=dev))
         self.init_for_pc()
 
+    def _init_mla(self, vllm_config, cfg, max_block_per_seq):
+        """Two encoders (latent and rope part), persistent retrieval buffers and, for CUDA-graph runs, the
+        fixed-address copies of the shortened-sequence scheduling metadata (gsa_on_device.py:167-185, 210-233)."""
+        dev = self.device
+        hf = vllm_config.model_config.hf_text_config
+        self.hash_reduction_head_num = cfg.vllm_hash_attention_reduction_head_num or 1
+        self.kv_lora_rank = getattr(hf, "kv_lora_rank", None)
+        self.qk_rope_head_dim = getattr(hf, "qk_rope_head_dim", None)
+        if not self.kv_lora_rank or not self.qk_rope_head_dim:
+            raise ValueError("MLA model config lacks kv_lora_rank / qk_rope_head_dim")
+        dtype = vllm_config.model_config.dtype
+        self.hash_encoder_nope = HashEncoder(input_dim=self.kv_lora_rank, hash_bits=self.kv_lora_rank, dtype=dtype,
+                                             device=dev)
+        self.hash_encoder_rope = HashEncoder(input_dim=self.qk_rope_head_dim, hash_bits=self.qk_rope_head_dim,
+                                             dtype=dtype, device=dev)
+        self.nope_words = self.kv_lora_rank // 32
+        self.rope_words = self.qk_rope_head_dim // 32
+        self.topk_blocks = self.hash_topk_tokens // self.block_size
+        kb = min(self.topk_blocks, max_block_per_seq)
+        self._workspace = ops.new_workspace(self.max_batch_size, 1, max_block_per_seq, dev, False)
+        self._retrieval = ops.Retrieval(
+            physical=torch.zeros((self.max_batch_size, 1, kb), dtype=torch.int32, device=dev),
+            logical=torch.zeros((self.max_batch_size, 1, kb), dtype=torch.int32, device=dev), scores=None,
+            valid_count=torch.zeros((self.max_batch_size,), dtype=torch.int32, device=dev),
+            new_seq_lens=torch.zeros((self.max_batch_size,), dtype=torch.int32, device=dev))
+        if not getattr(vllm_config.model_config, "enforce_eager", True):
+            num_sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            self.cg_buf_topk_tile_scheduler_metadata = torch.zeros((num_sms, 8), device=dev, dtype=torch.int32)
+            self.cg_buf_topk_num_splits = torch.empty((self.max_batch_size + 1,), device=dev, dtype=torch.int32)
+            self.cg_buf_topk_seq_lens = torch.empty((self.max_batch_size + 1,), device=dev, dtype=torch.int32)
+
     # ---- prefix-cache bookkeeping buffers (gsa_on_device.py:333-360) ------------------------------
     def init_for_pc(self):
         self.prefix_slot_mapping_buf = torch.empty(self.max_num_tokens * self.max_batch_size, device=self.device,
@@ -159,7 +199,20 @@ class GSAOnDevice(UcmSparseBase):
     # ---- hashing ---------------------------------------------------------------------------------
     def hash_code(self, nope=None, rope=None, reduction_head_num: int = 1, query: Optional[torch.Tensor] = None):
         """GQA branch of the reference (gsa_on_device.py:396-412): one code per kv head from the mean of
-        its query group.  Returns the packed codes viewed as bf16, like the reference."""
+        its query group.  MLA branch (:375-394): heads h, h + H/r, ... are averaged first (r =
+        ``reduction_head_num``), then the latent and the rope part are hashed by their own encoders.  Returns the
+        packed codes viewed as bf16, like the reference."""
+        if self.is_mla:
+            if nope is None or rope is None:
+                raise ValueError("MLA mode requires `nope` and `rope`.")
+            if reduction_head_num > 1:
+                nope = nope.view(nope.shape[0], reduction_head_num, nope.shape[1] // reduction_head_num,
+                                 nope.shape[2]).mean(dim=1)
+                rope = rope.view(rope.shape[0], reduction_head_num, rope.shape[1] // reduction_head_num,
+                                 rope.shape[2]).mean(dim=1)
+            hash_nope = self.hash_encoder_nope.compute_hash(nope)
+            hash_rope = self.hash_encoder_rope.compute_hash(rope)
+            return hash_nope.view(torch.bfloat16), hash_rope.view(torch.bfloat16)
         if query is None:
             raise ValueError("GQA mode requires `query`.")
         if self.num_q_heads > self.num_key_heads:
@@ -194,6 +247,97 @@ class GSAOnDevice(UcmSparseBase):
             # gsa_on_device.py:574-588; here one kernel reads the blocks where they lie)
             self.hash_encoder.compute_hash_of_blocks(k_pool, self.prefix_block_ids, k_hash,
                                                      block_tokens=self.prefix_block_tokens)
+
+    def _mla_code_cache_words(self, k_hash):
+        """The MLA code cache [NB, BS, 36] bf16 as words [NB, BS, 1, 18]."""
+        cw = ops.as_words(k_hash)
+        return cw.unsqueeze(2) if cw.dim() == 3 else cw
+
+    def cache_k_hash_mla_cuda(self, nope, rope, k_hash, attn_metadata, forward_context, layer_name):
+        """Latent code to words [0, 16), rope code to words [16, 18) of each token's cache row: the reference
+        hashes both and joins them with vLLM's concat_and_cache_mla (gsa_on_device.py:426-455)."""
+        slot_mapping = attn_metadata.slot_mapping.flatten()
+        n = slot_mapping.numel()
+        cw = self._mla_code_cache_words(k_hash)
+        enc_n, enc_r = self.hash_encoder_nope, self.hash_encoder_rope
+        nope3 = nope.reshape(nope.shape[0], 1, nope.shape[-1])[:n]
+        rope3 = rope.reshape(rope.shape[0], 1, rope.shape[-1])[:n]
+        ops.hash_encode_and_cache(enc_n._as_bf16(nope3), slot_mapping, cw, enc_n.hash_weights_bf16, word_offset=0)
+        ops.hash_encode_and_cache(enc_r._as_bf16(rope3), slot_mapping, cw, enc_r.hash_weights_bf16,
+                                  word_offset=self.nope_words)
+        if self.has_pc_hit:
+            # the hit's latent + rope vectors are already in the paged cache [NB, BS, 512 + 64]
+            attn = forward_context.no_compile_layers[layer_name]
+            kv = attn.kv_cache[forward_context.virtual_engine][0]
+            kv4 = kv.unsqueeze(2) if kv.dim() == 3 else kv
+            ids = self.prefix_block_ids.to(torch.int32)
+            ops.hash_encode_blocks(kv4[..., : self.kv_lora_rank], ids, cw, enc_n.hash_weights_bf16,
+                                   block_tokens=self.prefix_block_tokens, word_offset=0)
+            ops.hash_encode_blocks(kv4[..., self.kv_lora_rank:], ids, cw, enc_r.hash_weights_bf16,
+                                   block_tokens=self.prefix_block_tokens, word_offset=self.nope_words)
+
+    def update_decode_topk_mla_cuda(self, is_rollback_layer, is_skip_hash_layer, attn_metadata, decode_ql_nope,
+                                    decode_q_pe, k_hash):
+        """Reference: gsa_on_device.py:667-714.  The decode metadata carries the shortened sequence lengths and
+        their FlashMLA scheduling data (built once per step by ``build_decode_hash``); this swaps them in
+        together with the selected block table, ``attention_finished`` swaps them back."""
+        if is_rollback_layer:
+            return
+        dec = attn_metadata.decode
+        if is_skip_hash_layer:
+            assert dec.topk_block_table is not None
+            block_table = dec.topk_block_table
+        else:
+            q_nope_hash, q_rope_hash = self.hash_code(nope=decode_ql_nope, rope=decode_q_pe,
+                                                      reduction_head_num=self.hash_reduction_head_num)
+            q_hash = ops.as_words(torch.cat([q_nope_hash, q_rope_hash], dim=-1))       # [B, heads/r, 18]
+            n = q_hash.shape[0]
+            kb = self._retrieval.physical.shape[2]
+            out = ops.Retrieval(physical=self._retrieval.physical[:n], logical=self._retrieval.logical[:n],
+                                scores=None, valid_count=self._retrieval.valid_count[:n],
+                                new_seq_lens=self._retrieval.new_seq_lens[:n])
+            ops.hamming_topk(self._mla_code_cache_words(k_hash), q_hash, dec.block_table, dec.seq_lens, kb,
+                             reduce=self.gsa_on_device_config.reduce, reduce_kvhead=False,
+                             workspace=self._workspace, out=out, want_scores=False, **self._forced())
+            block_table = out.physical[:, 0, :]
+            dec.topk_block_table = block_table
+        self.ori_block_table_decode = dec.block_table
+        self.ori_seq_lens_decode = dec.seq_lens
+        self.origin_tile_scheduler_metadata = dec.tile_scheduler_metadata
+        self.origin_num_splits = dec.num_splits
+        dec.block_table = block_table
+        dec.seq_lens = dec.topk_seq_lens
+        dec.tile_scheduler_metadata = dec.topk_tile_scheduler_metadata
+        dec.num_splits = dec.topk_num_splits
+
+    def build_decode_hash(self, seq_lens):
+        """Shortened sequence lengths of a decode step and FlashMLA's scheduling metadata for them
+        (gsa_on_device.py:1083-1096); called by the patched FlashMLA metadata builder."""
+        topk_seq_lens = update_seq_lens(seq_lens, topk_token=self.hash_topk_tokens, block_size=self.block_size)
+        fn = self.mla_metadata_fn
+        if fn is None:
+            try:
+                from vllm.attention.ops.flashmla import get_mla_metadata as fn
+            except Exception as exc:  # the scheduling metadata is FlashMLA's own format: no stand-in
+                raise RuntimeError("vLLM's FlashMLA ops (vllm.attention.ops.flashmla.get_mla_metadata) are needed "
+                                   "for MLA decode metadata; set plugin.mla_metadata_fn otherwise") from exc
+        topk_tile_scheduler_metadata, topk_num_splits = fn(topk_seq_lens, self.num_q_heads, 1)
+        return topk_seq_lens, topk_tile_scheduler_metadata, topk_num_splits
+
+    def maybe_init_cudagraph_buffers_for_topk(self, n, tile_scheduler_metadata, topk_tile_scheduler_metadata,
+                                              topk_num_splits, topk_seq_lens):
+        """Copies the step's metadata into fixed-address buffers for CUDA-graph replays (gsa_on_device.py:1382-1405)."""
+        sm_parts = tile_scheduler_metadata.size(0)
+        view = self.cg_buf_topk_tile_scheduler_metadata[:sm_parts]
+        view.copy_(topk_tile_scheduler_metadata)
+        topk_tile_scheduler_metadata = view
+        view = self.cg_buf_topk_num_splits[:n]
+        view.copy_(topk_num_splits)
+        self.cg_buf_topk_num_splits[n:].fill_(topk_num_splits[-1])
+        topk_num_splits = view
+        view = self.cg_buf_topk_seq_lens[: topk_seq_lens.size(0)]
+        view.copy_(topk_seq_lens)
+        return topk_tile_scheduler_metadata, topk_num_splits, view
 
     # ---- retrieval ---------------------------------------------------------------------------------
     def _forced(self):
@@ -235,8 +379,16 @@ class GSAOnDevice(UcmSparseBase):
         is_rollback_layer, is_skip_hash_layer = self.get_layer_state(layer_name)
         # key codes are cached even while retrieval is off, so that it can switch on later
         if not is_rollback_layer and not is_skip_hash_layer:
-            self.cache_k_hash_gqa_cuda(key, attn_metadata, k_hash, forward_context, layer_name)
+            if self.is_mla:
+                self.cache_k_hash_mla_cuda(key, value, k_hash, attn_metadata, forward_context, layer_name)
+            else:
+                self.cache_k_hash_gqa_cuda(key, attn_metadata, k_hash, forward_context, layer_name)
         if not self.gsa_enabled:
+            return query, key, value, output
+        if self.is_mla:
+            if phase == "decode":
+                self.update_decode_topk_mla_cuda(is_rollback_layer, is_skip_hash_layer, attn_metadata, decode_ql_nope,
+                                                 decode_q_pe, k_hash)
             return query, key, value, output
         if self.has_decode and not is_rollback_layer:
             if is_skip_hash_layer:
@@ -250,6 +402,16 @@ class GSAOnDevice(UcmSparseBase):
         if not self.gsa_enabled:
             return
         attn_metadata = self.get_layer_attn_metadata(forward_context, layer_name)
+        if self.is_mla:
+            if phase == "decode":
+                is_rollback_layer, _ = self.get_layer_state(layer_name)
+                if not is_rollback_layer:
+                    dec = attn_metadata.decode
+                    dec.block_table = self.ori_block_table_decode
+                    dec.seq_lens = self.ori_seq_lens_decode
+                    dec.tile_scheduler_metadata = self.origin_tile_scheduler_metadata
+                    dec.num_splits = self.origin_num_splits
+            return
         if self.has_decode:
             is_rollback_layer, _ = self.get_layer_state(layer_name)
             if not is_rollback_layer:
@@ -282,7 +444,7 @@ class GSAOnDevice(UcmSparseBase):
         for layer_name, kv_cache in kv_caches.items():
             is_rollback_layer, is_skip_hash_layer = self.get_layer_state(layer_name)
             if not is_rollback_layer and not is_skip_hash_layer:
-                shape = list(kv_cache[0].shape)
+                shape = list((kv_cache if self.is_mla else kv_cache[0]).shape)
                 shape[-1] //= dtype.itemsize * 8
                 khash_cache = torch.zeros(shape, dtype=dtype, device=device)
             else:
@@ -304,6 +466,40 @@ class GSAOnDevice(UcmSparseBase):
         token_block_numbers = prefix_block_ids.index_select(0, block_indices)
         return num_prefix_tokens, num_prefix_blocks, prefix_block_ids, token_block_numbers * block_size + block_offsets
 
+    def get_seq_lens(self, attn_metadata):
+        """Sequence lengths of the step (gsa_on_device.py:1211-1233); MLA metadata keeps them per phase."""
+        if not self.is_mla:
+            return getattr(attn_metadata, "seq_lens", None)
+        dec = getattr(attn_metadata, "decode", None)
+        if dec is not None:
+            return getattr(dec, "seq_lens", None)
+        pre = getattr(attn_metadata, "prefill", None)
+        if pre is None:
+            return None
+        chunked = getattr(pre, "chunked_context", None)
+        if chunked is not None:
+            return getattr(chunked, "seq_lens", None)
+        qsl = getattr(pre, "query_start_loc", None)
+        if qsl is not None:
+            return qsl[1:] - qsl[:-1]
+        return getattr(pre, "seq_lens", None)
+
+    def get_block_table_row(self, attn_metadata, req_row_id, qlen):
+        """Block-table row of a request (gsa_on_device.py:1176-1209): MLA splits the table by phase."""
+        if not self.is_mla:
+            return attn_metadata.block_table[req_row_id]
+        dec = getattr(attn_metadata, "decode", None)
+        pre = getattr(attn_metadata, "prefill", None)
+        num_decode_rows = int(dec.block_table.size(0)) if dec is not None else 0
+        if qlen == 1 and dec is not None and req_row_id < num_decode_rows:
+            return dec.block_table[req_row_id]
+        if pre is not None:
+            local = req_row_id - num_decode_rows
+            if 0 <= local < int(pre.block_table.size(0)):
+                return pre.block_table[local]
+        raise RuntimeError(f"Failed to resolve MLA block_table row for request: req_row_id={req_row_id}, qlen={qlen}, "
+                           f"num_decode_rows={num_decode_rows}")
+
     def prepare_cuda_decode_sparse_meta(self, attn_metadata, num_decodes):
         n = self.num_reqs
         self.full_seq_lens[:n].copy_(attn_metadata.seq_lens[:n], True)
@@ -323,7 +519,7 @@ class GSAOnDevice(UcmSparseBase):
         self.num_reqs = len(scheduler_output.num_scheduled_tokens)
         if isinstance(attn_metadata, dict):
             attn_metadata = next(iter(attn_metadata.values()))
-        seq_lens = getattr(attn_metadata, "seq_lens", None)
+        seq_lens = self.get_seq_lens(attn_metadata)
         if seq_lens is None:
             return None
         # retrieval is on only when enough long requests run together (one host sync per step)
@@ -349,8 +545,10 @@ class GSAOnDevice(UcmSparseBase):
                 ext_tokens = int(ext_tokens_map.get(req_id, 0))
                 if ext_tokens > 0:
                     (n_tok, n_blk, blk_ids, slots) = self.rebuild_prefix_cache_info_for_req(
-                        block_table_row=attn_metadata.block_table[req_row_id], num_prompt_tokens=req.num_prompt_tokens,
-                        qlen=int(compute_q_lens[req_row_id]), block_size=self.block_size)
+                        block_table_row=self.get_block_table_row(attn_metadata, req_row_id,
+                                                                 int(compute_q_lens[req_row_id])),
+                        num_prompt_tokens=req.num_prompt_tokens, qlen=int(compute_q_lens[req_row_id]),
+                        block_size=self.block_size)
                     self.prefix_slot_mapping_buf[all_prefix_tokens: all_prefix_tokens + n_tok] = slots
                     self.prefix_block_ids_buf[all_prefix_blocks: all_prefix_blocks + n_blk] = blk_ids
                     self.prefix_block_tokens_buf[all_prefix_blocks: all_prefix_blocks + n_blk] = self.block_size
@@ -365,7 +563,7 @@ class GSAOnDevice(UcmSparseBase):
             self.prefix_slot_mapping = self.prefix_slot_mapping_buf[:all_prefix_tokens]
             self.prefix_block_ids = self.prefix_block_ids_buf[:all_prefix_blocks]
             self.prefix_block_tokens = self.prefix_block_tokens_buf[:all_prefix_blocks]
-        if not self.gsa_enabled:
+        if self.is_mla or not self.gsa_enabled:
             return None
         self.has_decode = num_decodes > 0
         self.decode_only = self.has_decode and (num_decodes == self.num_reqs)

@@ -47,6 +47,9 @@ SIGNATURES = {
     "ucmr_hash_encode_query": (_i, [_vp, _i64, _i, _i64, _i64, _i, _vp, _i, _i, _vp, _vp, _vp]),
     "ucmr_hash_encode_and_cache": (_i, [_vp, _i64, _i, _i64, _i64, _vp, _i, _i, _vp, _i, _vp, _i64, _i, _vp, _vp]),
     "ucmr_hash_encode_blocks": (_i, [_vp, _i64, _i, _i, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _i, _i, _vp, _i64, _vp, _vp]),
+    "ucmr_hash_encode_and_cache_at": (_i, [_vp, _i64, _i, _i64, _i64, _vp, _i, _i, _vp, _i, _vp, _i64, _i, _i, _i, _vp, _vp]),
+    "ucmr_hash_encode_blocks_at": (_i, [_vp, _i64, _i, _i, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _i, _i, _vp, _i64, _i, _i,
+                                        _vp, _vp]),
     "ucmr_hash_encode_decode_step": (_i, [_vp, _i64, _i, _i64, _i64, _i, _vp, _vp, _i64, _i, _i64, _i64, _vp, _i, _vp, _i64,
                                           _i, _vp, _i, _i, _vp, _vp]),
     "ucmr_hamming_topk_workspace_bytes": (_sz, [_i, _i, _i, _i]),

@@ -123,9 +123,10 @@ def hash_encode_query(q: torch.Tensor, r: torch.Tensor, group_mean: int = 1,
 
 
 def hash_encode_and_cache(x: torch.Tensor, slot_mapping: torch.Tensor, cache: torch.Tensor, r: torch.Tensor,
-                          status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                          status: Optional[torch.Tensor] = None, word_offset: Optional[int] = None) -> torch.Tensor:
     """Encode x bf16 [T, H, in_dim] and scatter token t's codes to slot ``slot_mapping[t]`` of the paged
-    cache [NB, BS, H, W] (int32 words, or any dtype that views to them)."""
+    cache [NB, BS, H, W] (int32 words, or any dtype that views to them).  With ``word_offset`` the cache rows
+    may be wider than one code (W >= word_offset + hash_bits/32) and the code lands at that word."""
     _need_cuda("x", x, torch.bfloat16, contiguous=False)
     if x.dim() != 3 or x.stride(2) != 1:
         raise ValueError(f"x must be [T,H,K] with a unit inner stride, got {tuple(x.shape)}")
@@ -136,9 +137,17 @@ def hash_encode_and_cache(x: torch.Tensor, slot_mapping: torch.Tensor, cache: to
     cw = as_words(cache)
     t, h, in_dim = x.shape
     bits = _check_r(r, in_dim)
+    lib = _l.load_library()
+    if word_offset is not None:
+        if cw.dim() != 4 or cw.shape[2] != h or word_offset < 0 or word_offset + bits // 32 > cw.shape[3]:
+            raise ValueError(f"cache shape {tuple(cw.shape)} cannot hold {bits // 32} words at word {word_offset}")
+        _l.check(lib.ucmr_hash_encode_and_cache_at(_ptr(x), t, h, x.stride(0), x.stride(1), _ptr(r), in_dim, bits,
+                                                   _ptr(slot_mapping), int(slot_mapping.dtype == torch.int64), _ptr(cw),
+                                                   cw.shape[0], cw.shape[1], cw.shape[3], int(word_offset), _ptr(status),
+                                                   _stream(x)), "ucmr_hash_encode_and_cache_at")
+        return cache
     if cw.dim() != 4 or cw.shape[2] != h or cw.shape[3] != bits // 32:
         raise ValueError(f"cache shape {tuple(cw.shape)} does not match [NB, BS, {h}, {bits // 32}]")
-    lib = _l.load_library()
     _l.check(lib.ucmr_hash_encode_and_cache(_ptr(x), t, h, x.stride(0), x.stride(1), _ptr(r), in_dim, bits,
                                             _ptr(slot_mapping), int(slot_mapping.dtype == torch.int64), _ptr(cw),
                                             cw.shape[0], cw.shape[1], _ptr(status), _stream(x)),
@@ -147,7 +156,8 @@ def hash_encode_and_cache(x: torch.Tensor, slot_mapping: torch.Tensor, cache: to
 
 
 def hash_encode_blocks(k_cache: torch.Tensor, block_ids: torch.Tensor, cache: torch.Tensor, r: torch.Tensor,
-                       block_tokens: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       block_tokens: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
+                       word_offset: Optional[int] = None) -> torch.Tensor:
     """Re-hash key blocks in place of the paged K cache: for every listed block id, encode its first
     ``block_tokens[i]`` tokens (all of them when None) of k_cache bf16 [NB, BS, H, in_dim] into the same block of the
     code cache [NB_codes, BS, H, W].  No gathered copy of the keys is made."""
@@ -165,9 +175,19 @@ def hash_encode_blocks(k_cache: torch.Tensor, block_ids: torch.Tensor, cache: to
     cw = as_words(cache)
     nb, bs, h, in_dim = k_cache.shape
     bits = _check_r(r, in_dim)
+    lib = _l.load_library()
+    if word_offset is not None:  # rows wider than one code, see hash_encode_and_cache
+        if (cw.dim() != 4 or cw.shape[1] != bs or cw.shape[2] != h or word_offset < 0
+                or word_offset + bits // 32 > cw.shape[3]):
+            raise ValueError(f"cache shape {tuple(cw.shape)} cannot hold {bits // 32} words at word {word_offset}")
+        _l.check(lib.ucmr_hash_encode_blocks_at(_ptr(k_cache), nb, bs, h, k_cache.stride(0), k_cache.stride(1),
+                                                k_cache.stride(2), _ptr(block_ids), _ptr(block_tokens),
+                                                block_ids.numel(), _ptr(r), in_dim, bits, _ptr(cw), cw.shape[0],
+                                                cw.shape[3], int(word_offset), _ptr(status), _stream(k_cache)),
+                 "ucmr_hash_encode_blocks_at")
+        return cache
     if cw.dim() != 4 or cw.shape[1] != bs or cw.shape[2] != h or cw.shape[3] != bits // 32:
         raise ValueError(f"cache shape {tuple(cw.shape)} does not match [*, {bs}, {h}, {bits // 32}]")
-    lib = _l.load_library()
     _l.check(lib.ucmr_hash_encode_blocks(_ptr(k_cache), nb, bs, h, k_cache.stride(0), k_cache.stride(1),
                                          k_cache.stride(2), _ptr(block_ids), _ptr(block_tokens), block_ids.numel(),
                                          _ptr(r), in_dim, bits, _ptr(cw), cw.shape[0], _ptr(status), _stream(k_cache)),
