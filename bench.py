@@ -308,9 +308,11 @@ def run_profile_case(what: str) -> None:
     def rnd_codes(shape):
         return torch.randint(-2**31, 2**31 - 1, shape, dtype=torch.int32, device=dev, generator=g)
 
-    if what in ("scan", "scan_min", "select", "scan_256bit"):
+    if what in ("scan", "scan_min", "select", "scan_256bit", "scan_mla"):
         if what == "scan_256bit":
             B, Hkv, Hq, W, BS, seq, k = 2, 8, 32, 8, 64, 262144, 256     # million-token shard shape
+        elif what == "scan_mla":
+            B, Hkv, Hq, W, BS, seq, k = 16, 1, 64, 18, 64, 131072, 32    # MLA: 576-bit codes, 64 query codes: 151 MB
         else:
             B, Hkv, Hq, W, BS, seq, k = 8, 8, 32, 4, 128, 131072, 16     # half of the benchmark batch: 134 MB
         mb = seq // BS
@@ -320,12 +322,18 @@ def run_profile_case(what: str) -> None:
         sl = torch.full((B,), seq, dtype=torch.int32, device=dev)
         ws = ops.new_workspace(B, Hkv, mb, dev)
         for _ in range(3):
-            ops.hamming_topk(codes, q, bt, sl, k, reduce="min" if what == "scan_min" else "sum",
+            ops.hamming_topk(codes, q, bt, sl, k, reduce="min" if what in ("scan_min", "scan_mla") else "sum",
                              must_select=MUST_SELECT, workspace=ws)
     elif what == "encode":
         x = torch.randn((65536, 8, 128), device=dev, dtype=torch.bfloat16)          # 134 MB of keys
         r = (torch.randn((128, 128), device=dev) / 128 ** 0.5).to(torch.bfloat16)
         out = torch.empty((65536, 8, 4), dtype=torch.int32, device=dev)
+        for _ in range(3):
+            ops.hash_encode(x, r, out=out)
+    elif what == "encode_wide":
+        x = torch.randn((262144, 512), device=dev, dtype=torch.bfloat16)            # MLA latent vectors: 268 MB
+        r = (torch.randn((512, 512), device=dev) / 512 ** 0.5).to(torch.bfloat16)
+        out = torch.empty((262144, 16), dtype=torch.int32, device=dev)
         for _ in range(3):
             ops.hash_encode(x, r, out=out)
     elif what == "encode_step":
