@@ -258,6 +258,18 @@ int ucmr_gather_kv(const void* k_pool, const void* v_pool, int64_t NB, int64_t b
                    int64_t row_bytes, void* out_k, void* out_v, int32_t* status_word,
                    void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ *  Block copies through pointer lists, on the bulk-copy engine.
+ *     Stands in for the three CudaSMCopyAsync / CudaCopyKernel overloads
+ *     (ucm/shared/trans/cuda/cuda_sm_kernel.cu:52-114) that land store-loaded blocks: `num` blocks of
+ *     `size` bytes (a multiple of 16) go from src_ptrs[i] (a DEVICE array of pointers) or from
+ *     src_base + i*size to dst_ptrs[i] or dst_base + i*size.  Exactly one of src_ptrs / src_base and one
+ *     of dst_ptrs / dst_base is non-NULL.  List entries that are NULL or not 16-byte aligned are skipped
+ *     and flagged (UCMR_DEV_BAD_BLOCK_ID) in status_word.
+ * ------------------------------------------------------------------------------------------ */
+int ucmr_copy_blocks(const void* const* src_ptrs, const void* src_base, void* const* dst_ptrs, void* dst_base,
+                     int64_t size, int64_t num, int32_t* status_word, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -90,3 +90,50 @@ def test_retrieve_then_gather_round_trip(cuda_device):
                          must_select=(0, -2, -1))
     assert np.array_equal(gk.view(torch.int16).cpu().numpy().view(np.uint16), O.gather_kv(kp, ref["physical"][:, 0]))
     assert np.array_equal(gv.view(torch.int16).cpu().numpy().view(np.uint16), O.gather_kv(vp, ref["physical"][:, 0]))
+
+
+@pytest.mark.parametrize("size", [256 * 1024, 48 * 1024 + 16, 4096])
+def test_copy_blocks_pointer_lists(cuda_device, size):
+    """The three pointer-list copies of the reference's landing path: list -> list, list -> contiguous,
+    contiguous -> list; a null and a misaligned entry are skipped and flagged."""
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    g = torch.Generator(device=dev).manual_seed(size)
+    num, pool_blocks = 37, 90
+    pool = torch.randint(0, 256, (pool_blocks, size), dtype=torch.uint8, device=dev, generator=g)
+    land = torch.zeros((pool_blocks, size), dtype=torch.uint8, device=dev)
+    src_ids = torch.randperm(pool_blocks, generator=torch.Generator().manual_seed(1))[:num]
+    dst_ids = torch.randperm(pool_blocks, generator=torch.Generator().manual_seed(2))[:num]
+    sp = torch.tensor([pool.data_ptr() + int(i) * size for i in src_ids], dtype=torch.int64, device=dev)
+    dp = torch.tensor([land.data_ptr() + int(i) * size for i in dst_ids], dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.copy_blocks(size, num, src_ptrs=sp, dst_ptrs=dp, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(land[dst_ids.to(dev)], pool[src_ids.to(dev)])
+    untouched = torch.ones(pool_blocks, dtype=torch.bool, device=dev)
+    untouched[dst_ids.to(dev)] = False
+    assert int(land[untouched].sum().item()) == 0
+    flat = torch.zeros((num, size), dtype=torch.uint8, device=dev)
+    ops.copy_blocks(size, num, src_ptrs=sp, dst=flat, status=status)
+    torch.cuda.synchronize()
+    assert torch.equal(flat, pool[src_ids.to(dev)])
+    land.zero_()
+    ops.copy_blocks(size, num, src=flat, dst_ptrs=dp, status=status)
+    torch.cuda.synchronize()
+    assert torch.equal(land[dst_ids.to(dev)], flat) and int(status.item()) == 0
+    # bad entries
+    land.zero_()
+    sp_bad = sp.clone()
+    sp_bad[3] = 0
+    sp_bad[5] += 8
+    ops.copy_blocks(size, num, src_ptrs=sp_bad, dst_ptrs=dp, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) & 1
+    ok = torch.ones(num, dtype=torch.bool)
+    ok[3] = ok[5] = False
+    assert torch.equal(land[dst_ids[ok].to(dev)], pool[src_ids[ok].to(dev)])
+    assert int(land[dst_ids[~ok].to(dev)].sum().item()) == 0
+    with pytest.raises(ValueError):
+        ops.copy_blocks(size, num, src_ptrs=sp, src=flat, dst=flat)

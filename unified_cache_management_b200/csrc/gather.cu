@@ -10,6 +10,8 @@
 // Device-to-device form of the reference's kv_cache[block_ids]
 // (ucm/sparse/gsa_on_device/gsa_on_device.py:579-580) and of CudaCopyKernel's
 // scattered-blocks-to-one-buffer overload (ucm/shared/trans/cuda/cuda_sm_kernel.cu:66-78).
+// ucmr_copy_blocks is the pointer-list form of all three CudaCopyKernel overloads (:52-92: list -> list,
+// list -> contiguous, contiguous -> list) on the same copy-engine loop.
 #include "common.cuh"
 
 namespace ucmr {
@@ -29,23 +31,12 @@ struct GatherParams {
     int32_t* status;
 };
 
-__global__ void __launch_bounds__(32) gather_blocks_kernel(const GatherParams p)
-{
-    extern __shared__ __align__(128) char s_buf[];
-    __shared__ __align__(8) uint64_t s_full[kGatherStages];
-    if (threadIdx.x != 0) return;  // a single thread drives the copy engine
-
-    for (int s = 0; s < kGatherStages; ++s) mbar_init(&s_full[s], 1);
-    fence_mbar_init();
-
-    const int64_t total = p.n_sel * p.n_pools * p.chunks_per_block;
-    const int64_t first = blockIdx.x, step = gridDim.x;
-    const int64_t my_count = first < total ? (total - first + step - 1) / step : 0;
-    constexpr int AHEAD = kGatherStages - kGatherLag;  // loads in flight before the first store
-    bool dead = false;
-
-    auto locate = [&](int64_t i, const char*& src, char*& dst, uint32_t& bytes) -> bool {
-        const int64_t c = first + i * step;
+// Where chunk c of a copy job comes from and goes to; false = skip it (bad id / misaligned pointer, flagged).
+struct GatherLocator {
+    GatherParams p;
+    __device__ int64_t total() const { return p.n_sel * p.n_pools * p.chunks_per_block; }
+    __device__ bool operator()(int64_t c, const char*& src, char*& dst, uint32_t& bytes) const
+    {
         const int chunk = (int)(c % p.chunks_per_block);
         const int64_t t = c / p.chunks_per_block;
         const int which = (int)(t % p.n_pools);
@@ -58,7 +49,57 @@ __global__ void __launch_bounds__(32) gather_blocks_kernel(const GatherParams p)
         src = p.pool[which] + (int64_t)phys * p.block_bytes + off;
         dst = p.out[which] + s * p.block_bytes + off;
         return true;
-    };
+    }
+    __device__ int32_t* status() const { return p.status; }
+};
+
+// Pointer-list form: block i goes from src_ptrs[i] (or src_base + i*size) to dst_ptrs[i] (or dst_base + i*size).
+struct CopyListParams {
+    const void* const* src_ptrs;
+    const char* src_base;
+    void* const* dst_ptrs;
+    char* dst_base;
+    int64_t size, num;
+    int chunks_per_block;
+    int32_t* status;
+};
+
+struct ListLocator {
+    CopyListParams p;
+    __device__ int64_t total() const { return p.num * p.chunks_per_block; }
+    __device__ bool operator()(int64_t c, const char*& src, char*& dst, uint32_t& bytes) const
+    {
+        const int chunk = (int)(c % p.chunks_per_block);
+        const int64_t i = c / p.chunks_per_block;
+        const int64_t off = (int64_t)chunk * kGatherChunk;
+        const int64_t left = p.size - off;
+        bytes = (uint32_t)(left < kGatherChunk ? left : kGatherChunk);
+        const char* sb = p.src_ptrs ? static_cast<const char*>(p.src_ptrs[i]) : p.src_base + i * p.size;
+        char* db = p.dst_ptrs ? static_cast<char*>(p.dst_ptrs[i]) : p.dst_base + i * p.size;
+        // the copy engine needs 16-byte aligned addresses; a null or misaligned entry is skipped and flagged
+        if (!sb || !db || (reinterpret_cast<uintptr_t>(sb) & 15u) || (reinterpret_cast<uintptr_t>(db) & 15u)) return false;
+        src = sb + off;
+        dst = db + off;
+        return true;
+    }
+    __device__ int32_t* status() const { return p.status; }
+};
+
+template <typename Locator>
+__global__ void __launch_bounds__(32) bulk_copy_kernel(const Locator loc)
+{
+    extern __shared__ __align__(128) char s_buf[];
+    __shared__ __align__(8) uint64_t s_full[kGatherStages];
+    if (threadIdx.x != 0) return;  // a single thread drives the copy engine
+
+    for (int s = 0; s < kGatherStages; ++s) mbar_init(&s_full[s], 1);
+    fence_mbar_init();
+
+    const int64_t total = loc.total();
+    const int64_t first = blockIdx.x, step = gridDim.x;
+    const int64_t my_count = first < total ? (total - first + step - 1) / step : 0;
+    constexpr int AHEAD = kGatherStages - kGatherLag;  // loads in flight before the first store
+    bool dead = false;
 
     for (int64_t it = 0; it < my_count + AHEAD; ++it) {
         if (it < my_count && !dead) {
@@ -66,11 +107,11 @@ __global__ void __launch_bounds__(32) gather_blocks_kernel(const GatherParams p)
             // the store that last read this stage was committed LAG groups ago
             if (it >= kGatherStages) bulk_wait_read<kGatherLag - 1>();
             const char* src; char* dst; uint32_t bytes;
-            if (locate(it, src, dst, bytes)) {
+            if (loc(first + it * step, src, dst, bytes)) {
                 mbar_expect_tx(&s_full[stage], bytes);
                 bulk_g2s(s_buf + (size_t)stage * kGatherChunk, src, bytes, &s_full[stage]);
             } else {
-                flag_status(p.status, UCMR_DEV_BAD_BLOCK_ID);
+                flag_status(loc.status(), UCMR_DEV_BAD_BLOCK_ID);
                 mbar_arrive(&s_full[stage]);  // keep the phase sequence; nothing is stored for it
             }
         }
@@ -79,16 +120,29 @@ __global__ void __launch_bounds__(32) gather_blocks_kernel(const GatherParams p)
             const int stage = (int)(c % kGatherStages);
             const uint32_t parity = (uint32_t)((c / kGatherStages) & 1);
             if (!mbar_wait(&s_full[stage], parity)) {
-                flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT);
+                flag_status(loc.status(), UCMR_DEV_WAIT_TIMEOUT);
                 dead = true;
             } else {
                 const char* src; char* dst; uint32_t bytes;
-                if (locate(c, src, dst, bytes)) bulk_s2g(dst, s_buf + (size_t)stage * kGatherChunk, bytes);
+                if (loc(first + c * step, src, dst, bytes)) bulk_s2g(dst, s_buf + (size_t)stage * kGatherChunk, bytes);
                 bulk_commit();  // one group per chunk, empty or not, so the wait counts stay aligned
             }
         }
     }
     bulk_wait_all<0>();
+}
+
+template <typename Locator>
+static int launch_bulk_copy(const Locator& loc, int64_t total_chunks, cudaStream_t st)
+{
+    const size_t smem = (size_t)kGatherStages * kGatherChunk;
+    cudaError_t e = cudaFuncSetAttribute(bulk_copy_kernel<Locator>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = (int)(total_chunks < sms ? total_chunks : sms);
+    bulk_copy_kernel<Locator><<<grid, 32, smem, st>>>(loc);
+    return check_launch();
 }
 
 struct GatherRowsParams {
@@ -168,19 +222,7 @@ extern "C" int ucmr_gather_kv(const void* k_pool, const void* v_pool, int64_t NB
         p.n_pools = n; p.NB = NB; p.block_bytes = block_bytes; p.sel = sel; p.n_sel = (int64_t)B * k;
         p.chunks_per_block = (int)((block_bytes + kGatherChunk - 1) / kGatherChunk);
         p.status = status_word;
-        const size_t smem = (size_t)kGatherStages * kGatherChunk;
-        static bool attr_set = false;  // idempotent attribute; a race only repeats the call
-        if (!attr_set) {
-            cudaError_t e = cudaFuncSetAttribute(gather_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
-            attr_set = true;
-        }
-        const int64_t total = p.n_sel * n * p.chunks_per_block;
-        int dev = 0, sms = 148;
-        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        int grid = (int)(total < sms ? total : sms);
-        gather_blocks_kernel<<<grid, 32, smem, st>>>(p);
-        return check_launch();
+        return launch_bulk_copy(GatherLocator{p}, p.n_sel * n * p.chunks_per_block, st);
     }
 
     if (BS <= 0 || Hkv <= 0 || row_bytes <= 0 || row_bytes % 16 != 0) return UCMR_ERR_UNSUPPORTED;
@@ -195,4 +237,21 @@ extern "C" int ucmr_gather_kv(const void* k_pool, const void* v_pool, int64_t NB
     if (grid < 1) grid = 1;
     gather_rows_kernel<<<grid, 256, 0, st>>>(p);
     return check_launch();
+}
+
+extern "C" int ucmr_copy_blocks(const void* const* src_ptrs, const void* src_base, void* const* dst_ptrs, void* dst_base,
+                                int64_t size, int64_t num, int32_t* status_word, void* stream)
+{
+    if ((src_ptrs == nullptr) == (src_base == nullptr) || (dst_ptrs == nullptr) == (dst_base == nullptr)) return UCMR_ERR_BAD_ARG;
+    if (size <= 0 || num < 0) return UCMR_ERR_BAD_ARG;
+    if (size % 16 != 0) return UCMR_ERR_UNSUPPORTED;
+    if ((src_base && reinterpret_cast<uintptr_t>(src_base) % 16) || (dst_base && reinterpret_cast<uintptr_t>(dst_base) % 16))
+        return UCMR_ERR_UNSUPPORTED;
+    if (num == 0) return UCMR_OK;
+    CopyListParams p{};
+    p.src_ptrs = src_ptrs; p.src_base = static_cast<const char*>(src_base);
+    p.dst_ptrs = dst_ptrs; p.dst_base = static_cast<char*>(dst_base);
+    p.size = size; p.num = num; p.chunks_per_block = (int)((size + kGatherChunk - 1) / kGatherChunk);
+    p.status = status_word;
+    return launch_bulk_copy(ListLocator{p}, num * p.chunks_per_block, static_cast<cudaStream_t>(stream));
 }

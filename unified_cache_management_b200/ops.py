@@ -506,3 +506,26 @@ def gather_kv(k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], se
                                               int(per_head), bs, hkv, row_bytes, _ptr(out_k), _ptr(out_v),
                                               _ptr(status), _stream(pool)), "ucmr_gather_kv")
     return out_k, out_v
+
+
+def copy_blocks(size: int, num: int, *, src_ptrs: Optional[torch.Tensor] = None, src: Optional[torch.Tensor] = None,
+                dst_ptrs: Optional[torch.Tensor] = None, dst: Optional[torch.Tensor] = None,
+                status: Optional[torch.Tensor] = None) -> None:
+    """``num`` blocks of ``size`` bytes through the copy engine: from the addresses in ``src_ptrs`` (int64 CUDA tensor
+    of device pointers) or from the contiguous tensor ``src``, to the addresses in ``dst_ptrs`` or the contiguous
+    ``dst``.  The three forms of the reference's CudaSMCopyAsync."""
+    if (src_ptrs is None) == (src is None) or (dst_ptrs is None) == (dst is None):
+        raise ValueError("give exactly one of src_ptrs / src and one of dst_ptrs / dst")
+    ref = src_ptrs if src_ptrs is not None else src
+    for name, t in (("src_ptrs", src_ptrs), ("dst_ptrs", dst_ptrs)):
+        if t is not None:
+            _need_cuda(name, t, torch.int64)
+            if t.numel() < num:
+                raise ValueError(f"{name} holds fewer than {num} pointers")
+    for name, t in (("src", src), ("dst", dst)):
+        if t is not None:
+            _need_cuda(name, t)
+            if t.numel() * t.element_size() < size * num:
+                raise ValueError(f"{name} is smaller than {num} blocks of {size} bytes")
+    _l.check(_l.load_library().ucmr_copy_blocks(_ptr(src_ptrs), _ptr(src), _ptr(dst_ptrs), _ptr(dst), int(size),
+                                                int(num), _ptr(status), _stream(ref)), "ucmr_copy_blocks")
