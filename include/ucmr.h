@@ -270,6 +270,41 @@ int ucmr_gather_kv(const void* k_pool, const void* v_pool, int64_t NB, int64_t b
 int ucmr_copy_blocks(const void* const* src_ptrs, const void* src_base, void* const* dst_ptrs, void* dst_base,
                      int64_t size, int64_t num, int32_t* status_word, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ *  Float block retrieval (the ESA / KVStar plugins' CPU path, on the device).
+ *
+ *  ucmr_block_repr_mean: representation of KV blocks = mean of the keys over groups of `merge` tokens
+ *     (merge = BS: one vector per block, ucm/sparse/esa/esa.py:254-263; smaller: ucm/sparse/kvstar/
+ *     multistep.py:322-327).  k_cache bf16 [NB, BS, row_elems] with strides in elements; for listed
+ *     block i, out[i, m, :] = mean of tokens [m*merge, (m+1)*merge), float32 accumulation, bf16 result.
+ *     out is [n_blocks, BS/merge, row_elems] bf16.
+ *  ucmr_dot_topk: per request b the k candidates with the largest inner product <q[b], repr[idx]>,
+ *     idx running over indexes[b, 0..n) (entries < 0 or >= N are not candidates) - what the reference's
+ *     RetrievalWorkerBackend computes on worker threads (ucm/sparse/esa/retrieval/cpy/
+ *     retrieval_backend.cpp:206-225).  repr bf16 [N, dim], q bf16 [B, dim], float32 accumulation.
+ *     out_scores float32 / out_ids int32 [B, k]: the chosen candidates in the order of the index list
+ *     (the reference returns them by descending score), equal scores go to the earlier candidate,
+ *     missing entries are (-inf, -1).  workspace: ucmr_dot_topk_workspace_bytes(B, n) bytes.
+ * ------------------------------------------------------------------------------------------ */
+int ucmr_block_repr_mean(const void* k_cache, int64_t NB, int BS, int row_elems, int64_t stride_block,
+                         int64_t stride_t, const int32_t* block_ids, int64_t n_blocks, int merge, void* out,
+                         int32_t* status_word, void* stream);
+size_t ucmr_dot_topk_workspace_bytes(int B, int n);
+int ucmr_dot_topk(const void* repr, int64_t N, int dim, const void* q, const int32_t* indexes, int B, int n,
+                  int k, float* out_scores, int32_t* out_ids, void* workspace, size_t workspace_bytes,
+                  void* stream);
+
+/*  ucmr_softmax_topk: KVStar's block scores for one request (ucm/sparse/kvstar/retrieve/core/domain/
+ *     retrieve_task/simd_compute_kernel.cpp:884-960): repr bf16 [n_blocks*M, Hkv, D] (M representations per
+ *     block), q bf16 [X, Hq, D] (X query tokens); for every (token, query head) the inner products with the
+ *     representations of its kv head, a softmax over all n_blocks*M of them, and score(block) = sum over
+ *     rows and over the block's M representations of the softmax.  out_block_scores float32 [n_blocks]
+ *     (may be NULL); the k best blocks go to out_scores / out_ids [k] in ascending block order.        */
+size_t ucmr_softmax_topk_workspace_bytes(int X, int Hq, int n_blocks, int M);
+int ucmr_softmax_topk(const void* repr, int n_blocks, int M, int Hkv, int D, const void* q, int X, int Hq, int k,
+                      float* out_block_scores, float* out_scores, int32_t* out_ids, void* workspace,
+                      size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -407,3 +407,58 @@ def merge_topk(cand_scores, cand_ids, k):
             out_s[bi, hi, :len(order)] = s[order]
             out_i[bi, hi, :len(order)] = i[order]
     return out_s, out_i
+
+
+# ----------------------------------------------------------------------------------------------
+# float block retrieval (ESA / KVStar plugins)
+# ----------------------------------------------------------------------------------------------
+def block_repr_mean(k_bf16: np.ndarray, block_ids, merge: int = 0):
+    """Mean key over groups of ``merge`` tokens of each listed block (0 = the whole block): esa.py:254-263
+    (``k_cache[ids].mean(1)``) and kvstar/multistep.py:322-327 (``reshape(n, M, c, h, d).mean(dim=2)``).
+    k_bf16 uint16 [NB, BS, H, D].  Returns (bf16 bits [n, BS/merge, H, D], float64 means): torch accumulates in
+    float32 and rounds once; the float64 mean is kept to tell a rounding tie from an error."""
+    k = bf16_bits_to_f32(np.asarray(k_bf16)).astype(np.float64)
+    blk = k[np.asarray(block_ids, dtype=np.int64)]
+    n, bs, h, d = blk.shape
+    merge = bs if merge <= 0 else merge
+    m64 = blk.reshape(n, bs // merge, merge, h, d).mean(axis=2)
+    return f32_to_bf16_bits(m64.astype(np.float32)), m64
+
+
+def dot_topk(repr_bf16: np.ndarray, q_bf16: np.ndarray, indexes: np.ndarray, k: int):
+    """Inner-product retrieval of retrieval_backend.cpp:206-225: per request the k allowed indexes with the largest
+    <q, data[idx]>.  Returns (scores float64 [B, n] for every candidate position (-inf where none), chosen candidate
+    POSITIONS by descending score as a list per request)."""
+    data = bf16_bits_to_f32(np.asarray(repr_bf16)).astype(np.float64)
+    data = data.reshape(data.shape[0], -1)
+    q = bf16_bits_to_f32(np.asarray(q_bf16)).astype(np.float64).reshape(len(q_bf16), -1)
+    idx = np.asarray(indexes)
+    scores = np.full(idx.shape, -np.inf)
+    chosen = []
+    for b in range(idx.shape[0]):
+        ok = (idx[b] >= 0) & (idx[b] < data.shape[0])
+        scores[b, ok] = data[idx[b, ok]] @ q[b]
+        order = [p for p in np.argsort(-scores[b], kind="stable") if ok[p]][:k]
+        chosen.append(order)
+    return scores, chosen
+
+
+def softmax_block_scores(repr_bf16: np.ndarray, q_bf16: np.ndarray) -> np.ndarray:
+    """KVStar block scores (kvstar/retrieve/core/domain/retrieve_task/simd_compute_kernel.cpp:884-947):
+    repr [n_blocks, M, Hkv, D], q [X, Hq, D]; per (token, query head) softmax over all n_blocks*M inner products
+    with its kv head's representations, summed over rows and over each block's M.  float64."""
+    r = bf16_bits_to_f32(np.asarray(repr_bf16)).astype(np.float64)
+    q = bf16_bits_to_f32(np.asarray(q_bf16)).astype(np.float64)
+    n, m, hkv, d = r.shape
+    x, hq, _ = q.shape
+    g = hq // hkv
+    out = np.zeros(n)
+    for xi in range(x):
+        for hh in range(hq):
+            logits = r[:, :, hh // g, :].reshape(n * m, d) @ q[xi, hh]
+            e = np.exp(logits - logits.max())
+            s = e.sum()
+            if s > 1e-9:
+                e = e / s
+            out += e.reshape(n, m).sum(axis=1)
+    return out

@@ -163,3 +163,19 @@ def test_reference_cpp_backend_min_scores():
         assert np.array_equal(np.sort(s)[:k], res["scores"][b])
         pos = {int(p): i for i, p in enumerate(allowed)}
         assert all(s[pos[int(p)]] == sc for p, sc in zip(res["indices"][b], res["scores"][b]))
+
+
+def test_golden_float_retrieval():
+    """Block representations as torch computes them in the ESA / KVStar plugins, and the inner-product top-k."""
+    g = np.load(os.path.join(GOLDEN, "float_retrieval.npz"))
+    r, _ = O.block_repr_mean(g["k_cache"], g["block_ids"])
+    assert np.array_equal(r[:, 0], g["repr_esa"])
+    r, _ = O.block_repr_mean(g["k_cache"], g["block_ids"], int(g["merge"]))
+    assert np.array_equal(r, g["repr_kvstar"])
+    scores, chosen = O.dot_topk(g["pool"], g["q"], g["indexes"], int(g["k"]))
+    fin = np.isfinite(g["scores"])
+    assert np.array_equal(fin, np.isfinite(scores))
+    assert np.allclose(scores[fin], g["scores"][fin], rtol=1e-5, atol=1e-5)
+    for b, pos in enumerate(chosen):
+        want = [int(i) for i in g["top_ids"][b] if i >= 0]
+        assert [int(g["indexes"][b][p]) for p in pos] == want

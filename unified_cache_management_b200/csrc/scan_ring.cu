@@ -9,7 +9,8 @@
 //   block-table entry, arm the barrier, launch the copy: several hundred cycles) is spread over twelve
 //   instruction streams and overlaps their math.  Up to 12 x 16 KiB are in flight per SM.  Each
 //   barrier has a single waiter that sees every phase in order, so a parity wait is never ambiguous.
-//   The lanes of a warp resolve the warp's next 32 items in parallel (one round of global loads).
+//   Work split: the first 7/8 of the items statically (CTA c, warp w), the rest claimed one by one from an
+//   atomic counter so that all SMs finish together; claim and block-table load run one item ahead of use.
 //
 //     sum mode: the distance sum over a block only depends on how many of its tokens have each code
 //       bit set.  A lane owns one 32-bit column (kv head, word) of the block and folds all its tokens
@@ -20,7 +21,10 @@
 //       bandwidth-bound: the per-token popcount form is limited by the SM's POPC rate (16/clk) once
 //       G >= 4.
 //     min mode: per-token distances are needed, so a lane owns a 16-byte piece of each token
-//       (XOR + popcount per query head) and keeps the running minimum.
+//       (XOR per query head, then one carry-save popcount sum over the 4*G words) and keeps the running minimum.
+//     token-row mode (one kv head, 18 words per token: MLA codes, up to 255 query codes): a lane owns a token;
+//       the per-token sum over the query codes comes from bit-sliced per-bit counts of the query codes
+//       (1 + log2 G popcount sums per token instead of G), either mode of block reduce.
 //
 // Output: int32 [B, Hout, max_blocks] block scores, bit-identical to the register kernel in scan.cu,
 // which remains the path for shapes this one does not cover.
@@ -58,8 +62,8 @@ struct RingParams {
     int RW;            // words per token row = Hkv * W
     int bps;           // blocks per stage
     int block_bytes;   // BS * RW * 4
-    int block_stride;  // = block_bytes (blocks of a stage sit back to back on 128-byte boundaries)
-    int stage_bytes;   // bps * block_stride, rounded up to 128
+    int block_stride;  // = block_bytes (blocks of a stage sit back to back)
+    int stage_bytes;   // bps * block_stride
     int n_active;      // warps (= stages) in use: min(kRingWarps, ring bytes / stage bytes)
 };
 

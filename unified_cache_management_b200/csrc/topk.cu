@@ -483,6 +483,7 @@ struct MergeParams {
     int R, B, H, kl, k, n_cached;
     float* out_scores;  // [B, H, k]
     int32_t* out_ids;
+    int largest;        // 0: the k smallest scores win (distances); 1: the k largest (inner products)
 };
 
 __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
@@ -494,7 +495,7 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
     const int n = p.R * p.kl;
     const int64_t obase = (int64_t)row * p.k;
     for (int i = tid; i < p.k; i += kSelThreads) {
-        p.out_scores[obase + i] = INFINITY;
+        p.out_scores[obase + i] = p.largest ? -INFINITY : INFINITY;
         p.out_ids[obase + i] = -1;
     }
     __syncthreads();
@@ -519,7 +520,7 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
         __device__ uint32_t key(int, Rec r) const
         {
             if (r.id < 0) return kKeyInvalid;
-            const uint32_t k = f32_order_key(r.score);
+            const uint32_t k = f32_order_key(p.largest ? -r.score : r.score);
             return k == kKeyInvalid ? kKeyInvalid - 1u : k;
         }
         __device__ uint32_t key_fast(int i, Rec r) const { return key(i, r); }
@@ -702,8 +703,20 @@ extern "C" int ucmr_topk_candidates(const uint32_t* codes, int64_t NB, int BS, i
                       static_cast<cudaStream_t>(stream));
 }
 
+namespace ucmr {
+int run_merge(const float* cand_scores, const int32_t* cand_ids, int64_t rank_stride, int R, int B, int Hout, int kl, int k,
+              int largest, float* out_scores, int32_t* out_ids, cudaStream_t st);
+}
+
 extern "C" int ucmr_merge_topk(const float* cand_scores, const int32_t* cand_ids, int64_t rank_stride, int R,
                                int B, int Hout, int kl, int k, float* out_scores, int32_t* out_ids, void* stream)
+{
+    return run_merge(cand_scores, cand_ids, rank_stride, R, B, Hout, kl, k, 0, out_scores, out_ids,
+                     static_cast<cudaStream_t>(stream));
+}
+
+int ucmr::run_merge(const float* cand_scores, const int32_t* cand_ids, int64_t rank_stride, int R, int B, int Hout, int kl,
+                    int k, int largest, float* out_scores, int32_t* out_ids, cudaStream_t stream)
 {
     if (rank_stride == 0) rank_stride = (int64_t)B * Hout * kl;
     if (rank_stride < (int64_t)B * Hout * kl) return UCMR_ERR_BAD_ARG;
@@ -711,13 +724,13 @@ extern "C" int ucmr_merge_topk(const float* cand_scores, const int32_t* cand_ids
     if (R <= 0 || B < 0 || Hout <= 0 || kl <= 0 || k < 0) return UCMR_ERR_BAD_ARG;
     if ((int64_t)R * kl > INT_MAX) return UCMR_ERR_UNSUPPORTED;
     if (B == 0 || k == 0) return UCMR_OK;
-    MergeParams p{cand_scores, cand_ids, rank_stride, R, B, Hout, kl, k, 0, out_scores, out_ids};
+    MergeParams p{cand_scores, cand_ids, rank_stride, R, B, Hout, kl, k, 0, out_scores, out_ids, largest ? 1 : 0};
     const int n = R * kl;
     p.n_cached = n < kSelMaxCachedKeys ? n : kSelMaxCachedKeys;
     const size_t smem = (size_t)p.n_cached * sizeof(uint32_t);
     int rc = set_dyn_smem(merge_kernel, smem);
     if (rc != UCMR_OK) return rc;
-    return launch_kernel(merge_kernel, dim3(B * Hout), dim3(kSelThreads), smem, static_cast<cudaStream_t>(stream), p);
+    return launch_kernel(merge_kernel, dim3(B * Hout), dim3(kSelThreads), smem, stream, p);
 }
 
 extern "C" int ucmr_update_seq_lens(const int32_t* seq_lens, int B, int topk_tokens, int BS, int32_t* out,

@@ -529,3 +529,78 @@ def copy_blocks(size: int, num: int, *, src_ptrs: Optional[torch.Tensor] = None,
                 raise ValueError(f"{name} is smaller than {num} blocks of {size} bytes")
     _l.check(_l.load_library().ucmr_copy_blocks(_ptr(src_ptrs), _ptr(src), _ptr(dst_ptrs), _ptr(dst), int(size),
                                                 int(num), _ptr(status), _stream(ref)), "ucmr_copy_blocks")
+
+
+# ----------------------------------------------------------------------------------------------
+# float block retrieval (ESA / KVStar style)
+# ----------------------------------------------------------------------------------------------
+def block_repr_mean(k_cache: torch.Tensor, block_ids: torch.Tensor, merge: Optional[int] = None,
+                    out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Mean key of each listed block over groups of ``merge`` tokens (default: the whole block).
+    k_cache bf16 [NB, BS, H, D] -> [n, BS/merge, H, D] bf16."""
+    _need_cuda("k_cache", k_cache, torch.bfloat16, contiguous=False)
+    if k_cache.dim() != 4 or k_cache.stride(3) != 1 or k_cache.stride(2) != k_cache.shape[3]:
+        raise ValueError("k_cache must be [NB, BS, H, D] with contiguous token rows")
+    _need_cuda("block_ids", block_ids, torch.int32)
+    nb, bs, h, d = k_cache.shape
+    merge = bs if merge is None else int(merge)
+    if merge <= 0 or bs % merge != 0:
+        raise ValueError(f"merge={merge} must divide the block size {bs}")
+    n = block_ids.numel()
+    if out is None:
+        out = torch.empty((n, bs // merge, h, d), dtype=torch.bfloat16, device=k_cache.device)
+    else:
+        _need_cuda("out", out, torch.bfloat16)
+    _l.check(_l.load_library().ucmr_block_repr_mean(_ptr(k_cache), nb, bs, h * d, k_cache.stride(0), k_cache.stride(1),
+                                                    _ptr(block_ids), n, merge, _ptr(out), _ptr(status),
+                                                    _stream(k_cache)), "ucmr_block_repr_mean")
+    return out
+
+
+def dot_topk(repr_pool: torch.Tensor, q: torch.Tensor, indexes: torch.Tensor, k: int,
+             workspace: Optional[torch.Tensor] = None):
+    """Per request the k candidates of ``indexes[b]`` (-1 padded) with the largest inner product with q[b].
+    repr_pool bf16 [N, dim], q bf16 [B, dim] -> (scores float32 [B, k], ids int32 [B, k]), in candidate order."""
+    _need_cuda("repr_pool", repr_pool, torch.bfloat16)
+    _need_cuda("q", q, torch.bfloat16)
+    _need_cuda("indexes", indexes, torch.int32)
+    rp = repr_pool.reshape(repr_pool.shape[0], -1)
+    qq = q.reshape(q.shape[0], -1)
+    if qq.shape[1] != rp.shape[1] or indexes.dim() != 2 or indexes.shape[0] != qq.shape[0]:
+        raise ValueError("q must be [B, dim] with the pool's dim and indexes [B, n]")
+    b, n = indexes.shape
+    lib = _l.load_library()
+    need = lib.ucmr_dot_topk_workspace_bytes(b, n)
+    if workspace is None:
+        workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=rp.device)
+    scores = torch.empty((b, k), dtype=torch.float32, device=rp.device)
+    ids = torch.empty((b, k), dtype=torch.int32, device=rp.device)
+    if b == 0 or k == 0:
+        return scores, ids
+    _l.check(lib.ucmr_dot_topk(_ptr(rp), rp.shape[0], rp.shape[1], _ptr(qq), _ptr(indexes), b, n, int(k), _ptr(scores),
+                               _ptr(ids), _ptr(workspace), workspace.numel(), _stream(rp)), "ucmr_dot_topk")
+    return scores, ids
+
+
+def softmax_topk(repr_blocks: torch.Tensor, q: torch.Tensor, k: int, workspace: Optional[torch.Tensor] = None):
+    """KVStar block scores of one request: repr_blocks bf16 [n_blocks, M, Hkv, D], q bf16 [X, Hq, D] ->
+    (block_scores float32 [n_blocks], top scores float32 [k], top block ids int32 [k] in ascending block order)."""
+    _need_cuda("repr_blocks", repr_blocks, torch.bfloat16)
+    _need_cuda("q", q, torch.bfloat16)
+    if repr_blocks.dim() != 4 or q.dim() != 3 or q.shape[2] != repr_blocks.shape[3]:
+        raise ValueError("repr_blocks must be [n_blocks, M, Hkv, D] and q [X, Hq, D]")
+    n, m, hkv, d = repr_blocks.shape
+    x, hq, _ = q.shape
+    if hq % hkv != 0:
+        raise ValueError("query heads must be a multiple of kv heads")
+    lib = _l.load_library()
+    need = lib.ucmr_softmax_topk_workspace_bytes(x, hq, n, m)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    block_scores = torch.empty((n,), dtype=torch.float32, device=q.device)
+    scores = torch.empty((k,), dtype=torch.float32, device=q.device)
+    ids = torch.empty((k,), dtype=torch.int32, device=q.device)
+    _l.check(lib.ucmr_softmax_topk(_ptr(repr_blocks), n, m, hkv, d, _ptr(q), x, hq, int(k), _ptr(block_scores),
+                                   _ptr(scores), _ptr(ids), _ptr(workspace), workspace.numel(), _stream(q)),
+             "ucmr_softmax_topk")
+    return block_scores, scores, ids
