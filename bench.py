@@ -489,6 +489,10 @@ def run_extra_workload(args, rank, world, local_rank):
     launch_mode = "one CUDA graph per layer-step"
     run = step
     try:
+        if name == "million_token_sharded" and world > 1:
+            # a captured NCCL all-gather did not complete here (the ranks stalled in the replay), so the step
+            # with the collective is launched stream-ordered from Python
+            raise RuntimeError("collective in the step")
         side = torch.cuda.Stream()
         graphs = []
         with torch.cuda.stream(side):
@@ -502,7 +506,7 @@ def run_extra_workload(args, rank, world, local_rank):
         for i in range(W):
             run(i % L)
     except Exception as exc:  # noqa: BLE001
-        launch_mode = f"stream-ordered launches from Python (graph capture refused: {type(exc).__name__})"
+        launch_mode = f"stream-ordered launches from Python ({exc})"
         run = step
     barrier()
     sampler = ClockSampler(local_rank)
