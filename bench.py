@@ -467,9 +467,12 @@ def run_extra_workload(args, rank, world, local_rank):
         launches = 3
 
         if world > 1:
+            plan_r = sharded.shard_plan(seq_g, BS, nblk_total, world, rank)
+
             def step(layer):
                 sharded.sharded_hamming_topk(caches[layer], q, bt_local, seq_g, k, BS, nblk_total, scale, reduce="sum",
-                                             must_select=MUST_SELECT, workspace=ws, gather_buffer=gbuf, send_buffer=sbuf)
+                                             must_select=MUST_SELECT, workspace=ws, gather_buffer=gbuf, send_buffer=sbuf,
+                                             plan=plan_r)
         else:
             plan = sharded.shard_plan(seq_g, BS, nblk_total, 1, 0)
 

@@ -50,15 +50,17 @@ def sharded_hamming_topk(codes_local, q_codes, block_table_local, seq_lens_globa
                          max_blocks_global: int, score_scale: float, *, group=None, reduce="sum",
                          reduce_kvhead: bool = False, must_select: Sequence[int] = (), sink_tokens: int = 0,
                          recent_tokens: int = 0, workspace=None, gather_buffer: Optional[torch.Tensor] = None,
-                         send_buffer: Optional[torch.Tensor] = None,
+                         send_buffer: Optional[torch.Tensor] = None, plan: Optional[ShardPlan] = None,
                          candidates_fn: Callable = _default_candidates, merge_fn: Callable = _default_merge):
     """Returns (scores float32 [B,Hout,k], global logical block ids int32 [B,Hout,k]), identical on
     every rank.  block_table_local is this rank's slice [B, max_blocks_global/world] of the table.
     ``send_buffer`` (int32 [2, B, Hout, min(k, blocks per rank)]) lets the local selection write its records
-    straight into the message; ``gather_buffer`` (int32 [world*2, ...]) receives all ranks' messages."""
+    straight into the message; ``gather_buffer`` (int32 [world*2, ...]) receives all ranks' messages; ``plan`` is
+    a ``shard_plan`` result to reuse while the sequence lengths do not change."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
-    plan = shard_plan(seq_lens_global, block_size, max_blocks_global, world, rank)
+    if plan is None:
+        plan = shard_plan(seq_lens_global, block_size, max_blocks_global, world, rank)
     kl = min(k, plan.blocks_per_rank)
     extra = {}
     if send_buffer is not None and candidates_fn is _default_candidates:
