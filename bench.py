@@ -466,8 +466,22 @@ def run_extra_workload(args, rank, world, local_rank):
         sbuf = torch.empty((2, B, Hkv, min(k, per)), dtype=torch.int32, device=dev)
         launches = 3
 
-        if world > 1:
+        exchange_kind = "one rank"
+        if world > 1 and args.exchange == "p2p":
+            # records stored by the selection kernel into every rank's buffer over NVLink; the merge kernel waits
             plan_r = sharded.shard_plan(seq_g, BS, nblk_total, world, rank)
+            ex = sharded.PeerExchange(B, Hkv, min(k, per), dev)
+            st_word = torch.zeros(1, dtype=torch.int32, device=dev)
+            exchange_kind = "peer-memory stores from the selection kernel + flag wait in the merge kernel (no collective)"
+            launches = 3
+
+            def step(layer):
+                sharded.sharded_hamming_topk_p2p(caches[layer], q, bt_local, seq_g, k, BS, nblk_total, scale, ex,
+                                                 reduce="sum", must_select=MUST_SELECT, workspace=ws, plan=plan_r,
+                                                 status=st_word)
+        elif world > 1:
+            plan_r = sharded.shard_plan(seq_g, BS, nblk_total, world, rank)
+            exchange_kind = "NCCL all-gather of (score, id) records"
 
             def step(layer):
                 sharded.sharded_hamming_topk(caches[layer], q, bt_local, seq_g, k, BS, nblk_total, scale, reduce="sum",
@@ -480,7 +494,7 @@ def run_extra_workload(args, rank, world, local_rank):
                 cs, ci = ops.topk_candidates(caches[layer], q, bt_local, plan.seq_lens_local, seq_g, k, 0, scale,
                                              reduce="sum", must_select=MUST_SELECT, workspace=ws)
                 ops.merge_topk(cs.unsqueeze(0), ci.unsqueeze(0), k)
-        par, scaling = f"sequence shards over {world} rank(s), one NCCL all-gather of (score, id) records", "strong"
+        par, scaling = f"sequence shards over {world} rank(s); exchange: {exchange_kind}", "strong"
         total_tokens = B * seq_total
         alg = dict(scan_bytes_per_gpu=B * per * BS * Hkv * Wd * 4, allgather_bytes_per_rank=2 * B * Hkv * min(k, per) * 4)
 
@@ -492,7 +506,7 @@ def run_extra_workload(args, rank, world, local_rank):
     launch_mode = "one CUDA graph per layer-step"
     run = step
     try:
-        if name == "million_token_sharded" and world > 1:
+        if name == "million_token_sharded" and world > 1 and args.exchange == "nccl":
             # a captured NCCL all-gather did not complete here (the ranks stalled in the replay), so the step
             # with the collective is launched stream-ordered from Python
             raise RuntimeError("collective in the step")
@@ -548,6 +562,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama3_8b_decode16", choices=sorted(WORKLOADS) + sorted(EXTRA_WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="million_token_sharded on several GPUs: how the candidate records travel")
     ap.add_argument("--ncu-case", default=None,
                     help="run a small single-kernel case for a profiler capture and exit "
                          "(scan, scan_min, scan_256bit, select, encode, encode_step, gather)")

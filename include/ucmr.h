@@ -259,6 +259,34 @@ int ucmr_gather_kv(const void* k_pool, const void* v_pool, int64_t NB, int64_t b
                    void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ *  Sequence-sharded retrieval without a collective call: the local selection writes its records
+ *  straight into every rank's gather buffer over peer memory (NVLink) and publishes a step number;
+ *  the merge waits for the step number of every rank, then merges.  One process per GPU; the buffers
+ *  are peer-mapped by the caller (symmetric memory / IPC).
+ *
+ *  ucmr_topk_candidates_p2p: as ucmr_topk_candidates, but the records go to peer_scores[r] /
+ *     peer_ids[r] for r < n_peers (<= 8; HOST arrays of device pointers, each pointing at THIS rank's
+ *     [B, Hout, k] slice of rank r's buffer - the own buffer included), and when the launch's last CTA
+ *     is done `seq` is stored (release, system scope) to *peer_flags[r] (this rank's flag word on rank
+ *     r).  Needs k > 0.  Uses the workspace header as an arrival counter.
+ *  ucmr_merge_topk_wait: as ucmr_merge_topk, after waiting (at most 1 s, then UCMR_DEV_WAIT_TIMEOUT in
+ *     status_word and the output left as padding) until flags[r] == seq for every r < R.
+ *  A step's records must not be overwritten while a slower rank still merges them: alternate between
+ *  two buffers (and two flag arrays) by the parity of seq.
+ * ------------------------------------------------------------------------------------------ */
+int ucmr_topk_candidates_p2p(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
+                             const uint32_t* q_codes, int Hq, const int32_t* block_table, int max_blocks,
+                             int64_t block_table_stride, const int32_t* seq_lens_local,
+                             const int32_t* seq_lens_global, int B, int k, int block_id_offset,
+                             float score_scale, int reduce_mode, int reduce_kvhead,
+                             const int32_t* must_select, int n_must, int sink_tokens, int recent_tokens,
+                             float* const* peer_scores, int32_t* const* peer_ids, int32_t* const* peer_flags,
+                             int n_peers, int seq, void* workspace, size_t workspace_bytes, void* stream);
+int ucmr_merge_topk_wait(const float* cand_scores, const int32_t* cand_ids, int64_t rank_stride, int R, int B,
+                         int Hout, int kl, int k, float* out_scores, int32_t* out_ids, const int32_t* flags,
+                         int seq, int32_t* status_word, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  *  Block copies through pointer lists, on the bulk-copy engine.
  *     Stands in for the three CudaSMCopyAsync / CudaCopyKernel overloads
  *     (ucm/shared/trans/cuda/cuda_sm_kernel.cu:52-114) that land store-loaded blocks: `num` blocks of

@@ -37,7 +37,18 @@ def _worker(rank, world, port, ret):
         torch.cuda.synchronize()
         full = O.hamming_topk(case["codes"], case["q"], case["block_table"], seq, k, O.REDUCE_SUM, False,
                               must_select=must)
-        ret[rank] = bool(np.array_equal(ids.cpu().numpy(), full["logical"]))
+        ok = bool(np.array_equal(ids.cpu().numpy(), full["logical"]))
+        # the same through peer memory: records stored into every rank's buffer over NVLink, no collective
+        ex = sharded.PeerExchange(B, Hkv, min(k, per), dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        for _ in range(3):   # three steps: both buffer parities and a reuse
+            s2, ids2 = sharded.sharded_hamming_topk_p2p(H.to_dev_i32(case["codes"], dev), H.to_dev_i32(case["q"], dev),
+                                                        bt_local, H.to_dev_i32(seq, dev), k, BS, nblk, 1.0 / (BS * G),
+                                                        ex, must_select=must, status=status)
+            torch.cuda.synchronize()
+            ok = ok and bool(np.array_equal(ids2.cpu().numpy(), full["logical"])) and int(status.item()) == 0
+            ok = ok and bool(torch.equal(s2, s))
+        ret[rank] = ok
     finally:
         dist.destroy_process_group()
 

@@ -103,3 +103,67 @@ def test_long_shards_cluster_candidates(cuda_device):
     torch.cuda.synchronize()
     full = O.hamming_topk(case["codes"], case["q"], case["block_table"], seq, k, O.REDUCE_SUM, False, must_select=must)
     assert np.array_equal(mi.cpu().numpy(), full["logical"])
+
+
+@pytest.mark.parametrize("R", [2, 4])
+def test_peer_memory_exchange_emulated_on_one_gpu(cuda_device, R):
+    """The collective-free exchange with the ranks emulated one after the other on one GPU: every rank's
+    selection writes its records into all R gather buffers and publishes the step number, then every rank's
+    merge (launched after all selections, so nothing waits for a later launch) must equal the unsharded top-k.
+    Two steps, to exercise the alternating buffers."""
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    B, Hkv, G, W, BS, k = 2, 4, 2, 4, 32, 20
+    nblk = 48 * R
+    per = nblk // R
+    slab = B * Hkv * k
+    bufs_s = [[torch.zeros((R, B, Hkv, k), dtype=torch.float32, device=dev) for _ in range(R)] for _ in range(2)]
+    bufs_i = [[torch.zeros((R, B, Hkv, k), dtype=torch.int32, device=dev) for _ in range(R)] for _ in range(2)]
+    flags = [[torch.zeros((R,), dtype=torch.int32, device=dev) for _ in range(R)] for _ in range(2)]
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    for step in (1, 2, 3):
+        par = step & 1
+        seq = np.array([nblk * BS - step, nblk * BS - 9 * BS - 3], dtype=np.int32)
+        case = H.make_paged_case(300 + step, B, Hkv, G, W, BS, nblk, seq_lens=seq)
+        codes, q = H.to_dev_i32(case["codes"], dev), H.to_dev_i32(case["q"], dev)
+        seq_g = H.to_dev_i32(seq, dev)
+        must = (0, -1)
+        for r in range(R):
+            bt_local = H.to_dev_i32(np.ascontiguousarray(case["block_table"][:, r * per:(r + 1) * per]), dev)
+            seq_local = H.to_dev_i32(np.clip(seq - r * per * BS, 0, per * BS).astype(np.int32), dev)
+            ps = [bufs_s[par][d].data_ptr() + 4 * r * slab for d in range(R)]
+            pi = [bufs_i[par][d].data_ptr() + 4 * r * slab for d in range(R)]
+            pf = [flags[par][d].data_ptr() + 4 * r for d in range(R)]
+            ops.topk_candidates_p2p(codes, q, bt_local, seq_local, seq_g, k, r * per, 1.0 / (BS * G), ps, pi, pf, step,
+                                    must_select=must)
+        full = O.hamming_topk(case["codes"], case["q"], case["block_table"], seq, k, O.REDUCE_SUM, False,
+                              must_select=must)
+        for d in range(R):
+            ms, mi = ops.merge_topk_wait(bufs_s[par][d], bufs_i[par][d], k, flags[par][d], step, status=status)
+            torch.cuda.synchronize()
+            assert flags[par][d].cpu().tolist() == [step] * R
+            assert np.array_equal(mi.cpu().numpy(), full["logical"])
+        assert int(status.item()) == 0
+
+
+def test_merge_wait_gives_up_when_a_rank_never_delivers(cuda_device):
+    """A flag that nothing sets: the wait runs out after its time limit, the status word says so, the output stays
+    padding and the context remains usable."""
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    R, B, Hh, k = 2, 1, 1, 4
+    s = torch.zeros((R, B, Hh, k), dtype=torch.float32, device=dev)
+    i = torch.zeros((R, B, Hh, k), dtype=torch.int32, device=dev)
+    flags = torch.tensor([5, 0], dtype=torch.int32, device=dev)      # rank 1 never publishes step 5
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ms, mi = ops.merge_topk_wait(s, i, k, flags, 5, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) & 2
+    assert (mi.cpu().numpy() == -1).all() and np.isinf(ms.cpu().numpy()).all()
+    flags[1] = 5
+    status.zero_()
+    ms, mi = ops.merge_topk_wait(s, i, k, flags, 5, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and (mi.cpu().numpy() >= 0).all()

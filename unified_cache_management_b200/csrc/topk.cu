@@ -52,6 +52,19 @@ __device__ __forceinline__ bool block_is_forced(const ForcedSpec& f, int j, int 
     return false;
 }
 
+constexpr int kMaxPeers = 8;  // ranks of one NVLink domain that exchange candidate records directly
+
+__device__ __forceinline__ void st_release_sys(int32_t* p, int v)
+{
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int32_t* p)
+{
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 constexpr int kDigitBits = 11;
 constexpr int kBins = 1 << kDigitBits;
 constexpr int kBinsPerThread = kBins / kSelThreads;
@@ -366,6 +379,15 @@ struct SelectParams {
     float scale;
     int32_t* sched;  // the scan's work counter, cleared here for the next launch
     int cluster;     // CTAs per row (thread-block cluster size), 1 = one CTA per row
+    // Candidate records written straight into every rank's gather buffer over peer memory (n_peers > 0): entry r
+    // points at this rank's slice of rank r's buffer; when the last CTA is done, the step number is stored to
+    // this rank's flag word on every rank.
+    int n_peers;
+    float* peer_scores[kMaxPeers];
+    int32_t* peer_ids[kMaxPeers];
+    int32_t* peer_flags[kMaxPeers];
+    int seq;
+    int32_t* arrive;  // CTA arrival counter (workspace header), zero between launches
 };
 
 // CL: p.cluster consecutive CTAs (one thread-block cluster) share a row.
@@ -394,8 +416,15 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     // padding first; the chosen entries overwrite positions [0, kb) (in a cluster: after its first barrier)
     for (int i = tid; lead && i < p.k; i += kSelThreads) {
         if (CANDIDATES) {
-            p.cand_scores[obase + i] = INFINITY;
-            p.cand_ids[obase + i] = -1;
+            if (p.n_peers > 0) {
+                for (int r = 0; r < p.n_peers; ++r) {
+                    p.peer_scores[r][obase + i] = INFINITY;
+                    p.peer_ids[r][obase + i] = -1;
+                }
+            } else {
+                p.cand_scores[obase + i] = INFINITY;
+                p.cand_ids[obase + i] = -1;
+            }
         } else {
             const bool pass = masked && i < kb;
             p.out_phys[obase + i] = pass ? btrow[i] : 0;
@@ -458,8 +487,16 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         if (CANDIDATES) {
             if (valid) {
                 const bool forced = block_is_forced(p.forced, j + p.id_offset, nb_g, seq_g, p.BS);
-                p.cand_scores[obase + pos] = forced ? -1.0f : (float)srow[j] * p.scale;
-                p.cand_ids[obase + pos] = j + p.id_offset;
+                const float sc_v = forced ? -1.0f : (float)srow[j] * p.scale;
+                if (p.n_peers > 0) {
+                    for (int r = 0; r < p.n_peers; ++r) {
+                        p.peer_scores[r][obase + pos] = sc_v;
+                        p.peer_ids[r][obase + pos] = j + p.id_offset;
+                    }
+                } else {
+                    p.cand_scores[obase + pos] = sc_v;
+                    p.cand_ids[obase + pos] = j + p.id_offset;
+                }
             }
         } else {
             p.out_phys[obase + pos] = btrow[j];
@@ -468,6 +505,20 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         }
     };
     select_row<CL>(n, kb, p.key_bits, key_of, emit, s_keys, p.n_cached, sc);
+    if (CANDIDATES && p.n_peers > 0) {
+        // records are in the peers' memory: make them visible system-wide, then the last CTA of the launch
+        // publishes the step number on every rank
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+            const int done = atomicAdd(p.arrive, 1);
+            if (done == (int)gridDim.x - 1) {
+                *p.arrive = 0;
+                __threadfence_system();
+                for (int r = 0; r < p.n_peers; ++r) st_release_sys(p.peer_flags[r], p.seq);
+            }
+        }
+    }
 }
 
 __device__ __forceinline__ uint32_t f32_order_key(float x)
@@ -484,6 +535,10 @@ struct MergeParams {
     float* out_scores;  // [B, H, k]
     int32_t* out_ids;
     int largest;        // 0: the k smallest scores win (distances); 1: the k largest (inner products)
+    // records arrive from other GPUs: wait (bounded) until flag r holds wait_seq for every rank r < R
+    const int32_t* wait_flags;
+    int wait_seq;
+    int32_t* status;
 };
 
 __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
@@ -497,6 +552,28 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
     for (int i = tid; i < p.k; i += kSelThreads) {
         p.out_scores[obase + i] = p.largest ? -INFINITY : INFINITY;
         p.out_ids[obase + i] = -1;
+    }
+    if (p.wait_flags != nullptr) {
+        __shared__ int s_timed_out;
+        if (tid == 0) s_timed_out = 0;
+        __syncthreads();
+        if (tid < p.R) {
+            unsigned long long t0 = 0;
+            uint32_t polls = 0;
+            while (ld_acquire_sys(p.wait_flags + tid) != p.wait_seq) {
+                if ((++polls & (kWaitPollsPerClockCheck - 1)) == 0) {
+                    unsigned long long now;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > kWaitLimitNs) { s_timed_out = 1; break; }
+                }
+            }
+        }
+        __syncthreads();
+        if (s_timed_out) {  // a rank never delivered: leave the padding as the result and report
+            if (tid == 0) flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT);
+            return;
+        }
     }
     __syncthreads();
     auto at = [&](int i) -> int64_t {
@@ -515,7 +592,7 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
         __device__ Rec raw(int i) const
         {
             const int64_t a = at(i);
-            return Rec{p.cand_ids[a], p.cand_scores[a]};
+            return Rec{__ldcg(p.cand_ids + a), __ldcg(p.cand_scores + a)};
         }
         __device__ uint32_t key(int, Rec r) const
         {
@@ -529,9 +606,10 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
     const KeyOf key_of{p, row};
     auto emit = [&](int pos, int i) {
         const int64_t a = at(i);
-        if (p.cand_ids[a] >= 0) {
-            p.out_scores[obase + pos] = p.cand_scores[a];
-            p.out_ids[obase + pos] = p.cand_ids[a];
+        const int32_t id = __ldcg(p.cand_ids + a);
+        if (id >= 0) {
+            p.out_scores[obase + pos] = __ldcg(p.cand_scores + a);
+            p.out_ids[obase + pos] = id;
         }
     };
     select_row<false>(n, min(p.k, n), 32, key_of, emit, s_keys, p.n_cached, sc);
@@ -600,6 +678,13 @@ extern "C" int ucmr_workspace_status(const void* workspace, int* host_status, vo
     return *host_status == 0 ? UCMR_OK : UCMR_ERR_DEVICE;
 }
 
+struct PeerDest {
+    int n_peers, seq;
+    float* scores[kMaxPeers];
+    int32_t* ids[kMaxPeers];
+    int32_t* flags[kMaxPeers];
+};
+
 static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
                       const uint32_t* q_codes, int Hq, const int32_t* bt, int max_blocks, int64_t bt_stride,
                       const int32_t* seq_local, const int32_t* seq_global, int B, int k,
@@ -607,10 +692,10 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
                       const int32_t* must, int n_must, int sink, int recent, int id_offset, float scale,
                       int32_t* out_phys, int32_t* out_logical, int32_t* out_scores, int32_t* out_valid,
                       int32_t* out_newseq, float* cand_scores, int32_t* cand_ids, void* workspace,
-                      size_t workspace_bytes, cudaStream_t st)
+                      size_t workspace_bytes, cudaStream_t st, const PeerDest* peers = nullptr)
 {
     if (k < 0 || k > max_blocks) return UCMR_ERR_BAD_ARG;
-    if (candidates ? (!cand_scores || !cand_ids) : !out_phys) return UCMR_ERR_BAD_ARG;
+    if (candidates ? (!peers && (!cand_scores || !cand_ids)) : !out_phys) return UCMR_ERR_BAD_ARG;
     if (!workspace) return UCMR_ERR_WORKSPACE;
     if (workspace_bytes < ucmr_hamming_topk_workspace_bytes(B, Hkv, max_blocks, reduce_kvhead)) return UCMR_ERR_WORKSPACE;
     SelectParams p{};
@@ -622,6 +707,7 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
     rc = run_scan(codes, NB, BS, Hkv, W, q_codes, Hq, bt, max_blocks, bt_stride, seq_local, B, reduce_mode,
                   reduce_kvhead, scores, status, sched, st);
     if (rc != UCMR_OK || B == 0) return rc;
+    if (k == 0 && peers) return UCMR_ERR_BAD_ARG;
     if (k == 0) {  // no selection kernel will run: clear the counter here
         cudaError_t e = cudaMemsetAsync(sched, 0, sizeof(int32_t), st);
         if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
@@ -645,6 +731,12 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
     p.out_phys = out_phys; p.out_logical = out_logical; p.out_scores = out_scores;
     p.out_valid = out_valid; p.out_newseq = out_newseq;
     p.cand_scores = cand_scores; p.cand_ids = cand_ids; p.scale = scale; p.sched = sched;
+    if (peers) {
+        p.n_peers = peers->n_peers; p.seq = peers->seq; p.arrive = status + 3;
+        for (int r = 0; r < peers->n_peers; ++r) {
+            p.peer_scores[r] = peers->scores[r]; p.peer_ids[r] = peers->ids[r]; p.peer_flags[r] = peers->flags[r];
+        }
+    }
     const int rows = B * p.Hout;
     // Few long rows: split each over a thread-block cluster so that the selection uses more than `rows` SMs.
     p.cluster = 1;
@@ -706,6 +798,9 @@ extern "C" int ucmr_topk_candidates(const uint32_t* codes, int64_t NB, int BS, i
 namespace ucmr {
 int run_merge(const float* cand_scores, const int32_t* cand_ids, int64_t rank_stride, int R, int B, int Hout, int kl, int k,
               int largest, float* out_scores, int32_t* out_ids, cudaStream_t st);
+static int run_merge_wait(const float* cand_scores, const int32_t* cand_ids, int64_t rank_stride, int R, int B, int Hout,
+                          int kl, int k, int largest, float* out_scores, int32_t* out_ids, const int32_t* wait_flags,
+                          int wait_seq, int32_t* status, cudaStream_t st);
 }
 
 extern "C" int ucmr_merge_topk(const float* cand_scores, const int32_t* cand_ids, int64_t rank_stride, int R,
@@ -718,13 +813,23 @@ extern "C" int ucmr_merge_topk(const float* cand_scores, const int32_t* cand_ids
 int ucmr::run_merge(const float* cand_scores, const int32_t* cand_ids, int64_t rank_stride, int R, int B, int Hout, int kl,
                     int k, int largest, float* out_scores, int32_t* out_ids, cudaStream_t stream)
 {
+    return run_merge_wait(cand_scores, cand_ids, rank_stride, R, B, Hout, kl, k, largest, out_scores, out_ids, nullptr, 0,
+                          nullptr, stream);
+}
+
+static int ucmr::run_merge_wait(const float* cand_scores, const int32_t* cand_ids, int64_t rank_stride, int R, int B,
+                                int Hout, int kl, int k, int largest, float* out_scores, int32_t* out_ids,
+                                const int32_t* wait_flags, int wait_seq, int32_t* status, cudaStream_t stream)
+{
     if (rank_stride == 0) rank_stride = (int64_t)B * Hout * kl;
     if (rank_stride < (int64_t)B * Hout * kl) return UCMR_ERR_BAD_ARG;
     if (!cand_scores || !cand_ids || !out_scores || !out_ids) return UCMR_ERR_BAD_ARG;
     if (R <= 0 || B < 0 || Hout <= 0 || kl <= 0 || k < 0) return UCMR_ERR_BAD_ARG;
     if ((int64_t)R * kl > INT_MAX) return UCMR_ERR_UNSUPPORTED;
     if (B == 0 || k == 0) return UCMR_OK;
-    MergeParams p{cand_scores, cand_ids, rank_stride, R, B, Hout, kl, k, 0, out_scores, out_ids, largest ? 1 : 0};
+    if (wait_flags && R > kSelThreads) return UCMR_ERR_UNSUPPORTED;
+    MergeParams p{cand_scores, cand_ids, rank_stride, R, B, Hout, kl, k, 0, out_scores, out_ids, largest ? 1 : 0,
+                  wait_flags, wait_seq, status};
     const int n = R * kl;
     p.n_cached = n < kSelMaxCachedKeys ? n : kSelMaxCachedKeys;
     const size_t smem = (size_t)p.n_cached * sizeof(uint32_t);
@@ -740,4 +845,39 @@ extern "C" int ucmr_update_seq_lens(const int32_t* seq_lens, int B, int topk_tok
     if (B == 0) return UCMR_OK;
     update_seq_lens_kernel<<<(B + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(seq_lens, B, topk_tokens, BS, out);
     return check_launch();
+}
+
+/* Peer-memory form of the sequence-sharded exchange (see include/ucmr.h). */
+extern "C" int ucmr_topk_candidates_p2p(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
+                                        const uint32_t* q_codes, int Hq, const int32_t* block_table, int max_blocks,
+                                        int64_t block_table_stride, const int32_t* seq_lens_local,
+                                        const int32_t* seq_lens_global, int B, int k, int block_id_offset,
+                                        float score_scale, int reduce_mode, int reduce_kvhead,
+                                        const int32_t* must_select, int n_must, int sink_tokens, int recent_tokens,
+                                        float* const* peer_scores, int32_t* const* peer_ids,
+                                        int32_t* const* peer_flags, int n_peers, int seq, void* workspace,
+                                        size_t workspace_bytes, void* stream)
+{
+    if (block_id_offset < 0 || !peer_scores || !peer_ids || !peer_flags || n_peers <= 0 || n_peers > kMaxPeers)
+        return UCMR_ERR_BAD_ARG;
+    PeerDest pd{};
+    pd.n_peers = n_peers; pd.seq = seq;
+    for (int r = 0; r < n_peers; ++r) {
+        if (!peer_scores[r] || !peer_ids[r] || !peer_flags[r]) return UCMR_ERR_BAD_ARG;
+        pd.scores[r] = peer_scores[r]; pd.ids[r] = peer_ids[r]; pd.flags[r] = peer_flags[r];
+    }
+    return run_select(true, codes, NB, BS, Hkv, W, q_codes, Hq, block_table, max_blocks, block_table_stride,
+                      seq_lens_local, seq_lens_global, B, k, nullptr, nullptr, reduce_mode, reduce_kvhead,
+                      must_select, n_must, sink_tokens, recent_tokens, block_id_offset, score_scale, nullptr,
+                      nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, workspace, workspace_bytes,
+                      static_cast<cudaStream_t>(stream), &pd);
+}
+
+extern "C" int ucmr_merge_topk_wait(const float* cand_scores, const int32_t* cand_ids, int64_t rank_stride, int R, int B,
+                                    int Hout, int kl, int k, float* out_scores, int32_t* out_ids,
+                                    const int32_t* flags, int seq, int32_t* status_word, void* stream)
+{
+    if (!flags) return UCMR_ERR_BAD_ARG;
+    return run_merge_wait(cand_scores, cand_ids, rank_stride, R, B, Hout, kl, k, 0, out_scores, out_ids, flags, seq,
+                          status_word, static_cast<cudaStream_t>(stream));
 }

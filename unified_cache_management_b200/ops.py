@@ -442,6 +442,57 @@ def topk_candidates(codes, q_codes, block_table, seq_lens_local, seq_lens_global
     return out_scores, out_ids
 
 
+def topk_candidates_p2p(codes, q_codes, block_table, seq_lens_local, seq_lens_global, k: int, block_id_offset: int,
+                        score_scale: float, peer_scores_ptrs: Sequence[int], peer_ids_ptrs: Sequence[int],
+                        peer_flag_ptrs: Sequence[int], seq: int, *, reduce="sum", reduce_kvhead=False, must_select=(),
+                        sink_tokens=0, recent_tokens=0, workspace=None) -> None:
+    """``topk_candidates`` whose records go straight into every rank's gather buffer over peer memory: the three
+    pointer lists hold, per rank r, the device address of THIS rank's [B,Hout,k] slice of rank r's score / id
+    buffers and of this rank's flag word on rank r; ``seq`` is published to the flags when the launch is done."""
+    codes, q_codes, bt_stride = _scan_args(codes, q_codes, block_table, seq_lens_local)
+    _need_cuda("seq_lens_global", seq_lens_global, torch.int32)
+    nb, bs, hkv, w = codes.shape
+    b, hq, _ = q_codes.shape
+    mb = block_table.shape[1]
+    if k <= 0 or k > mb:
+        raise ValueError(f"k={k} outside [1, max_blocks={mb}]")
+    n = len(peer_scores_ptrs)
+    if n == 0 or n != len(peer_ids_ptrs) or n != len(peer_flag_ptrs):
+        raise ValueError("the three pointer lists must have one entry per rank")
+    if workspace is None:
+        workspace = new_workspace(b, hkv, mb, codes.device, reduce_kvhead)
+    arr = C.c_void_p * n
+    must, n_must = _must_array(must_select)
+    _l.check(_l.load_library().ucmr_topk_candidates_p2p(
+        _ptr(codes), nb, bs, hkv, w, _ptr(q_codes), hq, _ptr(block_table), mb, bt_stride, _ptr(seq_lens_local),
+        _ptr(seq_lens_global), b, k, int(block_id_offset), float(score_scale), reduce_mode(reduce),
+        int(bool(reduce_kvhead)), must, n_must, int(sink_tokens), int(recent_tokens),
+        arr(*[int(p) for p in peer_scores_ptrs]), arr(*[int(p) for p in peer_ids_ptrs]),
+        arr(*[int(p) for p in peer_flag_ptrs]), n, int(seq), _ptr(workspace), workspace.numel(), _stream(codes)),
+        "ucmr_topk_candidates_p2p")
+
+
+def merge_topk_wait(cand_scores: torch.Tensor, cand_ids: torch.Tensor, k: int, flags: torch.Tensor, seq: int,
+                    status: Optional[torch.Tensor] = None, out_scores=None, out_ids=None):
+    """``merge_topk`` that first waits until ``flags[r] == seq`` for every rank (the records were written by the
+    other GPUs' ``topk_candidates_p2p``).  cand_* dense [R, B, Hout, kl]."""
+    _need_cuda("cand_scores", cand_scores, torch.float32)
+    _need_cuda("cand_ids", cand_ids, torch.int32)
+    _need_cuda("flags", flags, torch.int32)
+    r, b, h, kl = cand_scores.shape
+    if flags.numel() < r:
+        raise ValueError("one flag per rank is needed")
+    dev = cand_scores.device
+    if out_scores is None:
+        out_scores = torch.empty((b, h, k), dtype=torch.float32, device=dev)
+    if out_ids is None:
+        out_ids = torch.empty((b, h, k), dtype=torch.int32, device=dev)
+    _l.check(_l.load_library().ucmr_merge_topk_wait(_ptr(cand_scores), _ptr(cand_ids), b * h * kl, r, b, h, kl, int(k),
+                                                    _ptr(out_scores), _ptr(out_ids), _ptr(flags), int(seq),
+                                                    _ptr(status), _stream(cand_scores)), "ucmr_merge_topk_wait")
+    return out_scores, out_ids
+
+
 def merge_topk(cand_scores: torch.Tensor, cand_ids: torch.Tensor, k: int, out_scores=None, out_ids=None):
     """cand_* [R, B, Hout, kl] (ascending shard order) -> global top-k [B, Hout, k], ascending id.
     The two tensors may be strided views of one gathered buffer as long as each shard's [B,Hout,kl]

@@ -78,3 +78,70 @@ def sharded_hamming_topk(codes_local, q_codes, block_table_local, seq_lens_globa
     cand_scores = gathered[:, 0].view(torch.float32)
     cand_ids = gathered[:, 1]
     return merge_fn(cand_scores, cand_ids, k)
+
+
+class PeerExchange:
+    """Gather buffers of all ranks mapped into each other's address space (torch symmetric memory), for the
+    collective-free form of the sharded retrieval: every rank's selection kernel stores its records into all
+    ranks' buffers over NVLink and publishes the step number; the merge kernel waits for all step numbers.
+
+    Per rank and per step parity: scores float32 [world, B, H, kl], ids int32 [world, B, H, kl], flags int32 [world]
+    (padded to 64 words).  Two parities alternate so that a rank that is one step ahead never overwrites records a
+    slower rank still merges."""
+
+    def __init__(self, batch: int, heads: int, kl: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("the peer exchange serves up to 8 ranks of one NVLink domain")
+        self.shape = (self.world, batch, heads, kl)
+        self.slab = batch * heads * kl                      # records of one rank
+        self.words_per_parity = 2 * self.world * self.slab + 64
+        self.buf = symm_mem.empty(2 * self.words_per_parity, dtype=torch.int32, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, self.group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)                            # every rank's flags are zero before any store
+        self.seq = 0
+
+    def _offsets(self, parity: int):
+        base = parity * self.words_per_parity
+        return base, base + self.world * self.slab, base + 2 * self.world * self.slab   # scores, ids, flags (words)
+
+    def next_step(self):
+        """Returns (seq, pointer lists for topk_candidates_p2p, local views for merge_topk_wait)."""
+        self.seq += 1
+        o_s, o_i, o_f = self._offsets(self.seq & 1)
+        mine = self.rank * self.slab
+        ps = [p + 4 * (o_s + mine) for p in self.ptrs]
+        pi = [p + 4 * (o_i + mine) for p in self.ptrs]
+        pf = [p + 4 * (o_f + self.rank) for p in self.ptrs]
+        n = self.world * self.slab
+        scores = self.buf[o_s:o_s + n].view(torch.float32).view(self.shape)
+        ids = self.buf[o_i:o_i + n].view(self.shape)
+        flags = self.buf[o_f:o_f + self.world]
+        return self.seq, (ps, pi, pf), (scores, ids, flags)
+
+
+def sharded_hamming_topk_p2p(codes_local, q_codes, block_table_local, seq_lens_global, k: int, block_size: int,
+                             max_blocks_global: int, score_scale: float, exchange: PeerExchange, *, reduce="sum",
+                             reduce_kvhead: bool = False, must_select: Sequence[int] = (), sink_tokens: int = 0,
+                             recent_tokens: int = 0, workspace=None, plan: Optional[ShardPlan] = None,
+                             status: Optional[torch.Tensor] = None):
+    """``sharded_hamming_topk`` with the all-gather folded into the two kernels (see ``PeerExchange``): two launches
+    per step and no collective call."""
+    from . import ops
+    if plan is None:
+        plan = shard_plan(seq_lens_global, block_size, max_blocks_global, exchange.world, exchange.rank)
+    kl = min(k, plan.blocks_per_rank)
+    if kl != exchange.shape[3]:
+        raise ValueError("the exchange was sized for a different number of records per rank")
+    seq, (ps, pi, pf), (scores, ids, flags) = exchange.next_step()
+    ops.topk_candidates_p2p(codes_local, q_codes, block_table_local, plan.seq_lens_local, seq_lens_global, kl,
+                            plan.block_offset, score_scale, ps, pi, pf, seq, reduce=reduce, reduce_kvhead=reduce_kvhead,
+                            must_select=must_select, sink_tokens=sink_tokens, recent_tokens=recent_tokens,
+                            workspace=workspace)
+    return ops.merge_topk_wait(scores, ids, k, flags, seq, status=status)
