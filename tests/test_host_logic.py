@@ -81,3 +81,23 @@ def test_scheduler_role_needs_no_device_buffers():
         GSAOnDevice(F.make_vllm_config("Qwen/Qwen3-4B", device_type="npu"), base.UcmSparseRole.SCHEDULER)
     with pytest.raises(AssertionError):   # top-k budget above the context limit
         GSAOnDevice(F.make_vllm_config("Qwen/Qwen3-4B", max_model_len=1024), base.UcmSparseRole.SCHEDULER)
+
+
+def test_peer_exchange_layout_keeps_slices_and_parities_apart():
+    """Offsets of the collective-free exchange buffer: per parity scores / ids / flags do not overlap, ranks' slices
+    are disjoint, and consecutive steps use different halves."""
+    from unified_cache_management_b200.sharded import exchange_layout
+    world, slab = 4, 96
+    seen = {}
+    for seq in (1, 2):
+        for rank in range(world):
+            o_s, o_i, o_f, mine, words = exchange_layout(world, rank, slab, seq)
+            assert words == 2 * world * slab + 64 and o_s == (seq & 1) * words
+            spans = [(o_s + mine, o_s + mine + slab), (o_i + mine, o_i + mine + slab), (o_f + rank, o_f + rank + 1)]
+            for lo, hi in spans:
+                assert o_s <= lo and hi <= o_s + words
+                for (l2, h2) in seen.values():
+                    assert hi <= l2 or h2 <= lo
+            for n, sp in enumerate(spans):
+                seen[(seq, rank, n)] = sp
+    assert exchange_layout(world, 0, slab, 3)[0] == exchange_layout(world, 0, slab, 1)[0]

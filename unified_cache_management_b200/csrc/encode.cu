@@ -165,6 +165,42 @@ __device__ __forceinline__ void build_rt_swizzled(uint8_t* s_b, const __nv_bfloa
     }
 }
 
+// The same in two steps for 128 threads (two 8x8 blocks per thread), so that the global loads can be issued early
+// and the transposing stores late, with other memory traffic in between.
+__device__ __forceinline__ void rt_load_128(uint4 (&v)[2][8], const __nv_bfloat16* R, int tid)
+{
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+        const int blk = tid + it * 128;
+        const int kc = blk / (kEncBits / 8), nc = blk % (kEncBits / 8);
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            v[it][r] = __ldg(reinterpret_cast<const uint4*>(R + (size_t)(kc * 8 + r) * kEncBits + nc * 8));
+    }
+}
+
+__device__ __forceinline__ void rt_store_128(uint8_t* s_b, const uint4 (&v)[2][8], int tid)
+{
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+        const int blk = tid + it * 128;
+        const int kc = blk / (kEncBits / 8), nc = blk % (kEncBits / 8);
+        const int half = kc >> 3, chunk = kc & 7;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+            uint4 o;
+            o.x = __byte_perm(reinterpret_cast<const uint32_t*>(&v[it][0])[j >> 1], reinterpret_cast<const uint32_t*>(&v[it][1])[j >> 1], sel);
+            o.y = __byte_perm(reinterpret_cast<const uint32_t*>(&v[it][2])[j >> 1], reinterpret_cast<const uint32_t*>(&v[it][3])[j >> 1], sel);
+            o.z = __byte_perm(reinterpret_cast<const uint32_t*>(&v[it][4])[j >> 1], reinterpret_cast<const uint32_t*>(&v[it][5])[j >> 1], sel);
+            o.w = __byte_perm(reinterpret_cast<const uint32_t*>(&v[it][6])[j >> 1], reinterpret_cast<const uint32_t*>(&v[it][7])[j >> 1], sel);
+            const int n = nc * 8 + j;
+            const uint32_t off = (uint32_t)half * kEncHalfBytes + (uint32_t)n * 128u + ((uint32_t)(chunk ^ (n & 7)) << 4);
+            *reinterpret_cast<uint4*>(s_b + off) = o;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kEncThreads, 1)
 encode_tc_kernel(const __grid_constant__ CUtensorMap x_map, const EncParams p)
 {
@@ -567,9 +603,22 @@ __global__ void __launch_bounds__(kTileThreads) encode_tile_kernel(const TilePar
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // Every global load of the kernel is issued before the first dependent instruction: R (32 KiB, through L2), the
+    // destination slot of the thread's output row, then the A tile (possibly across the bus from host memory);
+    // the kernel then costs about one memory round trip plus the MMA.
+    static_assert(kTileThreads == 128, "rt_load_128 / rt_store_128 assume 128 threads");
+    uint4 vr[2][8];
+    rt_load_128(vr, p.R, tid);
+    int64_t my_slot = -1;
+    {
+        const int64_t row = row0 + tid;  // the row this thread writes in the epilogue (warp * 32 + lane = tid)
+        if (jb.slot_mapping != nullptr && row < rows) {
+            const int64_t tok = row / H_out;
+            my_slot = jb.slot_is_int64 ? static_cast<const int64_t*>(jb.slot_mapping)[tok]
+                                       : (int64_t) static_cast<const int32_t*>(jb.slot_mapping)[tok];
+        }
+    }
     // A tile: row r of the tile, 16-byte chunk c (8 elements) -> K half c >> 3, chunk (c & 7) ^ (r & 7).
-    // All of a thread's global loads are issued before the first shared-memory store, so the tile costs
-    // one memory round trip, not sixteen.
     const int64_t t_base = row0 / H_out;
     const int h_base = (int)(row0 - t_base * H_out);
     constexpr int kChunksPerThread = kEncTileM * (kEncD / 8) / kTileThreads;  // 16
@@ -637,7 +686,7 @@ __global__ void __launch_bounds__(kTileThreads) encode_tile_kernel(const TilePar
             }
         }
     }
-    build_rt_swizzled(s_b, p.R, tid, kTileThreads);
+    rt_store_128(s_b, vr, tid);
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
@@ -675,8 +724,7 @@ __global__ void __launch_bounds__(kTileThreads) encode_tile_kernel(const TilePar
             } else {
                 const int64_t tok = row / H_out;
                 const int h = (int)(row - tok * H_out);
-                const int64_t slot = jb.slot_is_int64 ? static_cast<const int64_t*>(jb.slot_mapping)[tok]
-                                                      : (int64_t) static_cast<const int32_t*>(jb.slot_mapping)[tok];
+                const int64_t slot = my_slot;
                 if (slot >= 0 && slot < jb.n_slots) *reinterpret_cast<uint4*>(jb.out + (slot * H_out + h) * 4) = code;
             }
         }

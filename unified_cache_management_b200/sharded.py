@@ -80,6 +80,15 @@ def sharded_hamming_topk(codes_local, q_codes, block_table_local, seq_lens_globa
     return merge_fn(cand_scores, cand_ids, k)
 
 
+def exchange_layout(world: int, rank: int, slab: int, seq: int):
+    """Word offsets inside one rank's exchange buffer for step ``seq``: two parities, each
+    [scores: world*slab | ids: world*slab | flags: world (padded to 64)].  Returns (scores_off, ids_off, flags_off,
+    my_slice_off, words_per_parity): where a rank's records start and where THIS rank's slice and flag sit."""
+    words = 2 * world * slab + 64
+    base = (seq & 1) * words
+    return base, base + world * slab, base + 2 * world * slab, rank * slab, words
+
+
 class PeerExchange:
     """Gather buffers of all ranks mapped into each other's address space (torch symmetric memory), for the
     collective-free form of the sharded retrieval: every rank's selection kernel stores its records into all
@@ -98,7 +107,7 @@ class PeerExchange:
             raise ValueError("the peer exchange serves up to 8 ranks of one NVLink domain")
         self.shape = (self.world, batch, heads, kl)
         self.slab = batch * heads * kl                      # records of one rank
-        self.words_per_parity = 2 * self.world * self.slab + 64
+        self.words_per_parity = exchange_layout(self.world, self.rank, self.slab, 0)[4]
         self.buf = symm_mem.empty(2 * self.words_per_parity, dtype=torch.int32, device=device)
         self.buf.zero_()
         self.handle = symm_mem.rendezvous(self.buf, self.group)
@@ -107,15 +116,10 @@ class PeerExchange:
         dist.barrier(self.group)                            # every rank's flags are zero before any store
         self.seq = 0
 
-    def _offsets(self, parity: int):
-        base = parity * self.words_per_parity
-        return base, base + self.world * self.slab, base + 2 * self.world * self.slab   # scores, ids, flags (words)
-
     def next_step(self):
         """Returns (seq, pointer lists for topk_candidates_p2p, local views for merge_topk_wait)."""
         self.seq += 1
-        o_s, o_i, o_f = self._offsets(self.seq & 1)
-        mine = self.rank * self.slab
+        o_s, o_i, o_f, mine, _ = exchange_layout(self.world, self.rank, self.slab, self.seq)
         ps = [p + 4 * (o_s + mine) for p in self.ptrs]
         pi = [p + 4 * (o_i + mine) for p in self.ptrs]
         pf = [p + 4 * (o_f + self.rank) for p in self.ptrs]
