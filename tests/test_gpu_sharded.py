@@ -105,8 +105,8 @@ def test_long_shards_cluster_candidates(cuda_device):
     assert np.array_equal(mi.cpu().numpy(), full["logical"])
 
 
-@pytest.mark.parametrize("R", [2, 4])
-def test_peer_memory_exchange_emulated_on_one_gpu(cuda_device, R):
+@pytest.mark.parametrize("R,blocks_per_rank", [(2, 48), (4, 48), (8, 12)])
+def test_peer_memory_exchange_emulated_on_one_gpu(cuda_device, R, blocks_per_rank):
     """The collective-free exchange with the ranks emulated one after the other on one GPU: every rank's
     selection writes its records into all R gather buffers and publishes the step number, then every rank's
     merge (launched after all selections, so nothing waits for a later launch) must equal the unsharded top-k.
@@ -115,11 +115,12 @@ def test_peer_memory_exchange_emulated_on_one_gpu(cuda_device, R):
     from unified_cache_management_b200 import ops
     dev = cuda_device
     B, Hkv, G, W, BS, k = 2, 4, 2, 4, 32, 20
-    nblk = 48 * R
+    nblk = blocks_per_rank * R
     per = nblk // R
-    slab = B * Hkv * k
-    bufs_s = [[torch.zeros((R, B, Hkv, k), dtype=torch.float32, device=dev) for _ in range(R)] for _ in range(2)]
-    bufs_i = [[torch.zeros((R, B, Hkv, k), dtype=torch.int32, device=dev) for _ in range(R)] for _ in range(2)]
+    kl = min(k, per)              # a rank holding fewer than k blocks sends all of them
+    slab = B * Hkv * kl
+    bufs_s = [[torch.zeros((R, B, Hkv, kl), dtype=torch.float32, device=dev) for _ in range(R)] for _ in range(2)]
+    bufs_i = [[torch.zeros((R, B, Hkv, kl), dtype=torch.int32, device=dev) for _ in range(R)] for _ in range(2)]
     flags = [[torch.zeros((R,), dtype=torch.int32, device=dev) for _ in range(R)] for _ in range(2)]
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     for step in (1, 2, 3):
@@ -135,7 +136,7 @@ def test_peer_memory_exchange_emulated_on_one_gpu(cuda_device, R):
             ps = [bufs_s[par][d].data_ptr() + 4 * r * slab for d in range(R)]
             pi = [bufs_i[par][d].data_ptr() + 4 * r * slab for d in range(R)]
             pf = [flags[par][d].data_ptr() + 4 * r for d in range(R)]
-            ops.topk_candidates_p2p(codes, q, bt_local, seq_local, seq_g, k, r * per, 1.0 / (BS * G), ps, pi, pf, step,
+            ops.topk_candidates_p2p(codes, q, bt_local, seq_local, seq_g, kl, r * per, 1.0 / (BS * G), ps, pi, pf, step,
                                     must_select=must)
         full = O.hamming_topk(case["codes"], case["q"], case["block_table"], seq, k, O.REDUCE_SUM, False,
                               must_select=must)
