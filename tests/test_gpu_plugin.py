@@ -317,6 +317,76 @@ def test_mla_prefill_then_decode(cuda_device):
     assert dec.block_table is bt_dev
 
 
+def test_mla_prefix_cache_hit_rehashes_latent_cache_in_place(cuda_device):
+    """MLA with a prefix-cache hit: the hit's latent + rope vectors are hashed straight from the paged cache
+    [NB, BS, 512 + 64] into the 18-word rows (one request ends its prefix inside a block)."""
+    import torch
+    from unified_cache_management_b200.base import UcmSparseRole
+    from unified_cache_management_b200.gsa_on_device import GSAOnDevice
+    dev = cuda_device
+    BS = 64
+    cfg = F.make_vllm_config(model="deepseek-ai/DeepSeek-V2-Lite-Chat", mla=True, block_size=BS, num_q_heads=16,
+                             num_kv_heads=1, head_size=576, max_model_len=32 * BS, max_num_seqs=4,
+                             overrides=dict(vllm_hash_attention_topk=4 * BS, gpu_seq_len_threshold=4 * BS,
+                                            gpu_concurrency_threshold=1, vllm_hash_attention_rollback_layers=[0],
+                                            vllm_hash_attention_skip_layers=[False, False]))
+    plugin = GSAOnDevice(cfg, UcmSparseRole.WORKER)
+    NB, mb = 40, 32
+    prompt = [5 * BS + 7, 4 * BS]
+    prefix = [3 * BS + 9, 2 * BS]
+    rng = np.random.default_rng(21)
+    perm = rng.permutation(NB)
+    bt = np.zeros((2, mb), dtype=np.int32)
+    off = 0
+    for b, ln in enumerate(prompt):
+        n = -(-ln // BS)
+        bt[b, :n] = perm[off:off + n]
+        off += n
+    layer = "model.layers.1.self_attn.attn"
+    kv_bits = H.bf16_normal(rng, (NB, BS, 576))
+    kv = H.bf16_to_dev(kv_bits, dev)
+    kv_caches = {"model.layers.0.self_attn.attn": torch.zeros_like(kv), layer: kv}
+    plugin.initialize_kv_hash_cache_tensors(kv_caches, dev)
+    k_hash = kv_caches[layer][1]
+    requests = {f"r{b}": F.FakeRequest(num_computed_tokens=prefix[b], num_prompt_tokens=prompt[b]) for b in range(2)}
+    input_batch = SimpleNamespace(req_id_to_index={"r0": 0, "r1": 1})
+    qlens = [prompt[b] - prefix[b] for b in range(2)]
+    T = sum(qlens)
+    nope, rope = H.bf16_normal(rng, (T, 512)), H.bf16_normal(rng, (T, 1, 64))
+    slots = np.concatenate([bt[b, np.arange(prefix[b], prompt[b]) // BS].astype(np.int64) * BS
+                            + np.arange(prefix[b], prompt[b]) % BS for b in range(2)])
+    qsl = torch.from_numpy(np.concatenate([[0], np.cumsum(qlens)]).astype(np.int32)).to(dev)
+    bt_dev = torch.from_numpy(bt).to(dev)
+    meta = SimpleNamespace(decode=None, prefill=SimpleNamespace(query_start_loc=qsl, block_table=bt_dev, chunked_context=None),
+                           slot_mapping=torch.from_numpy(slots).to(dev), query_start_loc=qsl)
+    fc = SimpleNamespace(attn_metadata={layer: meta}, virtual_engine=0,
+                         no_compile_layers={layer: SimpleNamespace(kv_cache=[kv_caches[layer]])})
+    so = F.scheduler_output({"r0": qlens[0], "r1": qlens[1]})
+    so.num_external_computed_tokens_per_req = {"r0": prefix[0], "r1": prefix[1]}
+    plugin.update_states(so)
+    plugin.build_sparse_meta(so, requests, input_batch, {layer: meta})
+    assert plugin.has_pc_hit and plugin.prefix_block_tokens.cpu().tolist() == [BS, BS, BS, 9, BS, BS]
+    plugin.attention_begin(None, H.bf16_to_dev(nope, dev), H.bf16_to_dev(rope, dev), layer, fc, phase="prefill",
+                           k_hash=k_hash)
+    torch.cuda.synchronize()
+    rn = _bf16_bits(plugin.hash_encoder_nope.hash_weights_bf16)
+    rr = _bf16_bits(plugin.hash_encoder_rope.hash_weights_bf16)
+    codes = k_hash.view(torch.int32).cpu().numpy().view(np.uint32).reshape(NB * BS, 18)
+    rows = kv_bits.reshape(NB * BS, 576)
+    touched = np.zeros(NB * BS, dtype=bool)
+    o = 0
+    for b in range(2):
+        pos = np.arange(prompt[b])
+        slot = bt[b, pos // BS].astype(np.int64) * BS + pos % BS
+        src_n = np.concatenate([rows[slot[:prefix[b]], :512], nope[o:o + qlens[b]]])
+        src_r = np.concatenate([rows[slot[:prefix[b]], 512:], rope[o:o + qlens[b], 0]])
+        o += qlens[b]
+        assert O.count_code_mismatches(codes[slot, :16], O.hash_encode(src_n, rn)[1])[0] == 0
+        assert O.count_code_mismatches(codes[slot, 16:], O.hash_encode(src_r, rr)[1])[0] == 0
+        touched[slot] = True
+    assert (codes[~touched] == 0).all()
+
+
 def test_reference_hamming_topk_module_interface(cuda_device):
     """cuda_hamming_topk / update_seq_lens with the reference's argument list."""
     import torch
