@@ -1,5 +1,7 @@
 // Exact per-row top-k over block scores (sm_100a): radix select in shared memory + ordered
-// compaction.  One CTA per (request, kv head) row.
+// compaction.  One CTA per (request, kv head) row; a few very long rows are split over a thread-block cluster
+// (distributed shared memory).  The same routine merges the candidate records of sequence shards, which arrive
+// either through a collective or as peer-memory stores of the other GPUs' selection kernels (flag wait).
 //
 // Each candidate j has a key (forced block -> 0, valid block -> score + 1, past the request's length ->
 // all ones).  Two or three 11-bit histogram passes find the k-th smallest key T and how many keys equal
