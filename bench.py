@@ -693,6 +693,26 @@ def main():
     s1.record()
     torch.cuda.synchronize()
     scan_ms_mean = s0.elapsed_time(s1) / K
+    # the same launch as a CUDA graph of its own, replayed back to back: launches of different replays do not
+    # overlap, so this is the duration of one launch including its own prologue and drain
+    scan_graphs = []
+    with torch.cuda.stream(side):
+        for layer in range(L):
+            gph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gph, stream=side):
+                ops.block_scores(wl["caches"][layer], q_codes, wl["bt"], wl["seq_lens"], reduce="sum", out=scores)
+            scan_graphs.append(gph)
+    torch.cuda.synchronize()
+    n_iso = min(K, 500)
+    for i in range(W):
+        scan_graphs[i % L].replay()
+    torch.cuda.synchronize()
+    s0.record()
+    for i in range(n_iso):
+        scan_graphs[i % L].replay()
+    s1.record()
+    torch.cuda.synchronize()
+    scan_ms_isolated = s0.elapsed_time(s1) / n_iso
 
     # end to end with HOST buffers: a step's inputs (q and the new keys, bf16) sit in page-locked host memory
     # and the selected block ids must land in page-locked host memory; the host waits for them every step.
@@ -772,7 +792,11 @@ def main():
                          "traffic": int(round(1.025 * sb)) if args.workload == "llama3_8b_decode16" else None,
                          "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a half-batch launch, scaled by blocks scanned",
                          "algorithmic_bytes_per_launch": sb,
-                         "launch_us_mean": scan_t * 1e6, "launches_timed": K},
+                         "launch_us_mean": scan_t * 1e6, "launches_timed": K,
+                         "launch_us_isolated": scan_ms_isolated * 1e3,
+                         "note": "launch_us_mean: K launches back to back on one stream, where a launch sets itself up "
+                                 "while its predecessor drains (programmatic dependent launch), as consecutive layers "
+                                 "do; launch_us_isolated: the launch as a CUDA graph of its own, replays do not overlap"},
             "prefill_encode": {"kernel": "encode_tc_kernel (tcgen05)", **prefill,
                                "frac_hbm": prefill["gbs"] / peaks["hbm_gbs"]},
             "e2e": {"value": world * tokens_per_step * K / (e2e_ms * 1e-3), "unit": "tokens/s",

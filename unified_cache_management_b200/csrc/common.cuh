@@ -4,6 +4,7 @@
 
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "ucmr.h"
 
@@ -35,6 +36,57 @@ inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t
     cfg.stream = st;
     cfg.attrs = nullptr;
     cfg.numAttrs = 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e != cudaSuccess) {
+        note_cuda_error(e);
+        (void)cudaGetLastError();
+        return UCMR_ERR_LAUNCH;
+    }
+    return UCMR_OK;
+}
+
+// Programmatic dependent launch (UCMR_PDL=0 turns it off): a kernel launched with `early = true` may start while
+// the kernel before it in the stream is still running, once that kernel has executed grid_launch_dependents() in
+// all its CTAs (or has finished); it must call grid_dependency_wait() before touching anything the earlier kernel
+// writes.  That hides the launch latency and the prologue (barrier set-up, prefix sums, block-table loads) of the
+// retrieval's dependent kernels.
+inline bool pdl_enabled()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("UCMR_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+// Same as launch_kernel, optionally as a thread-block cluster launch (cluster_x > 1: that many consecutive CTAs
+// form a cluster, grid.x % cluster_x == 0) and / or as a programmatic dependent launch (early).
+template <typename... KArgs, typename... Args>
+inline int launch_kernel_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                            int cluster_x, bool early, Args... args)
+{
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = (unsigned)cluster_x;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (early && pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cfg.attrs = n ? attr : nullptr;
+    cfg.numAttrs = n;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
     if (e != cudaSuccess) {
         note_cuda_error(e);
@@ -76,6 +128,10 @@ constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s
 constexpr uint32_t kWaitPollsPerClockCheck = 2048;
 
 #ifdef __CUDACC__
+
+// See launch_kernel_ex.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ void flag_status(int32_t* status, int bits)
 {

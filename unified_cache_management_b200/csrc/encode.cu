@@ -589,6 +589,7 @@ __global__ void __launch_bounds__(kTileThreads) encode_tile_kernel(const TilePar
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
+    grid_launch_dependents();  // a scan launched right after this kernel may set itself up meanwhile
     const bool second = (int64_t)blockIdx.x >= p.job[0].tiles;
     const TileJob& jb = p.job[second ? 1 : 0];
     const int64_t tile = (int64_t)blockIdx.x - (second ? p.job[0].tiles : 0);

@@ -253,6 +253,7 @@ scan_ring_kernel(const RingParams p)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int Hout = p.reduce_kvhead ? 1 : p.Hkv;
+    grid_launch_dependents();  // a scan launched right behind this one (the next layer's) may set itself up
 
     if (tid == 0) {
         for (int s = 0; s < kRingWarps; ++s) mbar_init(&s_full[s], 1);
@@ -298,6 +299,7 @@ scan_ring_kernel(const RingParams p)
         }
     };
     if (warp >= p.n_active) {
+        grid_dependency_wait();
         mark_past_end();
         return;
     }
@@ -365,6 +367,9 @@ scan_ring_kernel(const RingParams p)
 
     Item cur = resolve(claim_finish(claim_start()));
     int token = claim_start();
+    // Everything above read only the sequence lengths and the block table.  The code cache, the query codes and the
+    // score buffer may still be in use by the kernel before this one (the step's encode) until here.
+    grid_dependency_wait();
     issue(cur);
     mark_past_end();  // while the first block is on its way
     Item nxt = resolve(claim_finish(token));
@@ -758,7 +763,7 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     // idempotent attribute, set on every call: cheap, and correct on every device of a process
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
     if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
-    return launch_kernel(kernel, dim3(grid), dim3(kRingThreads), smem, st, p);
+    return launch_kernel_ex(kernel, dim3(grid), dim3(kRingThreads), smem, st, 1, true, p);
 }
 
 }  // namespace ucmr

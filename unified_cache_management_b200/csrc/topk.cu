@@ -401,7 +401,6 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     const int tid = threadIdx.x;
     const int row = CL ? blockIdx.x / p.cluster : blockIdx.x;
     const bool lead = !CL || blockIdx.x % p.cluster == 0;  // the CTA that writes the row's padding and scalars
-    if (blockIdx.x == 0 && tid == 0 && p.sched != nullptr) *p.sched = 0;
     const int b = row / p.Hout;
     const int n = p.max_blocks;
     const int seq_l = p.seq_local[b];
@@ -415,6 +414,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     const bool masked = p.mask != nullptr && p.mask[b] == 0;
     const int64_t obase = (int64_t)row * p.k;
 
+    if (masked) grid_dependency_wait();  // pass-through rows copy scores below
     // padding first; the chosen entries overwrite positions [0, kb) (in a cluster: after its first barrier)
     for (int i = tid; lead && i < p.k; i += kSelThreads) {
         if (CANDIDATES) {
@@ -445,6 +445,10 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
             p.out_newseq[b] = ns;
         }
     }
+    // Up to here only the sequence lengths and the block table were read and only outputs written: the scan
+    // that produces the scores may still be running (programmatic dependent launch).
+    grid_dependency_wait();
+    if (blockIdx.x == 0 && tid == 0 && p.sched != nullptr) *p.sched = 0;
     if (masked) return;
     __syncthreads();  // padding stores precede the emits of the same CTA
 
@@ -759,9 +763,10 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
                    : (use_cluster ? select_kernel<false, true> : select_kernel<false, false>);
     rc = set_dyn_smem(kernel, smem);
     if (rc != UCMR_OK) return rc;
-    if (use_cluster)
-        return launch_kernel_cluster(kernel, dim3(rows * p.cluster), dim3(kSelThreads), smem, st, p.cluster, p);
-    return launch_kernel(kernel, dim3(rows), dim3(kSelThreads), smem, st, p);
+    // (not launched early: selection CTAs that sit on SMs waiting for the scan to end cost more than the launch
+    // latency they would hide - measured 1 to 8 us slower)
+    return launch_kernel_ex(kernel, dim3(rows * (use_cluster ? p.cluster : 1)), dim3(kSelThreads), smem, st,
+                            use_cluster ? p.cluster : 1, false, p);
 }
 
 extern "C" int ucmr_hamming_topk(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
