@@ -805,7 +805,7 @@ def main():
                                 "themselves (unified addressing); host waits for every step"},
             "gpu_launches": 3 * K, "device_status_word": status, "clocks": clocks,
         }
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:   # baselines are timed on one rank with the box to itself
             ref_gpu = time_reference_gpu(cfg, wl, dev)
             if ref_gpu is not None:
                 line["reference_gpu_kernel"] = ref_gpu
