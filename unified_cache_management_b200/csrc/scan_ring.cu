@@ -394,7 +394,10 @@ scan_ring_kernel(const RingParams p)
         __shared__ uint32_t s_qp[kRingWarps][kQPlanes][ROW];
         uint32_t* const qp = &s_qp[warp][0][0];
         const int G = p.G;
-        const int nq = 32 - __clz(G);  // planes needed for counts 0..G
+        // Per request: the counts are stored minus their minimum cmin over the 32*ROW bit positions, so only
+        // bits(max - min) planes are needed (query heads agree on most bits far less often than never or always:
+        // the counts sit in a band), and  sum_i k_i c_i = cmin * popc(k) + sum_p 2^p popc(k & Q_p).
+        int nq = 0, gk = G;  // planes in use; gk = G - 2 * cmin, the factor of popc(k)
         int ctot = 0;
         while (cur.valid) {
             if (!mbar_wait(full, phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
@@ -423,9 +426,34 @@ scan_ring_kernel(const RingParams p)
                             }
                         }
                     }
+                }
+                // minimum and maximum count over all bit positions: bitwise search from the top plane
+                int cmin = 0, cmax = 0;
+                {
+                    uint32_t mlo = lane < W ? 0xFFFFFFFFu : 0u, mhi = mlo;  // positions still tied for min / max
+#pragma unroll
+                    for (int pl = kQPlanes - 1; pl >= 0; --pl) {
+                        const uint32_t z = mlo & ~P[pl];
+                        if (__any_sync(0xffffffffu, z != 0u)) mlo = z; else cmin |= 1 << pl;
+                        const uint32_t o = mhi & P[pl];
+                        if (__any_sync(0xffffffffu, o != 0u)) { mhi = o; cmax |= 1 << pl; }
+                    }
+                }
+                if (G == 1) cmin = 0;  // plane 0 is then used as the query code itself (see below)
+                if (lane < W) {
+                    uint32_t borrow = 0u;  // bit-sliced subtraction of the constant cmin
+#pragma unroll
+                    for (int pl = 0; pl < kQPlanes; ++pl) {
+                        const uint32_t b = ((cmin >> pl) & 1) ? 0xFFFFFFFFu : 0u;
+                        const uint32_t a = P[pl];
+                        P[pl] = a ^ b ^ borrow;
+                        borrow = (~a & (b | borrow)) | (b & borrow);
+                    }
 #pragma unroll
                     for (int pl = 0; pl < kQPlanes; ++pl) qp[pl * W + lane] = P[pl];
                 }
+                nq = 32 - __clz(cmax - cmin);  // 0 when every position has the same count
+                gk = G - 2 * cmin;
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) cpop += __shfl_xor_sync(0xffffffffu, cpop, off);
                 ctot = cpop;
@@ -485,8 +513,8 @@ scan_ring_kernel(const RingParams p)
                     d[0] = hs_popc<W>(v0);
                     d[1] = hs_popc<W>(v1);
                 } else {
-                    d[0] = ctot + G * hs_popc<W>(k[0]);
-                    d[1] = ctot + G * hs_popc<W>(k[1]);
+                    d[0] = ctot + gk * hs_popc<W>(k[0]);
+                    d[1] = ctot + gk * hs_popc<W>(k[1]);
                 }
                 for (int pl = 0; pl < (G == 1 ? 0 : nq); ++pl) {
                     uint32_t v0[W], v1[W];
