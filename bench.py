@@ -181,7 +181,7 @@ def make_step(cfg, wl, dev):
         kk = wl["k_new"][layer] if k_new is None else k_new
         ops.hash_encode_decode_step(qq, kk, wl["last_slot"], wl["caches"][layer], wl["R"], q_codes_out=q_codes)
         ops.hamming_topk(wl["caches"][layer], q_codes, wl["bt"], wl["seq_lens"], k, reduce="sum",
-                         must_select=MUST_SELECT, workspace=ws, out=out, want_scores=False)
+                         must_select=MUST_SELECT, workspace=ws, out=out, want_scores=False, inputs_stable=True)
         return out
 
     return step, ws, q_codes, out
@@ -422,7 +422,7 @@ def run_extra_workload(args, rank, world, local_rank):
 
         def step(layer):
             ops.hamming_topk(caches[layer], q, bt, seq_d, k, reduce="sum", reduce_kvhead=True, must_select=MUST_SELECT,
-                             workspace=ws, out=ret, want_scores=False)
+                             workspace=ws, out=ret, want_scores=False, inputs_stable=True)
             ops.gather_kv(kp, vp, ret.physical.view(B, k), ok, ov)
         par, scaling = f"dp{world} (independent replicas)", "weak"
         total_tokens = tokens * world
@@ -445,7 +445,7 @@ def run_extra_workload(args, rank, world, local_rank):
 
         def step(layer):
             ops.hamming_topk(caches[layer], q, bt, seq_d, k, reduce="sum", must_select=MUST_SELECT, workspace=ws,
-                             out=ret, want_scores=False)
+                             out=ret, want_scores=False, inputs_stable=True)
         par, scaling = f"tp{world} by kv head, no collective", "strong"
         total_tokens = B * seq_len
         alg = dict(scan_bytes_per_gpu=B * seq_len * Hkv * Wd * 4)
@@ -478,7 +478,7 @@ def run_extra_workload(args, rank, world, local_rank):
             def step(layer):
                 sharded.sharded_hamming_topk_p2p(caches[layer], q, bt_local, seq_g, k, BS, nblk_total, scale, ex,
                                                  reduce="sum", must_select=MUST_SELECT, workspace=ws, plan=plan_r,
-                                                 status=st_word)
+                                                 status=st_word, inputs_stable=True)
         elif world > 1:
             plan_r = sharded.shard_plan(seq_g, BS, nblk_total, world, rank)
             exchange_kind = "NCCL all-gather of (score, id) records"
@@ -486,13 +486,13 @@ def run_extra_workload(args, rank, world, local_rank):
             def step(layer):
                 sharded.sharded_hamming_topk(caches[layer], q, bt_local, seq_g, k, BS, nblk_total, scale, reduce="sum",
                                              must_select=MUST_SELECT, workspace=ws, gather_buffer=gbuf, send_buffer=sbuf,
-                                             plan=plan_r)
+                                             plan=plan_r, inputs_stable=True)
         else:
             plan = sharded.shard_plan(seq_g, BS, nblk_total, 1, 0)
 
             def step(layer):
                 cs, ci = ops.topk_candidates(caches[layer], q, bt_local, plan.seq_lens_local, seq_g, k, 0, scale,
-                                             reduce="sum", must_select=MUST_SELECT, workspace=ws)
+                                             reduce="sum", must_select=MUST_SELECT, workspace=ws, inputs_stable=True)
                 ops.merge_topk(cs.unsqueeze(0), ci.unsqueeze(0), k)
         par, scaling = f"sequence shards over {world} rank(s); exchange: {exchange_kind}", "strong"
         total_tokens = B * seq_total
@@ -684,12 +684,12 @@ def main():
     # K timed ones, same rotation over the layer caches
     scores = torch.empty((cfg["B"], cfg["Hkv"], wl["mb"]), dtype=torch.int32, device=dev)
     for i in range(W):
-        ops.block_scores(wl["caches"][i % L], q_codes, wl["bt"], wl["seq_lens"], reduce="sum", out=scores)
+        ops.block_scores(wl["caches"][i % L], q_codes, wl["bt"], wl["seq_lens"], reduce="sum", out=scores, inputs_stable=True)
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     s0.record()
     for i in range(K):
-        ops.block_scores(wl["caches"][i % L], q_codes, wl["bt"], wl["seq_lens"], reduce="sum", out=scores)
+        ops.block_scores(wl["caches"][i % L], q_codes, wl["bt"], wl["seq_lens"], reduce="sum", out=scores, inputs_stable=True)
     s1.record()
     torch.cuda.synchronize()
     scan_ms_mean = s0.elapsed_time(s1) / K
@@ -700,7 +700,7 @@ def main():
         for layer in range(L):
             gph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(gph, stream=side):
-                ops.block_scores(wl["caches"][layer], q_codes, wl["bt"], wl["seq_lens"], reduce="sum", out=scores)
+                ops.block_scores(wl["caches"][layer], q_codes, wl["bt"], wl["seq_lens"], reduce="sum", out=scores, inputs_stable=True)
             scan_graphs.append(gph)
     torch.cuda.synchronize()
     n_iso = min(K, 500)
@@ -729,7 +729,7 @@ def main():
         ops.hash_encode_decode_step(q_pin[layer], k_pin[layer], wl["last_slot"], wl["caches"][layer], wl["R"],
                                     q_codes_out=q_codes)
         ops.hamming_topk(wl["caches"][layer], q_codes, wl["bt"], wl["seq_lens"], cfg["k"], reduce="sum",
-                         must_select=MUST_SELECT, workspace=ws, out=out_host, want_scores=False)
+                         must_select=MUST_SELECT, workspace=ws, out=out_host, want_scores=False, inputs_stable=True)
 
     e2e_graphs = []
     with torch.cuda.stream(side):

@@ -45,6 +45,11 @@ extern "C" {
 
 #define UCMR_REDUCE_MIN 0 /* block score = min over tokens (reference behaviour)                 */
 #define UCMR_REDUCE_SUM 1 /* block score = sum over tokens (mean * BS * G)                       */
+/* May be OR-ed into reduce_mode: the caller guarantees that seq_lens and block_table are NOT written by the
+ * kernel launched right before this call on the stream (true in a decode loop, where they are prepared at
+ * the start of the step).  The scan then resolves its first work items (prefix sums, block-table loads)
+ * while that earlier kernel is still draining instead of after it (programmatic dependent launch).     */
+#define UCMR_FLAG_INPUTS_STABLE 0x100
 
 #define UCMR_MAX_MUST_SELECT 16
 #define UCMR_WORKSPACE_HEADER_BYTES 256

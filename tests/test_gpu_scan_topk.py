@@ -241,3 +241,31 @@ def test_many_long_rows_uncached_keys(cuda_device):
     ref = OC.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], 300, O.REDUCE_SUM, False,
                           must_select=(0, -1))
     _cmp(out, ref)
+
+
+def test_inputs_stable_flag_changes_nothing_but_the_schedule(cuda_device):
+    """UCMR_FLAG_INPUTS_STABLE only moves the scan's dependency wait: same results, back to back launches included;
+    unknown flag bits are refused."""
+    import torch
+    from unified_cache_management_b200 import lib, ops
+    B, Hkv, G, W, BS, mb = 4, 8, 4, 4, 128, 300
+    case = H.make_paged_case(5, B, Hkv, G, W, BS, mb)
+    dev = cuda_device
+    args = [H.to_dev_i32(case[n], dev) for n in ("codes", "q", "block_table", "seq_lens")]
+    ws = ops.new_workspace(B, Hkv, mb, dev)
+    ref = O.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], 9, O.REDUCE_SUM, False,
+                         must_select=(0, -1))
+    for _ in range(3):   # consecutive launches overlap their set-up with the predecessor's drain
+        out = ops.hamming_topk(*args, 9, reduce="sum", must_select=(0, -1), workspace=ws, inputs_stable=True)
+    torch.cuda.synchronize()
+    _cmp(out, ref)
+    s0 = ops.block_scores(*args, reduce="min")
+    s1 = ops.block_scores(*args, reduce="min", inputs_stable=True)
+    torch.cuda.synchronize()
+    assert torch.equal(s0, s1)
+    with pytest.raises(ValueError):
+        codes, q, bt, sl = args
+        rc = lib.load_library().ucmr_block_scores(codes.data_ptr(), codes.shape[0], BS, Hkv, W, q.data_ptr(), Hkv * G,
+                                                  bt.data_ptr(), mb, mb, sl.data_ptr(), B, 1 | 0x200, 0, s0.data_ptr(),
+                                                  None, None)
+        lib.check(rc, "ucmr_block_scores")

@@ -48,8 +48,8 @@ inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t
 // Programmatic dependent launch (UCMR_PDL=0 turns it off): a kernel launched with `early = true` may start while
 // the kernel before it in the stream is still running, once that kernel has executed grid_launch_dependents() in
 // all its CTAs (or has finished); it must call grid_dependency_wait() before touching anything the earlier kernel
-// writes.  That hides the launch latency and the prologue (barrier set-up, prefix sums, block-table loads) of the
-// retrieval's dependent kernels.
+// writes - or reads anything that kernel might write: the kernel before it can be any kernel of the caller.  That
+// hides the launch latency of the scan and lets its CTAs take over SMs one by one as the earlier kernel drains.
 inline bool pdl_enabled()
 {
     static int v = -1;

@@ -311,11 +311,14 @@ int run_scan(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const ui
     int rc = validate_scan_args(codes, NB, BS, Hkv, W, q, Hq, bt, max_blocks, bt_stride, seq_lens, B);
     if (rc != UCMR_OK) return rc;
     if (!out) return UCMR_ERR_BAD_ARG;
+    const int mode_flags = reduce_mode & ~0xFF;  // UCMR_FLAG_* bits travel with the mode
+    reduce_mode &= 0xFF;
+    if (mode_flags & ~UCMR_FLAG_INPUTS_STABLE) return UCMR_ERR_BAD_ARG;
     if (reduce_mode != UCMR_REDUCE_MIN && reduce_mode != UCMR_REDUCE_SUM) return UCMR_ERR_BAD_ARG;
     if (B == 0) return UCMR_OK;
 
     if (!force_register_scan()) {
-        rc = run_scan_ring(codes, NB, BS, Hkv, W, q, Hq, bt, max_blocks, bt_stride, seq_lens, B, reduce_mode,
+        rc = run_scan_ring(codes, NB, BS, Hkv, W, q, Hq, bt, max_blocks, bt_stride, seq_lens, B, reduce_mode | mode_flags,
                            reduce_kvhead, out, status, sched, st);
         if (rc != UCMR_ERR_UNSUPPORTED) return rc;
     }

@@ -65,6 +65,7 @@ struct RingParams {
     int block_stride;  // = block_bytes (blocks of a stage sit back to back)
     int stage_bytes;   // bps * block_stride
     int n_active;      // warps (= stages) in use: min(kRingWarps, ring bytes / stage bytes)
+    int early_setup;   // UCMR_FLAG_INPUTS_STABLE: sequence lengths and block table may be read before the dependency wait
 };
 
 struct __align__(16) StageMeta {
@@ -260,6 +261,11 @@ scan_ring_kernel(const RingParams p)
         fence_mbar_init();
         s_pool_empty = 0;
     }
+    // Launched early (programmatic dependent launch): the CTA is resident and its barriers are set up while the
+    // kernel before it in the stream drains.  Nothing in global memory is read before the wait, because that kernel
+    // may be the one that writes the sequence lengths or the block table - unless the caller has ruled that out
+    // (early_setup): then the wait moves behind the resolution of the first work items.
+    if (!p.early_setup) grid_dependency_wait();
     if (warp == 0) {  // prefix sum of items per request
         int run = 0;
         for (int b0 = 0; b0 < p.B; b0 += 32) {
@@ -299,7 +305,7 @@ scan_ring_kernel(const RingParams p)
         }
     };
     if (warp >= p.n_active) {
-        grid_dependency_wait();
+        if (p.early_setup) grid_dependency_wait();
         mark_past_end();
         return;
     }
@@ -367,9 +373,9 @@ scan_ring_kernel(const RingParams p)
 
     Item cur = resolve(claim_finish(claim_start()));
     int token = claim_start();
-    // Everything above read only the sequence lengths and the block table.  The code cache, the query codes and the
-    // score buffer may still be in use by the kernel before this one (the step's encode) until here.
-    grid_dependency_wait();
+    // (early_setup) up to here only the sequence lengths and the block table were read; the code cache, the query
+    // codes and the score buffer may still be in use by the kernel before this one
+    if (p.early_setup) grid_dependency_wait();
     issue(cur);
     mark_past_end();  // while the first block is on its way
     Item nxt = resolve(claim_finish(token));
@@ -714,6 +720,8 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
                   const int32_t* bt, int max_blocks, int64_t bt_stride, const int32_t* seq_lens, int B,
                   int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, int32_t* sched, cudaStream_t st)
 {
+    const bool inputs_stable = (reduce_mode & UCMR_FLAG_INPUTS_STABLE) != 0;
+    reduce_mode &= 0xFF;
     const int G = Hq / Hkv;
     const int64_t RW = (int64_t)Hkv * W;
     // MLA codes: one latent "head" of 576 bits; blocks of 8, 16 or a multiple of 32 tokens
@@ -745,7 +753,7 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     p.NB = NB; p.BS = BS; p.Hkv = Hkv; p.W = W; p.G = G; p.Hq = Hq;
     p.q = q; p.bt = bt; p.max_blocks = max_blocks; p.bt_stride = bt_stride; p.seq_lens = seq_lens; p.B = B;
     p.reduce_kvhead = reduce_kvhead ? 1 : 0; p.out = out; p.status = status; p.sched = sched;
-    p.RW = (int)RW; p.bps = bps; p.block_bytes = (int)block_bytes;
+    p.RW = (int)RW; p.bps = bps; p.block_bytes = (int)block_bytes; p.early_setup = inputs_stable ? 1 : 0;
     if (block_bytes % (row_mode ? 16 : 128) != 0) return UCMR_ERR_UNSUPPORTED;
     if (!is_min && RW < 32 && BS > 240) return UCMR_ERR_UNSUPPORTED;
     p.block_stride = (int)block_bytes;

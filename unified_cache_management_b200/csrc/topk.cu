@@ -710,7 +710,9 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
     int32_t* status = static_cast<int32_t*>(workspace);
     int32_t* scores = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + UCMR_WORKSPACE_HEADER_BYTES);
     int32_t* sched = status + 2;  // work counter of the scan; zero between launches
-    rc = run_scan(codes, NB, BS, Hkv, W, q_codes, Hq, bt, max_blocks, bt_stride, seq_local, B, reduce_mode,
+    const int scan_mode = reduce_mode;  // with its UCMR_FLAG_* bits
+    reduce_mode &= 0xFF;
+    rc = run_scan(codes, NB, BS, Hkv, W, q_codes, Hq, bt, max_blocks, bt_stride, seq_local, B, scan_mode,
                   reduce_kvhead, scores, status, sched, st);
     if (rc != UCMR_OK || B == 0) return rc;
     if (k == 0 && peers) return UCMR_ERR_BAD_ARG;

@@ -30,6 +30,15 @@ def reduce_mode(mode) -> int:
     return int(mode)
 
 
+FLAG_INPUTS_STABLE = 0x100  # UCMR_FLAG_INPUTS_STABLE
+
+
+def _mode(reduce, inputs_stable: bool) -> int:
+    """reduce mode with the caller's promise that seq_lens / block_table are not written by the kernel launched
+    right before the call (lets the scan set itself up while that kernel drains)."""
+    return reduce_mode(reduce) | (FLAG_INPUTS_STABLE if inputs_stable else 0)
+
+
 def _stream(t: torch.Tensor) -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
@@ -297,7 +306,7 @@ def hamming_topk(codes: torch.Tensor, q_codes: torch.Tensor, block_table: torch.
                  k: int, *, reduce="sum", reduce_kvhead: bool = False, must_select: Sequence[int] = (),
                  sink_tokens: int = 0, recent_tokens: int = 0, k_per_request: Optional[torch.Tensor] = None,
                  request_mask: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
-                 out: Optional[Retrieval] = None, want_scores: bool = True) -> Retrieval:
+                 out: Optional[Retrieval] = None, want_scores: bool = True, inputs_stable: bool = False) -> Retrieval:
     """Scan + exact top-k in two launches.  See ``ucmr_hamming_topk`` in include/ucmr.h."""
     codes, q_codes, bt_stride = _scan_args(codes, q_codes, block_table, seq_lens)
     nb, bs, hkv, w = codes.shape
@@ -327,7 +336,7 @@ def hamming_topk(codes: torch.Tensor, q_codes: torch.Tensor, block_table: torch.
     lib = _l.load_library()
     _l.check(lib.ucmr_hamming_topk(
         _ptr(codes), nb, bs, hkv, w, _ptr(q_codes), hq, _ptr(block_table), mb, bt_stride, _ptr(seq_lens), b, k,
-        _ptr(k_per_request), _ptr(request_mask), reduce_mode(reduce), int(bool(reduce_kvhead)), must, n_must,
+        _ptr(k_per_request), _ptr(request_mask), _mode(reduce, inputs_stable), int(bool(reduce_kvhead)), must, n_must,
         int(sink_tokens), int(recent_tokens), _ptr(out.physical), _ptr(out.logical), _ptr(out.scores),
         _ptr(out.valid_count), _ptr(out.new_seq_lens), _ptr(workspace), workspace.numel(), _stream(codes)),
         "ucmr_hamming_topk")
@@ -362,7 +371,8 @@ def hamming_topk_static(codes: torch.Tensor, q_codes: torch.Tensor, block_table:
 
 
 def block_scores(codes, q_codes, block_table, seq_lens, *, reduce="sum", reduce_kvhead=False,
-                 out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
+                 inputs_stable: bool = False) -> torch.Tensor:
     """int32 [B, Hout, max_blocks] block scores (-1 past each request's length)."""
     codes, q_codes, bt_stride = _scan_args(codes, q_codes, block_table, seq_lens)
     nb, bs, hkv, w = codes.shape
@@ -373,7 +383,7 @@ def block_scores(codes, q_codes, block_table, seq_lens, *, reduce="sum", reduce_
         out = torch.empty((b, hout, mb), dtype=torch.int32, device=codes.device)
     lib = _l.load_library()
     _l.check(lib.ucmr_block_scores(_ptr(codes), nb, bs, hkv, w, _ptr(q_codes), hq, _ptr(block_table), mb, bt_stride,
-                                   _ptr(seq_lens), b, reduce_mode(reduce), int(bool(reduce_kvhead)), _ptr(out),
+                                   _ptr(seq_lens), b, _mode(reduce, inputs_stable), int(bool(reduce_kvhead)), _ptr(out),
                                    _ptr(status), _stream(codes)), "ucmr_block_scores")
     return out
 
@@ -415,7 +425,7 @@ def update_seq_lens(seq_lens: torch.Tensor, topk_token: int, block_size: int) ->
 # ----------------------------------------------------------------------------------------------
 def topk_candidates(codes, q_codes, block_table, seq_lens_local, seq_lens_global, k: int, block_id_offset: int,
                     score_scale: float, *, reduce="sum", reduce_kvhead=False, must_select=(), sink_tokens=0,
-                    recent_tokens=0, workspace=None, out_scores=None, out_ids=None):
+                    recent_tokens=0, workspace=None, out_scores=None, out_ids=None, inputs_stable: bool = False):
     """Local top-k of one sequence shard as (float32 score, int32 global block id) records [B,Hout,k]."""
     codes, q_codes, bt_stride = _scan_args(codes, q_codes, block_table, seq_lens_local)
     _need_cuda("seq_lens_global", seq_lens_global, torch.int32)
@@ -436,7 +446,7 @@ def topk_candidates(codes, q_codes, block_table, seq_lens_local, seq_lens_global
     lib = _l.load_library()
     _l.check(lib.ucmr_topk_candidates(
         _ptr(codes), nb, bs, hkv, w, _ptr(q_codes), hq, _ptr(block_table), mb, bt_stride, _ptr(seq_lens_local),
-        _ptr(seq_lens_global), b, k, int(block_id_offset), float(score_scale), reduce_mode(reduce),
+        _ptr(seq_lens_global), b, k, int(block_id_offset), float(score_scale), _mode(reduce, inputs_stable),
         int(bool(reduce_kvhead)), must, n_must, int(sink_tokens), int(recent_tokens), _ptr(out_scores),
         _ptr(out_ids), _ptr(workspace), workspace.numel(), _stream(codes)), "ucmr_topk_candidates")
     return out_scores, out_ids
@@ -445,7 +455,7 @@ def topk_candidates(codes, q_codes, block_table, seq_lens_local, seq_lens_global
 def topk_candidates_p2p(codes, q_codes, block_table, seq_lens_local, seq_lens_global, k: int, block_id_offset: int,
                         score_scale: float, peer_scores_ptrs: Sequence[int], peer_ids_ptrs: Sequence[int],
                         peer_flag_ptrs: Sequence[int], seq: int, *, reduce="sum", reduce_kvhead=False, must_select=(),
-                        sink_tokens=0, recent_tokens=0, workspace=None) -> None:
+                        sink_tokens=0, recent_tokens=0, workspace=None, inputs_stable: bool = False) -> None:
     """``topk_candidates`` whose records go straight into every rank's gather buffer over peer memory: the three
     pointer lists hold, per rank r, the device address of THIS rank's [B,Hout,k] slice of rank r's score / id
     buffers and of this rank's flag word on rank r; ``seq`` is published to the flags when the launch is done."""
@@ -465,7 +475,7 @@ def topk_candidates_p2p(codes, q_codes, block_table, seq_lens_local, seq_lens_gl
     must, n_must = _must_array(must_select)
     _l.check(_l.load_library().ucmr_topk_candidates_p2p(
         _ptr(codes), nb, bs, hkv, w, _ptr(q_codes), hq, _ptr(block_table), mb, bt_stride, _ptr(seq_lens_local),
-        _ptr(seq_lens_global), b, k, int(block_id_offset), float(score_scale), reduce_mode(reduce),
+        _ptr(seq_lens_global), b, k, int(block_id_offset), float(score_scale), _mode(reduce, inputs_stable),
         int(bool(reduce_kvhead)), must, n_must, int(sink_tokens), int(recent_tokens),
         arr(*[int(p) for p in peer_scores_ptrs]), arr(*[int(p) for p in peer_ids_ptrs]),
         arr(*[int(p) for p in peer_flag_ptrs]), n, int(seq), _ptr(workspace), workspace.numel(), _stream(codes)),

@@ -51,7 +51,7 @@ def sharded_hamming_topk(codes_local, q_codes, block_table_local, seq_lens_globa
                          reduce_kvhead: bool = False, must_select: Sequence[int] = (), sink_tokens: int = 0,
                          recent_tokens: int = 0, workspace=None, gather_buffer: Optional[torch.Tensor] = None,
                          send_buffer: Optional[torch.Tensor] = None, plan: Optional[ShardPlan] = None,
-                         candidates_fn: Callable = _default_candidates, merge_fn: Callable = _default_merge):
+                         inputs_stable: bool = False, candidates_fn: Callable = _default_candidates, merge_fn: Callable = _default_merge):
     """Returns (scores float32 [B,Hout,k], global logical block ids int32 [B,Hout,k]), identical on
     every rank.  block_table_local is this rank's slice [B, max_blocks_global/world] of the table.
     ``send_buffer`` (int32 [2, B, Hout, min(k, blocks per rank)]) lets the local selection write its records
@@ -63,14 +63,17 @@ def sharded_hamming_topk(codes_local, q_codes, block_table_local, seq_lens_globa
         plan = shard_plan(seq_lens_global, block_size, max_blocks_global, world, rank)
     kl = min(k, plan.blocks_per_rank)
     extra = {}
-    if send_buffer is not None and candidates_fn is _default_candidates:
-        extra = dict(out_scores=send_buffer[0].view(torch.float32), out_ids=send_buffer[1])
+    if candidates_fn is _default_candidates:
+        extra["inputs_stable"] = inputs_stable
+    direct = send_buffer is not None and candidates_fn is _default_candidates
+    if direct:
+        extra.update(out_scores=send_buffer[0].view(torch.float32), out_ids=send_buffer[1])
     sc, ids = candidates_fn(codes_local, q_codes, block_table_local, plan.seq_lens_local, seq_lens_global, kl,
                             plan.block_offset, score_scale, reduce=reduce, reduce_kvhead=reduce_kvhead,
                             must_select=must_select, sink_tokens=sink_tokens, recent_tokens=recent_tokens,
                             workspace=workspace, **extra)
     # one message per rank: [2, B, H, kl] int32 (float bits, then ids)
-    send = send_buffer if extra else torch.stack((sc.view(torch.int32), ids))
+    send = send_buffer if direct else torch.stack((sc.view(torch.int32), ids))
     if gather_buffer is None:
         gather_buffer = torch.empty((world * 2,) + tuple(send.shape[1:]), dtype=torch.int32, device=send.device)
     dist.all_gather_into_tensor(gather_buffer, send, group=group)   # concatenation along dim 0
@@ -134,7 +137,7 @@ def sharded_hamming_topk_p2p(codes_local, q_codes, block_table_local, seq_lens_g
                              max_blocks_global: int, score_scale: float, exchange: PeerExchange, *, reduce="sum",
                              reduce_kvhead: bool = False, must_select: Sequence[int] = (), sink_tokens: int = 0,
                              recent_tokens: int = 0, workspace=None, plan: Optional[ShardPlan] = None,
-                             status: Optional[torch.Tensor] = None):
+                             status: Optional[torch.Tensor] = None, inputs_stable: bool = False):
     """``sharded_hamming_topk`` with the all-gather folded into the two kernels (see ``PeerExchange``): two launches
     per step and no collective call."""
     from . import ops
@@ -147,5 +150,5 @@ def sharded_hamming_topk_p2p(codes_local, q_codes, block_table_local, seq_lens_g
     ops.topk_candidates_p2p(codes_local, q_codes, block_table_local, plan.seq_lens_local, seq_lens_global, kl,
                             plan.block_offset, score_scale, ps, pi, pf, seq, reduce=reduce, reduce_kvhead=reduce_kvhead,
                             must_select=must_select, sink_tokens=sink_tokens, recent_tokens=recent_tokens,
-                            workspace=workspace)
+                            workspace=workspace, inputs_stable=inputs_stable)
     return ops.merge_topk_wait(scores, ids, k, flags, seq, status=status)
