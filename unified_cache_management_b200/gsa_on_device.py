@@ -298,7 +298,7 @@ class GSAOnDevice(UcmSparseBase):
                                 new_seq_lens=self._retrieval.new_seq_lens[:n])
             ops.hamming_topk(self._mla_code_cache_words(k_hash), q_hash, dec.block_table, dec.seq_lens, kb,
                              reduce=self.gsa_on_device_config.reduce, reduce_kvhead=False,
-                             workspace=self._workspace, out=out, want_scores=False, **self._forced())
+                             workspace=self._workspace, out=out, want_scores=False, inputs_stable=True, **self._forced())
             block_table = out.physical[:, 0, :]
             dec.topk_block_table = block_table
         self.ori_block_table_decode = dec.block_table
@@ -340,6 +340,8 @@ class GSAOnDevice(UcmSparseBase):
         return topk_tile_scheduler_metadata, topk_num_splits, view
 
     # ---- retrieval ---------------------------------------------------------------------------------
+    # (inputs_stable in the retrieval calls: block table and lengths come from the step's attention metadata, built
+    # before the forward pass; the kernel enqueued right before the scan is the query hashing, which writes neither)
     def _forced(self):
         if self.use_must_select_blocks:
             return dict(must_select=tuple(self.gsa_on_device_config.must_select_blocks))
@@ -353,7 +355,7 @@ class GSAOnDevice(UcmSparseBase):
                             valid_count=self._retrieval.valid_count[:n], new_seq_lens=self._retrieval.new_seq_lens[:n])
         ops.hamming_topk(k_hash, q_hash, attn_metadata.block_table[:n], attn_metadata.seq_lens[:n], kb,
                          reduce=self.gsa_on_device_config.reduce, reduce_kvhead=self.num_key_heads > 1,
-                         workspace=self._workspace, out=out, want_scores=False, **self._forced())
+                         workspace=self._workspace, out=out, want_scores=False, inputs_stable=True, **self._forced())
         block_table_decode = out.physical[:, 0, :]
         topk = kb
         if self.decode_only:
