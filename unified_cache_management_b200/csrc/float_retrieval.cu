@@ -140,34 +140,56 @@ struct SoftmaxParams {
     int32_t* ids;               // [n_blocks] = 0, 1, 2, ...
 };
 
-// grid = (ceil(S / kDotWarps), X * Hq); a warp per representation, the row's query vector in shared memory.
+// grid = (ceil(S / reps per CTA), X * Hkv): a group of lanes per representation (16 lanes for D = 128, so two
+// representations per warp); the representation is read once and multiplied with the G query heads of its kv head,
+// whose vectors sit in shared memory as float32.
+constexpr int kLogitMaxG = 16;
+
 __global__ void __launch_bounds__(kDotWarps * 32) kv_logits_kernel(const SoftmaxParams p)
 {
-    extern __shared__ float s_q[];  // [D]
-    const int row = blockIdx.y;     // x * Hq + H
-    const int Hh = row % p.Hq;
-    const int h = Hh / (p.Hq / p.Hkv);
-    for (int e = threadIdx.x; e < p.D; e += blockDim.x) s_q[e] = __bfloat162float(p.q[(int64_t)row * p.D + e]);
+    extern __shared__ float s_q[];  // [G][D]
+    const int G = p.Hq / p.Hkv;
+    const int x = blockIdx.y / p.Hkv, h = blockIdx.y % p.Hkv;
+    const int row0 = x * p.Hq + h * G;  // first query row of this kv head
+    for (int e = threadIdx.x; e < G * p.D; e += blockDim.x) s_q[e] = __bfloat162float(p.q[(int64_t)row0 * p.D + e]);
     __syncthreads();
+    const int chunks = p.D / 8;
+    int lanes_per = 1;
+    while (lanes_per < chunks && lanes_per < 32) lanes_per <<= 1;
+    const int reps_per_warp = 32 / lanes_per;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int sidx = blockIdx.x * kDotWarps + warp;
-    if (sidx >= p.S) return;
-    const uint4* kr = reinterpret_cast<const uint4*>(p.repr + ((int64_t)sidx * p.Hkv + h) * p.D);
-    float acc = 0.f;
-    for (int c = lane; c < p.D / 8; c += 32) {
-        const uint4 v = __ldg(kr + c);
-        const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v);
-        const float* qv = s_q + c * 8;
+    const int sub = lane / lanes_per, sl = lane % lanes_per;
+    const int sidx = (blockIdx.x * kDotWarps + warp) * reps_per_warp + sub;
+    const bool live = sidx < p.S;
+    float acc[kLogitMaxG];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float2 f = __bfloat1622float2(hv[j]);
-            acc = fmaf(f.x, qv[2 * j], acc);
-            acc = fmaf(f.y, qv[2 * j + 1], acc);
+    for (int g = 0; g < kLogitMaxG; ++g) acc[g] = 0.f;
+    if (live) {
+        const uint4* kr = reinterpret_cast<const uint4*>(p.repr + ((int64_t)sidx * p.Hkv + h) * p.D);
+        for (int c = sl; c < chunks; c += lanes_per) {
+            const uint4 v = __ldg(kr + c);
+            const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v);
+            float kf[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(hv[j]); kf[2 * j] = f.x; kf[2 * j + 1] = f.y; }
+#pragma unroll
+            for (int g = 0; g < kLogitMaxG; ++g) {
+                if (g < G) {
+                    const float* qv = s_q + g * p.D + c * 8;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[g] = fmaf(kf[j], qv[j], acc[g]);
+                }
+            }
         }
     }
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    if (lane == 0) p.logits[(int64_t)row * p.S + sidx] = acc;
+    for (int g = 0; g < kLogitMaxG; ++g) {
+        if (g < G) {  // (G is the same for the whole warp)
+            float a = acc[g];
+            for (int off = lanes_per >> 1; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+            if (live && sl == 0) p.logits[(int64_t)(row0 + g) * p.S + sidx] = a;
+        }
+    }
 }
 
 // One CTA per row: max, then sum of exp(l - max).
@@ -294,8 +316,12 @@ extern "C" int ucmr_softmax_topk(const void* repr, int n_blocks, int M, int Hkv,
     float* scores = p.stats + (size_t)rows * 2;
     p.out = out_block_scores ? out_block_scores : scores;
     p.ids = reinterpret_cast<int32_t*>(scores + n_blocks);
-    int rc = launch_kernel(kv_logits_kernel, dim3((unsigned)((p.S + kDotWarps - 1) / kDotWarps), (unsigned)rows),
-                           dim3(kDotWarps * 32), (size_t)D * sizeof(float), st, p);
+    if (Hq / Hkv > kLogitMaxG || (size_t)(Hq / Hkv) * D * sizeof(float) > 48 * 1024) return UCMR_ERR_UNSUPPORTED;
+    int lanes_per = 1;
+    while (lanes_per < D / 8 && lanes_per < 32) lanes_per <<= 1;
+    const int reps_per_cta = kDotWarps * (32 / lanes_per);
+    int rc = launch_kernel(kv_logits_kernel, dim3((unsigned)((p.S + reps_per_cta - 1) / reps_per_cta), (unsigned)(X * Hkv)),
+                           dim3(kDotWarps * 32), (size_t)(Hq / Hkv) * D * sizeof(float), st, p);
     if (rc != UCMR_OK) return rc;
     rc = launch_kernel(softmax_stats_kernel, dim3((unsigned)rows), dim3(256), 0, st, p);
     if (rc != UCMR_OK) return rc;
