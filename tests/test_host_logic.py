@@ -101,3 +101,11 @@ def test_peer_exchange_layout_keeps_slices_and_parities_apart():
             for n, sp in enumerate(spans):
                 seen[(seq, rank, n)] = sp
     assert exchange_layout(world, 0, slab, 3)[0] == exchange_layout(world, 0, slab, 1)[0]
+
+
+def test_reduce_mode_carries_the_inputs_stable_flag():
+    from unified_cache_management_b200 import ops
+    assert ops._mode("min", False) == 0 and ops._mode("sum", False) == 1
+    assert ops._mode("sum", True) == 1 | 0x100 and ops._mode("min", True) == 0x100
+    with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "ucmr.h")) as f:
+        assert "#define UCMR_FLAG_INPUTS_STABLE 0x100" in f.read()
