@@ -36,6 +36,10 @@ def _cmp(out, ref):
     (2, 2, 8, 4, 128, 17),   # Llama-3-70B at TP=4
     (2, 8, 4, 8, 64, 20),    # 256-bit codes, block 64
     (2, 4, 1, 4, 16, 33),    # plugin path: one code per kv head, vLLM block 16
+    (3, 8, 4, 4, 16, 70),    # 8 kv heads, block 16: eight 2 KiB blocks per stage, scanned one after the other
+    (2, 8, 1, 4, 16, 70),    # the same with one code per kv head (min mode: four blocks per stage, lane groups)
+    (2, 8, 4, 4, 32, 45),    # block 32: four blocks per stage
+    (2, 8, 2, 8, 16, 37),    # 256-bit codes, block 16: two passes per block, four blocks per stage
     (2, 8, 1, 16, 32, 9),    # 512-bit codes
     (1, 2, 3, 4, 128, 6),    # G outside {1,2,4,8}: query codes in shared memory
     (2, 1, 16, 18, 64, 7),   # 576-bit MLA codes, W=18: token-row path of the staged kernel

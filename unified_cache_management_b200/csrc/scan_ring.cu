@@ -105,9 +105,9 @@ __device__ __forceinline__ int hs_popc(const uint32_t (&v)[N])
     }
 }
 
-// A lane buffers CH tokens of its column in registers per chunk: 128, or 64 for blocks of at most 64 tokens
-// (half the carry-save work per chunk).  The vertical counters of a chunk then need log2(CH) + 1 planes.
-__host__ __device__ constexpr int planes_of(int ch) { return ch == 128 ? 8 : 7; }
+// A lane buffers CH tokens of its column in registers per chunk: 128, or 64 / 32 / 16 for blocks of at most that
+// many tokens (the carry-save work of a chunk is proportional to CH).  The vertical counters of a chunk then need log2(CH) + 1 planes.
+__host__ __device__ constexpr int planes_of(int ch) { return ch == 128 ? 8 : ch == 64 ? 7 : ch == 32 ? 6 : 5; }
 
 // Folds 16 words into planes 0..3 (carry-save) and returns the carry of weight 16.
 __device__ __forceinline__ uint32_t fold16(uint32_t& ones, uint32_t& twos, uint32_t& fours, uint32_t& eights,
@@ -153,24 +153,33 @@ __device__ __forceinline__ void add_planes(const uint32_t (&a)[NP], const uint32
 template <int CH>
 __device__ __forceinline__ void fold_chunk(const uint32_t (&x)[CH], uint32_t (&pl)[planes_of(CH)])
 {
-    static_assert(CH == 128 || CH == 64, "chunk size");
-    uint32_t q6[CH / 32][6];
-#pragma unroll
-    for (int c = 0; c < CH / 32; ++c) {
+    static_assert(CH == 128 || CH == 64 || CH == 32 || CH == 16, "chunk size");
+    if constexpr (CH == 16) {
         uint32_t p0 = 0, p1 = 0, p2 = 0, p3 = 0;
-        const uint32_t c0 = fold16(p0, p1, p2, p3, &x[c * 32]);
-        const uint32_t c1 = fold16(p0, p1, p2, p3, &x[c * 32 + 16]);
-        q6[c][0] = p0; q6[c][1] = p1; q6[c][2] = p2; q6[c][3] = p3;
-        q6[c][4] = c0 ^ c1;
-        q6[c][5] = c0 & c1;
-    }
-    if constexpr (CH == 128) {
-        uint32_t h7a[7], h7b[7];
-        add_planes<6>(q6[0], q6[1], h7a);
-        add_planes<6>(q6[2], q6[3], h7b);
-        add_planes<7>(h7a, h7b, pl);
+        const uint32_t c0 = fold16(p0, p1, p2, p3, &x[0]);
+        pl[0] = p0; pl[1] = p1; pl[2] = p2; pl[3] = p3; pl[4] = c0;
     } else {
-        add_planes<6>(q6[0], q6[1], pl);
+        uint32_t q6[CH / 32][6];
+#pragma unroll
+        for (int c = 0; c < CH / 32; ++c) {
+            uint32_t p0 = 0, p1 = 0, p2 = 0, p3 = 0;
+            const uint32_t c0 = fold16(p0, p1, p2, p3, &x[c * 32]);
+            const uint32_t c1 = fold16(p0, p1, p2, p3, &x[c * 32 + 16]);
+            q6[c][0] = p0; q6[c][1] = p1; q6[c][2] = p2; q6[c][3] = p3;
+            q6[c][4] = c0 ^ c1;
+            q6[c][5] = c0 & c1;
+        }
+        if constexpr (CH == 128) {
+            uint32_t h7a[7], h7b[7];
+            add_planes<6>(q6[0], q6[1], h7a);
+            add_planes<6>(q6[2], q6[3], h7b);
+            add_planes<7>(h7a, h7b, pl);
+        } else if constexpr (CH == 64) {
+            add_planes<6>(q6[0], q6[1], pl);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 6; ++i) pl[i] = q6[0][i];
+        }
     }
 }
 
@@ -581,16 +590,21 @@ scan_ring_kernel(const RingParams p)
             if (!mbar_wait(full, phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
             phase ^= 1u;
             const StageMeta m = s_meta[warp];
-            const int j = m.j0 + blk;
-            const bool have = blk < p.bps && ((m.valid_mask >> blk) & 1u);
+            bool reissued = false;
+            // rows of 32 words or more: the blocks of a stage (several when they are small) are scanned one after
+            // the other by the whole warp; narrower rows: one lane group per block, all at once
+            const int seq_blocks = (RW < 32) ? 1 : p.bps;
+            for (int sbi = 0; sbi < seq_blocks; ++sbi) {
+            const int blk_e = (RW < 32) ? blk : sbi;
+            const int j = m.j0 + blk_e;
+            const bool have = blk_e < p.bps && ((m.valid_mask >> blk_e) & 1u);
             const int ntok = have ? min(p.BS, m.seq - j * p.BS) : 0;
-            const uint8_t* sb = stage + blk * p.block_stride;
+            const uint8_t* sb = stage + blk_e * p.block_stride;
             int total = 0;  // per-head (or all-head) score, complete in the lanes that write
-            // tokens are walked in 128-token chunks; with several blocks per stage every lane group walks
-            // the whole block capacity (rotated), else only the valid tokens
+            // tokens are walked in chunks; with one lane group per block every group walks the whole block
+            // capacity (rotated), else only the valid tokens
             const int walk = (RW < 32) ? p.BS : ntok;
             const int n_chunks = (__reduce_max_sync(0xffffffffu, walk) + CH - 1) / CH;
-            bool reissued = false;
             const bool full_narrow = RW < 32 && p.BS == CH && __all_sync(0xffffffffu, ntok == CH);
             for (int ps = 0; ps < passes; ++ps) {
                 const int col = col0 + ps * 32;
@@ -606,7 +620,7 @@ scan_ring_kernel(const RingParams p)
                 for (int c = 0; c < n_chunks; ++c) {
                     uint32_t x[CH];
                     load_chunk<RW_T, CH>(x, colp, c * CH, ntok, RW, rot, p.BS, full_narrow);
-                    if (ps == passes - 1 && c == n_chunks - 1) {
+                    if (sbi == seq_blocks - 1 && ps == passes - 1 && c == n_chunks - 1) {
                         // the stage's last words are in registers: refill it before doing the math
                         __syncwarp();
                         advance();
@@ -626,9 +640,10 @@ scan_ring_kernel(const RingParams p)
             }
             cur_b = m.b;
             if (p.reduce_kvhead && have && col0 == 0) p.out[(int64_t)m.b * p.max_blocks + j] = total;
-            if (!have && blk < p.bps && col0 == 0 && j < p.max_blocks) {
+            if (!have && blk_e < p.bps && col0 == 0 && j < p.max_blocks) {
                 // block inside the stage but not loaded: past the request's end or a bad id
                 for (int h = 0; h < Hout; ++h) p.out[((int64_t)m.b * Hout + h) * p.max_blocks + j] = -1;
+            }
             }
             if (!reissued) {
                 __syncwarp();
@@ -740,12 +755,11 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
         if (W % 4 != 0 || reinterpret_cast<uintptr_t>(q) % 16 != 0) return UCMR_ERR_UNSUPPORTED;
         const int P = Hkv * (W / 4);
         if (P > 32) return UCMR_ERR_UNSUPPORTED;
-        // several small blocks share a stage so that a warp-load still spans >= 16 tokens per block
-        while (bps < kRingMaxBps && 32 / (bps * 2) >= P && block_bytes * bps * 2 <= 16 * 1024 &&
-               BS / (32 / (bps * 2) / P) >= 16)
-            bps *= 2;
+        // several small blocks share a stage (one lane group per block) as long as a group still covers a token
+        while (bps < kRingMaxBps && 32 / (bps * 2) >= P && block_bytes * bps * 2 <= 16 * 1024) bps *= 2;
     } else {
         if (RW < 32) bps = (int)(32 / RW);
+        else while (bps < kRingMaxBps && block_bytes * (bps + 1) <= 16 * 1024) ++bps;  // small blocks: several per stage
         if (bps > kRingMaxBps) return UCMR_ERR_UNSUPPORTED;
     }
     RingParams p{};
@@ -786,7 +800,11 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     if (p.RW == RWV && G == GV) kernel = scan_ring_kernel<false, RWV, GV, CHV, 0>;
 #define UCMR_RING_ROW(RWV, CHV) \
     UCMR_RING_CASE(RWV, 1, CHV) UCMR_RING_CASE(RWV, 2, CHV) UCMR_RING_CASE(RWV, 4, CHV) UCMR_RING_CASE(RWV, 8, CHV)
-        if (short_blocks) {
+        if (BS <= 16) {
+            UCMR_RING_ROW(32, 16) UCMR_RING_ROW(64, 16)
+        } else if (BS <= 32) {
+            UCMR_RING_ROW(32, 32) UCMR_RING_ROW(64, 32)
+        } else if (short_blocks) {
             UCMR_RING_ROW(32, 64) UCMR_RING_ROW(64, 64)
         }
         if (!kernel) {
