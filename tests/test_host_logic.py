@@ -32,15 +32,53 @@ def test_config_round_trip_and_validation(tmp_path):
     assert cfg.must_select_blocks == [0, -2, -1] and cfg.vllm_hash_attention_topk == 4096
 
 
-def test_reference_json_files_load_unchanged():
+# sha256 of json.dumps(parsed, sort_keys=True, separators=(",", ":")) of the reference's six per-model files
+# (ucm/sparse/gsa_on_device/configs/*.json): the shipped files must parse to the same values.
+_REFERENCE_CONFIG_DIGESTS = {
+    "gsa_on_device_deepseek_r1_awq_config.json": "c720deaba07e98dfd800e845f21bb5bdf212d1847e30ba3b624fe0c5fc093b73",
+    "gsa_on_device_deepseek_v2_lite_config.json": "6001244e3b7887374b2b77faaee07e37bb70c971dcbc6f95e9721f2463b5be7e",
+    "gsa_on_device_qwen3_32B_config.json": "290541b311437409c8f10be10ef3cbe36df73fb35a4d75f8fefa70e9f1676251",
+    "gsa_on_device_qwen3_4B_config.json": "b2da5f9dc1895d932cabba441ff91dd68c05638bbb5088cc2c6b217d1010a75d",
+    "gsa_on_device_qwen3_coder_30B_A3B_config.json": "f76c044baa2ac3b2f5b4681eaffebb686191072941a0ec65b397d0f0ef5c42ac",
+    "gsa_on_device_qwq_32B_config.json": "61743382310d630b70bd878107a5d0565965636bdb82bb6a7ecece46582bda35",
+}
+# per-model files this repository adds (the reference ships none for these models)
+_ADDED_CONFIGS = {"gsa_on_device_llama3_8B_config.json", "gsa_on_device_llama3_70B_config.json"}
+
+
+def _config_dir():
+    return os.path.join(os.path.dirname(base.__file__), "configs")
+
+
+def test_shipped_config_files_load():
     """Every key of the shipped per-model files is a field of the dataclass (same names as the reference)."""
-    d = os.path.join(os.path.dirname(base.__file__), "configs")
-    files = [f for f in os.listdir(d) if f.endswith(".json")]
-    assert files
+    d = _config_dir()
+    files = {f for f in os.listdir(d) if f.endswith(".json")}
+    assert files == set(_REFERENCE_CONFIG_DIGESTS) | _ADDED_CONFIGS
     for f in files:
         cfg = GSAOnDeviceConfig.from_json(os.path.join(d, f))
-        assert cfg.vllm_hash_attention_topk % 128 == 0
         assert len(cfg.top_k_ratio_per_layer) == cfg.num_hidden_layers
+        if cfg.vllm_hash_attention_topk is not None:   # the reference's QwQ file carries no vLLM keys
+            assert cfg.vllm_hash_attention_topk % 128 == 0
+            assert len(cfg.vllm_hash_attention_skip_layers) == cfg.num_hidden_layers
+
+
+def test_shipped_config_values_are_the_reference_values():
+    """The six files named like the reference's hold the reference's values: compared with the checkout when
+    UCM_REFERENCE_ROOT points at one, and with the digests of its parsed files in any case."""
+    import hashlib
+    d = _config_dir()
+    ref_root = os.environ.get("UCM_REFERENCE_ROOT")
+    for name, digest in _REFERENCE_CONFIG_DIGESTS.items():
+        with open(os.path.join(d, name)) as f:
+            mine = json.load(f)
+        canon = json.dumps(mine, sort_keys=True, separators=(",", ":")).encode()
+        assert hashlib.sha256(canon).hexdigest() == digest, name
+        if ref_root:
+            ref_file = os.path.join(ref_root, "ucm", "sparse", "gsa_on_device", "configs", name)
+            if os.path.exists(ref_file):
+                with open(ref_file) as f:
+                    assert json.load(f) == mine, name
 
 
 def test_model_lookup():

@@ -106,6 +106,11 @@ class GSAOnDevice(UcmSparseBase):
         self.hash_skip_layers = cfg.vllm_hash_attention_skip_layers
         self.seq_len_threshold = cfg.gpu_seq_len_threshold
         self.concurrency_threshold = cfg.gpu_concurrency_threshold
+        if self.hash_topk_tokens is None:
+            # the reference's QwQ-32B file has no vLLM keys: its plugin stops at the comparison below with a
+            # TypeError; say what is missing instead
+            raise ValueError(f"{os.path.basename(path)} has no vllm_hash_attention_topk; set it (and the rollback / "
+                             "skip layer lists) in ucm_sparse_config or in the file")
         assert self.seq_len_threshold >= self.hash_topk_tokens, \
             "seq_len_threshold must be larger than or equal to vllm_hash_attention_topk"
         assert self.hash_topk_tokens % self.block_size == 0, "vllm_hash_attention_topk must be divisible by block_size"
