@@ -3,9 +3,19 @@
  *
  * Every entry point takes raw device pointers, sizes and an explicit CUDA
  * stream (a cudaStream_t passed as void*; NULL = legacy default stream),
- * launches asynchronously on that stream, allocates nothing, keeps no global
- * state and returns an int status (0 = ok, negative = error, see UCMR_ERR_*).
- * Nothing here throws or aborts.  The caller owns all buffers.
+ * launches asynchronously on that stream, allocates nothing and returns an
+ * int status (0 = ok, negative = error, see UCMR_ERR_*).  Nothing here throws
+ * or aborts.  The caller owns all buffers.
+ *
+ * State kept by the library, all of it process-wide and none of it per call:
+ *   - ucmr_hamming_topk_static uses one fixed device array per GPU and a
+ *     mutex-guarded table of its per-device addresses (see its declaration);
+ *   - the tuning switches UCMR_PDL, UCMR_SCAN, UCMR_SEL_CLUSTER and
+ *     UCMR_FORCE_SIMT_ENCODE are environment variables read once, on the
+ *     first call that consults them, and cached for the life of the process;
+ *   - the text of the last CUDA error is kept per host thread.
+ * Everything else (scores between two kernels, work counters, device status)
+ * lives in the caller's workspace.
  *
  * Each declaration names the interface of the reference project
  * (ModelEngine-Group/unified-cache-management, paths relative to its root) that it
@@ -45,10 +55,13 @@ extern "C" {
 
 #define UCMR_REDUCE_MIN 0 /* block score = min over tokens (reference behaviour)                 */
 #define UCMR_REDUCE_SUM 1 /* block score = sum over tokens (mean * BS * G)                       */
-/* May be OR-ed into reduce_mode: the caller guarantees that seq_lens and block_table are NOT written by the
- * kernel launched right before this call on the stream (true in a decode loop, where they are prepared at
- * the start of the step).  The scan then resolves its first work items (prefix sums, block-table loads)
- * while that earlier kernel is still draining instead of after it (programmatic dependent launch).     */
+/* May be OR-ed into reduce_mode: the caller guarantees that seq_lens and block_table are NOT written by any
+ * kernel that may still be in flight on the stream when this call's scan starts - not only the kernel right
+ * before it: kernels that release their successor early (this library's scan and decode-step encode do, and so
+ * may a caller's own programmatic-dependent-launch kernels) let a flagged scan become resident while a kernel
+ * two or more positions earlier is still running.  True in a decode loop, where both arrays are prepared at
+ * the start of the step and only read afterwards.  The scan then resolves its first work items (prefix sums,
+ * block-table loads) while the earlier kernels drain instead of after them.                              */
 #define UCMR_FLAG_INPUTS_STABLE 0x100
 
 #define UCMR_MAX_MUST_SELECT 16

@@ -14,7 +14,15 @@
   ``oracle/_ref/hamming_cuda/``: the GPU-side checker and the "reference kernel
   recompiled for B200" timing leg.  About two minutes of nvcc.
 
-Run ``python oracle/build_oracle.py`` to build the CPU pair; add ``--cuda-ref`` for the third.
+* ``build_ref_esa()`` compiles the reference project's ESA float-retrieval backend
+  (``ucm/sparse/esa/retrieval/cpy/retrieval_backend.cpp``, unmodified) into ``oracle/_ref/``.  The
+  file includes ``<numaif.h>``; where libnuma is not installed the stand-in header under
+  ``oracle/shim/`` is put on the include path.
+
+The reference checkout is found through the ``UCM_REFERENCE_ROOT`` environment variable (or the
+``reference_root`` argument); without it only modules built earlier are used.
+
+Run ``python oracle/build_oracle.py`` to build the CPU modules; add ``--cuda-ref`` for the CUDA one.
 """
 from __future__ import annotations
 
@@ -28,6 +36,15 @@ BUILD_DIR = os.path.join(HERE, "_build")
 REF_DIR = os.path.join(HERE, "_ref")
 ORACLE_SO = os.path.join(BUILD_DIR, "liboracle.so")
 REF_SRC_REL = "ucm/sparse/gsa_on_device/csrc/cuda/hash_retrieval/cpy/hash_retrieval_backend.cpp"
+
+
+REF_ESA_SRC_REL = "ucm/sparse/esa/retrieval/cpy/retrieval_backend.cpp"
+SHIM_DIR = os.path.join(HERE, "shim")
+
+
+def _reference_root(arg: str | None) -> str:
+    """The reference checkout: the argument, else $UCM_REFERENCE_ROOT, else a path that does not exist."""
+    return arg or os.environ.get("UCM_REFERENCE_ROOT") or os.path.join(HERE, "_no_reference_checkout")
 
 
 def _newer(target: str, *sources: str) -> bool:
@@ -55,7 +72,7 @@ def ref_module_path() -> str:
 
 def build_ref(reference_root: str | None = None, force: bool = False) -> str | None:
     """Returns the module path, or None when neither source nor prebuilt module exists."""
-    reference_root = reference_root or os.environ.get("UCM_REFERENCE_ROOT", "/root/reference")
+    reference_root = _reference_root(reference_root)
     src = os.path.join(reference_root, REF_SRC_REL)
     out = ref_module_path()
     if not os.path.exists(src):
@@ -69,6 +86,49 @@ def build_ref(reference_root: str | None = None, force: bool = False) -> str | N
            src, "-o", out, "-lpthread"]
     subprocess.check_call(cmd)
     return out
+
+
+def ref_esa_module_path() -> str:
+    suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+    return os.path.join(REF_DIR, "retrieval_backend" + suffix)
+
+
+def _have_system_numaif() -> bool:
+    probe = subprocess.run(["g++", "-x", "c++", "-E", "-"], input=b"#include <numaif.h>\n", capture_output=True)
+    return probe.returncode == 0
+
+
+def build_ref_esa(reference_root: str | None = None, force: bool = False) -> str | None:
+    """ESA float-retrieval backend of the reference, compiled unmodified.  Returns the module path, or None when
+    neither source nor prebuilt module exists."""
+    reference_root = _reference_root(reference_root)
+    src = os.path.join(reference_root, REF_ESA_SRC_REL)
+    out = ref_esa_module_path()
+    if not os.path.exists(src):
+        return out if os.path.exists(out) else None
+    if not force and _newer(out, src):
+        return out
+    import pybind11
+    os.makedirs(REF_DIR, exist_ok=True)
+    cmd = ["g++", "-O3", "-shared", "-fPIC", "-std=c++17", "-I" + pybind11.get_include(),
+           "-I" + sysconfig.get_paths()["include"]]
+    if not _have_system_numaif():
+        cmd.append("-I" + SHIM_DIR)
+    cmd += [src, "-o", out, "-lpthread"]
+    subprocess.check_call(cmd)
+    return out
+
+
+def load_ref_esa():
+    """Import the compiled ESA backend, or return None if it was never built."""
+    path = ref_esa_module_path()
+    if not os.path.exists(path):
+        return None
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("retrieval_backend", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
 
 
 REF_CUDA_DIR_REL = "ucm/sparse/gsa_on_device/csrc/cuda/ham_dist"
@@ -87,7 +147,7 @@ def ref_cuda_module_path() -> str:
 
 def build_ref_cuda(reference_root: str | None = None, force: bool = False) -> str | None:
     """Returns the module path, or None when neither source nor prebuilt module exists."""
-    reference_root = reference_root or os.environ.get("UCM_REFERENCE_ROOT", "/root/reference")
+    reference_root = _reference_root(reference_root)
     src_dir = os.path.join(reference_root, REF_CUDA_DIR_REL)
     sources = [os.path.join(src_dir, "paged_ham_dist_mla.cu"), os.path.join(src_dir, "cpy", "hamming.cpp")]
     out = ref_cuda_module_path()
@@ -132,5 +192,6 @@ def load_ref():
 if __name__ == "__main__":
     print(build_oracle_c(force="--force" in sys.argv))
     print(build_ref(force="--force" in sys.argv))
+    print(build_ref_esa(force="--force" in sys.argv))
     if "--cuda-ref" in sys.argv:
         print(build_ref_cuda(force="--force" in sys.argv))

@@ -10,7 +10,7 @@ scripts assert nothing).  The restatement is pinned instead against (a) outputs
 of the reference's own Python functions run on CPU (fixtures under
 ``tests/golden``, produced by ``tests/golden/make_golden.py``) and (b) the
 reference's C++ retrieval backend compiled from its own source
-(``oracle/build_ref.py``).
+(recipe: ``oracle/build_oracle.py``).
 
 Reference lines followed (paths inside the reference project):
 

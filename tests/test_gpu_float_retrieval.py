@@ -121,6 +121,38 @@ def test_dot_topk_random(cuda_device):
     _check_topk(s.cpu().numpy(), i.cpu().numpy(), sc, clean, k)
 
 
+def test_dot_topk_matches_reference_esa_backend(cuda_device):
+    """ucmr_dot_topk against the reference's own RetrievalWorkerBackend (retrieval_backend.cpp:206-225, compiled
+    unmodified by oracle/build_oracle.py): same chosen candidates, scores within 1e-5 relative of its float32 loop."""
+    import torch
+    from oracle import build_oracle
+    from tests.test_oracle import run_esa_backend
+    from unified_cache_management_b200 import ops
+    mod = build_oracle.load_ref_esa()
+    if mod is None:
+        pytest.skip("ESA backend of the reference not built on this machine")
+    rng = np.random.default_rng(33)
+    N, dim, B, n, k = 3000, 1024, 6, 2000, 64
+    pool = H.bf16_normal(rng, (N, dim))
+    q = H.bf16_normal(rng, (B, dim))
+    indexes = np.full((B, n), -1, dtype=np.int32)
+    for b, cnt in enumerate([2000, 1000, 500, 64, 10, 1]):
+        indexes[b, :cnt] = rng.permutation(N)[:cnt]
+    res = run_esa_backend(mod, O.bf16_bits_to_f32(pool), O.bf16_bits_to_f32(q), indexes, k)
+    s, i = ops.dot_topk(H.bf16_to_dev(pool, cuda_device), H.bf16_to_dev(q, cuda_device),
+                        torch.from_numpy(indexes).to(cuda_device), k)
+    torch.cuda.synchronize()
+    s, i = s.cpu().numpy(), i.cpu().numpy()
+    for b in range(B):
+        ref_ids = [int(x) for x in res["indices"][b]]
+        ref_scores = {int(x): float(v) for x, v in zip(res["indices"][b], res["scores"][b])}
+        mine = [int(x) for x in i[b] if x >= 0]
+        assert sorted(mine) == sorted(ref_ids)
+        for pos, idx in enumerate(i[b]):
+            if idx >= 0:
+                assert abs(float(s[b, pos]) - ref_scores[int(idx)]) <= 1e-5 * abs(ref_scores[int(idx)]) + 1e-4
+
+
 @pytest.mark.parametrize("n,M,Hkv,G,D,X", [(300, 4, 2, 4, 128, 1), (64, 1, 8, 4, 128, 3), (1000, 16, 1, 2, 64, 2)])
 def test_softmax_block_scores_and_topk(cuda_device, n, M, Hkv, G, D, X):
     import torch

@@ -110,7 +110,6 @@ def test_golden_topk_tail():
         mine = np.where(s < 0, np.inf, np.where(forced, 0.0, s))
         assert np.array_equal(mine, ref_scores[b])
         kth = np.sort(ref_scores[b])[k - 1]
-        ref_sel = set(np.searchsorted(np.sort(bt[b][:int((seq[b] + BS - 1) // BS)]), []).tolist())  # placeholder
         # map the reference's physical ids back to logical positions
         nb = int((seq[b] + BS - 1) // BS)
         phys_to_log = {int(bt[b, j]): j for j in range(nb)}
@@ -163,6 +162,47 @@ def test_reference_cpp_backend_min_scores():
         assert np.array_equal(np.sort(s)[:k], res["scores"][b])
         pos = {int(p): i for i, p in enumerate(allowed)}
         assert all(s[pos[int(p)]] == sc for p, sc in zip(res["indices"][b], res["scores"][b]))
+
+
+def run_esa_backend(mod, pool_f32, q_f32, indexes, k):
+    """submit / wait / get_result round trips through the reference's RetrievalWorkerBackend, one request at a
+    time: its get_result copies as many entries for every request as the FIRST request produced
+    (retrieval_backend.cpp:133-141), which reads past the end of shorter result lists in a ragged batch."""
+    backend = mod.RetrievalWorkerBackend(np.ascontiguousarray(pool_f32, dtype=np.float32), {0: [0]})
+    out = {"indices": [], "scores": []}
+    for b in range(len(q_f32)):
+        rid = backend.submit(np.ascontiguousarray(q_f32[b:b + 1], dtype=np.float32), int(k),
+                             np.ascontiguousarray(indexes[b:b + 1], dtype=np.int32))
+        backend.wait(rid)
+        res = backend.get_result(rid)
+        out["indices"].append(np.asarray(res["indices"])[0].copy())
+        out["scores"].append(np.asarray(res["scores"])[0].copy())
+    del backend
+    return out
+
+
+def test_reference_esa_backend_dot_topk():
+    """ucm/sparse/esa/retrieval/cpy/retrieval_backend.cpp compiled unmodified (its <numaif.h> include is met by a
+    stand-in header where libnuma is missing): inner products and the k best per request.  The oracle's float64
+    scores must match its float32 scalar loop to 1e-5 and pick the same candidates in the same order."""
+    build_oracle.build_ref_esa()
+    mod = build_oracle.load_ref_esa()
+    if mod is None:
+        pytest.skip("ESA backend not built (no reference checkout on this machine)")
+    rng = np.random.default_rng(21)
+    N, dim, B, n, k = 400, 256, 4, 120, 9
+    pool = H.bf16_normal(rng, (N, dim))
+    q = H.bf16_normal(rng, (B, dim))
+    indexes = np.full((B, n), -1, dtype=np.int32)
+    for b, cnt in enumerate([120, 60, 9, 3]):
+        indexes[b, :cnt] = rng.permutation(N)[:cnt]
+    res = run_esa_backend(mod, O.bf16_bits_to_f32(pool), O.bf16_bits_to_f32(q), indexes, k)
+    scores, chosen = O.dot_topk(pool, q, indexes, k)
+    for b in range(B):
+        got_idx = [int(i) for i in res["indices"][b]]
+        want_idx = [int(indexes[b][p]) for p in chosen[b]]
+        assert got_idx == want_idx            # continuous random scores: no ties, so the order is determined
+        assert np.allclose(np.asarray(res["scores"][b], dtype=np.float64), scores[b][chosen[b]], rtol=1e-5, atol=1e-5)
 
 
 def test_golden_float_retrieval():

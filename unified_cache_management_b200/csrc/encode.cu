@@ -923,11 +923,9 @@ static int launch_tc(const void* x, int64_t T, int H, int64_t stride_t, int64_t 
     p.out = out; p.slot_mapping = slot_mapping; p.slot_is_int64 = slot_is_int64; p.n_slots = n_slots;
     p.R = static_cast<const __nv_bfloat16*>(R); p.status = status;
 
-    static bool attr_set = false;
-    if (!attr_set) {
+    {   // idempotent attribute, set on every call: a flag kept per process would leave a second device without it
         cudaError_t e = cudaFuncSetAttribute(encode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kEncSmemBytes);
         if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
-        attr_set = true;
     }
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

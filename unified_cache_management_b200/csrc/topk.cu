@@ -684,6 +684,16 @@ extern "C" int ucmr_workspace_status(const void* workspace, int* host_status, vo
     return *host_status == 0 ? UCMR_OK : UCMR_ERR_DEVICE;
 }
 
+// Value of the UCMR_SEL_CLUSTER environment switch, looked up on the first call only (-1 = not set).
+static int sel_cluster_override()
+{
+    static const int v = [] {
+        const char* env = getenv("UCMR_SEL_CLUSTER");
+        return env ? atoi(env) : -1;
+    }();
+    return v;
+}
+
 struct PeerDest {
     int n_peers, seq;
     float* scores[kMaxPeers];
@@ -702,6 +712,7 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
 {
     if (k < 0 || k > max_blocks) return UCMR_ERR_BAD_ARG;
     if (candidates ? (!peers && (!cand_scores || !cand_ids)) : !out_phys) return UCMR_ERR_BAD_ARG;
+    if (k == 0 && peers) return UCMR_ERR_BAD_ARG;
     if (!workspace) return UCMR_ERR_WORKSPACE;
     if (workspace_bytes < ucmr_hamming_topk_workspace_bytes(B, Hkv, max_blocks, reduce_kvhead)) return UCMR_ERR_WORKSPACE;
     SelectParams p{};
@@ -715,7 +726,12 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
     rc = run_scan(codes, NB, BS, Hkv, W, q_codes, Hq, bt, max_blocks, bt_stride, seq_local, B, scan_mode,
                   reduce_kvhead, scores, status, sched, st);
     if (rc != UCMR_OK || B == 0) return rc;
-    if (k == 0 && peers) return UCMR_ERR_BAD_ARG;
+    // From here on the scan is enqueued and will leave its work counter non-zero; the selection kernel clears it.
+    // If that kernel cannot be launched, clear it here, or the next call on this workspace would skip work items.
+    auto fail_after_scan = [&](int code) {
+        (void)cudaMemsetAsync(sched, 0, sizeof(int32_t), st);
+        return code;
+    };
     if (k == 0) {  // no selection kernel will run: clear the counter here
         cudaError_t e = cudaMemsetAsync(sched, 0, sizeof(int32_t), st);
         if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
@@ -750,8 +766,8 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
     p.cluster = 1;
     while (p.cluster < 8 && rows * p.cluster * 2 <= 160 && max_blocks > p.cluster * kSelClusterSlice) p.cluster *= 2;
     bool use_cluster = p.cluster > 1;
-    if (const char* env = getenv("UCMR_SEL_CLUSTER")) {  // tuning aid: 0 = never split, 1/2/4/8 = force that size
-        const int v = atoi(env);
+    {   // tuning aid UCMR_SEL_CLUSTER (read once per process): 0 = never split, 1/2/4/8 = force that size
+        const int v = sel_cluster_override();
         if (v == 0) { p.cluster = 1; use_cluster = false; }
         else if (v == 1 || v == 2 || v == 4 || v == 8) { p.cluster = v; use_cluster = true; }
     }
@@ -764,11 +780,12 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
         candidates ? (use_cluster ? select_kernel<true, true> : select_kernel<true, false>)
                    : (use_cluster ? select_kernel<false, true> : select_kernel<false, false>);
     rc = set_dyn_smem(kernel, smem);
-    if (rc != UCMR_OK) return rc;
+    if (rc != UCMR_OK) return fail_after_scan(rc);
     // (not launched early: selection CTAs that sit on SMs waiting for the scan to end cost more than the launch
     // latency they would hide - measured 1 to 8 us slower)
-    return launch_kernel_ex(kernel, dim3(rows * (use_cluster ? p.cluster : 1)), dim3(kSelThreads), smem, st,
-                            use_cluster ? p.cluster : 1, false, p);
+    rc = launch_kernel_ex(kernel, dim3(rows * (use_cluster ? p.cluster : 1)), dim3(kSelThreads), smem, st,
+                          use_cluster ? p.cluster : 1, false, p);
+    return rc == UCMR_OK ? rc : fail_after_scan(rc);
 }
 
 extern "C" int ucmr_hamming_topk(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,

@@ -34,8 +34,8 @@ FLAG_INPUTS_STABLE = 0x100  # UCMR_FLAG_INPUTS_STABLE
 
 
 def _mode(reduce, inputs_stable: bool) -> int:
-    """reduce mode with the caller's promise that seq_lens / block_table are not written by the kernel launched
-    right before the call (lets the scan set itself up while that kernel drains)."""
+    """reduce mode with the caller's promise that seq_lens / block_table are not written by any kernel that may
+    still be in flight on the stream (lets the scan set itself up while earlier kernels drain)."""
     return reduce_mode(reduce) | (FLAG_INPUTS_STABLE if inputs_stable else 0)
 
 
@@ -270,6 +270,27 @@ class Retrieval:
     new_seq_lens: torch.Tensor   # int32 [B]
 
 
+def _check_out(out: "Retrieval", b: int, hout: int, k: int, device) -> None:
+    """Every non-None member of ``out`` must be what the kernel writes: int32, contiguous, on the codes' device,
+    [B, Hout, k] for the id / score arrays and [B] for the two per-request arrays.  ``physical`` alone may be
+    page-locked host memory.  The kernel writes B*Hout*k entries whatever the tensor's size, so a buffer shaped for
+    another k or head mode is refused here."""
+    for name, t, shape, host_ok in (("physical", out.physical, (b, hout, k), True),
+                                    ("logical", out.logical, (b, hout, k), False),
+                                    ("scores", out.scores, (b, hout, k), False),
+                                    ("valid_count", out.valid_count, (b,), False),
+                                    ("new_seq_lens", out.new_seq_lens, (b,), False)):
+        if t is None:
+            if name == "physical":
+                raise ValueError("out.physical is required")
+            continue
+        (_need_cuda_or_pinned if host_ok else _need_cuda)(f"out.{name}", t, torch.int32)
+        if tuple(t.shape) != shape:
+            raise ValueError(f"out.{name} must have shape {shape}, got {tuple(t.shape)}")
+        if t.is_cuda and t.device != device:
+            raise ValueError(f"out.{name} is on {t.device}, the codes are on {device}")
+
+
 def _scan_args(codes, q_codes, block_table, seq_lens):
     _need_cuda("codes", codes)
     codes = as_words(codes)
@@ -331,7 +352,7 @@ def hamming_topk(codes: torch.Tensor, q_codes: torch.Tensor, block_table: torch.
             new_seq_lens=torch.empty((b,), dtype=torch.int32, device=dev))
     if b == 0:
         return out
-    _need_cuda_or_pinned("out.physical", out.physical, torch.int32)  # may be written straight to pinned host memory
+    _check_out(out, b, hout, k, dev)
     must, n_must = _must_array(must_select)
     lib = _l.load_library()
     _l.check(lib.ucmr_hamming_topk(
@@ -360,6 +381,7 @@ def hamming_topk_static(codes: torch.Tensor, q_codes: torch.Tensor, block_table:
         raise ValueError(f"k={k} outside [0, max_blocks={mb}]")
     if b == 0:
         return out
+    _check_out(out, b, 1 if reduce_kvhead else hkv, k, codes.device)
     must, n_must = _must_array(must_select)
     lib = _l.load_library()
     _l.check(lib.ucmr_hamming_topk_static(
