@@ -304,6 +304,33 @@ int ucmr_merge_topk_wait(const float* cand_scores, const int32_t* cand_ids, int6
                          int Hout, int kl, int k, float* out_scores, int32_t* out_ids, const int32_t* flags,
                          int seq, int32_t* status_word, void* stream);
 
+/*  Replay-safe forms of the two calls above.  `seq` above is a by-value argument: a launch captured in a CUDA
+ *  graph publishes and waits for the SAME step number on every replay, so after the first replay nothing waits any
+ *  more and a rank may merge records that a faster peer is already overwriting.  Use these forms whenever the step is
+ *  captured.  The step number lives in a device word of this rank: both kernels read s = *step_word + 1, the
+ *  selection publishes s, the merge waits for s and its last CTA stores s back to *step_word.  The parity of s picks
+ *  one of two pointer sets, so the captured launch alternates buffers by itself.
+ *     ucmr_topk_candidates_p2p_step: peer_scores / peer_ids / peer_flags hold 2 * n_peers entries, the n_peers
+ *        pointers of parity 0 followed by those of parity 1.
+ *     ucmr_merge_topk_wait_step: cand_* and flags point at parity 0; parity 1 lies parity_stride (elements of the
+ *        records arrays) resp. flags_parity_stride (flag words) further.  arrive_word is a device int32 that is
+ *        zero between launches.  *step_word and *arrive_word start at 0; the first step is number 1.
+ *  The merge of a step and the selection of the next step must be ordered on one stream (they are in a decode
+ *  loop); no counterpart in the reference.                                                                    */
+int ucmr_topk_candidates_p2p_step(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
+                                  const uint32_t* q_codes, int Hq, const int32_t* block_table, int max_blocks,
+                                  int64_t block_table_stride, const int32_t* seq_lens_local,
+                                  const int32_t* seq_lens_global, int B, int k, int block_id_offset,
+                                  float score_scale, int reduce_mode, int reduce_kvhead,
+                                  const int32_t* must_select, int n_must, int sink_tokens, int recent_tokens,
+                                  float* const* peer_scores, int32_t* const* peer_ids, int32_t* const* peer_flags,
+                                  int n_peers, const int32_t* step_word, void* workspace, size_t workspace_bytes,
+                                  void* stream);
+int ucmr_merge_topk_wait_step(const float* cand_scores, const int32_t* cand_ids, int64_t parity_stride,
+                              int64_t rank_stride, int R, int B, int Hout, int kl, int k, float* out_scores,
+                              int32_t* out_ids, const int32_t* flags, int64_t flags_parity_stride,
+                              int32_t* step_word, int32_t* arrive_word, int32_t* status_word, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  *  Block copies through pointer lists, on the bulk-copy engine.
  *     Stands in for the three CudaSMCopyAsync / CudaCopyKernel overloads

@@ -25,6 +25,7 @@ def _worker(rank, world, port, ret):
     try:
         from oracle import oracle as O
         from tests import helpers as H
+        from unified_cache_management_b200 import ops as ops_mod
         from unified_cache_management_b200 import sharded
         B, Hkv, G, W, BS, nblk, k = 2, 8, 4, 8, 64, 256, 24
         seq = np.array([nblk * BS, nblk * BS - 5 * BS - 7], dtype=np.int32)
@@ -48,6 +49,30 @@ def _worker(rank, world, port, ret):
             torch.cuda.synchronize()
             ok = ok and bool(np.array_equal(ids2.cpu().numpy(), full["logical"])) and int(status.item()) == 0
             ok = ok and bool(torch.equal(s2, s))
+        # the same step captured once in a CUDA graph and replayed: the step number is counted on the device, so
+        # every replay publishes / waits for a new number (a by-value number would be frozen by the capture)
+        codes_d, q_d, seq_d = H.to_dev_i32(case["codes"], dev), H.to_dev_i32(case["q"], dev), H.to_dev_i32(seq, dev)
+        ws = ops_mod.new_workspace(B, Hkv, per, dev)
+        plan = sharded.shard_plan(seq_d, BS, nblk, world, rank)
+        o_s = torch.empty((B, Hkv, k), dtype=torch.float32, device=dev)
+        o_i = torch.empty((B, Hkv, k), dtype=torch.int32, device=dev)
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        dist.barrier()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                sharded.sharded_hamming_topk_p2p(codes_d, q_d, bt_local, seq_d, k, BS, nblk, 1.0 / (BS * G), ex,
+                                                 must_select=must, status=status, workspace=ws, plan=plan,
+                                                 out_scores=o_s, out_ids=o_i)
+        torch.cuda.synchronize()
+        dist.barrier()
+        for rep in range(4):
+            o_i.fill_(-5)
+            graph.replay()
+            torch.cuda.synchronize()
+            ok = ok and bool(np.array_equal(o_i.cpu().numpy(), full["logical"])) and int(status.item()) == 0
+        ok = ok and ex.state.cpu().tolist() == [3 + 4, 0]
         ret[rank] = ok
     finally:
         dist.destroy_process_group()

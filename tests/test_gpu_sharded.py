@@ -148,6 +148,76 @@ def test_peer_memory_exchange_emulated_on_one_gpu(cuda_device, R, blocks_per_ran
         assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("R", [2, 8])
+def test_peer_exchange_step_word_survives_graph_replay(cuda_device, R):
+    """The replay-safe exchange (step number counted in a device word) with the ranks emulated on one GPU: all
+    selections, then all merges, captured ONCE in a CUDA graph and replayed with new query codes each time.  A
+    by-value step number would be frozen by the capture; here every replay publishes and waits for the next number
+    and alternates the buffer parity by itself."""
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    B, Hkv, G, W, BS, k, per = 2, 4, 2, 4, 32, 20, 24
+    nblk = per * R
+    kl = min(k, per)
+    slab = B * Hkv * kl
+    words = 2 * R * slab + 64                                   # one parity: scores | ids | flags (padded)
+    bufs = [torch.zeros(2 * words, dtype=torch.int32, device=dev) for _ in range(R)]   # rank d's exchange buffer
+    states = [torch.zeros(2, dtype=torch.int32, device=dev) for _ in range(R)]
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    seq = np.array([nblk * BS - 1, nblk * BS - 9 * BS - 3], dtype=np.int32)
+    case = H.make_paged_case(500 + R, B, Hkv, G, W, BS, nblk, seq_lens=seq)
+    codes = H.to_dev_i32(case["codes"], dev)
+    q = H.to_dev_i32(case["q"], dev)
+    seq_g = H.to_dev_i32(seq, dev)
+    must = (0, -1)
+    bt_local = [H.to_dev_i32(np.ascontiguousarray(case["block_table"][:, r * per:(r + 1) * per]), dev) for r in range(R)]
+    seq_local = [H.to_dev_i32(np.clip(seq - r * per * BS, 0, per * BS).astype(np.int32), dev) for r in range(R)]
+    wss = [ops.new_workspace(B, Hkv, per, dev) for _ in range(R)]
+    outs = [(torch.empty((B, Hkv, k), dtype=torch.float32, device=dev),
+             torch.empty((B, Hkv, k), dtype=torch.int32, device=dev)) for _ in range(R)]
+
+    def all_ranks_one_step():
+        for r in range(R):
+            ps, pi, pf = [], [], []
+            for par in (0, 1):
+                base = par * words
+                ps += [bufs[d].data_ptr() + 4 * (base + r * slab) for d in range(R)]
+                pi += [bufs[d].data_ptr() + 4 * (base + R * slab + r * slab) for d in range(R)]
+                pf += [bufs[d].data_ptr() + 4 * (base + 2 * R * slab + r) for d in range(R)]
+            ops.topk_candidates_p2p_step(codes, q, bt_local[r], seq_local[r], seq_g, kl, r * per, 1.0 / (BS * G),
+                                         ps, pi, pf, states[r][0:1], must_select=must, workspace=wss[r])
+        for d in range(R):
+            sc = bufs[d][0:R * slab].view(torch.float32).view(R, B, Hkv, kl)
+            ids = bufs[d][R * slab:2 * R * slab].view(R, B, Hkv, kl)
+            flags = bufs[d][2 * R * slab:2 * R * slab + R]
+            ops.merge_topk_wait_step(sc, ids, k, flags, words, words, states[d], status=status,
+                                     out_scores=outs[d][0], out_ids=outs[d][1])
+
+    all_ranks_one_step()                                         # warm-up outside the capture: step 1
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            all_ranks_one_step()
+    torch.cuda.synchronize()
+    rng = np.random.default_rng(9)
+    for step in (2, 3, 4):
+        qh = H.rand_codes(rng, case["q"].shape)
+        q.copy_(H.to_dev_i32(qh, dev))
+        graph.replay()
+        torch.cuda.synchronize()
+        full = O.hamming_topk(case["codes"], qh, case["block_table"], seq, k, O.REDUCE_SUM, False, must_select=must)
+        for d in range(R):
+            assert states[d].cpu().tolist() == [step, 0]
+            par = step & 1
+            flags = bufs[d][par * words + 2 * R * slab: par * words + 2 * R * slab + R]
+            assert flags.cpu().tolist() == [step] * R
+            assert np.array_equal(outs[d][1].cpu().numpy(), full["logical"])
+    assert int(status.item()) == 0
+
+
 def test_merge_wait_gives_up_when_a_rank_never_delivers(cuda_device):
     """A flag that nothing sets: the wait runs out after its time limit, the status word says so, the output stays
     padding and the context remains usable."""

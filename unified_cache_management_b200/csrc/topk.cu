@@ -384,11 +384,15 @@ struct SelectParams {
     // Candidate records written straight into every rank's gather buffer over peer memory (n_peers > 0): entry r
     // points at this rank's slice of rank r's buffer; when the last CTA is done, the step number is stored to
     // this rank's flag word on every rank.
+    // With step_word != null the step number is read on the device (*step_word + 1) instead of taken from `seq`,
+    // and its parity picks one of two pointer sets: a launch captured in a CUDA graph then stays correct when
+    // replayed, which a by-value step number does not.
     int n_peers;
-    float* peer_scores[kMaxPeers];
-    int32_t* peer_ids[kMaxPeers];
-    int32_t* peer_flags[kMaxPeers];
+    float* peer_scores[2][kMaxPeers];
+    int32_t* peer_ids[2][kMaxPeers];
+    int32_t* peer_flags[2][kMaxPeers];
     int seq;
+    const int32_t* step_word;
     int32_t* arrive;  // CTA arrival counter (workspace header), zero between launches
 };
 
@@ -413,6 +417,14 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     if (p.k_per_request) kb = max(0, min(p.k_per_request[b], p.k));
     const bool masked = p.mask != nullptr && p.mask[b] == 0;
     const int64_t obase = (int64_t)row * p.k;
+    // peer exchange: step number of this launch and the pointer set of its parity
+    int step_no = p.seq, par = 0;
+    if (CANDIDATES && p.n_peers > 0 && p.step_word != nullptr) {
+        step_no = *p.step_word + 1;
+        par = step_no & 1;
+    }
+    float* const* const peer_scores = p.peer_scores[par];
+    int32_t* const* const peer_ids = p.peer_ids[par];
 
     if (masked) grid_dependency_wait();  // pass-through rows copy scores below
     // padding first; the chosen entries overwrite positions [0, kb) (in a cluster: after its first barrier)
@@ -420,8 +432,8 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         if (CANDIDATES) {
             if (p.n_peers > 0) {
                 for (int r = 0; r < p.n_peers; ++r) {
-                    p.peer_scores[r][obase + i] = INFINITY;
-                    p.peer_ids[r][obase + i] = -1;
+                    peer_scores[r][obase + i] = INFINITY;
+                    peer_ids[r][obase + i] = -1;
                 }
             } else {
                 p.cand_scores[obase + i] = INFINITY;
@@ -496,8 +508,8 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
                 const float sc_v = forced ? -1.0f : (float)srow[j] * p.scale;
                 if (p.n_peers > 0) {
                     for (int r = 0; r < p.n_peers; ++r) {
-                        p.peer_scores[r][obase + pos] = sc_v;
-                        p.peer_ids[r][obase + pos] = j + p.id_offset;
+                        peer_scores[r][obase + pos] = sc_v;
+                        peer_ids[r][obase + pos] = j + p.id_offset;
                     }
                 } else {
                     p.cand_scores[obase + pos] = sc_v;
@@ -521,7 +533,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
             if (done == (int)gridDim.x - 1) {
                 *p.arrive = 0;
                 __threadfence_system();
-                for (int r = 0; r < p.n_peers; ++r) st_release_sys(p.peer_flags[r], p.seq);
+                for (int r = 0; r < p.n_peers; ++r) st_release_sys(p.peer_flags[par][r], step_no);
             }
         }
     }
@@ -545,6 +557,13 @@ struct MergeParams {
     const int32_t* wait_flags;
     int wait_seq;
     int32_t* status;
+    // Replay-safe form: the step number is *step_word + 1, its parity selects the records (cand_* + parity *
+    // parity_stride) and the flags (wait_flags + parity * flags_parity_stride); the launch's last CTA stores the
+    // step number back to *step_word (arrive_word counts the CTAs and is zero between launches).
+    int32_t* step_word;
+    int32_t* arrive_word;
+    int64_t parity_stride;
+    int64_t flags_parity_stride;
 };
 
 __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
@@ -559,14 +578,37 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
         p.out_scores[obase + i] = p.largest ? -INFINITY : INFINITY;
         p.out_ids[obase + i] = -1;
     }
-    if (p.wait_flags != nullptr) {
+    int wait_seq = p.wait_seq;
+    const float* cand_scores = p.cand_scores;
+    const int32_t* cand_ids = p.cand_ids;
+    const int32_t* wait_flags = p.wait_flags;
+    if (p.step_word != nullptr) {
+        wait_seq = *p.step_word + 1;
+        const int par = wait_seq & 1;
+        cand_scores += par * p.parity_stride;
+        cand_ids += par * p.parity_stride;
+        wait_flags += par * p.flags_parity_stride;
+    }
+    // Every CTA has read the step word by the time it arrives here; the last one to arrive advances it.
+    auto advance_step = [&]() {
+        if (p.step_word == nullptr) return;
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence();
+            if (atomicAdd(p.arrive_word, 1) == (int)gridDim.x - 1) {
+                *p.arrive_word = 0;
+                *p.step_word = wait_seq;
+            }
+        }
+    };
+    if (wait_flags != nullptr) {
         __shared__ int s_timed_out;
         if (tid == 0) s_timed_out = 0;
         __syncthreads();
         if (tid < p.R) {
             unsigned long long t0 = 0;
             uint32_t polls = 0;
-            while (ld_acquire_sys(p.wait_flags + tid) != p.wait_seq) {
+            while (ld_acquire_sys(wait_flags + tid) != wait_seq) {
                 if ((++polls & (kWaitPollsPerClockCheck - 1)) == 0) {
                     unsigned long long now;
                     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
@@ -578,6 +620,7 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
         __syncthreads();
         if (s_timed_out) {  // a rank never delivered: leave the padding as the result and report
             if (tid == 0) flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT);
+            advance_step();
             return;
         }
     }
@@ -590,6 +633,8 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
     struct KeyOf {
         const MergeParams& p;
         int row;
+        const float* cand_scores;
+        const int32_t* cand_ids;
         __device__ int64_t at(int i) const
         {
             const int r = i / p.kl, c = i - r * p.kl;
@@ -598,7 +643,7 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
         __device__ Rec raw(int i) const
         {
             const int64_t a = at(i);
-            return Rec{__ldcg(p.cand_ids + a), __ldcg(p.cand_scores + a)};
+            return Rec{__ldcg(cand_ids + a), __ldcg(cand_scores + a)};
         }
         __device__ uint32_t key(int, Rec r) const
         {
@@ -609,16 +654,17 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
         __device__ uint32_t key_fast(int i, Rec r) const { return key(i, r); }
         __device__ void fixup(uint32_t*, int, int) const {}
     };
-    const KeyOf key_of{p, row};
+    const KeyOf key_of{p, row, cand_scores, cand_ids};
     auto emit = [&](int pos, int i) {
         const int64_t a = at(i);
-        const int32_t id = __ldcg(p.cand_ids + a);
+        const int32_t id = __ldcg(cand_ids + a);
         if (id >= 0) {
-            p.out_scores[obase + pos] = __ldcg(p.cand_scores + a);
+            p.out_scores[obase + pos] = __ldcg(cand_scores + a);
             p.out_ids[obase + pos] = id;
         }
     };
     select_row<false>(n, min(p.k, n), 32, key_of, emit, s_keys, p.n_cached, sc);
+    advance_step();
 }
 
 __global__ void update_seq_lens_kernel(const int32_t* seq, int B, int topk_tokens, int BS, int32_t* out)
@@ -696,9 +742,10 @@ static int sel_cluster_override()
 
 struct PeerDest {
     int n_peers, seq;
-    float* scores[kMaxPeers];
-    int32_t* ids[kMaxPeers];
-    int32_t* flags[kMaxPeers];
+    float* scores[2][kMaxPeers];   // [parity][rank]; the by-value form fills parity 0 only
+    int32_t* ids[2][kMaxPeers];
+    int32_t* flags[2][kMaxPeers];
+    const int32_t* step_word;      // null = step number given by value (seq)
 };
 
 static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
@@ -756,10 +803,12 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
     p.out_valid = out_valid; p.out_newseq = out_newseq;
     p.cand_scores = cand_scores; p.cand_ids = cand_ids; p.scale = scale; p.sched = sched;
     if (peers) {
-        p.n_peers = peers->n_peers; p.seq = peers->seq; p.arrive = status + 3;
-        for (int r = 0; r < peers->n_peers; ++r) {
-            p.peer_scores[r] = peers->scores[r]; p.peer_ids[r] = peers->ids[r]; p.peer_flags[r] = peers->flags[r];
-        }
+        p.n_peers = peers->n_peers; p.seq = peers->seq; p.step_word = peers->step_word; p.arrive = status + 3;
+        for (int par = 0; par < 2; ++par)
+            for (int r = 0; r < peers->n_peers; ++r) {
+                p.peer_scores[par][r] = peers->scores[par][r]; p.peer_ids[par][r] = peers->ids[par][r];
+                p.peer_flags[par][r] = peers->flags[par][r];
+            }
     }
     const int rows = B * p.Hout;
     // Few long rows: split each over a thread-block cluster so that the selection uses more than `rows` SMs.
@@ -824,9 +873,14 @@ extern "C" int ucmr_topk_candidates(const uint32_t* codes, int64_t NB, int BS, i
 namespace ucmr {
 int run_merge(const float* cand_scores, const int32_t* cand_ids, int64_t rank_stride, int R, int B, int Hout, int kl, int k,
               int largest, float* out_scores, int32_t* out_ids, cudaStream_t st);
+struct MergeStep {  // replay-safe step counting, see MergeParams
+    int32_t* step_word;
+    int32_t* arrive_word;
+    int64_t parity_stride, flags_parity_stride;
+};
 static int run_merge_wait(const float* cand_scores, const int32_t* cand_ids, int64_t rank_stride, int R, int B, int Hout,
                           int kl, int k, int largest, float* out_scores, int32_t* out_ids, const int32_t* wait_flags,
-                          int wait_seq, int32_t* status, cudaStream_t st);
+                          int wait_seq, int32_t* status, cudaStream_t st, const MergeStep* step = nullptr);
 }
 
 extern "C" int ucmr_merge_topk(const float* cand_scores, const int32_t* cand_ids, int64_t rank_stride, int R,
@@ -845,7 +899,8 @@ int ucmr::run_merge(const float* cand_scores, const int32_t* cand_ids, int64_t r
 
 static int ucmr::run_merge_wait(const float* cand_scores, const int32_t* cand_ids, int64_t rank_stride, int R, int B,
                                 int Hout, int kl, int k, int largest, float* out_scores, int32_t* out_ids,
-                                const int32_t* wait_flags, int wait_seq, int32_t* status, cudaStream_t stream)
+                                const int32_t* wait_flags, int wait_seq, int32_t* status, cudaStream_t stream,
+                                const MergeStep* step)
 {
     if (rank_stride == 0) rank_stride = (int64_t)B * Hout * kl;
     if (rank_stride < (int64_t)B * Hout * kl) return UCMR_ERR_BAD_ARG;
@@ -855,7 +910,11 @@ static int ucmr::run_merge_wait(const float* cand_scores, const int32_t* cand_id
     if (B == 0 || k == 0) return UCMR_OK;
     if (wait_flags && R > kSelThreads) return UCMR_ERR_UNSUPPORTED;
     MergeParams p{cand_scores, cand_ids, rank_stride, R, B, Hout, kl, k, 0, out_scores, out_ids, largest ? 1 : 0,
-                  wait_flags, wait_seq, status};
+                  wait_flags, wait_seq, status, nullptr, nullptr, 0, 0};
+    if (step) {
+        p.step_word = step->step_word; p.arrive_word = step->arrive_word;
+        p.parity_stride = step->parity_stride; p.flags_parity_stride = step->flags_parity_stride;
+    }
     const int n = R * kl;
     p.n_cached = n < kSelMaxCachedKeys ? n : kSelMaxCachedKeys;
     const size_t smem = (size_t)p.n_cached * sizeof(uint32_t);
@@ -890,7 +949,7 @@ extern "C" int ucmr_topk_candidates_p2p(const uint32_t* codes, int64_t NB, int B
     pd.n_peers = n_peers; pd.seq = seq;
     for (int r = 0; r < n_peers; ++r) {
         if (!peer_scores[r] || !peer_ids[r] || !peer_flags[r]) return UCMR_ERR_BAD_ARG;
-        pd.scores[r] = peer_scores[r]; pd.ids[r] = peer_ids[r]; pd.flags[r] = peer_flags[r];
+        pd.scores[0][r] = peer_scores[r]; pd.ids[0][r] = peer_ids[r]; pd.flags[0][r] = peer_flags[r];
     }
     return run_select(true, codes, NB, BS, Hkv, W, q_codes, Hq, block_table, max_blocks, block_table_stride,
                       seq_lens_local, seq_lens_global, B, k, nullptr, nullptr, reduce_mode, reduce_kvhead,
@@ -906,4 +965,46 @@ extern "C" int ucmr_merge_topk_wait(const float* cand_scores, const int32_t* can
     if (!flags) return UCMR_ERR_BAD_ARG;
     return run_merge_wait(cand_scores, cand_ids, rank_stride, R, B, Hout, kl, k, 0, out_scores, out_ids, flags, seq,
                           status_word, static_cast<cudaStream_t>(stream));
+}
+
+/* Replay-safe forms of the peer-memory exchange: the step number lives in a device word (see include/ucmr.h). */
+extern "C" int ucmr_topk_candidates_p2p_step(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,
+                                             const uint32_t* q_codes, int Hq, const int32_t* block_table,
+                                             int max_blocks, int64_t block_table_stride,
+                                             const int32_t* seq_lens_local, const int32_t* seq_lens_global, int B,
+                                             int k, int block_id_offset, float score_scale, int reduce_mode,
+                                             int reduce_kvhead, const int32_t* must_select, int n_must,
+                                             int sink_tokens, int recent_tokens, float* const* peer_scores,
+                                             int32_t* const* peer_ids, int32_t* const* peer_flags, int n_peers,
+                                             const int32_t* step_word, void* workspace, size_t workspace_bytes,
+                                             void* stream)
+{
+    if (block_id_offset < 0 || !peer_scores || !peer_ids || !peer_flags || !step_word || n_peers <= 0 ||
+        n_peers > kMaxPeers)
+        return UCMR_ERR_BAD_ARG;
+    PeerDest pd{};
+    pd.n_peers = n_peers; pd.seq = 0; pd.step_word = step_word;
+    for (int par = 0; par < 2; ++par)
+        for (int r = 0; r < n_peers; ++r) {
+            const int i = par * n_peers + r;
+            if (!peer_scores[i] || !peer_ids[i] || !peer_flags[i]) return UCMR_ERR_BAD_ARG;
+            pd.scores[par][r] = peer_scores[i]; pd.ids[par][r] = peer_ids[i]; pd.flags[par][r] = peer_flags[i];
+        }
+    return run_select(true, codes, NB, BS, Hkv, W, q_codes, Hq, block_table, max_blocks, block_table_stride,
+                      seq_lens_local, seq_lens_global, B, k, nullptr, nullptr, reduce_mode, reduce_kvhead,
+                      must_select, n_must, sink_tokens, recent_tokens, block_id_offset, score_scale, nullptr,
+                      nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, workspace, workspace_bytes,
+                      static_cast<cudaStream_t>(stream), &pd);
+}
+
+extern "C" int ucmr_merge_topk_wait_step(const float* cand_scores, const int32_t* cand_ids, int64_t parity_stride,
+                                         int64_t rank_stride, int R, int B, int Hout, int kl, int k,
+                                         float* out_scores, int32_t* out_ids, const int32_t* flags,
+                                         int64_t flags_parity_stride, int32_t* step_word, int32_t* arrive_word,
+                                         int32_t* status_word, void* stream)
+{
+    if (!flags || !step_word || !arrive_word || parity_stride < 0 || flags_parity_stride < 0) return UCMR_ERR_BAD_ARG;
+    const MergeStep ms{step_word, arrive_word, parity_stride, flags_parity_stride};
+    return run_merge_wait(cand_scores, cand_ids, rank_stride, R, B, Hout, kl, k, 0, out_scores, out_ids, flags, 0,
+                          status_word, static_cast<cudaStream_t>(stream), &ms);
 }

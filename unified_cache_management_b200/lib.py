@@ -75,6 +75,10 @@ SIGNATURES = {
                                       C.POINTER(C.c_int32), _i, _i, _i, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                       C.POINTER(C.c_void_p), _i, _i, _vp, _sz, _vp]),
     "ucmr_merge_topk_wait": (_i, [_vp, _vp, _i64, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp]),
+    "ucmr_topk_candidates_p2p_step": (_i, [_vp, _i64, _i, _i, _i, _vp, _i, _vp, _i, _i64, _vp, _vp, _i, _i, _i, _f, _i, _i,
+                                           C.POINTER(C.c_int32), _i, _i, _i, C.POINTER(C.c_void_p),
+                                           C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), _i, _vp, _vp, _sz, _vp]),
+    "ucmr_merge_topk_wait_step": (_i, [_vp, _vp, _i64, _i64, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp]),
     "ucmr_copy_blocks": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp]),
     "ucmr_gather_kv": (_i, [_vp, _vp, _i64, _i64, _vp, _i, _i, _i, _i, _i, _i64, _vp, _vp, _vp, _vp]),
 }

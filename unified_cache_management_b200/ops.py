@@ -525,6 +525,65 @@ def merge_topk_wait(cand_scores: torch.Tensor, cand_ids: torch.Tensor, k: int, f
     return out_scores, out_ids
 
 
+def topk_candidates_p2p_step(codes, q_codes, block_table, seq_lens_local, seq_lens_global, k: int, block_id_offset: int,
+                             score_scale: float, peer_scores_ptrs: Sequence[int], peer_ids_ptrs: Sequence[int],
+                             peer_flag_ptrs: Sequence[int], step_word: torch.Tensor, *, reduce="sum",
+                             reduce_kvhead=False, must_select=(), sink_tokens=0, recent_tokens=0, workspace=None,
+                             inputs_stable: bool = False) -> None:
+    """``topk_candidates_p2p`` whose step number is read on the device from ``step_word`` (int32, one element, this
+    rank's memory): safe to capture in a CUDA graph and replay.  The pointer lists hold the ranks' pointers of buffer
+    parity 0 followed by those of parity 1."""
+    codes, q_codes, bt_stride = _scan_args(codes, q_codes, block_table, seq_lens_local)
+    _need_cuda("seq_lens_global", seq_lens_global, torch.int32)
+    _need_cuda("step_word", step_word, torch.int32)
+    nb, bs, hkv, w = codes.shape
+    b, hq, _ = q_codes.shape
+    mb = block_table.shape[1]
+    if k <= 0 or k > mb:
+        raise ValueError(f"k={k} outside [1, max_blocks={mb}]")
+    n2 = len(peer_scores_ptrs)
+    if n2 == 0 or n2 % 2 or n2 != len(peer_ids_ptrs) or n2 != len(peer_flag_ptrs):
+        raise ValueError("the three pointer lists must have two entries (one per buffer parity) per rank")
+    if workspace is None:
+        workspace = new_workspace(b, hkv, mb, codes.device, reduce_kvhead)
+    arr = C.c_void_p * n2
+    must, n_must = _must_array(must_select)
+    _l.check(_l.load_library().ucmr_topk_candidates_p2p_step(
+        _ptr(codes), nb, bs, hkv, w, _ptr(q_codes), hq, _ptr(block_table), mb, bt_stride, _ptr(seq_lens_local),
+        _ptr(seq_lens_global), b, k, int(block_id_offset), float(score_scale), _mode(reduce, inputs_stable),
+        int(bool(reduce_kvhead)), must, n_must, int(sink_tokens), int(recent_tokens),
+        arr(*[int(p) for p in peer_scores_ptrs]), arr(*[int(p) for p in peer_ids_ptrs]),
+        arr(*[int(p) for p in peer_flag_ptrs]), n2 // 2, _ptr(step_word), _ptr(workspace), workspace.numel(),
+        _stream(codes)), "ucmr_topk_candidates_p2p_step")
+
+
+def merge_topk_wait_step(cand_scores: torch.Tensor, cand_ids: torch.Tensor, k: int, flags: torch.Tensor,
+                         parity_stride: int, flags_parity_stride: int, step_state: torch.Tensor,
+                         status: Optional[torch.Tensor] = None, out_scores=None, out_ids=None):
+    """``merge_topk_wait`` for the replay-safe exchange: ``cand_*`` [R, B, Hout, kl] and ``flags`` are the views of
+    buffer parity 0, parity 1 lies ``parity_stride`` elements / ``flags_parity_stride`` words further;
+    ``step_state`` is int32 [2] = (step word, arrival counter), zero before the first step."""
+    _need_cuda("cand_scores", cand_scores, torch.float32)
+    _need_cuda("cand_ids", cand_ids, torch.int32)
+    _need_cuda("flags", flags, torch.int32)
+    _need_cuda("step_state", step_state, torch.int32)
+    if step_state.numel() < 2:
+        raise ValueError("step_state needs two words")
+    r, b, h, kl = cand_scores.shape
+    if flags.numel() < r:
+        raise ValueError("one flag per rank is needed")
+    dev = cand_scores.device
+    if out_scores is None:
+        out_scores = torch.empty((b, h, k), dtype=torch.float32, device=dev)
+    if out_ids is None:
+        out_ids = torch.empty((b, h, k), dtype=torch.int32, device=dev)
+    _l.check(_l.load_library().ucmr_merge_topk_wait_step(
+        _ptr(cand_scores), _ptr(cand_ids), int(parity_stride), b * h * kl, r, b, h, kl, int(k), _ptr(out_scores),
+        _ptr(out_ids), _ptr(flags), int(flags_parity_stride), C.c_void_p(step_state.data_ptr()),
+        C.c_void_p(step_state.data_ptr() + 4), _ptr(status), _stream(cand_scores)), "ucmr_merge_topk_wait_step")
+    return out_scores, out_ids
+
+
 def merge_topk(cand_scores: torch.Tensor, cand_ids: torch.Tensor, k: int, out_scores=None, out_ids=None):
     """cand_* [R, B, Hout, kl] (ascending shard order) -> global top-k [B, Hout, k], ascending id.
     The two tensors may be strided views of one gathered buffer as long as each shard's [B,Hout,kl]

@@ -51,12 +51,14 @@ def sharded_hamming_topk(codes_local, q_codes, block_table_local, seq_lens_globa
                          reduce_kvhead: bool = False, must_select: Sequence[int] = (), sink_tokens: int = 0,
                          recent_tokens: int = 0, workspace=None, gather_buffer: Optional[torch.Tensor] = None,
                          send_buffer: Optional[torch.Tensor] = None, plan: Optional[ShardPlan] = None,
-                         inputs_stable: bool = False, candidates_fn: Callable = _default_candidates, merge_fn: Callable = _default_merge):
+                         inputs_stable: bool = False, out_scores=None, out_ids=None,
+                         candidates_fn: Callable = _default_candidates, merge_fn: Callable = _default_merge):
     """Returns (scores float32 [B,Hout,k], global logical block ids int32 [B,Hout,k]), identical on
     every rank.  block_table_local is this rank's slice [B, max_blocks_global/world] of the table.
     ``send_buffer`` (int32 [2, B, Hout, min(k, blocks per rank)]) lets the local selection write its records
     straight into the message; ``gather_buffer`` (int32 [world*2, ...]) receives all ranks' messages; ``plan`` is
-    a ``shard_plan`` result to reuse while the sequence lengths do not change."""
+    a ``shard_plan`` result to reuse while the sequence lengths do not change; ``out_scores`` / ``out_ids`` receive
+    the merged result."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     if plan is None:
@@ -80,6 +82,8 @@ def sharded_hamming_topk(codes_local, q_codes, block_table_local, seq_lens_globa
     gathered = gather_buffer.view((world, 2) + tuple(send.shape[1:]))
     cand_scores = gathered[:, 0].view(torch.float32)
     cand_ids = gathered[:, 1]
+    if merge_fn is _default_merge:
+        return merge_fn(cand_scores, cand_ids, k, out_scores=out_scores, out_ids=out_ids)
     return merge_fn(cand_scores, cand_ids, k)
 
 
@@ -99,7 +103,8 @@ class PeerExchange:
 
     Per rank and per step parity: scores float32 [world, B, H, kl], ids int32 [world, B, H, kl], flags int32 [world]
     (padded to 64 words).  Two parities alternate so that a rank that is one step ahead never overwrites records a
-    slower rank still merges."""
+    slower rank still merges.  The step number is kept on the device (``state``: step word, arrival counter): both
+    kernels read it there and the merge advances it, so a step captured in a CUDA graph stays correct when replayed."""
 
     def __init__(self, batch: int, heads: int, kl: int, device, group=None):
         import torch.distributed._symmetric_memory as symm_mem
@@ -113,42 +118,59 @@ class PeerExchange:
         self.words_per_parity = exchange_layout(self.world, self.rank, self.slab, 0)[4]
         self.buf = symm_mem.empty(2 * self.words_per_parity, dtype=torch.int32, device=device)
         self.buf.zero_()
+        self.state = torch.zeros(2, dtype=torch.int32, device=device)   # step word, merge arrival counter
         self.handle = symm_mem.rendezvous(self.buf, self.group)
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
         torch.cuda.synchronize(device)
         dist.barrier(self.group)                            # every rank's flags are zero before any store
         self.seq = 0
+        # pointer lists for the step forms: parity 0's ranks, then parity 1's
+        self.step_ptrs = ([], [], [])
+        for par in (0, 1):
+            o_s, o_i, o_f, mine, _ = exchange_layout(self.world, self.rank, self.slab, par)
+            self.step_ptrs[0].extend(p + 4 * (o_s + mine) for p in self.ptrs)
+            self.step_ptrs[1].extend(p + 4 * (o_i + mine) for p in self.ptrs)
+            self.step_ptrs[2].extend(p + 4 * (o_f + self.rank) for p in self.ptrs)
+
+    def views(self, parity: int):
+        """Local views (scores [world,B,H,kl] float32, ids, flags [world]) of one buffer parity."""
+        o_s, o_i, o_f, _, _ = exchange_layout(self.world, self.rank, self.slab, parity)
+        n = self.world * self.slab
+        return (self.buf[o_s:o_s + n].view(torch.float32).view(self.shape), self.buf[o_i:o_i + n].view(self.shape),
+                self.buf[o_f:o_f + self.world])
 
     def next_step(self):
-        """Returns (seq, pointer lists for topk_candidates_p2p, local views for merge_topk_wait)."""
+        """By-value stepping with a host-side count (NOT for captured launches, and not to be mixed with the
+        device-counted form on the same exchange): returns (seq, pointer lists for topk_candidates_p2p, local views
+        for merge_topk_wait)."""
         self.seq += 1
         o_s, o_i, o_f, mine, _ = exchange_layout(self.world, self.rank, self.slab, self.seq)
         ps = [p + 4 * (o_s + mine) for p in self.ptrs]
         pi = [p + 4 * (o_i + mine) for p in self.ptrs]
         pf = [p + 4 * (o_f + self.rank) for p in self.ptrs]
-        n = self.world * self.slab
-        scores = self.buf[o_s:o_s + n].view(torch.float32).view(self.shape)
-        ids = self.buf[o_i:o_i + n].view(self.shape)
-        flags = self.buf[o_f:o_f + self.world]
-        return self.seq, (ps, pi, pf), (scores, ids, flags)
+        return self.seq, (ps, pi, pf), self.views(self.seq & 1)
 
 
 def sharded_hamming_topk_p2p(codes_local, q_codes, block_table_local, seq_lens_global, k: int, block_size: int,
                              max_blocks_global: int, score_scale: float, exchange: PeerExchange, *, reduce="sum",
                              reduce_kvhead: bool = False, must_select: Sequence[int] = (), sink_tokens: int = 0,
                              recent_tokens: int = 0, workspace=None, plan: Optional[ShardPlan] = None,
-                             status: Optional[torch.Tensor] = None, inputs_stable: bool = False):
+                             status: Optional[torch.Tensor] = None, inputs_stable: bool = False,
+                             out_scores=None, out_ids=None):
     """``sharded_hamming_topk`` with the all-gather folded into the two kernels (see ``PeerExchange``): two launches
-    per step and no collective call."""
+    per step and no collective call.  The step number is counted on the device, so the call may be captured in a
+    CUDA graph and replayed (every rank must replay the same number of steps)."""
     from . import ops
     if plan is None:
         plan = shard_plan(seq_lens_global, block_size, max_blocks_global, exchange.world, exchange.rank)
     kl = min(k, plan.blocks_per_rank)
     if kl != exchange.shape[3]:
         raise ValueError("the exchange was sized for a different number of records per rank")
-    seq, (ps, pi, pf), (scores, ids, flags) = exchange.next_step()
-    ops.topk_candidates_p2p(codes_local, q_codes, block_table_local, plan.seq_lens_local, seq_lens_global, kl,
-                            plan.block_offset, score_scale, ps, pi, pf, seq, reduce=reduce, reduce_kvhead=reduce_kvhead,
-                            must_select=must_select, sink_tokens=sink_tokens, recent_tokens=recent_tokens,
-                            workspace=workspace, inputs_stable=inputs_stable)
-    return ops.merge_topk_wait(scores, ids, k, flags, seq, status=status)
+    ps, pi, pf = exchange.step_ptrs
+    ops.topk_candidates_p2p_step(codes_local, q_codes, block_table_local, plan.seq_lens_local, seq_lens_global, kl,
+                                 plan.block_offset, score_scale, ps, pi, pf, exchange.state[0:1], reduce=reduce,
+                                 reduce_kvhead=reduce_kvhead, must_select=must_select, sink_tokens=sink_tokens,
+                                 recent_tokens=recent_tokens, workspace=workspace, inputs_stable=inputs_stable)
+    scores, ids, flags = exchange.views(0)
+    return ops.merge_topk_wait_step(scores, ids, k, flags, exchange.words_per_parity, exchange.words_per_parity,
+                                    exchange.state, status=status, out_scores=out_scores, out_ids=out_ids)
