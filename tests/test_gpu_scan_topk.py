@@ -273,3 +273,105 @@ def test_inputs_stable_flag_changes_nothing_but_the_schedule(cuda_device):
                                                   bt.data_ptr(), mb, mb, sl.data_ptr(), B, 1 | 0x200, 0, s0.data_ptr(),
                                                   None, None)
         lib.check(rc, "ucmr_block_scores")
+
+
+def test_selection_inside_the_scan_ragged_batch_repeated(cuda_device):
+    """Rows of up to 2048 blocks are selected by the scan kernel itself (per-request arrival counters, rows handed out
+    by ticket).  A ragged batch with empty, one-block and full requests, per-request k and a request mask, run
+    three times on one workspace: the counters must come back to zero every time."""
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    B, Hkv, G, W, BS, mb = 37, 8, 4, 4, 128, 96
+    rng = np.random.default_rng(11)
+    seq = rng.integers(1, mb * BS + 1, size=B).astype(np.int32)
+    seq[3], seq[7], seq[20], seq[36] = 0, 1, mb * BS, BS          # empty, one token, full, one block
+    case = H.make_paged_case(123, B, Hkv, G, W, BS, mb, seq_lens=seq)
+    kpr = rng.integers(0, 12, size=B).astype(np.int32)
+    mask = (rng.random(B) > 0.2).astype(np.uint8)
+    k = 10
+    codes, q = H.to_dev_i32(case["codes"], dev), H.to_dev_i32(case["q"], dev)
+    bt, sl = H.to_dev_i32(case["block_table"], dev), H.to_dev_i32(seq, dev)
+    ws = ops.new_workspace(B, Hkv, mb, dev, True)
+    for mode in ("sum", "min"):
+        for red in (False, True):
+            kw = dict(must_select=(0, -1), sink_tokens=100, recent_tokens=300)
+            ref = OC.hamming_topk(case["codes"], case["q"], case["block_table"], seq, k, MODES[mode], red,
+                                  k_per_request=kpr, request_mask=mask, **kw)
+            for _ in range(3):
+                out = ops.hamming_topk(codes, q, bt, sl, k, reduce=mode, reduce_kvhead=red, workspace=ws,
+                                       k_per_request=H.to_dev_i32(kpr, dev),
+                                       request_mask=torch.from_numpy(mask).to(dev), **kw)
+                torch.cuda.synchronize()
+                _cmp(out, ref)
+            assert ops.workspace_status(ws) == 0
+            head = ws[:ops._l.WORKSPACE_HEADER_BYTES].view(torch.int32).cpu().numpy()
+            assert not head.any(), "a counter of the workspace header was left non-zero"
+
+
+def test_selection_inside_the_scan_2048_blocks(cuda_device):
+    """2048 blocks per row (64 keys per lane of the selecting warp) and k = 32, with ties (small codes)."""
+    B, Hkv, G, W, BS, mb = 3, 2, 1, 4, 16, 2048
+    seq = [mb * BS, mb * BS - 7, 1500 * BS + 3]
+    case = H.make_paged_case(55, B, Hkv, G, W, BS, mb, seq_lens=seq)
+    for mode in ("sum", "min"):
+        for k in (1, 32, 700, 2048):
+            out = _run_dev(case, cuda_device, k, reduce=mode, must_select=(0, -2, -1))
+            ref = OC.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], k, MODES[mode], False,
+                                  must_select=(0, -2, -1))
+            _cmp(out, ref)
+
+
+def test_rejected_call_leaves_the_workspace_usable(cuda_device):
+    """A call that is refused (k larger than the block table) must not disturb the counters of the workspace: the next
+    call on it still matches the oracle."""
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    B, Hkv, G, W, BS, mb = 4, 8, 4, 4, 128, 300
+    case = H.make_paged_case(5, B, Hkv, G, W, BS, mb, seq_lens=[mb * BS] * B)
+    codes, q = H.to_dev_i32(case["codes"], dev), H.to_dev_i32(case["q"], dev)
+    bt, sl = H.to_dev_i32(case["block_table"], dev), H.to_dev_i32(case["seq_lens"], dev)
+    ws = ops.new_workspace(B, Hkv, mb, dev)
+    good = ops.hamming_topk(codes, q, bt, sl, 8, reduce="sum", workspace=ws)
+    with pytest.raises(ValueError):
+        ops.hamming_topk(codes, q, bt, sl, mb + 1, reduce="sum", workspace=ws)
+    with pytest.raises(ValueError):
+        ops.hamming_topk(codes, q, bt, sl, 8, reduce="sum", workspace=ws, must_select=tuple(range(17)))
+    again = ops.hamming_topk(codes, q, bt, sl, 8, reduce="sum", workspace=ws)
+    torch.cuda.synchronize()
+    ref = OC.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], 8, O.REDUCE_SUM, False)
+    _cmp(good, ref)
+    _cmp(again, ref)
+
+
+def test_separate_selection_kernel_still_matches(cuda_device):
+    """UCMR_FUSED_SELECT=0 keeps the selection in its own kernel for every shape (the switch is read once per process,
+    so this runs in a child process): same results as the oracle on a few shapes."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = r'''
+import numpy as np, torch, sys
+sys.path.insert(0, %r)
+from oracle import oracle as O
+from oracle import oracle_c as OC
+from tests import helpers as H
+from unified_cache_management_b200 import ops
+dev = torch.device("cuda:0")
+for (B, Hkv, G, W, BS, mb, k, red) in [(5, 8, 4, 4, 128, 40, 6, False), (3, 4, 1, 4, 16, 300, 20, True), (2, 8, 4, 8, 64, 1024, 16, False)]:
+    case = H.make_paged_case(B * 7 + mb, B, Hkv, G, W, BS, mb)
+    ws = ops.new_workspace(B, Hkv, mb, dev, True)
+    for _ in range(2):
+        out = ops.hamming_topk(H.to_dev_i32(case["codes"], dev), H.to_dev_i32(case["q"], dev), H.to_dev_i32(case["block_table"], dev),
+                               H.to_dev_i32(case["seq_lens"], dev), k, reduce="sum", reduce_kvhead=red, must_select=(0, -1), workspace=ws)
+        torch.cuda.synchronize()
+        ref = OC.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], k, O.REDUCE_SUM, red, must_select=(0, -1))
+        for name in ("logical", "physical", "scores", "valid_count", "new_seq_lens"):
+            assert np.array_equal(getattr(out, name).cpu().numpy(), ref[name]), name
+print("unfused ok")
+''' % root
+    env = dict(os.environ, UCMR_FUSED_SELECT="0")
+    res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "unfused ok" in res.stdout, res.stdout + res.stderr

@@ -25,6 +25,35 @@ inline int check_launch()
 
 inline bool is_pow2(int64_t v) { return v > 0 && (v & (v - 1)) == 0; }
 
+// Blocks that are selected whatever their score: listed block indices (>= 0 from the start, < 0 from the request's
+// block count) and every block that overlaps the first `sink` or the last `recent` tokens.
+struct ForcedSpec {
+    int must[UCMR_MAX_MUST_SELECT];
+    int n_must, sink, recent;
+};
+
+// Workspace layout (int32 words): [0] device status, [2] the scan's work counter, [3] CTA arrival counter of the
+// peer exchange, [4] count of scan CTAs that have finished; from byte 256 two arrays of kWsMaxBatch counters used
+// when the scan also runs the selection (items retired per request, rows handed out per request); the block
+// scores follow at UCMR_WORKSPACE_HEADER_BYTES.  Every counter is zero between launches.
+constexpr int kWsMaxBatch = 1024;
+
+// Selection folded into the staged scan (scan_ring.cu) for rows of at most kFuseMaxBlocks blocks: what the scan needs
+// to know to select a request's rows as soon as the request's last block has been scored.
+constexpr int kFuseMaxBlocks = 2048;
+struct FusedSel {
+    int enabled;
+    int Hout, k, key_bits, idx_bits;
+    const int32_t* k_per_request;
+    const uint8_t* mask;
+    ForcedSpec forced;
+    int32_t *out_phys, *out_logical, *out_scores, *out_valid, *out_newseq;
+    int32_t* row_done;  // [B] work items retired per request
+    int32_t* row_tick;  // [B] rows handed out per request
+    int32_t* cta_done;  // scan CTAs that have finished; the last one clears every counter for the next launch
+};
+static_assert(UCMR_WORKSPACE_HEADER_BYTES == 256 + 2 * kWsMaxBatch * 4, "workspace header layout");
+
 // Launches `kernel` on `st` and turns a refused launch into UCMR_ERR_LAUNCH.
 template <typename... KArgs, typename... Args>
 inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args)
@@ -136,6 +165,27 @@ __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepco
 __device__ __forceinline__ void flag_status(int32_t* status, int bits)
 {
     if (status != nullptr) atomicOr(status, bits);
+}
+
+__device__ __forceinline__ bool block_is_forced(const ForcedSpec& f, int j, int nb, int seq, int BS)
+{
+    if (j >= nb) return false;
+    for (int m = 0; m < f.n_must; ++m) {
+        const int t = f.must[m] >= 0 ? f.must[m] : nb + f.must[m];
+        if (t == j) return true;
+    }
+    const int lo = j * BS;
+    const int hi = min(lo + BS, seq);
+    if (f.sink > 0 && lo < f.sink) return true;
+    if (f.recent > 0 && hi > seq - f.recent) return true;
+    return false;
+}
+
+__device__ __forceinline__ int ld_acquire_gpu(const int32_t* p)
+{
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
 }
 
 // Streaming 16-byte load: read-only path, no L1 allocation (each code word is read once per scan).

@@ -287,7 +287,8 @@ int validate_scan_args(const void* codes, int64_t NB, int BS, int Hkv, int W, co
 
 int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const uint32_t* q, int Hq,
                   const int32_t* bt, int max_blocks, int64_t bt_stride, const int32_t* seq_lens, int B,
-                  int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, int32_t* sched, cudaStream_t st);
+                  int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, int32_t* sched, cudaStream_t st,
+                  const FusedSel* fuse);
 
 // UCMR_SCAN=register routes every scan through the register kernel of this file (debug aid; the
 // staged kernel in scan_ring.cu is the default wherever it covers the shape).
@@ -303,11 +304,14 @@ static bool force_register_scan()
 
 // Launches the scan into `out` ([B,Hout,max_blocks] int32).  Shared by the C entry points.  `sched` is an
 // optional zero-initialised int32 the staged kernel uses as its work counter; whoever passes it resets it
-// to zero after the launch (stream-ordered).
+// to zero after the launch (stream-ordered).  With `fuse` the staged kernel also runs the selection (and clears the
+// counter itself); *fused says whether it did - false when the shape went to a kernel that cannot.
 int run_scan(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const uint32_t* q, int Hq,
              const int32_t* bt, int max_blocks, int64_t bt_stride, const int32_t* seq_lens, int B,
-             int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, int32_t* sched, cudaStream_t st)
+             int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, int32_t* sched, cudaStream_t st,
+             const FusedSel* fuse, bool* fused)
 {
+    if (fused) *fused = false;
     int rc = validate_scan_args(codes, NB, BS, Hkv, W, q, Hq, bt, max_blocks, bt_stride, seq_lens, B);
     if (rc != UCMR_OK) return rc;
     if (!out) return UCMR_ERR_BAD_ARG;
@@ -319,8 +323,11 @@ int run_scan(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const ui
 
     if (!force_register_scan()) {
         rc = run_scan_ring(codes, NB, BS, Hkv, W, q, Hq, bt, max_blocks, bt_stride, seq_lens, B, reduce_mode | mode_flags,
-                           reduce_kvhead, out, status, sched, st);
-        if (rc != UCMR_ERR_UNSUPPORTED) return rc;
+                           reduce_kvhead, out, status, sched, st, fuse);
+        if (rc != UCMR_ERR_UNSUPPORTED) {
+            if (fused) *fused = rc == UCMR_OK && fuse != nullptr;
+            return rc;
+        }
     }
 
     ScanParams p{};
@@ -394,7 +401,8 @@ extern "C" int ucmr_block_scores(const uint32_t* codes, int64_t NB, int BS, int 
                                  int reduce_kvhead, int32_t* out_scores, int32_t* status_word, void* stream)
 {
     return run_scan(codes, NB, BS, Hkv, W, q_codes, Hq, block_table, max_blocks, block_table_stride, seq_lens,
-                    B, reduce_mode, reduce_kvhead, out_scores, status_word, nullptr, static_cast<cudaStream_t>(stream));
+                    B, reduce_mode, reduce_kvhead, out_scores, status_word, nullptr, static_cast<cudaStream_t>(stream),
+                    nullptr, nullptr);
 }
 
 extern "C" int ucmr_hamming_score(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,

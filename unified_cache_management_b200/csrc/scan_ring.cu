@@ -45,6 +45,13 @@ constexpr int kRingMaxBatch = 1024;  // requests per launch (prefix table in sha
 constexpr int kRingMaxBps = 8;       // blocks per stage
 constexpr int kRingMaxG = 16;
 
+// Selection folded into the scan (ucmr_hamming_topk with rows of at most kFuseMaxBlocks blocks): work items are handed
+// out request by request, every retired item bumps its request's counter, and the warp that retires a request's
+// last item selects that request's rows right there, while the rest of the grid keeps scanning the later requests.
+// The warps that retired one of the request's last Hout items offer to help (they take rows by ticket once they see
+// the counter complete, without ever waiting while they still hold unprocessed items), so the rows of the final
+// request are spread over several warps.  A row is selected by one warp: keys in registers, the k-th smallest
+// (key, block) pair found by bisection on its packed 32-bit form, then an ordered compaction by ballots.
 struct RingParams {
     const char* codes;
     int64_t NB;
@@ -66,6 +73,7 @@ struct RingParams {
     int stage_bytes;   // bps * block_stride
     int n_active;      // warps (= stages) in use: min(kRingWarps, ring bytes / stage bytes)
     int early_setup;   // UCMR_FLAG_INPUTS_STABLE: sequence lengths and block table may be read before the dependency wait
+    FusedSel sel;
 };
 
 struct __align__(16) StageMeta {
@@ -247,12 +255,102 @@ __device__ __forceinline__ void load_chunk(uint32_t (&x)[CH], const uint32_t* co
     }
 }
 
+// Exact top-k of one (request, kv head) row by ONE warp, same results as select_kernel in topk.cu: the first `kb`
+// blocks under (key, block index), key = 0 for forced blocks, score + 1 for valid ones, all ones past the request's
+// length; written in ascending block order, then padding.  Lane l holds blocks l, l + 32, ... as packed words
+// (key << idx_bits | block), which are distinct, so the kb-th smallest word T is found by bisection on the count of
+// words <= T (one warp-wide add per step) and the chosen set is {word <= T}.  NK = register slots per lane.
+// The scores were written by other SMs: read through L2 (the caller has fenced after seeing the request complete).
+template <int NK>
+__device__ __noinline__ void warp_select_row(const RingParams& p, int b, int h, int seq)
+{
+    const FusedSel& f = p.sel;
+    const int lane = threadIdx.x & 31;
+    const int n = p.max_blocks;
+    const int nb = max(0, min(n, (seq + p.BS - 1) / p.BS));
+    int kb = f.k;
+    if (f.k_per_request) kb = max(0, min(f.k_per_request[b], f.k));
+    const bool masked = f.mask != nullptr && f.mask[b] == 0;
+    const int row = b * f.Hout + h;
+    const int64_t obase = (int64_t)row * f.k;
+    const int32_t* srow = p.out + (int64_t)row * n;
+    const int32_t* btrow = p.bt + (int64_t)b * p.bt_stride;
+    if (h == 0 && lane == 0) {
+        if (f.out_valid) f.out_valid[b] = min(kb, nb);
+        if (f.out_newseq) {
+            int ns = seq;
+            if (!masked) {
+                const int over = max(seq - kb * p.BS, 0);
+                ns = seq - (over + p.BS - 1) / p.BS * p.BS;
+            }
+            f.out_newseq[b] = ns;
+        }
+    }
+    if (masked) {  // not retrieved: the head of the request's own block table
+        for (int i = lane; i < f.k; i += 32) {
+            const bool pass = i < kb;
+            f.out_phys[obase + i] = pass ? btrow[i] : 0;
+            if (f.out_logical) f.out_logical[obase + i] = pass ? i : -1;
+            if (f.out_scores) f.out_scores[obase + i] = (pass && i < nb) ? __ldcg(srow + i) : -1;
+        }
+        return;
+    }
+    const int take = min(kb, n);
+    const uint32_t key_invalid = (1u << f.key_bits) - 1u;
+    uint32_t pk[NK];
+    {
+        int sc[NK];
+#pragma unroll
+        for (int i = 0; i < NK; ++i) {
+            const int j = i * 32 + lane;
+            sc[i] = j < nb ? __ldcg(srow + j) : -1;
+        }
+#pragma unroll
+        for (int i = 0; i < NK; ++i) {
+            const int j = i * 32 + lane;
+            uint32_t key = key_invalid;
+            if (j < nb && sc[i] >= 0) key = block_is_forced(f.forced, j, nb, seq, p.BS) ? 0u : (uint32_t)sc[i] + 1u;
+            pk[i] = j < n ? ((key << f.idx_bits) | (uint32_t)j) : 0xFFFFFFFFu;
+        }
+    }
+    uint32_t lo = 0u, hi = (key_invalid << f.idx_bits) | (uint32_t)(n - 1);
+    while (lo < hi && take > 0) {
+        const uint32_t mid = lo + ((hi - lo) >> 1);
+        int cnt = 0;
+#pragma unroll
+        for (int i = 0; i < NK; ++i) cnt += pk[i] <= mid;
+        cnt = __reduce_add_sync(0xffffffffu, cnt);
+        if (cnt >= take) hi = mid; else lo = mid + 1u;
+    }
+    const uint32_t T = lo;
+    int base = 0;
+#pragma unroll
+    for (int i = 0; i < NK; ++i) {
+        if (base >= take) break;  // (uniform)
+        const bool chosen = take > 0 && pk[i] <= T;
+        const uint32_t bal = __ballot_sync(0xffffffffu, chosen);
+        if (chosen) {
+            const int pos = base + __popc(bal & ((1u << lane) - 1u));
+            const int j = i * 32 + lane;
+            f.out_phys[obase + pos] = btrow[j];
+            if (f.out_logical) f.out_logical[obase + pos] = j;
+            if (f.out_scores) f.out_scores[obase + pos] = j < nb ? max(__ldcg(srow + j), -1) : -1;
+        }
+        base += __popc(bal);
+    }
+    for (int i = take + lane; i < f.k; i += 32) {  // fewer than k entries: padding
+        f.out_phys[obase + i] = 0;
+        if (f.out_logical) f.out_logical[obase + i] = -1;
+        if (f.out_scores) f.out_scores[obase + i] = -1;
+    }
+}
+
 // MIN selects the per-token-minimum path; RW_T (sum mode only) and G_T are compile-time copies of the row
 // width and group size for the common shapes, 0 = read them from the parameters; CH is the sum mode's
 // chunk size.  ROW > 0 selects the token-row path for one kv head with ROW words per token (any group size).
 template <bool MIN, int RW_T, int G_T, int CH, int ROW>
 __global__ void __launch_bounds__(kRingThreads, 1)
-scan_ring_kernel(const RingParams p)
+scan_ring_kernel(const __grid_constant__ RingParams p)
 {
     extern __shared__ __align__(128) uint8_t s_ring[];
     __shared__ __align__(8) uint64_t s_full[kRingWarps];
@@ -260,6 +358,7 @@ scan_ring_kernel(const RingParams p)
     __shared__ int s_cum[kRingMaxBatch + 1];  // s_cum[b] = work items before request b
     __shared__ int s_seq[kRingMaxBatch];      // seq_lens[b]
     __shared__ volatile int s_pool_empty;     // a warp of this CTA found the dynamic item pool exhausted
+    __shared__ int s_warps_done;              // scanning warps of this CTA that have finished (fused selection)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int Hout = p.reduce_kvhead ? 1 : p.Hkv;
@@ -269,6 +368,7 @@ scan_ring_kernel(const RingParams p)
         for (int s = 0; s < kRingWarps; ++s) mbar_init(&s_full[s], 1);
         fence_mbar_init();
         s_pool_empty = 0;
+        s_warps_done = 0;
     }
     // Launched early (programmatic dependent launch): the CTA is resident and its barriers are set up while the
     // kernel before it in the stream drains.  Nothing in global memory is read before the wait, because that kernel
@@ -396,6 +496,52 @@ scan_ring_kernel(const RingParams p)
         nxt = resolve(claim_finish(token));
         token = claim_start();
     };
+    // ---- selection folded into the scan (see FusedSel) -----------------------------------------------------------
+    const bool fused = p.sel.enabled != 0;
+    int pending_b = -1;  // a request one of whose last items this warp retired: help with its rows once it is complete
+    auto take_rows = [&](int b) {  // all lanes; rows of a COMPLETE request are handed out by ticket
+        __threadfence();           // the scores of the request, written by other SMs, are read after this point
+        for (;;) {
+            int t = 0;
+            if (lane == 0) t = atomicAdd(&p.sel.row_tick[b], 1);
+            t = __shfl_sync(0xffffffffu, t, 0);
+            if (t >= p.sel.Hout) break;
+            if (p.max_blocks <= 1024) warp_select_row<32>(p, b, t, s_seq[b]);
+            else warp_select_row<kFuseMaxBlocks / 32>(p, b, t, s_seq[b]);
+        }
+    };
+    auto request_complete = [&](int b) -> bool {
+        int v = 0;
+        if (lane == 0) v = ld_acquire_gpu(&p.sel.row_done[b]);
+        v = __shfl_sync(0xffffffffu, v, 0);
+        return v == s_cum[b + 1] - s_cum[b];
+    };
+    // Called by all lanes after the scores of an item of request b have been stored.
+    auto retire_item = [&](int b) {
+        if (!fused) return;
+        __threadfence();  // this lane's score stores are visible device-wide before the counter moves
+        __syncwarp();
+        int c = 0;
+        if (lane == 0) c = atomicAdd(&p.sel.row_done[b], 1) + 1;
+        c = __shfl_sync(0xffffffffu, c, 0);
+        const int n_items = s_cum[b + 1] - s_cum[b];
+        if (c == n_items) {
+            take_rows(b);
+            if (pending_b == b) pending_b = -1;
+        } else if (c > n_items - p.sel.Hout) {
+            pending_b = b;
+        }
+        if (pending_b >= 0 && pending_b != b && request_complete(pending_b)) {
+            take_rows(pending_b);
+            pending_b = -1;
+        }
+    };
+    if (fused) {
+        // requests without any work item (length 0) are never retired: hand their rows out here
+        for (int b = blockIdx.x * p.n_active + warp; b < p.B; b += lanes_total)
+            if (s_cum[b + 1] == s_cum[b]) take_rows(b);
+    }
+
     int cur_b = -1;
     uint32_t phase = 0;
     if constexpr (ROW > 0) {
@@ -571,6 +717,7 @@ scan_ring_kernel(const RingParams p)
                 __syncwarp();
                 advance();
             }
+            retire_item(m.b);
         }
     } else if constexpr (!MIN) {
         // lane <-> (block in stage, column); a column is one 32-bit word of one kv head
@@ -649,6 +796,7 @@ scan_ring_kernel(const RingParams p)
                 __syncwarp();
                 advance();
             }
+            retire_item(m.b);
         }
     } else {
         // lane <-> (block in stage, 16-byte piece of a token row, token slot)
@@ -725,6 +873,33 @@ scan_ring_kernel(const RingParams p)
                     p.out[((int64_t)m.b * Hout + head) * p.max_blocks + j] = have ? best : -1;
                 }
             }
+            retire_item(m.b);
+        }
+    }
+    if (fused) {
+        // Out of work items.  A request this warp offered to help with may still be in flight in other warps: wait
+        // for it briefly (this warp holds no unprocessed item any more, so nothing can wait on it in turn) and give
+        // up silently after the limit - the warp that retires the request's last item takes whatever rows are left.
+        if (pending_b >= 0) {
+            const unsigned long long t0 = global_timer_ns();
+            bool done = request_complete(pending_b);
+            while (!done && global_timer_ns() - t0 < 200000ull) done = request_complete(pending_b);
+            if (done) take_rows(pending_b);
+        }
+        // The last warp of the last CTA clears the counters for the next launch on this workspace.
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) {
+            __threadfence();
+            if (atomicAdd(&s_warps_done, 1) == p.n_active - 1) last = atomicAdd(p.sel.cta_done, 1) == (int)gridDim.x - 1;
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+            for (int b = lane; b < p.B; b += 32) { p.sel.row_done[b] = 0; p.sel.row_tick[b] = 0; }
+            if (lane == 0) {
+                *p.sel.cta_done = 0;
+                if (p.sched != nullptr) *p.sched = 0;
+            }
         }
     }
 }
@@ -733,7 +908,8 @@ scan_ring_kernel(const RingParams p)
 // then uses the register kernel).
 int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const uint32_t* q, int Hq,
                   const int32_t* bt, int max_blocks, int64_t bt_stride, const int32_t* seq_lens, int B,
-                  int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, int32_t* sched, cudaStream_t st)
+                  int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, int32_t* sched, cudaStream_t st,
+                  const FusedSel* fuse)
 {
     const bool inputs_stable = (reduce_mode & UCMR_FLAG_INPUTS_STABLE) != 0;
     reduce_mode &= 0xFF;
@@ -768,6 +944,11 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     p.q = q; p.bt = bt; p.max_blocks = max_blocks; p.bt_stride = bt_stride; p.seq_lens = seq_lens; p.B = B;
     p.reduce_kvhead = reduce_kvhead ? 1 : 0; p.out = out; p.status = status; p.sched = sched;
     p.RW = (int)RW; p.bps = bps; p.block_bytes = (int)block_bytes; p.early_setup = inputs_stable ? 1 : 0;
+    if (fuse != nullptr) {
+        if (max_blocks > kFuseMaxBlocks || B > kWsMaxBatch || fuse->key_bits + fuse->idx_bits > 31) return UCMR_ERR_BAD_ARG;
+        p.sel = *fuse;
+        p.sel.enabled = 1;
+    }
     if (block_bytes % (row_mode ? 16 : 128) != 0) return UCMR_ERR_UNSUPPORTED;
     if (!is_min && RW < 32 && BS > 240) return UCMR_ERR_UNSUPPORTED;
     p.block_stride = (int)block_bytes;

@@ -24,7 +24,8 @@ namespace ucmr {
 
 int run_scan(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const uint32_t* q, int Hq,
              const int32_t* bt, int max_blocks, int64_t bt_stride, const int32_t* seq_lens, int B,
-             int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, int32_t* sched, cudaStream_t st);
+             int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, int32_t* sched, cudaStream_t st,
+             const FusedSel* fuse, bool* fused);
 
 constexpr int kSelThreads = 512;
 constexpr int kSelWarps = kSelThreads / 32;
@@ -34,25 +35,6 @@ constexpr uint32_t kKeyInvalid = 0xFFFFFFFFu;
 // Measured: a cluster launch costs about 2 us more than a plain one and large grids of clusters schedule
 // slowly, so shorter rows and launches of many rows stay with one CTA per row.
 constexpr int kSelClusterSlice = 2048;
-
-struct ForcedSpec {
-    int must[UCMR_MAX_MUST_SELECT];
-    int n_must, sink, recent;
-};
-
-__device__ __forceinline__ bool block_is_forced(const ForcedSpec& f, int j, int nb, int seq, int BS)
-{
-    if (j >= nb) return false;
-    for (int m = 0; m < f.n_must; ++m) {
-        const int t = f.must[m] >= 0 ? f.must[m] : nb + f.must[m];
-        if (t == j) return true;
-    }
-    const int lo = j * BS;
-    const int hi = min(lo + BS, seq);
-    if (f.sink > 0 && lo < f.sink) return true;
-    if (f.recent > 0 && hi > seq - f.recent) return true;
-    return false;
-}
 
 constexpr int kMaxPeers = 8;  // ranks of one NVLink domain that exchange candidate records directly
 
@@ -740,6 +722,16 @@ static int sel_cluster_override()
     return v;
 }
 
+// UCMR_FUSED_SELECT=0 (read once per process) keeps the selection in its own kernel for every shape.
+static bool fused_select_enabled()
+{
+    static const bool v = [] {
+        const char* env = getenv("UCMR_FUSED_SELECT");
+        return !(env && env[0] == '0');
+    }();
+    return v;
+}
+
 struct PeerDest {
     int n_peers, seq;
     float* scores[2][kMaxPeers];   // [parity][rank]; the by-value form fills parity 0 only
@@ -770,9 +762,34 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
     int32_t* sched = status + 2;  // work counter of the scan; zero between launches
     const int scan_mode = reduce_mode;  // with its UCMR_FLAG_* bits
     reduce_mode &= 0xFF;
+    {
+        const int G = Hkv > 0 ? Hq / Hkv : 1;
+        int64_t max_score = (int64_t)G * W * 32;
+        if (reduce_mode == UCMR_REDUCE_SUM) max_score *= (int64_t)BS * (reduce_kvhead ? Hkv : 1);
+        p.key_bits = 1;
+        while (p.key_bits < 32 && ((int64_t)1 << p.key_bits) - 1 <= max_score + 1) ++p.key_bits;
+    }
+    // Rows short enough for one warp each are selected inside the scan (no second launch): see FusedSel.
+    FusedSel fs{};
+    bool try_fuse = false;
+    if (!candidates && k > 0 && max_blocks <= kFuseMaxBlocks && B <= kWsMaxBatch && fused_select_enabled()) {
+        int idx_bits = 1;
+        while ((1 << idx_bits) < max_blocks) ++idx_bits;
+        if (p.key_bits + idx_bits <= 31) {
+            try_fuse = true;
+            fs.Hout = reduce_kvhead ? 1 : Hkv; fs.k = k; fs.key_bits = p.key_bits; fs.idx_bits = idx_bits;
+            fs.k_per_request = k_per_request; fs.mask = mask; fs.forced = p.forced;
+            fs.out_phys = out_phys; fs.out_logical = out_logical; fs.out_scores = out_scores;
+            fs.out_valid = out_valid; fs.out_newseq = out_newseq;
+            fs.cta_done = status + 4;
+            fs.row_done = status + 64;
+            fs.row_tick = status + 64 + kWsMaxBatch;
+        }
+    }
+    bool fused = false;
     rc = run_scan(codes, NB, BS, Hkv, W, q_codes, Hq, bt, max_blocks, bt_stride, seq_local, B, scan_mode,
-                  reduce_kvhead, scores, status, sched, st);
-    if (rc != UCMR_OK || B == 0) return rc;
+                  reduce_kvhead, scores, status, sched, st, try_fuse ? &fs : nullptr, &fused);
+    if (rc != UCMR_OK || B == 0 || fused) return rc;
     // From here on the scan is enqueued and will leave its work counter non-zero; the selection kernel clears it.
     // If that kernel cannot be launched, clear it here, or the next call on this workspace would skip work items.
     auto fail_after_scan = [&](int code) {
@@ -792,13 +809,6 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
     p.k = k; p.k_per_request = k_per_request; p.mask = mask;
     p.id_offset = id_offset;
     p.n_cached = max_blocks < kSelMaxCachedKeys ? max_blocks : kSelMaxCachedKeys;
-    {
-        const int G = Hq / Hkv;
-        int64_t max_score = (int64_t)G * W * 32;
-        if (reduce_mode == UCMR_REDUCE_SUM) max_score *= (int64_t)BS * (reduce_kvhead ? Hkv : 1);
-        p.key_bits = 1;
-        while (p.key_bits < 32 && ((int64_t)1 << p.key_bits) - 1 <= max_score + 1) ++p.key_bits;
-    }
     p.out_phys = out_phys; p.out_logical = out_logical; p.out_scores = out_scores;
     p.out_valid = out_valid; p.out_newseq = out_newseq;
     p.cand_scores = cand_scores; p.cand_ids = cand_ids; p.scale = scale; p.sched = sched;
