@@ -65,7 +65,7 @@ extern "C" {
 #define UCMR_FLAG_INPUTS_STABLE 0x100
 
 #define UCMR_MAX_MUST_SELECT 16
-#define UCMR_WORKSPACE_HEADER_BYTES 8448 /* status and work counters (256) + per-request counters (2 x 1024 x 4) */
+#define UCMR_WORKSPACE_HEADER_BYTES 256
 
 int ucmr_version(void);
 const char* ucmr_status_string(int status);

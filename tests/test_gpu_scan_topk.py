@@ -276,9 +276,9 @@ def test_inputs_stable_flag_changes_nothing_but_the_schedule(cuda_device):
 
 
 def test_selection_inside_the_scan_ragged_batch_repeated(cuda_device):
-    """Rows of up to 2048 blocks are selected by the scan kernel itself (per-request arrival counters, rows handed out
-    by ticket).  A ragged batch with empty, one-block and full requests, per-request k and a request mask, run
-    three times on one workspace: the counters must come back to zero every time."""
+    """A ragged batch with empty, one-block and full requests, per-request k and a request mask, run
+    three times on one workspace: the counters must come back to zero every time.  (Also run with the selection
+    folded into the scan kernel, see test_selection_folded_into_the_scan.)"""
     import torch
     from unified_cache_management_b200 import ops
     dev = cuda_device
@@ -305,7 +305,8 @@ def test_selection_inside_the_scan_ragged_batch_repeated(cuda_device):
                 torch.cuda.synchronize()
                 _cmp(out, ref)
             assert ops.workspace_status(ws) == 0
-            head = ws[:ops._l.WORKSPACE_HEADER_BYTES].view(torch.int32).cpu().numpy()
+            head = ws[:ops._l.WORKSPACE_HEADER_BYTES].view(torch.int32).cpu().numpy().copy()
+            head[36] = 0    # the "all blocks scored" word counts launches
             assert not head.any(), "a counter of the workspace header was left non-zero"
 
 
@@ -345,33 +346,29 @@ def test_rejected_call_leaves_the_workspace_usable(cuda_device):
     _cmp(again, ref)
 
 
-def test_separate_selection_kernel_still_matches(cuda_device):
-    """UCMR_FUSED_SELECT=0 keeps the selection in its own kernel for every shape (the switch is read once per process,
-    so this runs in a child process): same results as the oracle on a few shapes."""
+def test_selection_folded_into_the_scan(cuda_device):
+    """UCMR_FUSED_SELECT=1 makes the staged scan select the rows itself (rows of at most 2048 blocks).  The switch is
+    read once per process, so the cases run in a child process: the ragged repeated batch, the 2048-block rows, the
+    full-size config 0 and a few shapes of the oracle sweep, all through that path."""
     import os
     import subprocess
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    code = r'''
-import numpy as np, torch, sys
+    code = r"""
+import sys, torch
 sys.path.insert(0, %r)
-from oracle import oracle as O
-from oracle import oracle_c as OC
-from tests import helpers as H
-from unified_cache_management_b200 import ops
+from tests import test_gpu_scan_topk as T
 dev = torch.device("cuda:0")
-for (B, Hkv, G, W, BS, mb, k, red) in [(5, 8, 4, 4, 128, 40, 6, False), (3, 4, 1, 4, 16, 300, 20, True), (2, 8, 4, 8, 64, 1024, 16, False)]:
-    case = H.make_paged_case(B * 7 + mb, B, Hkv, G, W, BS, mb)
-    ws = ops.new_workspace(B, Hkv, mb, dev, True)
-    for _ in range(2):
-        out = ops.hamming_topk(H.to_dev_i32(case["codes"], dev), H.to_dev_i32(case["q"], dev), H.to_dev_i32(case["block_table"], dev),
-                               H.to_dev_i32(case["seq_lens"], dev), k, reduce="sum", reduce_kvhead=red, must_select=(0, -1), workspace=ws)
-        torch.cuda.synchronize()
-        ref = OC.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], k, O.REDUCE_SUM, red, must_select=(0, -1))
-        for name in ("logical", "physical", "scores", "valid_count", "new_seq_lens"):
-            assert np.array_equal(getattr(out, name).cpu().numpy(), ref[name]), name
-print("unfused ok")
-''' % root
-    env = dict(os.environ, UCMR_FUSED_SELECT="0")
-    res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
-    assert res.returncode == 0 and "unfused ok" in res.stdout, res.stdout + res.stderr
+T.test_selection_inside_the_scan_ragged_batch_repeated(dev)
+T.test_selection_inside_the_scan_2048_blocks(dev)
+T.test_config0_full_size(dev)
+T.test_rejected_call_leaves_the_workspace_usable(dev)
+for shape in [(3, 8, 4, 4, 128, 12), (2, 1, 4, 4, 128, 40), (2, 4, 1, 4, 16, 33), (3, 1, 64, 18, 64, 9), (2, 3, 2, 4, 128, 5)]:
+    for mode in ("min", "sum"):
+        for red in (False, True):
+            T.test_topk_matches_oracle(dev, shape, mode, red)
+print("fused ok")
+""" % root
+    env = dict(os.environ, UCMR_FUSED_SELECT="1")
+    res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0 and "fused ok" in res.stdout, res.stdout[-2000:] + res.stderr[-4000:]

@@ -32,14 +32,14 @@ struct ForcedSpec {
     int n_must, sink, recent;
 };
 
-// Workspace layout (int32 words): [0] device status, [2] the scan's work counter, [3] CTA arrival counter of the
-// peer exchange, [4] count of scan CTAs that have finished; from byte 256 two arrays of kWsMaxBatch counters used
-// when the scan also runs the selection (items retired per request, rows handed out per request); the block
-// scores follow at UCMR_WORKSPACE_HEADER_BYTES.  Every counter is zero between launches.
+// Workspace header (int32 words, UCMR_WORKSPACE_HEADER_BYTES in all): [0] device status, [2] the scan's work
+// counter, [3] CTA arrival counter of the peer exchange, and for a scan that also runs the selection [4] scan CTAs
+// that have scored all their blocks and [36] the "all blocks scored" word, which counts such launches.  The block
+// scores follow the header.  Every counter is zero between launches.
 constexpr int kWsMaxBatch = 1024;
 
 // Selection folded into the staged scan (scan_ring.cu) for rows of at most kFuseMaxBlocks blocks: what the scan needs
-// to know to select a request's rows as soon as the request's last block has been scored.
+// to know to select the rows itself once every block has been scored.
 constexpr int kFuseMaxBlocks = 2048;
 struct FusedSel {
     int enabled;
@@ -48,11 +48,10 @@ struct FusedSel {
     const uint8_t* mask;
     ForcedSpec forced;
     int32_t *out_phys, *out_logical, *out_scores, *out_valid, *out_newseq;
-    int32_t* row_done;  // [B] work items retired per request
-    int32_t* row_tick;  // [B] rows handed out per request
-    int32_t* cta_done;  // scan CTAs that have finished; the last one clears every counter for the next launch
+    int32_t* cta_done;    // scan CTAs whose warps have all run out of work items (zero between launches)
+    int32_t* all_scored;  // bumped by one when the last CTA has arrived: every block score is in memory
 };
-static_assert(UCMR_WORKSPACE_HEADER_BYTES == 256 + 2 * kWsMaxBatch * 4, "workspace header layout");
+
 
 // Launches `kernel` on `st` and turns a refused launch into UCMR_ERR_LAUNCH.
 template <typename... KArgs, typename... Args>
@@ -179,6 +178,19 @@ __device__ __forceinline__ bool block_is_forced(const ForcedSpec& f, int j, int 
     if (f.sink > 0 && lo < f.sink) return true;
     if (f.recent > 0 && hi > seq - f.recent) return true;
     return false;
+}
+
+// Atomic add / exchange with release semantics at device scope: everything this thread has observed or written
+// before is visible to whoever reads the new value with an acquire load (one instruction instead of fence + atomic).
+__device__ __forceinline__ int atom_add_release_gpu(int32_t* p, int v)
+{
+    int old;
+    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+    return old;
+}
+__device__ __forceinline__ void st_release_gpu(int32_t* p, int v)
+{
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ int ld_acquire_gpu(const int32_t* p)

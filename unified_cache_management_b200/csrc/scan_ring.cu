@@ -45,13 +45,15 @@ constexpr int kRingMaxBatch = 1024;  // requests per launch (prefix table in sha
 constexpr int kRingMaxBps = 8;       // blocks per stage
 constexpr int kRingMaxG = 16;
 
-// Selection folded into the scan (ucmr_hamming_topk with rows of at most kFuseMaxBlocks blocks): work items are handed
-// out request by request, every retired item bumps its request's counter, and the warp that retires a request's
-// last item selects that request's rows right there, while the rest of the grid keeps scanning the later requests.
-// The warps that retired one of the request's last Hout items offer to help (they take rows by ticket once they see
-// the counter complete, without ever waiting while they still hold unprocessed items), so the rows of the final
-// request are spread over several warps.  A row is selected by one warp: keys in registers, the k-th smallest
-// (key, block) pair found by bisection on its packed 32-bit form, then an ordered compaction by ballots.
+// Selection folded into the scan (ucmr_hamming_topk with rows of at most kFuseMaxBlocks blocks; parameters: FusedSel).
+// A warp that has run out of work items arrives at a CTA counter, the CTA's last warp at a grid counter; once every CTA
+// has arrived all block scores are in memory, and the warps - waiting for that moment with a bounded poll - take the
+// (request, kv head) rows one by one from a ticket counter and select them, one warp per row.  The warp that makes
+// the final arrival never waits and keeps taking tickets until none is left, so the result does not depend on the
+// others showing up: a warp whose wait ran out simply leaves.  Compared with a second kernel this saves a launch and
+// spreads the rows over all SMs while they are still resident.
+// A row is selected by one warp: keys in registers, the k-th smallest (key, block) pair found by bisection on its
+// packed 32-bit form, then an ordered compaction by ballots.
 struct RingParams {
     const char* codes;
     int64_t NB;
@@ -258,30 +260,35 @@ __device__ __forceinline__ void load_chunk(uint32_t (&x)[CH], const uint32_t* co
 // Exact top-k of one (request, kv head) row by ONE warp, same results as select_kernel in topk.cu: the first `kb`
 // blocks under (key, block index), key = 0 for forced blocks, score + 1 for valid ones, all ones past the request's
 // length; written in ascending block order, then padding.  Lane l holds blocks l, l + 32, ... as packed words
-// (key << idx_bits | block), which are distinct, so the kb-th smallest word T is found by bisection on the count of
-// words <= T (one warp-wide add per step) and the chosen set is {word <= T}.  NK = register slots per lane.
-// The scores were written by other SMs: read through L2 (the caller has fenced after seeing the request complete).
+// (key << idx_bits | block), which are distinct, so the chosen set is {word <= T} for the kb-th smallest word T.  For
+// kb <= 64 a bound on T from the lanes' two smallest words leaves a handful of candidates that are ranked exactly;
+// otherwise T is found by bisection on the count of words <= T.  NK = register slots per lane.
+// The scores were written by other SMs: read through L2 (the caller has fenced after seeing the scan complete).
+// `f` points at the CTA's shared-memory copy of the selection parameters (reading them through a generic pointer
+// into the kernel's parameter space is far slower).
+constexpr int kSelListLen = 128;  // chosen blocks a warp lists in shared memory before writing them out
+
 template <int NK>
-__device__ __noinline__ void warp_select_row(const RingParams& p, int b, int h, int seq)
+__device__ __noinline__ void warp_select_row(const FusedSel* fp, const int32_t* scores, const int32_t* bt,
+                                             int64_t bt_stride, int n, int BS, int b, int h, int seq, int* list)
 {
-    const FusedSel& f = p.sel;
+    const FusedSel& f = *fp;
     const int lane = threadIdx.x & 31;
-    const int n = p.max_blocks;
-    const int nb = max(0, min(n, (seq + p.BS - 1) / p.BS));
+    const int nb = max(0, min(n, (seq + BS - 1) / BS));
     int kb = f.k;
     if (f.k_per_request) kb = max(0, min(f.k_per_request[b], f.k));
     const bool masked = f.mask != nullptr && f.mask[b] == 0;
     const int row = b * f.Hout + h;
     const int64_t obase = (int64_t)row * f.k;
-    const int32_t* srow = p.out + (int64_t)row * n;
-    const int32_t* btrow = p.bt + (int64_t)b * p.bt_stride;
+    const int32_t* srow = scores + (int64_t)row * n;
+    const int32_t* btrow = bt + (int64_t)b * bt_stride;
     if (h == 0 && lane == 0) {
         if (f.out_valid) f.out_valid[b] = min(kb, nb);
         if (f.out_newseq) {
             int ns = seq;
             if (!masked) {
-                const int over = max(seq - kb * p.BS, 0);
-                ns = seq - (over + p.BS - 1) / p.BS * p.BS;
+                const int over = max(seq - kb * BS, 0);
+                ns = seq - (over + BS - 1) / BS * BS;
             }
             f.out_newseq[b] = ns;
         }
@@ -297,6 +304,9 @@ __device__ __noinline__ void warp_select_row(const RingParams& p, int b, int h, 
     }
     const int take = min(kb, n);
     const uint32_t key_invalid = (1u << f.key_bits) - 1u;
+    // forced blocks: the sink and recent windows are two ranges; the listed blocks are patched in afterwards
+    const int n_sink = f.forced.sink > 0 ? (f.forced.sink + BS - 1) / BS : 0;
+    const int first_recent = f.forced.recent > 0 ? max(0, (seq - f.forced.recent) / BS) : nb;
     uint32_t pk[NK];
     {
         int sc[NK];
@@ -309,34 +319,120 @@ __device__ __noinline__ void warp_select_row(const RingParams& p, int b, int h, 
         for (int i = 0; i < NK; ++i) {
             const int j = i * 32 + lane;
             uint32_t key = key_invalid;
-            if (j < nb && sc[i] >= 0) key = block_is_forced(f.forced, j, nb, seq, p.BS) ? 0u : (uint32_t)sc[i] + 1u;
+            if (j < nb && sc[i] >= 0) key = (j < n_sink || j >= first_recent) ? 0u : (uint32_t)sc[i] + 1u;
             pk[i] = j < n ? ((key << f.idx_bits) | (uint32_t)j) : 0xFFFFFFFFu;
         }
     }
-    uint32_t lo = 0u, hi = (key_invalid << f.idx_bits) | (uint32_t)(n - 1);
-    while (lo < hi && take > 0) {
-        const uint32_t mid = lo + ((hi - lo) >> 1);
-        int cnt = 0;
+    for (int m = 0; m < f.forced.n_must; ++m) {  // (uniform loop) listed blocks: key 0 unless past the end / bad id
+        const int t = f.forced.must[m] >= 0 ? f.forced.must[m] : nb + f.forced.must[m];
+        if (t < 0 || t >= nb) continue;
+        const int slot = t >> 5, owner = t & 31;
 #pragma unroll
-        for (int i = 0; i < NK; ++i) cnt += pk[i] <= mid;
-        cnt = __reduce_add_sync(0xffffffffu, cnt);
-        if (cnt >= take) hi = mid; else lo = mid + 1u;
+        for (int i = 0; i < NK; ++i)
+            if (i == slot && lane == owner && (pk[i] >> f.idx_bits) != key_invalid) pk[i] = (uint32_t)t;
     }
-    const uint32_t T = lo;
-    int base = 0;
+    auto write_out = [&](int pos, int j) {
+        f.out_phys[obase + pos] = btrow[j];
+        if (f.out_logical) f.out_logical[obase + pos] = j;
+        if (f.out_scores) f.out_scores[obase + pos] = j < nb ? max(__ldcg(srow + j), -1) : -1;
+    };
+    const uint32_t lt_mask = (1u << lane) - 1u;
+    const uint32_t idx_mask = (1u << f.idx_bits) - 1u;
+    uint32_t lo = 0u, hi = (key_invalid << f.idx_bits) | (uint32_t)(n - 1);
+    bool done = take <= 0;
+    if (!done && take <= 64) {
+        // Few blocks wanted (the usual case).  The `take` smallest of the 64 values {two smallest words of every
+        // lane} are `take` distinct words of the row, so the largest of them, T0, bounds the take-th smallest word
+        // of the whole row from above; the words <= T0 are then few, and the exact choice is made among them.
+        uint32_t m1 = 0xFFFFFFFFu, m2 = 0xFFFFFFFFu;
 #pragma unroll
-    for (int i = 0; i < NK; ++i) {
-        if (base >= take) break;  // (uniform)
-        const bool chosen = take > 0 && pk[i] <= T;
-        const uint32_t bal = __ballot_sync(0xffffffffu, chosen);
-        if (chosen) {
-            const int pos = base + __popc(bal & ((1u << lane) - 1u));
-            const int j = i * 32 + lane;
-            f.out_phys[obase + pos] = btrow[j];
-            if (f.out_logical) f.out_logical[obase + pos] = j;
-            if (f.out_scores) f.out_scores[obase + pos] = j < nb ? max(__ldcg(srow + j), -1) : -1;
+        for (int i = 0; i < NK; ++i) {
+            m2 = min(m2, max(m1, pk[i]));
+            m1 = min(m1, pk[i]);
         }
-        base += __popc(bal);
+        int r1 = 0, r2 = 0;  // how many of the 64 values are below m1 / m2
+#pragma unroll 8
+        for (int src = 0; src < 32; ++src) {
+            const uint32_t a = __shfl_sync(0xffffffffu, m1, src), c = __shfl_sync(0xffffffffu, m2, src);
+            r1 += (a < m1) + (c < m1);
+            r2 += (a < m2) + (c < m2);
+        }
+        const bool is1 = r1 == take - 1 && m1 != 0xFFFFFFFFu, is2 = r2 == take - 1 && m2 != 0xFFFFFFFFu;
+        const uint32_t who = __ballot_sync(0xffffffffu, is1 || is2);
+        if (who != 0u) {  // (always, for take <= n; kept as a guard)
+            const uint32_t T0 = __shfl_sync(0xffffffffu, is1 ? m1 : m2, __ffs(who) - 1);
+            hi = T0;
+            int c0 = 0, c1 = 0;
+#pragma unroll
+            for (int i = 0; i < NK; i += 2) { c0 += pk[i] <= T0; c1 += pk[i + 1] <= T0; }
+            const int cnt = __reduce_add_sync(0xffffffffu, c0 + c1);
+            if (cnt <= 64) {
+                // the candidates, in ascending block order, into the warp's shared list
+                int base = 0;
+#pragma unroll
+                for (int i = 0; i < NK; ++i) {
+                    const bool cand = pk[i] <= T0;
+                    const uint32_t bal = __ballot_sync(0xffffffffu, cand);
+                    if (cand) list[base + __popc(bal & lt_mask)] = (int)pk[i];
+                    base += __popc(bal);
+                }
+                __syncwarp();
+                const bool have_a = lane < cnt, have_b = lane + 32 < cnt;
+                const uint32_t va = have_a ? (uint32_t)list[lane] : 0xFFFFFFFFu;
+                const uint32_t vb = have_b ? (uint32_t)list[lane + 32] : 0xFFFFFFFFu;
+                int ra = 0, rb = 0;
+                for (int x = 0; x < cnt; ++x) {
+                    const uint32_t v = (uint32_t)list[x];
+                    ra += v < va;
+                    rb += v < vb;
+                }
+                const bool ca = have_a && ra < take, cb = have_b && rb < take;
+                const uint32_t bal_a = __ballot_sync(0xffffffffu, ca), bal_b = __ballot_sync(0xffffffffu, cb);
+                if (ca) write_out(__popc(bal_a & lt_mask), (int)(va & idx_mask));
+                if (cb) write_out(__popc(bal_a) + __popc(bal_b & lt_mask), (int)(vb & idx_mask));
+                __syncwarp();  // the list is reused for the warp's next row
+                done = true;
+            }
+        }
+    }
+    if (!done) {
+        // General case: bisection on the count of words <= T, then an ordered compaction by ballots.
+        while (lo < hi) {
+            const uint32_t mid = lo + ((hi - lo) >> 1);
+            int c0 = 0, c1 = 0, c2 = 0, c3 = 0;  // four chains: the adds of one are dependent
+#pragma unroll
+            for (int i = 0; i < NK; i += 4) {
+                c0 += pk[i] <= mid; c1 += pk[i + 1] <= mid; c2 += pk[i + 2] <= mid; c3 += pk[i + 3] <= mid;
+            }
+            const int cnt = __reduce_add_sync(0xffffffffu, (c0 + c1) + (c2 + c3));
+            if (cnt >= take) hi = mid; else lo = mid + 1u;
+        }
+        const uint32_t T = lo;
+        // The chosen blocks are first listed in shared memory, then written out one per lane, so that the block-table
+        // and score loads of different entries are in flight together instead of one load latency per register slot.
+        const bool listed = take <= kSelListLen;
+        int base = 0;
+#pragma unroll
+        for (int i = 0; i < NK; ++i) {
+            if (base >= take) break;  // (uniform)
+            const bool chosen = pk[i] <= T;
+            const uint32_t bal = __ballot_sync(0xffffffffu, chosen);
+            if (chosen) {
+                const int pos = base + __popc(bal & lt_mask);
+                const int j = i * 32 + lane;
+                if (listed) list[pos] = j; else write_out(pos, j);
+            }
+            base += __popc(bal);
+        }
+        if (listed) {
+            __syncwarp();
+#pragma unroll
+            for (int u = 0; u < kSelListLen / 32; ++u) {
+                const int pos = u * 32 + lane;
+                if (pos < take) write_out(pos, list[pos]);
+            }
+            __syncwarp();  // the list is reused for the warp's next row
+        }
     }
     for (int i = take + lane; i < f.k; i += 32) {  // fewer than k entries: padding
         f.out_phys[obase + i] = 0;
@@ -350,7 +446,7 @@ __device__ __noinline__ void warp_select_row(const RingParams& p, int b, int h, 
 // chunk size.  ROW > 0 selects the token-row path for one kv head with ROW words per token (any group size).
 template <bool MIN, int RW_T, int G_T, int CH, int ROW>
 __global__ void __launch_bounds__(kRingThreads, 1)
-scan_ring_kernel(const __grid_constant__ RingParams p)
+scan_ring_kernel(const RingParams p)
 {
     extern __shared__ __align__(128) uint8_t s_ring[];
     __shared__ __align__(8) uint64_t s_full[kRingWarps];
@@ -358,7 +454,12 @@ scan_ring_kernel(const __grid_constant__ RingParams p)
     __shared__ int s_cum[kRingMaxBatch + 1];  // s_cum[b] = work items before request b
     __shared__ int s_seq[kRingMaxBatch];      // seq_lens[b]
     __shared__ volatile int s_pool_empty;     // a warp of this CTA found the dynamic item pool exhausted
-    __shared__ int s_warps_done;              // scanning warps of this CTA that have finished (fused selection)
+    __shared__ int s_warps_done;                // warps of this CTA out of work items (fused selection)
+    __shared__ volatile int s_tail_state;       // 0 = scan still running somewhere, 1 = all scores complete, 2 = gave up waiting
+    __shared__ volatile int s_epoch;            // the "all scored" word as this launch found it
+    __shared__ volatile int s_leader;           // the warp that spoke for the CTA (valid once s_tail_state is set)
+    __shared__ FusedSel s_sel;                  // the selection parameters, for the warps that select rows
+    __shared__ int s_sel_list[kRingWarps][kSelListLen];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int Hout = p.reduce_kvhead ? 1 : p.Hkv;
@@ -369,12 +470,16 @@ scan_ring_kernel(const __grid_constant__ RingParams p)
         fence_mbar_init();
         s_pool_empty = 0;
         s_warps_done = 0;
+        s_tail_state = 0;
+        s_sel = p.sel;
     }
     // Launched early (programmatic dependent launch): the CTA is resident and its barriers are set up while the
     // kernel before it in the stream drains.  Nothing in global memory is read before the wait, because that kernel
     // may be the one that writes the sequence lengths or the block table - unless the caller has ruled that out
     // (early_setup): then the wait moves behind the resolution of the first work items.
     if (!p.early_setup) grid_dependency_wait();
+    const bool fused = p.sel.enabled != 0;  // selection folded into the scan (see FusedSel)
+    if (fused && !p.early_setup && tid == 0) s_epoch = ld_acquire_gpu(p.sel.all_scored);
     if (warp == 0) {  // prefix sum of items per request
         int run = 0;
         for (int b0 = 0; b0 < p.B; b0 += 32) {
@@ -484,7 +589,10 @@ scan_ring_kernel(const __grid_constant__ RingParams p)
     int token = claim_start();
     // (early_setup) up to here only the sequence lengths and the block table were read; the code cache, the query
     // codes and the score buffer may still be in use by the kernel before this one
-    if (p.early_setup) grid_dependency_wait();
+    if (p.early_setup) {
+        grid_dependency_wait();
+        if (fused && tid == 0) s_epoch = ld_acquire_gpu(p.sel.all_scored);  // (the kernel before this one may set it)
+    }
     issue(cur);
     mark_past_end();  // while the first block is on its way
     Item nxt = resolve(claim_finish(token));
@@ -496,52 +604,6 @@ scan_ring_kernel(const __grid_constant__ RingParams p)
         nxt = resolve(claim_finish(token));
         token = claim_start();
     };
-    // ---- selection folded into the scan (see FusedSel) -----------------------------------------------------------
-    const bool fused = p.sel.enabled != 0;
-    int pending_b = -1;  // a request one of whose last items this warp retired: help with its rows once it is complete
-    auto take_rows = [&](int b) {  // all lanes; rows of a COMPLETE request are handed out by ticket
-        __threadfence();           // the scores of the request, written by other SMs, are read after this point
-        for (;;) {
-            int t = 0;
-            if (lane == 0) t = atomicAdd(&p.sel.row_tick[b], 1);
-            t = __shfl_sync(0xffffffffu, t, 0);
-            if (t >= p.sel.Hout) break;
-            if (p.max_blocks <= 1024) warp_select_row<32>(p, b, t, s_seq[b]);
-            else warp_select_row<kFuseMaxBlocks / 32>(p, b, t, s_seq[b]);
-        }
-    };
-    auto request_complete = [&](int b) -> bool {
-        int v = 0;
-        if (lane == 0) v = ld_acquire_gpu(&p.sel.row_done[b]);
-        v = __shfl_sync(0xffffffffu, v, 0);
-        return v == s_cum[b + 1] - s_cum[b];
-    };
-    // Called by all lanes after the scores of an item of request b have been stored.
-    auto retire_item = [&](int b) {
-        if (!fused) return;
-        __threadfence();  // this lane's score stores are visible device-wide before the counter moves
-        __syncwarp();
-        int c = 0;
-        if (lane == 0) c = atomicAdd(&p.sel.row_done[b], 1) + 1;
-        c = __shfl_sync(0xffffffffu, c, 0);
-        const int n_items = s_cum[b + 1] - s_cum[b];
-        if (c == n_items) {
-            take_rows(b);
-            if (pending_b == b) pending_b = -1;
-        } else if (c > n_items - p.sel.Hout) {
-            pending_b = b;
-        }
-        if (pending_b >= 0 && pending_b != b && request_complete(pending_b)) {
-            take_rows(pending_b);
-            pending_b = -1;
-        }
-    };
-    if (fused) {
-        // requests without any work item (length 0) are never retired: hand their rows out here
-        for (int b = blockIdx.x * p.n_active + warp; b < p.B; b += lanes_total)
-            if (s_cum[b + 1] == s_cum[b]) take_rows(b);
-    }
-
     int cur_b = -1;
     uint32_t phase = 0;
     if constexpr (ROW > 0) {
@@ -717,7 +779,6 @@ scan_ring_kernel(const __grid_constant__ RingParams p)
                 __syncwarp();
                 advance();
             }
-            retire_item(m.b);
         }
     } else if constexpr (!MIN) {
         // lane <-> (block in stage, column); a column is one 32-bit word of one kv head
@@ -796,7 +857,6 @@ scan_ring_kernel(const __grid_constant__ RingParams p)
                 __syncwarp();
                 advance();
             }
-            retire_item(m.b);
         }
     } else {
         // lane <-> (block in stage, 16-byte piece of a token row, token slot)
@@ -873,32 +933,79 @@ scan_ring_kernel(const __grid_constant__ RingParams p)
                     p.out[((int64_t)m.b * Hout + head) * p.max_blocks + j] = have ? best : -1;
                 }
             }
-            retire_item(m.b);
         }
     }
     if (fused) {
-        // Out of work items.  A request this warp offered to help with may still be in flight in other warps: wait
-        // for it briefly (this warp holds no unprocessed item any more, so nothing can wait on it in turn) and give
-        // up silently after the limit - the warp that retires the request's last item takes whatever rows are left.
-        if (pending_b >= 0) {
-            const unsigned long long t0 = global_timer_ns();
-            bool done = request_complete(pending_b);
-            while (!done && global_timer_ns() - t0 < 200000ull) done = request_complete(pending_b);
-            if (done) take_rows(pending_b);
-        }
-        // The last warp of the last CTA clears the counters for the next launch on this workspace.
+        // Out of work items: arrive (after this warp's score stores are visible device-wide).  The last warp of the
+        // CTA to arrive speaks for the CTA: it makes the grid-level arrival and, unless that was the final one, polls
+        // the grid's "all scored" word; its sibling warps watch a shared-memory copy, so that word's L2 line sees
+        // one poller per SM.  The word counts launches: the final arrival sets it to the value read at the start of
+        // this launch plus one (and clears the counters for the next launch), so nothing has to be reset afterwards.
+        __threadfence();
         __syncwarp();
-        int last = 0;
+        const int grid = (int)gridDim.x;
+        int state = 0;
+        int cta_last = 0;
+        if (lane == 0) cta_last = atomicAdd(&s_warps_done, 1) == p.n_active - 1;
+        cta_last = __shfl_sync(0xffffffffu, cta_last, 0);
         if (lane == 0) {
-            __threadfence();
-            if (atomicAdd(&s_warps_done, 1) == p.n_active - 1) last = atomicAdd(p.sel.cta_done, 1) == (int)gridDim.x - 1;
+            if (cta_last) {
+                const int epoch = s_epoch;
+                if (atom_add_release_gpu(p.sel.cta_done, 1) == grid - 1) {
+                    *p.sel.cta_done = 0;
+                    if (p.sched != nullptr) *p.sched = 0;  // (no warp of the grid claims work any more)
+                    st_release_gpu(p.sel.all_scored, epoch + 1);
+                    state = 1;
+                } else {
+                    // (the timer is only consulted every 1024 polls: reading it costs far more than a poll)
+                    unsigned long long t0 = 0;
+                    state = 2;
+                    for (uint32_t polls = 1;; ++polls) {
+                        if (ld_acquire_gpu(p.sel.all_scored) != epoch) { state = 1; break; }
+                        if ((polls & 1023u) == 0u) {
+                            const unsigned long long now = global_timer_ns();
+                            if (t0 == 0) t0 = now;
+                            else if (now - t0 > kWaitLimitNs) break;
+                        }
+                        __nanosleep(40);
+                    }
+                }
+                s_leader = warp;
+                __threadfence_block();
+                s_tail_state = state;
+            } else {
+                unsigned long long t0 = 0;
+                state = 2;
+                for (uint32_t polls = 1;; ++polls) {
+                    const int v = s_tail_state;
+                    if (v != 0) { state = v; break; }
+                    if ((polls & 1023u) == 0u) {
+                        const unsigned long long now = global_timer_ns();
+                        if (t0 == 0) t0 = now;
+                        else if (now - t0 > kWaitLimitNs + kWaitLimitNs / 8) break;
+                    }
+                    __nanosleep(40);
+                }
+            }
         }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (last) {
-            for (int b = lane; b < p.B; b += 32) { p.sel.row_done[b] = 0; p.sel.row_tick[b] = 0; }
-            if (lane == 0) {
-                *p.sel.cta_done = 0;
-                if (p.sched != nullptr) *p.sched = 0;
+        state = __shfl_sync(0xffffffffu, state, 0);
+        if (state != 1) {
+            flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT);  // part of the grid never finished scanning: rows not selected
+        } else {
+            __threadfence();  // the scores written by the other SMs are read after this point
+            // Rows blockIdx.x, blockIdx.x + grid, ... belong to this CTA.  The warp that spoke for the CTA takes the
+            // first of them (it learns of the completion first), its siblings the others in order of warp index.
+            const int n_rows = p.B * p.sel.Hout;
+            int slot;  // this warp's position among the CTA's row takers
+            if (cta_last) slot = 0;
+            else slot = 1 + warp - (warp > s_leader ? 1 : 0);
+            for (int t = blockIdx.x + slot * grid; t < n_rows; t += lanes_total) {
+                const int b = t / p.sel.Hout, h = t - b * p.sel.Hout;
+                if (p.max_blocks <= 1024)
+                    warp_select_row<32>(&s_sel, p.out, p.bt, p.bt_stride, p.max_blocks, p.BS, b, h, s_seq[b], s_sel_list[warp]);
+                else
+                    warp_select_row<kFuseMaxBlocks / 32>(&s_sel, p.out, p.bt, p.bt_stride, p.max_blocks, p.BS, b, h,
+                                                         s_seq[b], s_sel_list[warp]);
             }
         }
     }

@@ -722,12 +722,15 @@ static int sel_cluster_override()
     return v;
 }
 
-// UCMR_FUSED_SELECT=0 (read once per process) keeps the selection in its own kernel for every shape.
+// UCMR_FUSED_SELECT=1 (read once per process) lets the staged scan run the selection itself for rows of at most
+// kFuseMaxBlocks blocks (one launch instead of two).  Off by default: measured on B200 the in-kernel hand-over (grid-wide
+// arrival, then one warp per row) takes as long as the second launch it saves - 55.6 vs 54.7 us for 16 x 1024-block rows
+// x 8 heads, 25.5 vs 23.3 us for 8 x 2048-block rows - so it only pays where launches are expensive (no CUDA graph).
 static bool fused_select_enabled()
 {
     static const bool v = [] {
         const char* env = getenv("UCMR_FUSED_SELECT");
-        return !(env && env[0] == '0');
+        return env != nullptr && env[0] == '1';
     }();
     return v;
 }
@@ -782,8 +785,7 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
             fs.out_phys = out_phys; fs.out_logical = out_logical; fs.out_scores = out_scores;
             fs.out_valid = out_valid; fs.out_newseq = out_newseq;
             fs.cta_done = status + 4;
-            fs.row_done = status + 64;
-            fs.row_tick = status + 64 + kWsMaxBatch;
+            fs.all_scored = status + 36;
         }
     }
     bool fused = false;

@@ -21,7 +21,7 @@ REDUCE_MIN = 0
 REDUCE_SUM = 1
 
 MAX_MUST_SELECT = 16
-WORKSPACE_HEADER_BYTES = 8448
+WORKSPACE_HEADER_BYTES = 256
 
 
 class UcmrError(RuntimeError):
