@@ -40,6 +40,10 @@ def _cmp(out, ref):
     (2, 8, 1, 4, 16, 70),    # the same with one code per kv head (min mode: four blocks per stage, lane groups)
     (2, 8, 4, 4, 32, 45),    # block 32: four blocks per stage
     (2, 8, 2, 8, 16, 37),    # 256-bit codes, block 16: two passes per block, four blocks per stage
+    (2, 4, 2, 8, 16, 50),    # 4 kv heads x 256-bit codes, block 16: a head spans two 16-byte pieces of the row
+    (2, 4, 4, 8, 32, 21),    # the same with block 32 and groups of 4
+    (2, 8, 8, 4, 32, 30),    # block 32, groups of 8
+    (1, 8, 2, 4, 16, 130),   # block 16, groups of 2, a long ragged row
     (2, 8, 1, 16, 32, 9),    # 512-bit codes
     (1, 2, 3, 4, 128, 6),    # G outside {1,2,4,8}: query codes in shared memory
     (2, 1, 16, 18, 64, 7),   # 576-bit MLA codes, W=18: token-row path of the staged kernel

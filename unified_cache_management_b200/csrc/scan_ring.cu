@@ -75,6 +75,7 @@ struct RingParams {
     int stage_bytes;   // bps * block_stride
     int n_active;      // warps (= stages) in use: min(kRingWarps, ring bytes / stage bytes)
     int early_setup;   // UCMR_FLAG_INPUTS_STABLE: sequence lengths and block table may be read before the dependency wait
+    int small_blocks;  // sum mode, rows of 32 words, blocks of 16 or 32 tokens: lane <-> 16-byte piece of the row (see kernel)
     FusedSel sel;
 };
 
@@ -781,6 +782,104 @@ scan_ring_kernel(const RingParams p)
             }
         }
     } else if constexpr (!MIN) {
+        bool small_done = false;
+        if constexpr (RW_T == 32 && G_T > 0 && (CH == 16 || CH == 32)) {
+            if (p.small_blocks) {
+                // Small blocks (16 or 32 tokens of 128 bytes: vLLM's default block sizes with 8 kv heads x 128 bits).
+                // Scanning such a block with the whole warp, one column per lane, spends more instructions on the
+                // per-block bookkeeping (lengths, shuffles, stores) than on the 16 words a lane folds.  Here a lane
+                // owns one 16-byte piece of the token row (4 consecutive words: a kv head of 128-bit codes, half a
+                // head of 256-bit ones) in the blocks  lane / 8, lane / 8 + 4, ...  of the stage: it reads its piece
+                // of every token with one 16-byte shared-memory load (the 8 lanes of a quarter warp cover the 128
+                // bytes of a row, so no bank is hit twice), folds the four columns as four independent carry-save
+                // chains and ends up with the whole head's score, so there is no cross-lane reduction for 128-bit
+                // codes and the query words stay in registers across blocks.
+                small_done = true;
+                constexpr int kBlocksPerLane = (CH == 16) ? 2 : 1;  // the stage holds 8 (4) blocks, a lane group of 8 takes every 4th
+                const int piece = lane & 7, grp = lane >> 3;
+                const int head = (piece * 4) / p.W, w0 = (piece * 4) % p.W;
+                uint32_t qv[4][G_T];  // [column of the piece][query head of the group]
+                while (cur.valid) {
+                    if (!mbar_wait(full, phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
+                    phase ^= 1u;
+                    const StageMeta m = s_meta[warp];
+                    if (m.b != cur_b) {
+#pragma unroll
+                        for (int g = 0; g < G_T; ++g) {
+                            const uint4 v = __ldg(reinterpret_cast<const uint4*>(
+                                p.q + ((int64_t)m.b * p.Hq + head * G_T + g) * p.W + w0));
+                            qv[0][g] = v.x; qv[1][g] = v.y; qv[2][g] = v.z; qv[3][g] = v.w;
+                        }
+                        cur_b = m.b;
+                    }
+                    int score[kBlocksPerLane];
+                    int ntoks[kBlocksPerLane];
+#pragma unroll
+                    for (int bi = 0; bi < kBlocksPerLane; ++bi) {
+                        const int blk_e = grp + 4 * bi;
+                        const int j = m.j0 + blk_e;
+                        const bool have = blk_e < p.bps && ((m.valid_mask >> blk_e) & 1u);
+                        const int ntok = have ? min(p.BS, m.seq - j * p.BS) : 0;
+                        ntoks[bi] = have ? ntok : -1;
+                        const uint4* sp = reinterpret_cast<const uint4*>(stage + blk_e * p.block_stride) + piece;
+                        int acc = 0;
+                        if constexpr (CH == 16) {
+                            uint32_t x0[CH], x1[CH], x2[CH], x3[CH];
+#pragma unroll
+                            for (int t = 0; t < CH; ++t) {
+                                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                                if (t < ntok) v = sp[t * 8];
+                                x0[t] = v.x; x1[t] = v.y; x2[t] = v.z; x3[t] = v.w;
+                            }
+                            if (bi == kBlocksPerLane - 1) {  // the stage's last words are in registers: refill it first
+                                __syncwarp();
+                                advance();
+                            }
+                            acc = chunk_score<G_T, CH>(x0, ntok, G_T, qv[0]) + chunk_score<G_T, CH>(x1, ntok, G_T, qv[1]) +
+                                  chunk_score<G_T, CH>(x2, ntok, G_T, qv[2]) + chunk_score<G_T, CH>(x3, ntok, G_T, qv[3]);
+                        } else {
+                            // 32 tokens: two columns at a time (64 registers of buffered words)
+                            const uint2* sp2 = reinterpret_cast<const uint2*>(sp);
+#pragma unroll
+                            for (int half = 0; half < 2; ++half) {
+                                uint32_t x0[CH], x1[CH];
+#pragma unroll
+                                for (int t = 0; t < CH; ++t) {
+                                    uint2 v = make_uint2(0u, 0u);
+                                    if (t < ntok) v = sp2[t * 16 + half];
+                                    x0[t] = v.x; x1[t] = v.y;
+                                }
+                                if (half == 1) {
+                                    __syncwarp();
+                                    advance();
+                                }
+                                acc += chunk_score<G_T, CH>(x0, ntok, G_T, qv[2 * half]) +
+                                       chunk_score<G_T, CH>(x1, ntok, G_T, qv[2 * half + 1]);
+                            }
+                        }
+                        score[bi] = acc;
+                    }
+#pragma unroll
+                    for (int bi = 0; bi < kBlocksPerLane; ++bi) {
+                        const int blk_e = grp + 4 * bi;
+                        const int j = m.j0 + blk_e;
+                        int acc = score[bi];
+                        // pieces of one head (256-bit codes: two), or of all heads, sit in neighbouring lanes
+                        const int span = p.reduce_kvhead ? 8 : p.W / 4;
+                        for (int off = 1; off < span; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+                        if (blk_e < p.bps && j < p.max_blocks) {
+                            const int v = ntoks[bi] >= 0 ? acc : -1;  // -1: past the request's end or a bad block id
+                            if (p.reduce_kvhead) {
+                                if (piece == 0) p.out[(int64_t)m.b * p.max_blocks + j] = v;
+                            } else if (w0 == 0) {
+                                p.out[((int64_t)m.b * Hout + head) * p.max_blocks + j] = v;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        if (!small_done) {
         // lane <-> (block in stage, column); a column is one 32-bit word of one kv head
         const int RW = RW_T > 0 ? RW_T : p.RW;
         const int G = G_T > 0 ? G_T : p.G;
@@ -858,6 +957,7 @@ scan_ring_kernel(const RingParams p)
                 advance();
             }
         }
+        }  // (!small_done)
     } else {
         // lane <-> (block in stage, 16-byte piece of a token row, token slot)
         const int PW = p.W / 4, P = p.Hkv * PW;
@@ -870,6 +970,16 @@ scan_ring_kernel(const RingParams p)
         constexpr int GMAX = G_T > 0 ? G_T : kRingMaxG;
         constexpr int kMinRounds = 16;  // 16-byte pieces a lane buffers in registers at a time
         uint4 qv[GMAX];
+        // Groups of 2, 4 or 8 query heads: sum_g popc(k ^ q_g) only depends, bit position by bit position, on the key
+        // bit and on c = how many of the G query codes have the bit set: the position contributes  k ? G - c : c.
+        // With c and G - c kept bit-sliced per query (planes cnt[p], alt[p]), plane p of the contribution is the mux
+        // k ? alt[p] : cnt[p] - one logic instruction per plane and word - and the distance is
+        // sum_p 2^p popc(plane p): P = bits(G) + ... planes instead of G XOR-popcounts per word.  For even G plane 0
+        // does not depend on k (G - c and c have the same parity) and is folded into a per-query constant.
+        constexpr int kMuxPlanes = G_T >= 8 ? 4 : G_T >= 4 ? 3 : 2;
+        constexpr int kMuxFirst = (G_T >= 2 && G_T % 2 == 0) ? 1 : 0;
+        uint4 cnt[kMuxPlanes], alt[kMuxPlanes];
+        int mux_const = 0;
         while (cur.valid) {
             if (!mbar_wait(full, phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
             phase ^= 1u;
@@ -883,6 +993,37 @@ scan_ring_kernel(const RingParams p)
                 for (int g = 0; g < GMAX; ++g)
                     if (g < G) qv[g] = __ldg(q4 + g * PW);
                 cur_b = m.b;
+                if constexpr (G_T >= 2) {
+                    uint32_t* cw = reinterpret_cast<uint32_t*>(cnt);
+                    uint32_t* aw = reinterpret_cast<uint32_t*>(alt);
+                    mux_const = 0;
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        uint32_t pl[kMuxPlanes];
+#pragma unroll
+                        for (int q = 0; q < kMuxPlanes; ++q) pl[q] = 0u;
+#pragma unroll
+                        for (int g = 0; g < G_T; ++g) {  // bit-sliced increment by query code g
+                            uint32_t carry = reinterpret_cast<const uint32_t*>(&qv[g])[w];
+#pragma unroll
+                            for (int q = 0; q < kMuxPlanes; ++q) {
+                                const uint32_t t = pl[q] & carry;
+                                pl[q] ^= carry;
+                                carry = t;
+                            }
+                        }
+                        uint32_t borrow = 0u;  // bit-sliced G - c
+#pragma unroll
+                        for (int q = 0; q < kMuxPlanes; ++q) {
+                            const uint32_t gb = ((G_T >> q) & 1) ? 0xFFFFFFFFu : 0u;
+                            const uint32_t c = pl[q];
+                            cw[q * 4 + w] = c;
+                            aw[q * 4 + w] = gb ^ c ^ borrow;
+                            borrow = (~gb & (c | borrow)) | (c & borrow);
+                        }
+                        if (kMuxFirst == 1) mux_const += __popc(pl[0]);
+                    }
+                }
             }
             const uint4* sb = reinterpret_cast<const uint4*>(stage + blk * p.block_stride);
             int best = INT_MAX;
@@ -904,13 +1045,14 @@ scan_ring_kernel(const RingParams p)
                     const int tok = (r0 + i) * TS + slot;
                     int d = 0;
                     if constexpr (G_T >= 2) {
-                        uint32_t v[4 * G_T];
+                        d = mux_const;
 #pragma unroll
-                        for (int g = 0; g < G_T; ++g) {
-                            v[4 * g + 0] = kb[i].x ^ qv[g].x; v[4 * g + 1] = kb[i].y ^ qv[g].y;
-                            v[4 * g + 2] = kb[i].z ^ qv[g].z; v[4 * g + 3] = kb[i].w ^ qv[g].w;
+                        for (int q = kMuxFirst; q < kMuxPlanes; ++q) {
+                            const uint4 k = kb[i], a = alt[q], c = cnt[q];
+                            const int s = __popc((k.x & a.x) | (~k.x & c.x)) + __popc((k.y & a.y) | (~k.y & c.y)) +
+                                          __popc((k.z & a.z) | (~k.z & c.z)) + __popc((k.w & a.w) | (~k.w & c.w));
+                            d += s << q;
                         }
-                        d = hs_popc<4 * G_T>(v);
                     } else {
 #pragma unroll
                         for (int g = 0; g < GMAX; ++g)
@@ -1011,6 +1153,16 @@ scan_ring_kernel(const RingParams p)
     }
 }
 
+// UCMR_SMALL_BLOCKS=0 (read once per process) sends blocks of 16 / 32 tokens through the general column-per-lane code.
+static bool small_blocks_enabled()
+{
+    static const bool v = [] {
+        const char* env = getenv("UCMR_SMALL_BLOCKS");
+        return !(env && env[0] == '0');
+    }();
+    return v;
+}
+
 // Returns UCMR_OK after launching, or UCMR_ERR_UNSUPPORTED when the shape is not covered (the caller
 // then uses the register kernel).
 int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const uint32_t* q, int Hq,
@@ -1051,6 +1203,10 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     p.q = q; p.bt = bt; p.max_blocks = max_blocks; p.bt_stride = bt_stride; p.seq_lens = seq_lens; p.B = B;
     p.reduce_kvhead = reduce_kvhead ? 1 : 0; p.out = out; p.status = status; p.sched = sched;
     p.RW = (int)RW; p.bps = bps; p.block_bytes = (int)block_bytes; p.early_setup = inputs_stable ? 1 : 0;
+    // small blocks of full-width rows: the lane <-> row-piece mapping (W = 4 or 8, and a stage of exactly 8 or 4 blocks)
+    p.small_blocks = (!row_mode && !is_min && RW == 32 && (W == 4 || W == 8) && (BS == 16 || BS == 32) &&
+                      (G == 1 || G == 2 || G == 4 || G == 8) && bps == (BS == 16 ? 8 : 4) &&
+                      reinterpret_cast<uintptr_t>(q) % 16 == 0 && small_blocks_enabled()) ? 1 : 0;
     if (fuse != nullptr) {
         if (max_blocks > kFuseMaxBlocks || B > kWsMaxBatch || fuse->key_bits + fuse->idx_bits > 31) return UCMR_ERR_BAD_ARG;
         p.sel = *fuse;
