@@ -37,10 +37,24 @@ struct GatherLocator {
     __device__ int64_t total() const { return p.n_sel * p.n_pools * p.chunks_per_block; }
     __device__ bool operator()(int64_t c, const char*& src, char*& dst, uint32_t& bytes) const
     {
-        const int chunk = (int)(c % p.chunks_per_block);
-        const int64_t t = c / p.chunks_per_block;
-        const int which = (int)(t % p.n_pools);
-        const int64_t s = t / p.n_pools;
+        // The one thread that drives a CTA's copies resolves two chunks per 16 KiB moved; 64-bit divisions here
+        // (a few hundred cycles each) would cost more than the copy engine needs per chunk, so chunk numbers that
+        // fit 32 bits - all practical sizes - are split with 32-bit arithmetic.
+        int chunk, which;
+        int64_t s;
+        if (c <= 0xFFFFFFFFll) {
+            const uint32_t c32 = (uint32_t)c, cpb = (uint32_t)p.chunks_per_block;
+            const uint32_t t = c32 / cpb;
+            chunk = (int)(c32 - t * cpb);
+            const uint32_t s32 = p.n_pools == 2 ? (t >> 1) : t;
+            which = p.n_pools == 2 ? (int)(t & 1u) : 0;
+            s = s32;
+        } else {
+            chunk = (int)(c % p.chunks_per_block);
+            const int64_t t = c / p.chunks_per_block;
+            which = (int)(t % p.n_pools);
+            s = t / p.n_pools;
+        }
         const int phys = p.sel[s];
         const int64_t off = (int64_t)chunk * kGatherChunk;
         const int64_t left = p.block_bytes - off;
@@ -69,8 +83,17 @@ struct ListLocator {
     __device__ int64_t total() const { return p.num * p.chunks_per_block; }
     __device__ bool operator()(int64_t c, const char*& src, char*& dst, uint32_t& bytes) const
     {
-        const int chunk = (int)(c % p.chunks_per_block);
-        const int64_t i = c / p.chunks_per_block;
+        int chunk;
+        int64_t i;
+        if (c <= 0xFFFFFFFFll) {  // 32-bit split, see GatherLocator
+            const uint32_t c32 = (uint32_t)c, cpb = (uint32_t)p.chunks_per_block;
+            const uint32_t q = c32 / cpb;
+            chunk = (int)(c32 - q * cpb);
+            i = q;
+        } else {
+            chunk = (int)(c % p.chunks_per_block);
+            i = c / p.chunks_per_block;
+        }
         const int64_t off = (int64_t)chunk * kGatherChunk;
         const int64_t left = p.size - off;
         bytes = (uint32_t)(left < kGatherChunk ? left : kGatherChunk);
@@ -90,6 +113,8 @@ __global__ void __launch_bounds__(32) bulk_copy_kernel(const Locator loc)
 {
     extern __shared__ __align__(128) char s_buf[];
     __shared__ __align__(8) uint64_t s_full[kGatherStages];
+    __shared__ char* s_dst[kGatherStages];       // where the chunk in each stage goes (null: nothing to store)
+    __shared__ uint32_t s_bytes[kGatherStages];
     if (threadIdx.x != 0) return;  // a single thread drives the copy engine
 
     for (int s = 0; s < kGatherStages; ++s) mbar_init(&s_full[s], 1);
@@ -106,11 +131,16 @@ __global__ void __launch_bounds__(32) bulk_copy_kernel(const Locator loc)
             const int stage = (int)(it % kGatherStages);
             // the store that last read this stage was committed LAG groups ago
             if (it >= kGatherStages) bulk_wait_read<kGatherLag - 1>();
+            // the chunk is resolved once, here; its destination waits in shared memory for the store side (a second
+            // resolution there would put another dependent load of the selection on this thread's critical path)
             const char* src; char* dst; uint32_t bytes;
             if (loc(first + it * step, src, dst, bytes)) {
+                s_dst[stage] = dst;
+                s_bytes[stage] = bytes;
                 mbar_expect_tx(&s_full[stage], bytes);
                 bulk_g2s(s_buf + (size_t)stage * kGatherChunk, src, bytes, &s_full[stage]);
             } else {
+                s_dst[stage] = nullptr;
                 flag_status(loc.status(), UCMR_DEV_BAD_BLOCK_ID);
                 mbar_arrive(&s_full[stage]);  // keep the phase sequence; nothing is stored for it
             }
@@ -123,8 +153,8 @@ __global__ void __launch_bounds__(32) bulk_copy_kernel(const Locator loc)
                 flag_status(loc.status(), UCMR_DEV_WAIT_TIMEOUT);
                 dead = true;
             } else {
-                const char* src; char* dst; uint32_t bytes;
-                if (loc(first + c * step, src, dst, bytes)) bulk_s2g(dst, s_buf + (size_t)stage * kGatherChunk, bytes);
+                char* const dst = s_dst[stage];
+                if (dst != nullptr) bulk_s2g(dst, s_buf + (size_t)stage * kGatherChunk, s_bytes[stage]);
                 bulk_commit();  // one group per chunk, empty or not, so the wait counts stay aligned
             }
         }
