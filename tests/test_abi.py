@@ -33,6 +33,8 @@ def test_version_and_status_strings():
     assert b"workspace" in lib.ucmr_status_string(L.UCMR_ERR_WORKSPACE)
     assert lib.ucmr_hamming_topk_workspace_bytes(16, 8, 1024, 0) == L.WORKSPACE_HEADER_BYTES + 16 * 8 * 1024 * 4
     assert lib.ucmr_hamming_topk_workspace_bytes(16, 8, 1024, 1) == L.WORKSPACE_HEADER_BYTES + 16 * 1024 * 4
+    # one kv head: room for the query planes of the token-row scan on top
+    assert lib.ucmr_hamming_topk_workspace_bytes(16, 1, 1024, 0) > L.WORKSPACE_HEADER_BYTES + 16 * 1024 * 4
 
 
 def test_host_argument_validation_needs_no_gpu():

@@ -376,3 +376,17 @@ print("fused ok")
     env = dict(os.environ, UCMR_FUSED_SELECT="1")
     res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=900)
     assert res.returncode == 0 and "fused ok" in res.stdout, res.stdout[-2000:] + res.stderr[-4000:]
+
+
+@pytest.mark.parametrize("BS,mb,G", [(64, 2400, 16), (16, 12000, 5), (128, 1300, 64), (32, 5000, 2)])
+def test_token_row_codes_many_ring_rounds(cuda_device, BS, mb, G):
+    """576-bit token-row codes (MLA) with enough blocks that every CTA of the producer / consumer kernel goes round
+    its ring of stages several times; ragged lengths, both block reduces."""
+    B = 4
+    seq = [mb * BS, mb * BS - 7, (mb // 2) * BS + 1, mb * BS - BS]
+    case = H.make_paged_case(600 + BS, B, 1, G, 18, BS, mb, seq_lens=seq)
+    for mode in ("min", "sum"):
+        out = _run_dev(case, cuda_device, 32, reduce=mode, must_select=(0, -2, -1))
+        ref = OC.hamming_topk(case["codes"], case["q"], case["block_table"], case["seq_lens"], 32, MODES[mode], False,
+                              must_select=(0, -2, -1))
+        _cmp(out, ref)

@@ -12,7 +12,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_PATH = os.path.join(PKG_DIR, "libucmr_b200.so")
-SOURCES = ["api.cu", "scan.cu", "scan_ring.cu", "topk.cu", "gather.cu", "encode.cu", "noalloc.cu", "float_retrieval.cu"]
+SOURCES = ["api.cu", "scan.cu", "scan_ring.cu", "scan_rows.cu", "topk.cu", "gather.cu", "encode.cu", "noalloc.cu", "float_retrieval.cu"]
 
 
 def _sources():

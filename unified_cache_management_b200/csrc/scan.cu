@@ -290,6 +290,10 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
                   int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, int32_t* sched, cudaStream_t st,
                   const FusedSel* fuse);
 
+int run_scan_rows(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const uint32_t* q, int Hq,
+                  const int32_t* bt, int max_blocks, int64_t bt_stride, const int32_t* seq_lens, int B,
+                  int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, void* scratch, cudaStream_t st);
+
 // UCMR_SCAN=register routes every scan through the register kernel of this file (debug aid; the
 // staged kernel in scan_ring.cu is the default wherever it covers the shape).
 static bool force_register_scan()
@@ -304,12 +308,13 @@ static bool force_register_scan()
 
 // Launches the scan into `out` ([B,Hout,max_blocks] int32).  Shared by the C entry points.  `sched` is an
 // optional zero-initialised int32 the staged kernel uses as its work counter; whoever passes it resets it
-// to zero after the launch (stream-ordered).  With `fuse` the staged kernel also runs the selection (and clears the
+// to zero after the launch (stream-ordered).  `row_scratch` (optional, rows_scratch_bytes(B) bytes) enables the
+// producer / consumer kernel for token-row codes.  With `fuse` the staged kernel also runs the selection (and clears the
 // counter itself); *fused says whether it did - false when the shape went to a kernel that cannot.
 int run_scan(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const uint32_t* q, int Hq,
              const int32_t* bt, int max_blocks, int64_t bt_stride, const int32_t* seq_lens, int B,
              int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, int32_t* sched, cudaStream_t st,
-             const FusedSel* fuse, bool* fused)
+             const FusedSel* fuse, bool* fused, void* row_scratch)
 {
     if (fused) *fused = false;
     int rc = validate_scan_args(codes, NB, BS, Hkv, W, q, Hq, bt, max_blocks, bt_stride, seq_lens, B);
@@ -321,6 +326,12 @@ int run_scan(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const ui
     if (reduce_mode != UCMR_REDUCE_MIN && reduce_mode != UCMR_REDUCE_SUM) return UCMR_ERR_BAD_ARG;
     if (B == 0) return UCMR_OK;
 
+    if (!force_register_scan() && fuse == nullptr && row_scratch != nullptr) {
+        // token-row codes (one kv head, 18 words): the producer / consumer kernel, which needs scratch for the planes
+        rc = run_scan_rows(codes, NB, BS, Hkv, W, q, Hq, bt, max_blocks, bt_stride, seq_lens, B, reduce_mode, reduce_kvhead,
+                           out, status, row_scratch, st);
+        if (rc != UCMR_ERR_UNSUPPORTED) return rc;
+    }
     if (!force_register_scan()) {
         rc = run_scan_ring(codes, NB, BS, Hkv, W, q, Hq, bt, max_blocks, bt_stride, seq_lens, B, reduce_mode | mode_flags,
                            reduce_kvhead, out, status, sched, st, fuse);
@@ -402,7 +413,7 @@ extern "C" int ucmr_block_scores(const uint32_t* codes, int64_t NB, int BS, int 
 {
     return run_scan(codes, NB, BS, Hkv, W, q_codes, Hq, block_table, max_blocks, block_table_stride, seq_lens,
                     B, reduce_mode, reduce_kvhead, out_scores, status_word, nullptr, static_cast<cudaStream_t>(stream),
-                    nullptr, nullptr);
+                    nullptr, nullptr, nullptr);
 }
 
 extern "C" int ucmr_hamming_score(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W,

@@ -25,7 +25,8 @@ namespace ucmr {
 int run_scan(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const uint32_t* q, int Hq,
              const int32_t* bt, int max_blocks, int64_t bt_stride, const int32_t* seq_lens, int B,
              int reduce_mode, int reduce_kvhead, int32_t* out, int32_t* status, int32_t* sched, cudaStream_t st,
-             const FusedSel* fuse, bool* fused);
+             const FusedSel* fuse, bool* fused, void* row_scratch);
+size_t rows_scratch_bytes(int B);
 
 constexpr int kSelThreads = 512;
 constexpr int kSelWarps = kSelThreads / 32;
@@ -691,7 +692,9 @@ using namespace ucmr;
 extern "C" size_t ucmr_hamming_topk_workspace_bytes(int B, int Hkv, int max_blocks, int reduce_kvhead)
 {
     if (B < 0 || Hkv <= 0 || max_blocks <= 0) return 0;
-    return UCMR_WORKSPACE_HEADER_BYTES + scores_bytes(B, reduce_kvhead ? 1 : Hkv, max_blocks);
+    // header, block scores, and for one kv head (where the codes may be token rows) the query planes of the row scan
+    return UCMR_WORKSPACE_HEADER_BYTES + scores_bytes(B, reduce_kvhead ? 1 : Hkv, max_blocks) +
+           (Hkv == 1 ? rows_scratch_bytes(B) : 0);
 }
 
 extern "C" int ucmr_workspace_init(void* workspace, size_t bytes, void* stream)
@@ -789,8 +792,11 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
         }
     }
     bool fused = false;
+    void* row_scratch = Hkv == 1 ? static_cast<char*>(workspace) + UCMR_WORKSPACE_HEADER_BYTES +
+                                       scores_bytes(B, 1, max_blocks)
+                                 : nullptr;
     rc = run_scan(codes, NB, BS, Hkv, W, q_codes, Hq, bt, max_blocks, bt_stride, seq_local, B, scan_mode,
-                  reduce_kvhead, scores, status, sched, st, try_fuse ? &fs : nullptr, &fused);
+                  reduce_kvhead, scores, status, sched, st, try_fuse ? &fs : nullptr, &fused, row_scratch);
     if (rc != UCMR_OK || B == 0 || fused) return rc;
     // From here on the scan is enqueued and will leave its work counter non-zero; the selection kernel clears it.
     // If that kernel cannot be launched, clear it here, or the next call on this workspace would skip work items.
