@@ -310,6 +310,15 @@ encode_tc_kernel(const __grid_constant__ CUtensorMap x_map, const EncParams p)
         for (int64_t it = 0; it < my_tiles; ++it) {
             const int a = (int)(it % kEncAccs);
             const uint32_t aph = (uint32_t)((it / kEncAccs) & 1);
+            // Where this thread's row goes is looked up before waiting for the accumulator: the slot is a dependent
+            // global load, and after the wait it would sit on the epilogue's critical path for every tile.
+            const int64_t tile_pre = first + it * step;
+            const int in_tile = q * 32 + lane;
+            const int64_t tok_pre = tile_pre * tok_per_tile + in_tile / p.H;  // (a tile holds whole tokens)
+            int64_t slot_pre = -1;
+            if (p.src_blocks == nullptr && p.slot_mapping != nullptr && tile_pre * kEncTileM + in_tile < p.rows)
+                slot_pre = p.slot_is_int64 ? static_cast<const int64_t*>(p.slot_mapping)[tok_pre]
+                                           : (int64_t) static_cast<const int32_t*>(p.slot_mapping)[tok_pre];
             if (!mbar_wait(&acc_full[a], aph)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kEncBits);
@@ -342,10 +351,8 @@ encode_tc_kernel(const __grid_constant__ CUtensorMap x_map, const EncParams p)
                 if (p.slot_mapping == nullptr) {
                     *reinterpret_cast<uint4*>(p.out + row * 4) = code;
                 } else {
-                    const int64_t tok = row / p.H;
-                    const int h = (int)(row - tok * p.H);
-                    const int64_t slot = p.slot_is_int64 ? static_cast<const int64_t*>(p.slot_mapping)[tok]
-                                                         : (int64_t) static_cast<const int32_t*>(p.slot_mapping)[tok];
+                    const int h = in_tile % p.H;
+                    const int64_t slot = slot_pre;
                     if (slot >= 0 && slot < p.n_slots)
                         *reinterpret_cast<uint4*>(p.out + (slot * p.H + h) * 4) = code;
                 }
