@@ -127,7 +127,7 @@ def test_prefill_then_decode_rewrites_and_restores_block_table(cuda_device):
     # finished requests drop their state; a resumed one starts as a prefill again
     so = F.scheduler_output({}, finished=["r0"], resumed=[("r1", True)])
     plugin.update_states(so)
-    assert "r0" not in plugin.is_prefill_flag and "r1" not in plugin.is_prefill_flag and "r2" in plugin.is_prefill_flag
+    assert "r0" not in plugin.phases and "r1" not in plugin.phases and "r2" in plugin.phases
 
 
 def test_prefix_cache_hit_rehashes_blocks_in_place(cuda_device):

@@ -30,6 +30,7 @@ from .base import INVALID_SLOT, UcmSparseBase, UcmSparseCpuGpuBuffer, UcmSparseM
 from .gsa_on_device_config import GSAOnDeviceConfig
 from .hamming_topk import update_seq_lens
 from .hash_encoder import HashEncoder
+from .request_state import RequestPhaseTracker, prefix_layout, prefix_slots
 
 ReqType = Union[str, int]
 _CONFIG_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "configs")
@@ -128,7 +129,8 @@ class GSAOnDevice(UcmSparseBase):
         self.has_pc_hit = False
         self.has_decode = False
         self.decode_only = False
-        self.is_prefill_flag: Dict[ReqType, bool] = {}
+        self.phases = RequestPhaseTracker()   # which live request is prefilling / decoding
+        self.step_plan = None
         self.num_reqs = 0
 
         self.max_batch_size = vllm_config.scheduler_config.max_num_seqs
@@ -202,42 +204,43 @@ class GSAOnDevice(UcmSparseBase):
         self.token_idx_buf = torch.arange(self.max_num_tokens, device=self.device, dtype=torch.int64)
 
     # ---- hashing ---------------------------------------------------------------------------------
+    @staticmethod
+    def _fold_heads(x: torch.Tensor, fold: int) -> torch.Tensor:
+        """[T, H, D] -> [T, H/fold, D]: heads h, h + H/fold, ... averaged (the MLA head reduction)."""
+        if fold <= 1:
+            return x
+        t, h, d = x.shape
+        return x.view(t, fold, h // fold, d).mean(dim=1)
+
     def hash_code(self, nope=None, rope=None, reduction_head_num: int = 1, query: Optional[torch.Tensor] = None):
-        """GQA branch of the reference (gsa_on_device.py:396-412): one code per kv head from the mean of
-        its query group.  MLA branch (:375-394): heads h, h + H/r, ... are averaged first (r =
-        ``reduction_head_num``), then the latent and the rope part are hashed by their own encoders.  Returns the
-        packed codes viewed as bf16, like the reference."""
+        """Query codes, viewed as bf16 like the reference's (gsa_on_device.py:375-412).
+        GQA: one code per kv head from the mean of its query group (the mean and the encode are one kernel).
+        MLA: ``reduction_head_num`` = r folds heads h, h + H/r, ... into one, then the latent and the rope part go
+        through their own encoders; returns the pair."""
         if self.is_mla:
             if nope is None or rope is None:
                 raise ValueError("MLA mode requires `nope` and `rope`.")
-            if reduction_head_num > 1:
-                nope = nope.view(nope.shape[0], reduction_head_num, nope.shape[1] // reduction_head_num,
-                                 nope.shape[2]).mean(dim=1)
-                rope = rope.view(rope.shape[0], reduction_head_num, rope.shape[1] // reduction_head_num,
-                                 rope.shape[2]).mean(dim=1)
-            hash_nope = self.hash_encoder_nope.compute_hash(nope)
-            hash_rope = self.hash_encoder_rope.compute_hash(rope)
-            return hash_nope.view(torch.bfloat16), hash_rope.view(torch.bfloat16)
+            codes = (self.hash_encoder_nope.compute_hash(self._fold_heads(nope, reduction_head_num)),
+                     self.hash_encoder_rope.compute_hash(self._fold_heads(rope, reduction_head_num)))
+            return tuple(c.view(torch.bfloat16) for c in codes)
         if query is None:
             raise ValueError("GQA mode requires `query`.")
-        if self.num_q_heads > self.num_key_heads:
-            codes = self.hash_encoder.compute_hash_grouped(query, self.num_q_heads // self.num_key_heads)
-        elif self.num_q_heads < self.num_key_heads:
-            query = torch.repeat_interleave(query, self.num_key_heads // self.num_q_heads, dim=1)
-            codes = self.hash_encoder.compute_hash_grouped(query, 1)
-        else:
-            codes = self.hash_encoder.compute_hash_grouped(query, 1)
-        return codes.view(torch.bfloat16)
+        hq, hkv = self.num_q_heads, self.num_key_heads
+        if hq < hkv:      # fewer query heads than kv heads: every query head answers for hkv / hq kv heads
+            query = torch.repeat_interleave(query, hkv // hq, dim=1)
+        group = hq // hkv if hq > hkv else 1
+        return self.hash_encoder.compute_hash_grouped(query, group).view(torch.bfloat16)
 
     def get_layer_attn_metadata(self, forward_context, layer_name: str):
         attn_meta = forward_context.attn_metadata
         return attn_meta[layer_name] if isinstance(attn_meta, dict) else attn_meta
 
     def get_layer_state(self, layer_name: str):
+        """(rollback layer: dense attention, no code cache; skip layer: reuses the previous layer's selection) for a
+        vLLM layer name such as ``model.layers.17.self_attn.attn`` (gsa_on_device.py:418-424)."""
         layer_id = int(layer_name.split(".")[2])
-        is_rollback_layer = layer_id in self.hash_rollback_layers
-        is_skip_hash_layer = layer_id < len(self.hash_skip_layers) and bool(self.hash_skip_layers[layer_id])
-        return is_rollback_layer, is_skip_hash_layer
+        skip = self.hash_skip_layers
+        return layer_id in self.hash_rollback_layers, bool(skip[layer_id]) if layer_id < len(skip) else False
 
     def cache_k_hash_gqa_cuda(self, key, attn_metadata, k_hash, forward_context, layer_name):
         slot_mapping = attn_metadata.slot_mapping.flatten()
@@ -331,18 +334,19 @@ class GSAOnDevice(UcmSparseBase):
 
     def maybe_init_cudagraph_buffers_for_topk(self, n, tile_scheduler_metadata, topk_tile_scheduler_metadata,
                                               topk_num_splits, topk_seq_lens):
-        """Copies the step's metadata into fixed-address buffers for CUDA-graph replays (gsa_on_device.py:1382-1405)."""
-        sm_parts = tile_scheduler_metadata.size(0)
-        view = self.cg_buf_topk_tile_scheduler_metadata[:sm_parts]
-        view.copy_(topk_tile_scheduler_metadata)
-        topk_tile_scheduler_metadata = view
-        view = self.cg_buf_topk_num_splits[:n]
-        view.copy_(topk_num_splits)
-        self.cg_buf_topk_num_splits[n:].fill_(topk_num_splits[-1])
-        topk_num_splits = view
-        view = self.cg_buf_topk_seq_lens[: topk_seq_lens.size(0)]
-        view.copy_(topk_seq_lens)
-        return topk_tile_scheduler_metadata, topk_num_splits, view
+        """The shortened-sequence scheduling metadata of the step, copied into the fixed-address buffers a CUDA-graph
+        replay reads (gsa_on_device.py:1382-1405).  Returns views of those buffers."""
+        def pinned(buf, src, rows):
+            view = buf[:rows]
+            view.copy_(src)
+            return view
+
+        meta = pinned(self.cg_buf_topk_tile_scheduler_metadata, topk_tile_scheduler_metadata,
+                      tile_scheduler_metadata.size(0))
+        splits = pinned(self.cg_buf_topk_num_splits, topk_num_splits, n)
+        self.cg_buf_topk_num_splits[n:].fill_(topk_num_splits[-1])   # padding rows repeat the last offset
+        lens = pinned(self.cg_buf_topk_seq_lens, topk_seq_lens, topk_seq_lens.size(0))
+        return meta, splits, lens
 
     # ---- retrieval ---------------------------------------------------------------------------------
     # (inputs_stable in the retrieval calls: block table and lengths come from the step's attention metadata, built
@@ -445,33 +449,31 @@ class GSAOnDevice(UcmSparseBase):
         return INVALID_SLOT
 
     def initialize_kv_hash_cache_tensors(self, kv_caches, device):
-        """kv_caches[layer] becomes (kv_cache, khash_cache); the code cache has the K cache's shape with
-        the last dim divided by 16 (bf16 storage, one bit per key element) - gsa_on_device.py:1020-1032."""
-        dtype = torch.bfloat16
-        for layer_name, kv_cache in kv_caches.items():
-            is_rollback_layer, is_skip_hash_layer = self.get_layer_state(layer_name)
-            if not is_rollback_layer and not is_skip_hash_layer:
-                shape = list((kv_cache if self.is_mla else kv_cache[0]).shape)
-                shape[-1] //= dtype.itemsize * 8
-                khash_cache = torch.zeros(shape, dtype=dtype, device=device)
-            else:
-                khash_cache = None
-            kv_caches[layer_name] = (kv_cache, khash_cache)
+        """Pairs every layer's KV cache with its code cache: ``kv_caches[layer] = (kv_cache, khash_cache)``.  The code
+        cache has the K cache's shape with the last dimension divided by 16 - one bit per key element, stored as bf16
+        words like the reference's (gsa_on_device.py:1020-1032) - and is None for layers that never retrieve."""
+        bits_per_word = torch.bfloat16.itemsize * 8
+        for name in list(kv_caches):
+            kv_cache = kv_caches[name]
+            rollback, skip = self.get_layer_state(name)
+            khash_cache = None
+            if not (rollback or skip):
+                k_shape = (kv_cache if self.is_mla else kv_cache[0]).shape
+                khash_cache = torch.zeros(tuple(k_shape[:-1]) + (k_shape[-1] // bits_per_word,), dtype=torch.bfloat16,
+                                          device=device)
+            kv_caches[name] = (kv_cache, khash_cache)
 
     # ---- per-step bookkeeping (host) -------------------------------------------------------------------
     def rebuild_prefix_cache_info_for_req(self, block_table_row, num_prompt_tokens: int, qlen: int, block_size: int):
-        assert 0 <= qlen <= num_prompt_tokens
-        num_prefix_tokens = num_prompt_tokens - qlen
-        if num_prefix_tokens <= 0:
+        """(prefix tokens, prefix blocks, their block ids, slot of every prefix token) of a first prefill chunk that
+        computes ``qlen`` of the prompt's tokens (same return value as the reference's method of this name,
+        gsa_on_device.py:1142-1174)."""
+        layout = prefix_layout(num_prompt_tokens, qlen, block_size)
+        if layout.empty:
             empty = block_table_row[:0]
             return 0, 0, empty, empty
-        num_prefix_blocks = cdiv(num_prefix_tokens, block_size)
-        prefix_block_ids = block_table_row[:num_prefix_blocks]
-        token_idx = self.token_idx_buf[:num_prefix_tokens]
-        block_indices = token_idx // block_size
-        block_offsets = token_idx - block_indices * block_size
-        token_block_numbers = prefix_block_ids.index_select(0, block_indices)
-        return num_prefix_tokens, num_prefix_blocks, prefix_block_ids, token_block_numbers * block_size + block_offsets
+        ids = block_table_row[: layout.n_blocks]
+        return layout.n_tokens, layout.n_blocks, ids, prefix_slots(ids, layout, block_size, self.token_idx_buf)
 
     def get_seq_lens(self, attn_metadata):
         """Sequence lengths of the step (gsa_on_device.py:1211-1233); MLA metadata keeps them per phase."""
@@ -533,61 +535,47 @@ class GSAOnDevice(UcmSparseBase):
         num_long_reqs = int((seq_lens[: self.num_reqs] >= self.seq_len_threshold).sum().item())
         self.gsa_enabled = num_long_reqs >= self.concurrency_threshold
 
-        num_decodes = num_pc_hit = all_prefix_tokens = all_prefix_blocks = 0
-        compute_q_lens = attn_metadata.query_start_loc[1:] - attn_metadata.query_start_loc[:-1]
+        q_lens = attn_metadata.query_start_loc[1:] - attn_metadata.query_start_loc[:-1]
+        plan = self.phases.plan_step(
+            scheduler_output.num_scheduled_tokens, requests, input_batch.req_id_to_index,
+            lambda row: int(q_lens[row]), self.block_size,
+            getattr(scheduler_output, "num_external_computed_tokens_per_req", None))
+        self.step_plan = plan
+        num_decodes = len(plan.decode_rows)
         self.decode_req_ids_buf.clear()
-        ext_tokens_map = getattr(scheduler_output, "num_external_computed_tokens_per_req", None) or {}
-        for req_id, num_scheduled_tokens in scheduler_output.num_scheduled_tokens.items():
-            req = requests[req_id]
-            is_decode = req_id in self.is_prefill_flag and not self.is_prefill_flag[req_id]
-            is_first_prefill = req_id not in self.is_prefill_flag
-            is_prefill = is_first_prefill or self.is_prefill_flag[req_id]
-            is_last_chunk = is_prefill and (req.num_computed_tokens + num_scheduled_tokens >= req.num_prompt_tokens)
-            if is_decode:
-                self.decode_req_ids_buf.np[num_decodes] = input_batch.req_id_to_index[req_id]
-                num_decodes += 1
-            if is_first_prefill:
-                self.is_prefill_flag[req_id] = True
-                req_row_id = input_batch.req_id_to_index[req_id]
-                ext_tokens = int(ext_tokens_map.get(req_id, 0))
-                if ext_tokens > 0:
-                    (n_tok, n_blk, blk_ids, slots) = self.rebuild_prefix_cache_info_for_req(
-                        block_table_row=self.get_block_table_row(attn_metadata, req_row_id,
-                                                                 int(compute_q_lens[req_row_id])),
-                        num_prompt_tokens=req.num_prompt_tokens, qlen=int(compute_q_lens[req_row_id]),
-                        block_size=self.block_size)
-                    self.prefix_slot_mapping_buf[all_prefix_tokens: all_prefix_tokens + n_tok] = slots
-                    self.prefix_block_ids_buf[all_prefix_blocks: all_prefix_blocks + n_blk] = blk_ids
-                    self.prefix_block_tokens_buf[all_prefix_blocks: all_prefix_blocks + n_blk] = self.block_size
-                    self.prefix_block_tokens_buf[all_prefix_blocks + n_blk - 1] = n_tok - (n_blk - 1) * self.block_size
-                    all_prefix_tokens += n_tok
-                    all_prefix_blocks += n_blk
-                    num_pc_hit += 1
-            if is_last_chunk:
-                self.is_prefill_flag[req_id] = False
-        self.has_pc_hit = num_pc_hit > 0
+        self.decode_req_ids_buf.np[:num_decodes] = plan.decode_rows
+        # prefix hits: their blocks are re-hashed in place by the first layer that sees them
+        tok0 = blk0 = 0
+        for hit in plan.prefix_hits:
+            lay = hit.layout
+            row = self.get_block_table_row(attn_metadata, hit.row, int(q_lens[hit.row]))
+            ids = row[: lay.n_blocks]
+            self.prefix_slot_mapping_buf[tok0: tok0 + lay.n_tokens] = prefix_slots(ids, lay, self.block_size,
+                                                                                   self.token_idx_buf)
+            self.prefix_block_ids_buf[blk0: blk0 + lay.n_blocks] = ids
+            self.prefix_block_tokens_buf[blk0: blk0 + lay.n_blocks] = self.block_size
+            self.prefix_block_tokens_buf[blk0 + lay.n_blocks - 1] = lay.tail_tokens
+            tok0 += lay.n_tokens
+            blk0 += lay.n_blocks
+        self.has_pc_hit = bool(plan.prefix_hits)
         if self.has_pc_hit:
-            self.prefix_slot_mapping = self.prefix_slot_mapping_buf[:all_prefix_tokens]
-            self.prefix_block_ids = self.prefix_block_ids_buf[:all_prefix_blocks]
-            self.prefix_block_tokens = self.prefix_block_tokens_buf[:all_prefix_blocks]
+            self.prefix_slot_mapping = self.prefix_slot_mapping_buf[:tok0]
+            self.prefix_block_ids = self.prefix_block_ids_buf[:blk0]
+            self.prefix_block_tokens = self.prefix_block_tokens_buf[:blk0]
         if self.is_mla or not self.gsa_enabled:
             return None
-        self.has_decode = num_decodes > 0
-        self.decode_only = self.has_decode and (num_decodes == self.num_reqs)
+        self.has_decode = plan.has_decode
+        self.decode_only = plan.decode_only
         if self.has_decode:
             self.prepare_cuda_decode_sparse_meta(attn_metadata, num_decodes)
         return None
 
-    def _free_cached_request(self, request_id: ReqType) -> None:
-        self.is_prefill_flag.pop(request_id, None)
-
     def update_states(self, scheduler_output) -> None:
-        for req_id in scheduler_output.finished_req_ids:
-            self._free_cached_request(req_id)
-        req_data = scheduler_output.scheduled_cached_reqs
-        for req_id, resumed in zip(req_data.req_ids, req_data.resumed_from_preemption):
-            if resumed:
-                self._free_cached_request(req_id)
+        """Finished requests are forgotten; so are requests resumed after a preemption, which start over as a first
+        prefill (gsa_on_device.py:1407-1421)."""
+        self.phases.forget_many(scheduler_output.finished_req_ids)
+        cached = scheduler_output.scheduled_cached_reqs
+        self.phases.forget_many(r for r, resumed in zip(cached.req_ids, cached.resumed_from_preemption) if resumed)
 
     def request_finished_in_worker(self, request_id: ReqType):
-        self._free_cached_request(request_id)
+        self.phases.forget(request_id)
