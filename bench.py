@@ -170,7 +170,10 @@ class Ranks:
             dist.destroy_process_group()
 
 
-def timed_reps(run_k, ranks: Ranks, min_ms: float = MIN_TIMED_MS, max_reps: int = 400, host_clock: bool = False):
+MAX_REPS = 400
+
+
+def timed_reps(run_k, ranks: Ranks, min_ms: float = MIN_TIMED_MS, max_reps: int = 0, host_clock: bool = False):
     """Times `run_k()` (which enqueues exactly K steps) `reps` times, each repetition between a barrier + synchronize
     on both sides, with CUDA events on the current stream (or the host clock around enqueue + synchronize when
     `host_clock`).  Each repetition's time is the max over the ranks; returns the median repetition and the spread.
@@ -194,7 +197,7 @@ def timed_reps(run_k, ranks: Ranks, min_ms: float = MIN_TIMED_MS, max_reps: int 
         return ms
 
     est = ranks.reduce([one()])[0]                       # also one more warm-up pass
-    reps = int(min(max_reps, max(3, math.ceil(min_ms / max(est, 1e-3)))))
+    reps = int(min(max_reps or MAX_REPS, max(3, math.ceil(min_ms / max(est, 1e-3)))))
     times = ranks.reduce([one() for _ in range(reps)])
     ranks.barrier()
     return dict(ms=float(np.median(times)), reps=reps, ms_min=float(min(times)), ms_max=float(max(times)))
@@ -887,6 +890,15 @@ def run_profile_case(what: str) -> None:
         out = torch.empty((65536, 8, 4), dtype=torch.int32, device=dev)
         for _ in range(3):
             ops.hash_encode(x, r, out=out)
+    elif what == "encode_cache":
+        x = torch.randn((65536, 8, 128), device=dev, dtype=torch.bfloat16)          # 134 MB of keys into a paged cache
+        r = (torch.randn((128, 128), device=dev) / 128 ** 0.5).to(torch.bfloat16)
+        cache = torch.zeros((512, 128, 8, 4), dtype=torch.int32, device=dev)
+        perm = torch.randperm(512, device=dev, generator=g)
+        pos = torch.arange(65536, device=dev)
+        slots = (perm[pos // 128] * 128 + pos % 128).to(torch.int64)
+        for _ in range(3):
+            ops.hash_encode_and_cache(x, slots, cache, r)
     elif what == "encode_wide":
         x = torch.randn((262144, 512), device=dev, dtype=torch.bfloat16)            # MLA latent vectors: 268 MB
         r = (torch.randn((512, 512), device=dev) / 512 ** 0.5).to(torch.bfloat16)
@@ -968,17 +980,21 @@ def main():
     ap.add_argument("--workload", default="llama3_8b_decode16", choices=sorted(WORKLOADS) + sorted(EXTRA_WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="headline workload only")
+    ap.add_argument("--max-reps", type=int, default=400,
+                    help="upper bound of the repetitions of a timed region (a profiler run wants few)")
     ap.add_argument("--exchange", default="both", choices=["both", "p2p", "nccl"],
                     help="million_token_sharded on several GPUs: how the candidate records travel")
     ap.add_argument("--ncu-case", default=None,
                     help="run a small single-kernel case for a profiler capture and exit "
                          "(scan, scan_min, scan_256bit, scan_mla, scan_bs16, scan_bs32, scan_tp8, select, encode, "
-                         "encode_wide, encode_step, gather)")
+                         "encode_cache, encode_wide, encode_step, gather)")
     args = ap.parse_args()
 
     if args.ncu_case:
         run_profile_case(args.ncu_case)
         return
+    global MAX_REPS
+    MAX_REPS = max(3, args.max_reps)
 
     ranks = Ranks()
     cfg = dict(WORKLOADS["llama3_8b_decode16"])
