@@ -138,44 +138,61 @@ __device__ __forceinline__ uint32_t pack_signs(const uint32_t (&r)[32])
 }
 
 
-// R[k][n] (row-major bf16) -> B[n][k], K-major with the 128-byte swizzle the MMA descriptors expect:
-// row n holds 64 k-values (128 bytes) per K half, and its 16-byte chunk c lives at chunk c ^ (n & 7).
-// Each thread transposes 8x8 blocks in registers: eight 16-byte loads in, eight 16-byte stores out.
-__device__ __forceinline__ void build_rt_swizzled(uint8_t* s_b, const __nv_bfloat16* R, int tid, int nthreads)
+// R[k][n] (row-major bf16, row stride ldr elements) -> B[n][k], K-major with the 128-byte swizzle the MMA descriptors
+// expect: row n holds 64 k-values (128 bytes) per K half, and its 16-byte chunk c lives at chunk c ^ (n & 7).
+// The unit of work is an 8x8 block (rows k = 8 kc .. 8 kc + 7, columns n0 + 8 nc .. + 7): eight 16-byte loads in,
+// a register transpose, eight 16-byte stores out.  The two halves are separate so that a kernel may issue the loads
+// early and the transposing stores late, with other memory traffic in between.
+__device__ __forceinline__ void rt_block_load(uint4 (&v)[8], const __nv_bfloat16* R, int ldr, int n0, int kc, int nc)
 {
-    for (int blk = tid; blk < (kEncD / 8) * (kEncBits / 8); blk += nthreads) {
-        const int kc = blk / (kEncBits / 8), nc = blk % (kEncBits / 8);
-        uint4 v[8];
 #pragma unroll
-        for (int r = 0; r < 8; ++r)
-            v[r] = __ldg(reinterpret_cast<const uint4*>(R + (size_t)(kc * 8 + r) * kEncBits + nc * 8));
-        const int half = kc >> 3, chunk = kc & 7;
+    for (int r = 0; r < 8; ++r)
+        v[r] = __ldg(reinterpret_cast<const uint4*>(R + (size_t)(kc * 8 + r) * ldr + n0 + nc * 8));
+}
+
+__device__ __forceinline__ void rt_block_store(uint8_t* s_b, const uint4 (&v)[8], int kc, int nc)
+{
+    const int half = kc >> 3, chunk = kc & 7;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
-            uint4 o;
-            o.x = __byte_perm(reinterpret_cast<const uint32_t*>(&v[0])[j >> 1], reinterpret_cast<const uint32_t*>(&v[1])[j >> 1], sel);
-            o.y = __byte_perm(reinterpret_cast<const uint32_t*>(&v[2])[j >> 1], reinterpret_cast<const uint32_t*>(&v[3])[j >> 1], sel);
-            o.z = __byte_perm(reinterpret_cast<const uint32_t*>(&v[4])[j >> 1], reinterpret_cast<const uint32_t*>(&v[5])[j >> 1], sel);
-            o.w = __byte_perm(reinterpret_cast<const uint32_t*>(&v[6])[j >> 1], reinterpret_cast<const uint32_t*>(&v[7])[j >> 1], sel);
-            const int n = nc * 8 + j;
-            const uint32_t off = (uint32_t)half * kEncHalfBytes + (uint32_t)n * 128u + ((uint32_t)(chunk ^ (n & 7)) << 4);
-            *reinterpret_cast<uint4*>(s_b + off) = o;
-        }
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;  // low or high bf16 of each 32-bit pair
+        const auto word = [&](int r) { return reinterpret_cast<const uint32_t*>(&v[r])[j >> 1]; };
+        uint4 o;
+        o.x = __byte_perm(word(0), word(1), sel);
+        o.y = __byte_perm(word(2), word(3), sel);
+        o.z = __byte_perm(word(4), word(5), sel);
+        o.w = __byte_perm(word(6), word(7), sel);
+        const int n = nc * 8 + j;
+        const uint32_t off = (uint32_t)half * kEncHalfBytes + (uint32_t)n * 128u + ((uint32_t)(chunk ^ (n & 7)) << 4);
+        *reinterpret_cast<uint4*>(s_b + off) = o;
     }
 }
 
-// The same in two steps for 128 threads (two 8x8 blocks per thread), so that the global loads can be issued early
-// and the transposing stores late, with other memory traffic in between.
+// Columns [n0, n0 + 128) of R[K][N] -> swizzled B, all threads of the CTA taking 8x8 blocks in turn.
+__device__ __forceinline__ void build_rt_chunk_swizzled(uint8_t* s_b, const __nv_bfloat16* R, int K, int N, int n0,
+                                                        int tid, int nthreads)
+{
+    for (int blk = tid; blk < (K / 8) * (kEncBits / 8); blk += nthreads) {
+        const int kc = blk / (kEncBits / 8), nc = blk % (kEncBits / 8);
+        uint4 v[8];
+        rt_block_load(v, R, N, n0, kc, nc);
+        rt_block_store(s_b, v, kc, nc);
+    }
+}
+
+// The whole 128 x 128 matrix.
+__device__ __forceinline__ void build_rt_swizzled(uint8_t* s_b, const __nv_bfloat16* R, int tid, int nthreads)
+{
+    build_rt_chunk_swizzled(s_b, R, kEncD, kEncBits, 0, tid, nthreads);
+}
+
+// The whole matrix by 128 threads in two steps (two 8x8 blocks per thread): loads first, stores later.
 __device__ __forceinline__ void rt_load_128(uint4 (&v)[2][8], const __nv_bfloat16* R, int tid)
 {
 #pragma unroll
     for (int it = 0; it < 2; ++it) {
         const int blk = tid + it * 128;
-        const int kc = blk / (kEncBits / 8), nc = blk % (kEncBits / 8);
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-            v[it][r] = __ldg(reinterpret_cast<const uint4*>(R + (size_t)(kc * 8 + r) * kEncBits + nc * 8));
+        rt_block_load(v[it], R, kEncBits, 0, blk / (kEncBits / 8), blk % (kEncBits / 8));
     }
 }
 
@@ -184,20 +201,7 @@ __device__ __forceinline__ void rt_store_128(uint8_t* s_b, const uint4 (&v)[2][8
 #pragma unroll
     for (int it = 0; it < 2; ++it) {
         const int blk = tid + it * 128;
-        const int kc = blk / (kEncBits / 8), nc = blk % (kEncBits / 8);
-        const int half = kc >> 3, chunk = kc & 7;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
-            uint4 o;
-            o.x = __byte_perm(reinterpret_cast<const uint32_t*>(&v[it][0])[j >> 1], reinterpret_cast<const uint32_t*>(&v[it][1])[j >> 1], sel);
-            o.y = __byte_perm(reinterpret_cast<const uint32_t*>(&v[it][2])[j >> 1], reinterpret_cast<const uint32_t*>(&v[it][3])[j >> 1], sel);
-            o.z = __byte_perm(reinterpret_cast<const uint32_t*>(&v[it][4])[j >> 1], reinterpret_cast<const uint32_t*>(&v[it][5])[j >> 1], sel);
-            o.w = __byte_perm(reinterpret_cast<const uint32_t*>(&v[it][6])[j >> 1], reinterpret_cast<const uint32_t*>(&v[it][7])[j >> 1], sel);
-            const int n = nc * 8 + j;
-            const uint32_t off = (uint32_t)half * kEncHalfBytes + (uint32_t)n * 128u + ((uint32_t)(chunk ^ (n & 7)) << 4);
-            *reinterpret_cast<uint4*>(s_b + off) = o;
-        }
+        rt_block_store(s_b, v[it], blk / (kEncBits / 8), blk % (kEncBits / 8));
     }
 }
 
@@ -395,32 +399,6 @@ struct WideParams {
     const __nv_bfloat16* R;    // [K, N] row-major
     int32_t* status;
 };
-
-// Columns [n0, n0 + 128) of R[k][n] -> B[n][k], K-major, one 128-byte-swizzled [128 n][64 k] block per 64 k.
-__device__ __forceinline__ void build_rt_chunk_swizzled(uint8_t* s_b, const __nv_bfloat16* R, int K, int N, int n0,
-                                                        int tid, int nthreads)
-{
-    for (int blk = tid; blk < (K / 8) * (kEncBits / 8); blk += nthreads) {
-        const int kc = blk / (kEncBits / 8), nc = blk % (kEncBits / 8);
-        uint4 v[8];
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-            v[r] = __ldg(reinterpret_cast<const uint4*>(R + (size_t)(kc * 8 + r) * N + n0 + nc * 8));
-        const int half = kc >> 3, chunk = kc & 7;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
-            uint4 o;
-            o.x = __byte_perm(reinterpret_cast<const uint32_t*>(&v[0])[j >> 1], reinterpret_cast<const uint32_t*>(&v[1])[j >> 1], sel);
-            o.y = __byte_perm(reinterpret_cast<const uint32_t*>(&v[2])[j >> 1], reinterpret_cast<const uint32_t*>(&v[3])[j >> 1], sel);
-            o.z = __byte_perm(reinterpret_cast<const uint32_t*>(&v[4])[j >> 1], reinterpret_cast<const uint32_t*>(&v[5])[j >> 1], sel);
-            o.w = __byte_perm(reinterpret_cast<const uint32_t*>(&v[6])[j >> 1], reinterpret_cast<const uint32_t*>(&v[7])[j >> 1], sel);
-            const int n = nc * 8 + j;
-            const uint32_t off = (uint32_t)half * kEncHalfBytes + (uint32_t)n * 128u + ((uint32_t)(chunk ^ (n & 7)) << 4);
-            *reinterpret_cast<uint4*>(s_b + off) = o;
-        }
-    }
-}
 
 __global__ void __launch_bounds__(kEncThreads, 1)
 encode_wide_kernel(const __grid_constant__ CUtensorMap x_map, const WideParams p)
@@ -1221,6 +1199,122 @@ extern "C" int ucmr_hash_encode_and_cache_at(const void* x, int64_t T, int H, in
                                  NB, BS, row_words, word_offset, status_word, stream);
 }
 
+static bool step_simt_enabled()
+{
+    static const bool v = [] {
+        const char* e = getenv("UCMR_STEP_ENCODE");
+        return !(e && e[0] == 't');
+    }();
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// decode step on CUDA cores: a few hundred rows, latency is everything
+// ---------------------------------------------------------------------------------------------
+// The two encodes of a decode step (B*Hq query rows, B*Hkv new key rows) are some 10 MFLOP: the tensor-core tile
+// kernel spends its time on the set-up chain around the MMA (TMEM allocation, swizzled staging, commit / wait, four
+// tcgen05.ld round trips, dealloc), not on the math.  Here a warp owns one output row: the CTA stages R (32 KiB) in
+// shared memory with one round of 16-byte loads while every warp fetches its row (from device memory or, across the
+// bus, from page-locked host memory), then each lane accumulates four adjacent columns over the 128 inputs in float32
+// (x broadcast by shuffle, R read with one 8-byte shared-memory load per input) and the 128 sign bits are packed with
+// three shuffle steps.  One memory round trip, about 1300 instructions per warp, one store.
+constexpr int kStepThreads = 256;
+constexpr int kStepRowsPerCta = kStepThreads / 32;
+
+__global__ void __launch_bounds__(kStepThreads) encode_step_kernel(const TileParams p)
+{
+    __shared__ __align__(16) __nv_bfloat16 s_r[kEncD * kEncBits];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    grid_launch_dependents();  // a scan launched right after this kernel may set itself up meanwhile
+    grid_dependency_wait();    // q and the new keys come from the kernel before this one
+    // R: 2048 16-byte chunks over 256 threads, all loads in flight before the first store
+    {
+        uint4 v[8];
+        const uint4* src = reinterpret_cast<const uint4*>(p.R);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = __ldg(src + tid + u * kStepThreads);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) reinterpret_cast<uint4*>(s_r)[tid + u * kStepThreads] = v[u];
+    }
+    // this warp's row: job 0 rows first, then job 1
+    const int H_out0 = p.job[0].H_in / p.job[0].G, H_out1 = p.job[1].x ? p.job[1].H_in / p.job[1].G : 1;
+    const int64_t rows0 = p.job[0].T * H_out0, rows1 = p.job[1].x ? p.job[1].T * H_out1 : 0;
+    int64_t row = (int64_t)blockIdx.x * kStepRowsPerCta + warp;
+    const bool second = row >= rows0;
+    if (second) row -= rows0;
+    const TileJob& jb = p.job[second ? 1 : 0];
+    const int H_out = second ? H_out1 : H_out0;
+    const bool live = row < (second ? rows1 : rows0);
+    float xv[4] = {0.f, 0.f, 0.f, 0.f};  // inputs 4*lane .. 4*lane+3 of the row
+    int64_t slot = -1;
+    int64_t tok = 0;
+    int ho = 0;
+    if (live) {
+        tok = row / H_out;
+        ho = (int)(row - tok * H_out);
+        const __nv_bfloat16* src = jb.x + tok * jb.stride_t + (int64_t)ho * jb.G * jb.stride_h + 4 * lane;
+        if (jb.slot_mapping != nullptr)
+            slot = jb.slot_is_int64 ? static_cast<const int64_t*>(jb.slot_mapping)[tok]
+                                    : (int64_t) static_cast<const int32_t*>(jb.slot_mapping)[tok];
+        for (int g = 0; g < jb.G; ++g) {
+            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)g * jb.stride_h));
+            const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xv[i] += __bfloat162float(e[i]);
+        }
+        if (jb.G > 1) {  // the group mean, rounded once to bf16 as torch's mean of a bf16 tensor is
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xv[i] = __bfloat162float(__float2bfloat16_rn(xv[i] / (float)jb.G));
+        }
+    }
+    __syncthreads();
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};  // columns 4*lane .. 4*lane+3
+    const uint2* rcol = reinterpret_cast<const uint2*>(s_r) + lane;  // row k of R: 32 pieces of 4 columns
+#pragma unroll 8
+    for (int k = 0; k < kEncD; ++k) {
+        const float x = __shfl_sync(0xffffffffu, xv[k & 3], k >> 2);
+        const uint2 rr = rcol[k * (kEncBits / 4)];
+        acc[0] = fmaf(x, __uint_as_float(rr.x << 16), acc[0]);
+        acc[1] = fmaf(x, __uint_as_float(rr.x & 0xFFFF0000u), acc[1]);
+        acc[2] = fmaf(x, __uint_as_float(rr.y << 16), acc[2]);
+        acc[3] = fmaf(x, __uint_as_float(rr.y & 0xFFFF0000u), acc[3]);
+    }
+    // word w of the code = columns 32w .. 32w+31 = lanes 8w .. 8w+7, four bits each
+    uint32_t nib = (uint32_t)(acc[0] > 0.f) | ((uint32_t)(acc[1] > 0.f) << 1) | ((uint32_t)(acc[2] > 0.f) << 2) |
+                   ((uint32_t)(acc[3] > 0.f) << 3);
+    uint32_t word = nib << (4 * (lane & 7));
+    word |= __shfl_xor_sync(0xffffffffu, word, 1);
+    word |= __shfl_xor_sync(0xffffffffu, word, 2);
+    word |= __shfl_xor_sync(0xffffffffu, word, 4);
+    // lanes 0, 8, 16, 24 hold words 0..3: gather them into lane 0
+    const uint32_t w1 = __shfl_sync(0xffffffffu, word, 8), w2 = __shfl_sync(0xffffffffu, word, 16),
+                   w3 = __shfl_sync(0xffffffffu, word, 24);
+    if (live && lane == 0) {
+        const uint4 code = make_uint4(word, w1, w2, w3);
+        if (jb.slot_mapping == nullptr) {
+            *reinterpret_cast<uint4*>(jb.out + row * 4) = code;
+        } else if (slot >= 0 && slot < jb.n_slots) {
+            *reinterpret_cast<uint4*>(jb.out + (slot * H_out + ho) * 4) = code;
+        }
+    }
+}
+
+// Rows of a decode step up to which the CUDA-core kernel is used (beyond it the tensor-core tiles win).
+constexpr int64_t kStepMaxRows = 4096;
+
+static int launch_step(const TileJob& jq, const TileJob& jk, const void* R, int32_t* status, cudaStream_t st)
+{
+    TileParams p{};
+    p.job[0] = jq;
+    p.job[1] = jk;
+    p.R = static_cast<const __nv_bfloat16*>(R);
+    p.status = status;
+    const int64_t rows = jq.T * (jq.H_in / jq.G) + jk.T * (jk.H_in / jk.G);
+    const int64_t grid = (rows + kStepRowsPerCta - 1) / kStepRowsPerCta;
+    if (grid <= 0) return UCMR_OK;
+    return launch_kernel_ex(encode_step_kernel, dim3((unsigned)grid), dim3(kStepThreads), 0, st, 1, true, p);
+}
+
 extern "C" int ucmr_hash_encode_decode_step(const void* q, int64_t Tq, int Hq, int64_t q_stride_t, int64_t q_stride_h,
                                             int group_mean, uint32_t* q_codes_out, const void* k, int64_t Tk, int Hk,
                                             int64_t k_stride_t, int64_t k_stride_h, const void* slot_mapping,
@@ -1239,6 +1333,10 @@ extern "C" int ucmr_hash_encode_decode_step(const void* q, int64_t Tq, int Hq, i
     if (fused) {
         const TileJob jq = make_job(q, Tq, Hq, group_mean, q_stride_t, q_stride_h, q_codes_out, nullptr, 0, 0);
         const TileJob jk = make_job(k, Tk, Hk, 1, k_stride_t, k_stride_h, cache, slot_mapping, slot_is_int64 ? 1 : 0, NB * BS);
+        // few rows: the CUDA-core kernel (shorter dependency chain); UCMR_STEP_ENCODE=tile keeps the tensor-core tiles
+        if (Tq * (Hq / group_mean) + Tk * Hk <= kStepMaxRows && step_simt_enabled() && q_stride_h % 4 == 0 &&
+            k_stride_h % 4 == 0 && q_stride_t % 4 == 0 && k_stride_t % 4 == 0)
+            return launch_step(jq, jk, R, status_word, st);
         return launch_tiles(jq, &jk, R, status_word, st);
     }
     rc = ucmr_hash_encode_and_cache(k, Tk, Hk, k_stride_t, k_stride_h, R, in_dim, hash_bits, slot_mapping, slot_is_int64,
