@@ -10,9 +10,11 @@
  * State kept by the library, all of it process-wide and none of it per call:
  *   - ucmr_hamming_topk_static uses one fixed device array per GPU and a
  *     mutex-guarded table of its per-device addresses (see its declaration);
- *   - the tuning switches UCMR_PDL, UCMR_SCAN, UCMR_SEL_CLUSTER and
- *     UCMR_FORCE_SIMT_ENCODE are environment variables read once, on the
- *     first call that consults them, and cached for the life of the process;
+ *   - the tuning switches UCMR_PDL, UCMR_SCAN, UCMR_SEL_CLUSTER,
+ *     UCMR_FORCE_SIMT_ENCODE, UCMR_STEP_ENCODE, UCMR_FUSED_SELECT,
+ *     UCMR_SMALL_BLOCKS and UCMR_ROWS_KERNEL are environment variables read
+ *     once, on the first call that consults them, and cached for the life of
+ *     the process;
  *   - the text of the last CUDA error is kept per host thread.
  * Everything else (scores between two kernels, work counters, device status)
  * lives in the caller's workspace.

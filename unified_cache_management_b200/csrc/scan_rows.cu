@@ -161,21 +161,33 @@ __device__ __forceinline__ void csa3(uint32_t& h, uint32_t& l, uint32_t a, uint3
 }
 
 // Sum of the popcounts of 18 words.  The logic pipe (which also runs the 18 mux instructions per plane) and the
-// popcount unit are separate: twelve words are compressed with carry-save adders (18 logic instructions, 5 popcounts),
-// the other six are counted directly, so that neither pipe carries the whole load.
+// popcount unit are separate: twelve words are compressed with carry-save adders, the other six are counted directly,
+// so that neither pipe carries the whole load.  The adders form a tree (four independent 3:2 steps first), not a chain:
+// with three or four warps per scheduler the kernel lives on instruction-level parallelism.
+__device__ __forceinline__ void half_add(uint32_t& h, uint32_t& l, uint32_t a, uint32_t b)
+{
+    h = a & b;
+    l = a ^ b;
+}
 __device__ __forceinline__ int popc18(const uint32_t (&v)[kRowW])
 {
-    uint32_t c1[6], ones = v[0];
-#pragma unroll
-    for (int i = 0; i < 5; ++i) csa3(c1[i], ones, ones, v[1 + 2 * i], v[2 + 2 * i]);
-    c1[5] = ones & v[11];
-    ones ^= v[11];
-    uint32_t c2[3], twos = c1[0];
-    csa3(c2[0], twos, twos, c1[1], c1[2]);
-    csa3(c2[1], twos, twos, c1[3], c1[4]);
-    c2[2] = twos & c1[5];
-    twos ^= c1[5];
-    const int compressed = __popc(ones) + 2 * __popc(twos) + 4 * (__popc(c2[0]) + __popc(c2[1]) + __popc(c2[2]));
+    uint32_t s0, s1, s2, s3, c0, c1, c2, c3;
+    csa3(c0, s0, v[0], v[1], v[2]);
+    csa3(c1, s1, v[3], v[4], v[5]);
+    csa3(c2, s2, v[6], v[7], v[8]);
+    csa3(c3, s3, v[9], v[10], v[11]);
+    uint32_t sa, ca, ones, cb;
+    csa3(ca, sa, s0, s1, s2);
+    half_add(cb, ones, sa, s3);
+    // weight 2: c0 c1 c2 c3 ca cb
+    uint32_t t0, t1, d0, d1, twos, d2;
+    csa3(d0, t0, c0, c1, c2);
+    csa3(d1, t1, c3, ca, cb);
+    half_add(d2, twos, t0, t1);
+    // weight 4: d0 d1 d2
+    uint32_t eights, fours;
+    csa3(eights, fours, d0, d1, d2);
+    const int compressed = (__popc(ones) + 2 * __popc(twos)) + (4 * __popc(fours) + 8 * __popc(eights));
     const int direct = (__popc(v[12]) + __popc(v[13]) + __popc(v[14])) + (__popc(v[15]) + __popc(v[16]) + __popc(v[17]));
     return compressed + direct;
 }
