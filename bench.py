@@ -65,6 +65,10 @@ EXTRA_WORKLOADS = {
     # config 4: sequence sharded over the ranks, local candidates -> exchange -> merge
     "million_token_sharded": dict(B=2, seq=4194304, Hkv=8, Hq=32, D=128, bits=256, BS=64, k=256, layers=2),
 }
+# What every timed step here may promise the scan about kernels still in flight before it: none writes sequence
+# lengths or block tables, and the only code-cache write is the decode-step encode of one new key per request, into
+# the request's last block (ucmr.h: UCMR_FLAG_INPUTS_STABLE, UCMR_FLAG_CACHE_APPEND_ONLY).
+STABLE = dict(inputs_stable=True, cache_append_only=True)
 MIN_TIMED_MS = 50.0
 
 
@@ -542,7 +546,7 @@ def suite_single_request(ranks, K, W, peaks):
 
     def step(layer):
         ops.hamming_topk(caches[layer], q, bt, sl, k, reduce="sum", must_select=MUST_SELECT, workspace=ws, out=out,
-                         want_scores=False, inputs_stable=True)
+                         want_scores=False, **STABLE)
 
     step(0)
     torch.cuda.synchronize()
@@ -598,7 +602,7 @@ def suite_paged_gather(ranks, K, W, peaks):
 
     def step(layer):
         ops.hamming_topk(caches[layer], q, bt_d, seq_d, k, reduce="sum", reduce_kvhead=True, must_select=MUST_SELECT,
-                         workspace=ws, out=ret, want_scores=False, inputs_stable=True)
+                         workspace=ws, out=ret, want_scores=False, **STABLE)
         ops.gather_kv(kp, vp, ret.physical.view(B, k), ok, ov)
 
     step(0)
@@ -672,7 +676,7 @@ def suite_tp(ranks, K, W, peaks):
     def step(layer):
         ops.hash_encode_decode_step(qf[layer], kn[layer], last_slot, caches[layer], R, q_codes_out=q_codes)
         ops.hamming_topk(caches[layer], q_codes, bt, sl, k, reduce="sum", must_select=MUST_SELECT, workspace=ws, out=out,
-                         want_scores=False, inputs_stable=True)
+                         want_scores=False, **STABLE)
 
     step(0)
     torch.cuda.synchronize()
@@ -770,7 +774,7 @@ def suite_sharded(ranks, K, W, peaks, exchanges=("p2p", "nccl")):
     if world == 1:
         def step(layer):
             cs, ci = ops.topk_candidates(caches[layer], q, bt_local, plan.seq_lens_local, seq_g, kl, 0, scale,
-                                         reduce="sum", must_select=MUST_SELECT, workspace=ws, inputs_stable=True,
+                                         reduce="sum", must_select=MUST_SELECT, workspace=ws, **STABLE,
                                          out_scores=cand_s, out_ids=cand_i)
             ops.merge_topk(cs.unsqueeze(0), ci.unsqueeze(0), k, out_scores=o_s, out_ids=o_i)
         cand_s = torch.empty((B, Hkv, kl), dtype=torch.float32, device=dev)
@@ -788,7 +792,7 @@ def suite_sharded(ranks, K, W, peaks, exchanges=("p2p", "nccl")):
                 def step(layer):
                     sharded.sharded_hamming_topk_p2p(caches[layer], q, bt_local, seq_g, k, BS, nblk_total, scale, ex,
                                                      reduce="sum", must_select=MUST_SELECT, workspace=ws, plan=plan,
-                                                     status=st_word, inputs_stable=True, out_scores=o_s, out_ids=o_i)
+                                                     status=st_word, **STABLE, out_scores=o_s, out_ids=o_i)
                 what = "peer-memory stores from the selection kernel + flag wait in the merge kernel (no collective); " \
                        "step number counted in a device word, so the captured step replays correctly"
                 use_graph, launches = True, 3
@@ -800,7 +804,7 @@ def suite_sharded(ranks, K, W, peaks, exchanges=("p2p", "nccl")):
                     s_, i_ = sharded.sharded_hamming_topk(caches[layer], q, bt_local, seq_g, k, BS, nblk_total, scale,
                                                           reduce="sum", must_select=MUST_SELECT, workspace=ws,
                                                           gather_buffer=gbuf, send_buffer=sbuf, plan=plan,
-                                                          inputs_stable=True, out_scores=o_s, out_ids=o_i)
+                                                          **STABLE, out_scores=o_s, out_ids=o_i)
                 what = "one NCCL all-gather of (score, id) records, stream-ordered launches (a captured all-gather did " \
                        "not complete on this pool)"
                 use_graph, launches = False, 4
@@ -1057,7 +1061,7 @@ def main():
         ops.hash_encode_decode_step(wl["q"][layer], wl["k_new"][layer], wl["last_slot"], wl["caches"][layer], wl["R"],
                                     q_codes_out=q_codes)
         ops.hamming_topk(wl["caches"][layer], q_codes, wl["bt"], wl["seq_lens"], cfg["k"], reduce="sum",
-                         must_select=MUST_SELECT, workspace=ws, out=out, want_scores=False, inputs_stable=True)
+                         must_select=MUST_SELECT, workspace=ws, out=out, want_scores=False, **STABLE)
 
     graphs = capture_graphs(step, L)
     for i in range(W):
@@ -1079,7 +1083,7 @@ def main():
     def scan_k():
         for i in range(K):
             ops.block_scores(wl["caches"][i % L], q_codes, wl["bt"], wl["seq_lens"], reduce="sum", out=scores,
-                             inputs_stable=True)
+                             **STABLE)
 
     for _ in range(2):
         scan_k()
@@ -1088,7 +1092,7 @@ def main():
     # the same launch as a CUDA graph of its own, replayed back to back: launches of different replays do not
     # overlap, so this is the duration of one launch including its own prologue and drain
     scan_graphs = capture_graphs(lambda layer: ops.block_scores(wl["caches"][layer], q_codes, wl["bt"], wl["seq_lens"],
-                                                                reduce="sum", out=scores, inputs_stable=True), L)
+                                                                reduce="sum", out=scores, **STABLE), L)
 
     def scan_iso_k():
         for i in range(K):
@@ -1110,7 +1114,7 @@ def main():
         ops.hash_encode_decode_step(q_pin[layer], k_pin[layer], wl["last_slot"], wl["caches"][layer], wl["R"],
                                     q_codes_out=q_codes)
         ops.hamming_topk(wl["caches"][layer], q_codes, wl["bt"], wl["seq_lens"], cfg["k"], reduce="sum",
-                         must_select=MUST_SELECT, workspace=ws, out=out_host, want_scores=False, inputs_stable=True)
+                         must_select=MUST_SELECT, workspace=ws, out=out_host, want_scores=False, **STABLE)
 
     e2e_graphs = capture_graphs(host_step, L)
 

@@ -65,6 +65,12 @@ extern "C" {
  * the start of the step and only read afterwards.  The scan then resolves its first work items (prefix sums,
  * block-table loads) while the earlier kernels drain instead of after them.                              */
 #define UCMR_FLAG_INPUTS_STABLE 0x100
+/* May be OR-ed in together with UCMR_FLAG_INPUTS_STABLE: of the code-cache blocks this call scans, the kernels that
+ * may still be in flight (same reading as above) write at most the block that holds the last token (seq_len - 1)
+ * of each request.  True for a decode step, where the only writer is the encode of the one new key per request.
+ * The scan then starts copying its first blocks - never a request's last one - before those kernels have finished;
+ * query codes are read and scores written only afterwards.  Ignored by the kernels that have no use for it.   */
+#define UCMR_FLAG_CACHE_APPEND_ONLY 0x200
 
 #define UCMR_MAX_MUST_SELECT 16
 #define UCMR_WORKSPACE_HEADER_BYTES 256

@@ -274,9 +274,66 @@ def test_inputs_stable_flag_changes_nothing_but_the_schedule(cuda_device):
     with pytest.raises(ValueError):
         codes, q, bt, sl = args
         rc = lib.load_library().ucmr_block_scores(codes.data_ptr(), codes.shape[0], BS, Hkv, W, q.data_ptr(), Hkv * G,
-                                                  bt.data_ptr(), mb, mb, sl.data_ptr(), B, 1 | 0x200, 0, s0.data_ptr(),
+                                                  bt.data_ptr(), mb, mb, sl.data_ptr(), B, 1 | 0x400, 0, s0.data_ptr(),
                                                   None, None)
         lib.check(rc, "ucmr_block_scores")
+
+
+@pytest.mark.parametrize("mode", ["min", "sum"])
+@pytest.mark.parametrize("BS,mb", [(128, 40), (16, 260), (64, 3)])
+def test_cache_append_only_scan_sees_the_new_token(cuda_device, mode, BS, mb):
+    """UCMR_FLAG_CACHE_APPEND_ONLY lets the scan copy blocks before the decode-step encode in front of it has finished,
+    except a request's last block.  Each step first poisons the slot of the newest token, then encodes a key equal to
+    the query (distance 0) into it and scans: the last block's score must come from the fresh code, stream-ordered
+    and as a replayed graph."""
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = cuda_device
+    B, Hkv, W, D = 5, 2, 4, 128
+    g = torch.Generator(device=dev)
+    g.manual_seed(77)
+    NB = B * mb
+    cache = torch.randint(-2**31, 2**31 - 1, (NB, BS, Hkv, W), dtype=torch.int32, device=dev, generator=g)
+    bt = torch.randperm(NB, device=dev, generator=g).to(torch.int32).view(B, mb).contiguous()
+    seq = torch.tensor([mb * BS, mb * BS - BS // 2, (mb - 1) * BS + 1, 5, max(1, mb // 2) * BS], dtype=torch.int32)
+    sl = seq.to(dev)
+    last = seq.to(torch.int64) - 1
+    slots = (bt.cpu()[torch.arange(B), last // BS].to(torch.int64) * BS + last % BS).to(dev)
+    R = (torch.randn((D, 32 * W), device=dev, generator=g) / D ** 0.5).to(torch.bfloat16)
+    k = min(4, mb)
+    ws = ops.new_workspace(B, Hkv, mb, dev)
+    qc = torch.empty((B, Hkv, W), dtype=torch.int32, device=dev)
+    out = ops.hamming_topk(cache, torch.zeros_like(qc), bt, sl, k, reduce=mode, workspace=ws)
+    flat = cache.view(NB * BS, Hkv, W)
+
+    def step(x):
+        ops.hash_encode_decode_step(x, x, slots, cache, R, q_codes_out=qc)
+        ops.hamming_topk(cache, qc, bt, sl, k, reduce=mode, workspace=ws, out=out, inputs_stable=True,
+                         cache_append_only=True)
+
+    def check(x):
+        torch.cuda.synchronize()
+        assert torch.equal(flat[slots], qc), "the new keys' codes equal the query codes"
+        ref = O.hamming_topk(cache.cpu().numpy().view(np.uint32), qc.cpu().numpy().view(np.uint32), bt.cpu().numpy(),
+                             seq.numpy(), k, MODES[mode], False)
+        _cmp(out, ref)
+        if mode == "min":   # the block with the new token has a token at distance 0
+            assert (out.scores.cpu().numpy() == 0).any(axis=2).all()
+
+    xs = [torch.randn((B, Hkv, D), device=dev, generator=g).to(torch.bfloat16) for _ in range(4)]
+    for x in xs:
+        flat[slots] = -1
+        step(x)
+        check(x)
+    x_static = xs[0].clone()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step(x_static)
+    for x in xs[1:]:
+        x_static.copy_(x)
+        flat[slots] = -1
+        graph.replay()
+        check(x)
 
 
 def test_selection_inside_the_scan_ragged_batch_repeated(cuda_device):

@@ -146,4 +146,8 @@ def test_reduce_mode_carries_the_inputs_stable_flag():
     assert ops._mode("min", False) == 0 and ops._mode("sum", False) == 1
     assert ops._mode("sum", True) == 1 | 0x100 and ops._mode("min", True) == 0x100
     with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "ucmr.h")) as f:
-        assert "#define UCMR_FLAG_INPUTS_STABLE 0x100" in f.read()
+        text = f.read()
+    assert "#define UCMR_FLAG_INPUTS_STABLE 0x100" in text and "#define UCMR_FLAG_CACHE_APPEND_ONLY 0x200" in text
+    assert ops._mode("sum", True, True) == 1 | 0x300
+    with pytest.raises(ValueError):
+        ops._mode("sum", False, True)

@@ -1216,7 +1216,7 @@ static bool step_simt_enabled()
 // tcgen05.ld round trips, dealloc), not on the math.  Here a warp owns one output row: the CTA stages R (32 KiB) in
 // shared memory with one round of 16-byte loads while every warp fetches its row (from device memory or, across the
 // bus, from page-locked host memory), then each lane accumulates four adjacent columns over the 128 inputs in float32
-// (x broadcast by shuffle, R read with one 8-byte shared-memory load per input) and the 128 sign bits are packed with
+// (x broadcast from shared memory, four inputs per load; R read with one 8-byte shared-memory load per input) and the 128 sign bits are packed with
 // three shuffle steps.  One memory round trip, about 1300 instructions per warp, one store.
 constexpr int kStepThreads = 256;
 constexpr int kStepRowsPerCta = kStepThreads / 32;
@@ -1224,6 +1224,7 @@ constexpr int kStepRowsPerCta = kStepThreads / 32;
 __global__ void __launch_bounds__(kStepThreads) encode_step_kernel(const TileParams p)
 {
     __shared__ __align__(16) __nv_bfloat16 s_r[kEncD * kEncBits];
+    __shared__ __align__(16) float s_x[kStepRowsPerCta][kEncD];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     grid_launch_dependents();  // a scan launched right after this kernel may set itself up meanwhile
     grid_dependency_wait();    // q and the new keys come from the kernel before this one
@@ -1267,18 +1268,31 @@ __global__ void __launch_bounds__(kStepThreads) encode_step_kernel(const TilePar
             for (int i = 0; i < 4; ++i) xv[i] = __bfloat162float(__float2bfloat16_rn(xv[i] / (float)jb.G));
         }
     }
+    // the row goes through shared memory: one 16-byte broadcast load then serves four inputs
+    reinterpret_cast<float4*>(s_x[warp])[lane] = make_float4(xv[0], xv[1], xv[2], xv[3]);
     __syncthreads();
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};  // columns 4*lane .. 4*lane+3
+    // columns 4*lane .. 4*lane+3, accumulated as two independent chains (even and odd groups of four inputs)
+    float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc_b[4] = {0.f, 0.f, 0.f, 0.f};
     const uint2* rcol = reinterpret_cast<const uint2*>(s_r) + lane;  // row k of R: 32 pieces of 4 columns
-#pragma unroll 8
-    for (int k = 0; k < kEncD; ++k) {
-        const float x = __shfl_sync(0xffffffffu, xv[k & 3], k >> 2);
-        const uint2 rr = rcol[k * (kEncBits / 4)];
-        acc[0] = fmaf(x, __uint_as_float(rr.x << 16), acc[0]);
-        acc[1] = fmaf(x, __uint_as_float(rr.x & 0xFFFF0000u), acc[1]);
-        acc[2] = fmaf(x, __uint_as_float(rr.y << 16), acc[2]);
-        acc[3] = fmaf(x, __uint_as_float(rr.y & 0xFFFF0000u), acc[3]);
+    const float4* xrow = reinterpret_cast<const float4*>(s_x[warp]);
+#pragma unroll 4
+    for (int k4 = 0; k4 < kEncD / 4; k4 += 2) {
+        const float4 xa = xrow[k4], xb = xrow[k4 + 1];
+        const float xs[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+        uint2 rr[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) rr[i] = rcol[(k4 * 4 + i) * (kEncBits / 4)];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float* a = i < 4 ? acc : acc_b;
+            a[0] = fmaf(xs[i], __uint_as_float(rr[i].x << 16), a[0]);
+            a[1] = fmaf(xs[i], __uint_as_float(rr[i].x & 0xFFFF0000u), a[1]);
+            a[2] = fmaf(xs[i], __uint_as_float(rr[i].y << 16), a[2]);
+            a[3] = fmaf(xs[i], __uint_as_float(rr[i].y & 0xFFFF0000u), a[3]);
+        }
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] += acc_b[i];
     // word w of the code = columns 32w .. 32w+31 = lanes 8w .. 8w+7, four bits each
     uint32_t nib = (uint32_t)(acc[0] > 0.f) | ((uint32_t)(acc[1] > 0.f) << 1) | ((uint32_t)(acc[2] > 0.f) << 2) |
                    ((uint32_t)(acc[3] > 0.f) << 3);

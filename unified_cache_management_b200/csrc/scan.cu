@@ -322,7 +322,7 @@ int run_scan(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, const ui
     if (!out) return UCMR_ERR_BAD_ARG;
     const int mode_flags = reduce_mode & ~0xFF;  // UCMR_FLAG_* bits travel with the mode
     reduce_mode &= 0xFF;
-    if (mode_flags & ~UCMR_FLAG_INPUTS_STABLE) return UCMR_ERR_BAD_ARG;
+    if (mode_flags & ~(UCMR_FLAG_INPUTS_STABLE | UCMR_FLAG_CACHE_APPEND_ONLY)) return UCMR_ERR_BAD_ARG;
     if (reduce_mode != UCMR_REDUCE_MIN && reduce_mode != UCMR_REDUCE_SUM) return UCMR_ERR_BAD_ARG;
     if (B == 0) return UCMR_OK;
 

@@ -75,6 +75,7 @@ struct RingParams {
     int stage_bytes;   // bps * block_stride
     int n_active;      // warps (= stages) in use: min(kRingWarps, ring bytes / stage bytes)
     int early_setup;   // UCMR_FLAG_INPUTS_STABLE: sequence lengths and block table may be read before the dependency wait
+    int early_loads;   // UCMR_FLAG_CACHE_APPEND_ONLY: code blocks other than a request's last one may be loaded before it too
     int small_blocks;  // sum mode, rows of 32 words, blocks of 16 or 32 tokens: lane <-> 16-byte piece of the row (see kernel)
     FusedSel sel;
 };
@@ -590,11 +591,16 @@ scan_ring_kernel(const RingParams p)
     int token = claim_start();
     // (early_setup) up to here only the sequence lengths and the block table were read; the code cache, the query
     // codes and the score buffer may still be in use by the kernel before this one
+    // (early_loads) the kernels still in flight only write the block that holds a request's newest token: the first
+    // item's copy starts now unless it contains that block, and travels while those kernels finish.  Everything else
+    // - query codes, score stores, the work counter - stays behind the wait.
+    const bool first_early = p.early_loads && cur.valid && (int64_t)(cur.j0 + p.bps) * p.BS < (int64_t)cur.seq;
+    if (first_early) issue(cur);
     if (p.early_setup) {
         grid_dependency_wait();
         if (fused && tid == 0) s_epoch = ld_acquire_gpu(p.sel.all_scored);  // (the kernel before this one may set it)
     }
-    issue(cur);
+    if (!first_early) issue(cur);
     mark_past_end();  // while the first block is on its way
     Item nxt = resolve(claim_finish(token));
     token = claim_start();
@@ -800,18 +806,18 @@ scan_ring_kernel(const RingParams p)
                 const int head = (piece * 4) / p.W, w0 = (piece * 4) % p.W;
                 uint32_t qv[4][G_T];  // [column of the piece][query head of the group]
                 while (cur.valid) {
-                    if (!mbar_wait(full, phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
-                    phase ^= 1u;
-                    const StageMeta m = s_meta[warp];
-                    if (m.b != cur_b) {
+                    if (cur.b != cur_b) {  // (before the wait: the query words travel while the block does)
 #pragma unroll
                         for (int g = 0; g < G_T; ++g) {
                             const uint4 v = __ldg(reinterpret_cast<const uint4*>(
-                                p.q + ((int64_t)m.b * p.Hq + head * G_T + g) * p.W + w0));
+                                p.q + ((int64_t)cur.b * p.Hq + head * G_T + g) * p.W + w0));
                             qv[0][g] = v.x; qv[1][g] = v.y; qv[2][g] = v.z; qv[3][g] = v.w;
                         }
-                        cur_b = m.b;
+                        cur_b = cur.b;
                     }
+                    if (!mbar_wait(full, phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
+                    phase ^= 1u;
+                    const StageMeta m = s_meta[warp];
                     int score[kBlocksPerLane];
                     int ntoks[kBlocksPerLane];
 #pragma unroll
@@ -893,7 +899,19 @@ scan_ring_kernel(const RingParams p)
         // passes' sets, wider rows reload per pass
         constexpr int QP = (RW_T == 64) ? 2 : 1;
         uint32_t qw[QP][GMAX];
+        const bool q_kept = passes <= QP;  // every pass has its own register set: loaded once per request
         while (cur.valid) {
+            if (q_kept && cur.b != cur_b) {  // (before the wait: the query words travel while the block does)
+#pragma unroll
+                for (int ps = 0; ps < QP; ++ps) {
+                    const int col = col0 + ps * 32;
+                    const int head = col / p.W, w = col - head * p.W;
+#pragma unroll
+                    for (int g = 0; g < GMAX; ++g)
+                        if (ps < passes && g < G) qw[ps][g] = __ldg(p.q + ((int64_t)cur.b * p.Hq + head * G + g) * p.W + w);
+                }
+                cur_b = cur.b;
+            }
             if (!mbar_wait(full, phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
             phase ^= 1u;
             const StageMeta m = s_meta[warp];
@@ -917,7 +935,7 @@ scan_ring_kernel(const RingParams p)
                 const int col = col0 + ps * 32;
                 const int head = col / p.W, w = col - head * p.W;
                 const int qs = (QP == 2) ? ps : 0;
-                if (m.b != cur_b || passes > QP) {
+                if (!q_kept) {
 #pragma unroll
                     for (int g = 0; g < GMAX; ++g)
                         if (g < G) qw[qs][g] = __ldg(p.q + ((int64_t)m.b * p.Hq + head * G + g) * p.W + w);
@@ -945,7 +963,6 @@ scan_ring_kernel(const RingParams p)
                     p.out[((int64_t)m.b * Hout + head) * p.max_blocks + j] = acc;
                 }
             }
-            cur_b = m.b;
             if (p.reduce_kvhead && have && col0 == 0) p.out[(int64_t)m.b * p.max_blocks + j] = total;
             if (!have && blk_e < p.bps && col0 == 0 && j < p.max_blocks) {
                 // block inside the stage but not loaded: past the request's end or a bad id
@@ -981,18 +998,12 @@ scan_ring_kernel(const RingParams p)
         uint4 cnt[kMuxPlanes], alt[kMuxPlanes];
         int mux_const = 0;
         while (cur.valid) {
-            if (!mbar_wait(full, phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
-            phase ^= 1u;
-            const StageMeta m = s_meta[warp];
-            const int j = m.j0 + blk;
-            const bool have = (m.valid_mask >> blk) & 1u;
-            const int ntok = have ? min(p.BS, m.seq - j * p.BS) : 0;
-            if (m.b != cur_b) {
-                const uint4* q4 = reinterpret_cast<const uint4*>(p.q) + ((int64_t)m.b * p.Hq + head * G) * PW + part;
+            if (cur.b != cur_b) {  // (before the wait: query words and planes are ready when the block lands)
+                const uint4* q4 = reinterpret_cast<const uint4*>(p.q) + ((int64_t)cur.b * p.Hq + head * G) * PW + part;
 #pragma unroll
                 for (int g = 0; g < GMAX; ++g)
                     if (g < G) qv[g] = __ldg(q4 + g * PW);
-                cur_b = m.b;
+                cur_b = cur.b;
                 if constexpr (G_T >= 2) {
                     uint32_t* cw = reinterpret_cast<uint32_t*>(cnt);
                     uint32_t* aw = reinterpret_cast<uint32_t*>(alt);
@@ -1025,6 +1036,12 @@ scan_ring_kernel(const RingParams p)
                     }
                 }
             }
+            if (!mbar_wait(full, phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
+            phase ^= 1u;
+            const StageMeta m = s_meta[warp];
+            const int j = m.j0 + blk;
+            const bool have = (m.valid_mask >> blk) & 1u;
+            const int ntok = have ? min(p.BS, m.seq - j * p.BS) : 0;
             const uint4* sb = reinterpret_cast<const uint4*>(stage + blk * p.block_stride);
             int best = INT_MAX;
             const int rounds = (p.BS + TS - 1) / TS;  // same trip count in every lane (shuffles inside)
@@ -1171,6 +1188,7 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
                   const FusedSel* fuse)
 {
     const bool inputs_stable = (reduce_mode & UCMR_FLAG_INPUTS_STABLE) != 0;
+    const bool append_only = (reduce_mode & UCMR_FLAG_CACHE_APPEND_ONLY) != 0;
     reduce_mode &= 0xFF;
     const int G = Hq / Hkv;
     const int64_t RW = (int64_t)Hkv * W;
@@ -1203,6 +1221,7 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     p.q = q; p.bt = bt; p.max_blocks = max_blocks; p.bt_stride = bt_stride; p.seq_lens = seq_lens; p.B = B;
     p.reduce_kvhead = reduce_kvhead ? 1 : 0; p.out = out; p.status = status; p.sched = sched;
     p.RW = (int)RW; p.bps = bps; p.block_bytes = (int)block_bytes; p.early_setup = inputs_stable ? 1 : 0;
+    p.early_loads = (inputs_stable && append_only) ? 1 : 0;
     // small blocks of full-width rows: the lane <-> row-piece mapping (W = 4 or 8, and a stage of exactly 8 or 4 blocks)
     p.small_blocks = (!row_mode && !is_min && RW == 32 && (W == 4 || W == 8) && (BS == 16 || BS == 32) &&
                       (G == 1 || G == 2 || G == 4 || G == 8) && bps == (BS == 16 ? 8 : 4) &&

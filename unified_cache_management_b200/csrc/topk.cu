@@ -32,6 +32,7 @@ constexpr int kSelThreads = 512;
 constexpr int kSelWarps = kSelThreads / 32;
 constexpr int kSelMaxCachedKeys = 40 * 1024;  // 160 KiB of keys in shared memory at most
 constexpr uint32_t kKeyInvalid = 0xFFFFFFFFu;
+constexpr int kSelInlineKeys = 8 * kSelThreads;  // rows (slices) up to this many keys apply the forced-block rule while loading
 // Rows longer than this are split over a thread-block cluster (2, 4 or 8 CTAs) when there are few enough rows.
 // Measured: a cluster launch costs about 2 us more than a plain one and large grids of clusters schedule
 // slowly, so shorter rows and launches of many rows stay with one CTA per row.
@@ -57,6 +58,7 @@ constexpr int kBinsPerThread = kBins / kSelThreads;
 struct SelScratch {
     int hist[3][kBins];  // one histogram per radix pass (keys have at most 32 bits: 3 passes of <= 11)
     int warp_a[kSelWarps], warp_b[kSelWarps];
+    uint32_t w_lo[kSelWarps], w_hi[kSelWarps];
     uint32_t prefix;
     int remaining;
     uint32_t kmin, kmax;  // range of the ordinary keys
@@ -113,9 +115,21 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
     n_cached = min(n_cached, len);
 
     for (int i = tid; i < 3 * kBins; i += kSelThreads) (&sc.hist[0][0])[i] = 0;
-    if (tid == 0) { sc.kmin = 0xFFFFFFFFu; sc.kmax = 0u; sc.n_zero = 0; sc.n_normal = 0; }
-    // keys into shared memory; the global loads of several entries are in flight together.  key_fast leaves
-    // out the forced-block rule, which fixup() then applies to the few entries it concerns.
+    const uint32_t key_top = key_bits >= 32 ? 0xFFFFFFFFu : (1u << key_bits) - 1u;  // "past the end" marker
+    // Range of the ordinary keys (neither 0 = forced nor key_top).  Block scores cluster in a narrow band,
+    // so radix digits are taken from (key - kmin): the histogram spreads over the band instead of piling
+    // onto a few bins of the top digit, and one pass usually pins the k-th key.
+    uint32_t r_lo = 0xFFFFFFFFu, r_hi = 0u;
+    int zeros = 0, normals = 0;
+    auto tally = [&](uint32_t key) {
+        if (key == 0u) ++zeros;
+        else if (key != key_top) { ++normals; r_lo = min(r_lo, key); r_hi = max(r_hi, key); }
+    };
+    // Keys into shared memory; the global loads of several entries are in flight together.  Rows of a few keys per
+    // thread apply every rule while loading (key) and take the range from the registers on the way: one barrier
+    // until the range is known.  Long rows use key_fast, which leaves out the forced-block rule; fixup() then applies
+    // it to the few entries it concerns, and the range comes from a pass over the cached keys.
+    const bool inline_rule = len <= kSelInlineKeys;
     constexpr int kU = 8;
     for (int i0 = tid; i0 < n_cached; i0 += kSelThreads * kU) {
         decltype(key_of.raw(0)) raw[kU];
@@ -127,60 +141,68 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
             const int i = i0 + u * kSelThreads;
-            if (i < n_cached) s_keys[i] = key_of.key_fast(j_lo + i, raw[u]);
+            if (i < n_cached) {
+                if (inline_rule) {
+                    const uint32_t key = key_of.key(j_lo + i, raw[u]);
+                    s_keys[i] = key;
+                    tally(key);
+                } else {
+                    s_keys[i] = key_of.key_fast(j_lo + i, raw[u]);
+                }
+            }
         }
     }
-    __syncthreads();
-    key_of.fixup(s_keys, j_lo, n_cached);
-    __syncthreads();
     auto get = [&](int j) -> uint32_t { return j - j_lo < n_cached ? s_keys[j - j_lo] : key_of.key(j, key_of.raw(j)); };
-    const uint32_t key_top = key_bits >= 32 ? 0xFFFFFFFFu : (1u << key_bits) - 1u;  // "past the end" marker
-
-    // Range of the ordinary keys (neither 0 = forced nor key_top).  Block scores cluster in a narrow band,
-    // so radix digits are taken from (key - kmin): the histogram spreads over the band instead of piling
-    // onto a few bins of the top digit, and one pass usually pins the k-th key.
-    {
-        uint32_t lo = 0xFFFFFFFFu, hi = 0u;
-        int zeros = 0, normals = 0;
-        for (int j = j_lo + tid; j < j_hi; j += kSelThreads) {
-            const uint32_t key = get(j);
-            if (key == 0u) ++zeros;
-            else if (key != key_top) { ++normals; lo = min(lo, key); hi = max(hi, key); }
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-            lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, off));
-            hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, off));
-            zeros += __shfl_xor_sync(0xffffffffu, zeros, off);
-            normals += __shfl_xor_sync(0xffffffffu, normals, off);
-        }
-        if (lane == 0) {
-            atomicMin(&sc.kmin, lo);
-            atomicMax(&sc.kmax, hi);
-            atomicAdd(&sc.n_zero, zeros);
-            atomicAdd(&sc.n_normal, normals);
-        }
+    if (inline_rule) {
+        for (int j = j_lo + n_cached + tid; j < j_hi; j += kSelThreads) tally(get(j));  // (keys beyond the cache)
+    } else {
+        __syncthreads();
+        key_of.fixup(s_keys, j_lo, n_cached);
+        __syncthreads();
+        for (int j = j_lo + tid; j < j_hi; j += kSelThreads) tally(get(j));
     }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        r_lo = min(r_lo, __shfl_xor_sync(0xffffffffu, r_lo, off));
+        r_hi = max(r_hi, __shfl_xor_sync(0xffffffffu, r_hi, off));
+        zeros += __shfl_xor_sync(0xffffffffu, zeros, off);
+        normals += __shfl_xor_sync(0xffffffffu, normals, off);
+    }
+    if (lane == 0) { sc.w_lo[warp] = r_lo; sc.w_hi[warp] = r_hi; sc.warp_a[warp] = zeros; sc.warp_b[warp] = normals; }
     __syncthreads();
-    int n_zero = sc.n_zero, n_normal = sc.n_normal;
-    uint32_t kmin = sc.kmin, kmax = sc.kmax;
+    // every warp folds the per-warp partials itself (no atomics, no second barrier)
+    static_assert(kSelWarps <= 32, "one lane per warp partial");
+    r_lo = lane < kSelWarps ? sc.w_lo[lane] : 0xFFFFFFFFu;
+    r_hi = lane < kSelWarps ? sc.w_hi[lane] : 0u;
+    zeros = lane < kSelWarps ? sc.warp_a[lane] : 0;
+    normals = lane < kSelWarps ? sc.warp_b[lane] : 0;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        r_lo = min(r_lo, __shfl_xor_sync(0xffffffffu, r_lo, off));
+        r_hi = max(r_hi, __shfl_xor_sync(0xffffffffu, r_hi, off));
+        zeros += __shfl_xor_sync(0xffffffffu, zeros, off);
+        normals += __shfl_xor_sync(0xffffffffu, normals, off);
+    }
+    int n_zero = zeros, n_normal = normals;
+    uint32_t kmin = r_lo, kmax = r_hi;
     if constexpr (CL) {
+        if (tid == 0) { sc.kmin = kmin; sc.kmax = kmax; sc.n_zero = n_zero; sc.n_normal = n_normal; }
         cluster_sync();
         if (warp == 0) {
             int z = 0, nn = 0;
-            uint32_t lo = 0xFFFFFFFFu, hi = 0u;
+            uint32_t glo = 0xFFFFFFFFu, ghi = 0u;
             if (lane < csize) {
                 const SelScratch* o = remote(lane);
-                z = o->n_zero; nn = o->n_normal; lo = o->kmin; hi = o->kmax;
+                z = o->n_zero; nn = o->n_normal; glo = o->kmin; ghi = o->kmax;
             }
 #pragma unroll
             for (int off = 4; off > 0; off >>= 1) {  // clusters have at most 8 CTAs
                 z += __shfl_xor_sync(0xffffffffu, z, off);
                 nn += __shfl_xor_sync(0xffffffffu, nn, off);
-                lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, off));
-                hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+                glo = min(glo, __shfl_xor_sync(0xffffffffu, glo, off));
+                ghi = max(ghi, __shfl_xor_sync(0xffffffffu, ghi, off));
             }
-            if (lane == 0) { sc.g_zero = z; sc.g_normal = nn; sc.g_kmin = lo; sc.g_kmax = hi; }
+            if (lane == 0) { sc.g_zero = z; sc.g_normal = nn; sc.g_kmin = glo; sc.g_kmax = ghi; }
         }
         __syncthreads();
         n_zero = sc.g_zero; n_normal = sc.g_normal; kmin = sc.g_kmin; kmax = sc.g_kmax;
@@ -194,13 +216,14 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
     } else {
         const uint32_t range = kmax - kmin;
         int hi = 32 - __clz(range | 1u);  // bits of (key - kmin) still undecided
-        if (tid == 0) { sc.prefix = 0u; sc.remaining = kb - n_zero; }
-        __syncthreads();
+        // every thread carries the decided prefix and the rank still to find; after a pass the one thread that
+        // found the bin publishes both through shared memory
+        uint32_t prefix = 0u;
+        int rem = kb - n_zero;
         for (int pass = 0; hi > 0; ++pass) {
             const int width = min(kDigitBits, hi);
             const int shift = hi - width;
             const uint32_t dmask = (1u << width) - 1u;
-            const uint32_t prefix = sc.prefix;
             int* hist = sc.hist[pass];
             const int len_round = (len + kSelThreads - 1) / kSelThreads * kSelThreads;
             for (int i = tid; i < len_round; i += kSelThreads) {
@@ -245,7 +268,6 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
                 if (lane >= off) incl += o;
             }
             if (lane == 31) sc.warp_a[warp] = incl;
-            const int rem = sc.remaining;
             __syncthreads();
             int excl = incl - sum;
             for (int w = 0; w < warp; ++w) excl += sc.warp_a[w];
@@ -262,9 +284,11 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
             }
             hi = shift;
             __syncthreads();
+            prefix = sc.prefix;
+            rem = sc.remaining;
         }
-        T = kmin + sc.prefix;
-        need = sc.remaining;  // how many keys equal to T are taken, lowest positions first
+        T = kmin + prefix;
+        need = rem;  // how many keys equal to T are taken, lowest positions first
     }
 
     const int ipt = (len + kSelThreads - 1) / kSelThreads;
@@ -429,22 +453,28 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
             if (p.out_scores) p.out_scores[obase + i] = pass ? (i < nb_l ? srow[i] : -1) : -1;
         }
     }
-    if (!CANDIDATES && lead && tid == 0 && row % p.Hout == 0) {
-        if (p.out_valid) p.out_valid[b] = min(kb, nb_l);
-        if (p.out_newseq) {
-            int ns = seq_l;
-            if (!masked) {
-                const int over = max(seq_l - kb * p.BS, 0);
-                ns = seq_l - (over + p.BS - 1) / p.BS * p.BS;
+    // per-request scalars: written at the end, so that nothing before the selection waits for the sequence length
+    auto write_scalars = [&]() {
+        if (!CANDIDATES && lead && tid == 0 && row % p.Hout == 0) {
+            if (p.out_valid) p.out_valid[b] = min(kb, nb_l);
+            if (p.out_newseq) {
+                int ns = seq_l;
+                if (!masked) {
+                    const int over = max(seq_l - kb * p.BS, 0);
+                    ns = seq_l - (over + p.BS - 1) / p.BS * p.BS;
+                }
+                p.out_newseq[b] = ns;
             }
-            p.out_newseq[b] = ns;
         }
-    }
+    };
     // Up to here only the sequence lengths and the block table were read and only outputs written: the scan
     // that produces the scores may still be running (programmatic dependent launch).
     grid_dependency_wait();
     if (blockIdx.x == 0 && tid == 0 && p.sched != nullptr) *p.sched = 0;
-    if (masked) return;
+    if (masked) {
+        write_scalars();
+        return;
+    }
     __syncthreads();  // padding stores precede the emits of the same CTA
 
     const uint32_t key_invalid = p.key_bits >= 32 ? kKeyInvalid : (1u << p.key_bits) - 1u;
@@ -453,7 +483,8 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         const int32_t* srow;
         int nb_l, nb_g, seq_g;
         uint32_t key_invalid;
-        __device__ int raw(int j) const { return j < nb_l ? srow[j] : -1; }
+        // (unconditional: j is below max_blocks, and the load then does not wait for the sequence length)
+        __device__ int raw(int j) const { return srow[j]; }
         __device__ uint32_t key_fast(int j, int s) const { return (j >= nb_l || s < 0) ? key_invalid : (uint32_t)s + 1u; }
         __device__ uint32_t key(int j, int s) const
         {
@@ -506,6 +537,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         }
     };
     select_row<CL>(n, kb, p.key_bits, key_of, emit, s_keys, p.n_cached, sc);
+    write_scalars();
     if (CANDIDATES && p.n_peers > 0) {
         // records are in the peers' memory: make them visible system-wide, then the last CTA of the launch
         // publishes the step number on every rank

@@ -351,6 +351,8 @@ class GSAOnDevice(UcmSparseBase):
     # ---- retrieval ---------------------------------------------------------------------------------
     # (inputs_stable in the retrieval calls: block table and lengths come from the step's attention metadata, built
     # before the forward pass; the kernel enqueued right before the scan is the query hashing, which writes neither)
+    # (cache_append_only in a decode-only step: the key hashing before the scan wrote one new token per request, which
+    # sits in the request's last block; a step with prefill chunks writes whole blocks and does not make the promise)
     def _forced(self):
         if self.use_must_select_blocks:
             return dict(must_select=tuple(self.gsa_on_device_config.must_select_blocks))
@@ -364,7 +366,8 @@ class GSAOnDevice(UcmSparseBase):
                             valid_count=self._retrieval.valid_count[:n], new_seq_lens=self._retrieval.new_seq_lens[:n])
         ops.hamming_topk(k_hash, q_hash, attn_metadata.block_table[:n], attn_metadata.seq_lens[:n], kb,
                          reduce=self.gsa_on_device_config.reduce, reduce_kvhead=self.num_key_heads > 1,
-                         workspace=self._workspace, out=out, want_scores=False, inputs_stable=True, **self._forced())
+                         workspace=self._workspace, out=out, want_scores=False, inputs_stable=True,
+                         cache_append_only=self.decode_only, **self._forced())
         block_table_decode = out.physical[:, 0, :]
         topk = kb
         if self.decode_only:

@@ -31,12 +31,18 @@ def reduce_mode(mode) -> int:
 
 
 FLAG_INPUTS_STABLE = 0x100  # UCMR_FLAG_INPUTS_STABLE
+FLAG_CACHE_APPEND_ONLY = 0x200  # UCMR_FLAG_CACHE_APPEND_ONLY
 
 
-def _mode(reduce, inputs_stable: bool) -> int:
-    """reduce mode with the caller's promise that seq_lens / block_table are not written by any kernel that may
-    still be in flight on the stream (lets the scan set itself up while earlier kernels drain)."""
-    return reduce_mode(reduce) | (FLAG_INPUTS_STABLE if inputs_stable else 0)
+def _mode(reduce, inputs_stable: bool, cache_append_only: bool = False) -> int:
+    """reduce mode with the caller's promises about kernels that may still be in flight on the stream:
+    inputs_stable - none of them writes seq_lens / block_table (the scan sets itself up while they drain);
+    cache_append_only (with inputs_stable) - of the code blocks scanned they write at most each request's last
+    block, as a decode step's key encode does (the scan starts copying its first blocks meanwhile)."""
+    if cache_append_only and not inputs_stable:
+        raise ValueError("cache_append_only needs inputs_stable")
+    return reduce_mode(reduce) | (FLAG_INPUTS_STABLE if inputs_stable else 0) | \
+        (FLAG_CACHE_APPEND_ONLY if cache_append_only else 0)
 
 
 def _stream(t: torch.Tensor) -> C.c_void_p:
@@ -327,7 +333,8 @@ def hamming_topk(codes: torch.Tensor, q_codes: torch.Tensor, block_table: torch.
                  k: int, *, reduce="sum", reduce_kvhead: bool = False, must_select: Sequence[int] = (),
                  sink_tokens: int = 0, recent_tokens: int = 0, k_per_request: Optional[torch.Tensor] = None,
                  request_mask: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
-                 out: Optional[Retrieval] = None, want_scores: bool = True, inputs_stable: bool = False) -> Retrieval:
+                 out: Optional[Retrieval] = None, want_scores: bool = True, inputs_stable: bool = False,
+                 cache_append_only: bool = False) -> Retrieval:
     """Scan + exact top-k in two launches.  See ``ucmr_hamming_topk`` in include/ucmr.h."""
     codes, q_codes, bt_stride = _scan_args(codes, q_codes, block_table, seq_lens)
     nb, bs, hkv, w = codes.shape
@@ -357,7 +364,8 @@ def hamming_topk(codes: torch.Tensor, q_codes: torch.Tensor, block_table: torch.
     lib = _l.load_library()
     _l.check(lib.ucmr_hamming_topk(
         _ptr(codes), nb, bs, hkv, w, _ptr(q_codes), hq, _ptr(block_table), mb, bt_stride, _ptr(seq_lens), b, k,
-        _ptr(k_per_request), _ptr(request_mask), _mode(reduce, inputs_stable), int(bool(reduce_kvhead)), must, n_must,
+        _ptr(k_per_request), _ptr(request_mask), _mode(reduce, inputs_stable, cache_append_only),
+        int(bool(reduce_kvhead)), must, n_must,
         int(sink_tokens), int(recent_tokens), _ptr(out.physical), _ptr(out.logical), _ptr(out.scores),
         _ptr(out.valid_count), _ptr(out.new_seq_lens), _ptr(workspace), workspace.numel(), _stream(codes)),
         "ucmr_hamming_topk")
@@ -394,7 +402,7 @@ def hamming_topk_static(codes: torch.Tensor, q_codes: torch.Tensor, block_table:
 
 def block_scores(codes, q_codes, block_table, seq_lens, *, reduce="sum", reduce_kvhead=False,
                  out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
-                 inputs_stable: bool = False) -> torch.Tensor:
+                 inputs_stable: bool = False, cache_append_only: bool = False) -> torch.Tensor:
     """int32 [B, Hout, max_blocks] block scores (-1 past each request's length)."""
     codes, q_codes, bt_stride = _scan_args(codes, q_codes, block_table, seq_lens)
     nb, bs, hkv, w = codes.shape
@@ -405,7 +413,8 @@ def block_scores(codes, q_codes, block_table, seq_lens, *, reduce="sum", reduce_
         out = torch.empty((b, hout, mb), dtype=torch.int32, device=codes.device)
     lib = _l.load_library()
     _l.check(lib.ucmr_block_scores(_ptr(codes), nb, bs, hkv, w, _ptr(q_codes), hq, _ptr(block_table), mb, bt_stride,
-                                   _ptr(seq_lens), b, _mode(reduce, inputs_stable), int(bool(reduce_kvhead)), _ptr(out),
+                                   _ptr(seq_lens), b, _mode(reduce, inputs_stable, cache_append_only),
+                                   int(bool(reduce_kvhead)), _ptr(out),
                                    _ptr(status), _stream(codes)), "ucmr_block_scores")
     return out
 
@@ -447,7 +456,8 @@ def update_seq_lens(seq_lens: torch.Tensor, topk_token: int, block_size: int) ->
 # ----------------------------------------------------------------------------------------------
 def topk_candidates(codes, q_codes, block_table, seq_lens_local, seq_lens_global, k: int, block_id_offset: int,
                     score_scale: float, *, reduce="sum", reduce_kvhead=False, must_select=(), sink_tokens=0,
-                    recent_tokens=0, workspace=None, out_scores=None, out_ids=None, inputs_stable: bool = False):
+                    recent_tokens=0, workspace=None, out_scores=None, out_ids=None, inputs_stable: bool = False,
+                    cache_append_only: bool = False):
     """Local top-k of one sequence shard as (float32 score, int32 global block id) records [B,Hout,k]."""
     codes, q_codes, bt_stride = _scan_args(codes, q_codes, block_table, seq_lens_local)
     _need_cuda("seq_lens_global", seq_lens_global, torch.int32)
@@ -468,7 +478,8 @@ def topk_candidates(codes, q_codes, block_table, seq_lens_local, seq_lens_global
     lib = _l.load_library()
     _l.check(lib.ucmr_topk_candidates(
         _ptr(codes), nb, bs, hkv, w, _ptr(q_codes), hq, _ptr(block_table), mb, bt_stride, _ptr(seq_lens_local),
-        _ptr(seq_lens_global), b, k, int(block_id_offset), float(score_scale), _mode(reduce, inputs_stable),
+        _ptr(seq_lens_global), b, k, int(block_id_offset), float(score_scale),
+        _mode(reduce, inputs_stable, cache_append_only),
         int(bool(reduce_kvhead)), must, n_must, int(sink_tokens), int(recent_tokens), _ptr(out_scores),
         _ptr(out_ids), _ptr(workspace), workspace.numel(), _stream(codes)), "ucmr_topk_candidates")
     return out_scores, out_ids
@@ -477,7 +488,8 @@ def topk_candidates(codes, q_codes, block_table, seq_lens_local, seq_lens_global
 def topk_candidates_p2p(codes, q_codes, block_table, seq_lens_local, seq_lens_global, k: int, block_id_offset: int,
                         score_scale: float, peer_scores_ptrs: Sequence[int], peer_ids_ptrs: Sequence[int],
                         peer_flag_ptrs: Sequence[int], seq: int, *, reduce="sum", reduce_kvhead=False, must_select=(),
-                        sink_tokens=0, recent_tokens=0, workspace=None, inputs_stable: bool = False) -> None:
+                        sink_tokens=0, recent_tokens=0, workspace=None, inputs_stable: bool = False,
+                        cache_append_only: bool = False) -> None:
     """``topk_candidates`` whose records go straight into every rank's gather buffer over peer memory: the three
     pointer lists hold, per rank r, the device address of THIS rank's [B,Hout,k] slice of rank r's score / id
     buffers and of this rank's flag word on rank r; ``seq`` is published to the flags when the launch is done."""
@@ -497,7 +509,8 @@ def topk_candidates_p2p(codes, q_codes, block_table, seq_lens_local, seq_lens_gl
     must, n_must = _must_array(must_select)
     _l.check(_l.load_library().ucmr_topk_candidates_p2p(
         _ptr(codes), nb, bs, hkv, w, _ptr(q_codes), hq, _ptr(block_table), mb, bt_stride, _ptr(seq_lens_local),
-        _ptr(seq_lens_global), b, k, int(block_id_offset), float(score_scale), _mode(reduce, inputs_stable),
+        _ptr(seq_lens_global), b, k, int(block_id_offset), float(score_scale),
+        _mode(reduce, inputs_stable, cache_append_only),
         int(bool(reduce_kvhead)), must, n_must, int(sink_tokens), int(recent_tokens),
         arr(*[int(p) for p in peer_scores_ptrs]), arr(*[int(p) for p in peer_ids_ptrs]),
         arr(*[int(p) for p in peer_flag_ptrs]), n, int(seq), _ptr(workspace), workspace.numel(), _stream(codes)),
@@ -529,7 +542,7 @@ def topk_candidates_p2p_step(codes, q_codes, block_table, seq_lens_local, seq_le
                              score_scale: float, peer_scores_ptrs: Sequence[int], peer_ids_ptrs: Sequence[int],
                              peer_flag_ptrs: Sequence[int], step_word: torch.Tensor, *, reduce="sum",
                              reduce_kvhead=False, must_select=(), sink_tokens=0, recent_tokens=0, workspace=None,
-                             inputs_stable: bool = False) -> None:
+                             inputs_stable: bool = False, cache_append_only: bool = False) -> None:
     """``topk_candidates_p2p`` whose step number is read on the device from ``step_word`` (int32, one element, this
     rank's memory): safe to capture in a CUDA graph and replay.  The pointer lists hold the ranks' pointers of buffer
     parity 0 followed by those of parity 1."""
@@ -550,7 +563,8 @@ def topk_candidates_p2p_step(codes, q_codes, block_table, seq_lens_local, seq_le
     must, n_must = _must_array(must_select)
     _l.check(_l.load_library().ucmr_topk_candidates_p2p_step(
         _ptr(codes), nb, bs, hkv, w, _ptr(q_codes), hq, _ptr(block_table), mb, bt_stride, _ptr(seq_lens_local),
-        _ptr(seq_lens_global), b, k, int(block_id_offset), float(score_scale), _mode(reduce, inputs_stable),
+        _ptr(seq_lens_global), b, k, int(block_id_offset), float(score_scale),
+        _mode(reduce, inputs_stable, cache_append_only),
         int(bool(reduce_kvhead)), must, n_must, int(sink_tokens), int(recent_tokens),
         arr(*[int(p) for p in peer_scores_ptrs]), arr(*[int(p) for p in peer_ids_ptrs]),
         arr(*[int(p) for p in peer_flag_ptrs]), n2 // 2, _ptr(step_word), _ptr(workspace), workspace.numel(),

@@ -51,7 +51,8 @@ def sharded_hamming_topk(codes_local, q_codes, block_table_local, seq_lens_globa
                          reduce_kvhead: bool = False, must_select: Sequence[int] = (), sink_tokens: int = 0,
                          recent_tokens: int = 0, workspace=None, gather_buffer: Optional[torch.Tensor] = None,
                          send_buffer: Optional[torch.Tensor] = None, plan: Optional[ShardPlan] = None,
-                         inputs_stable: bool = False, out_scores=None, out_ids=None,
+                         inputs_stable: bool = False, cache_append_only: bool = False, out_scores=None,
+                         out_ids=None,
                          candidates_fn: Callable = _default_candidates, merge_fn: Callable = _default_merge):
     """Returns (scores float32 [B,Hout,k], global logical block ids int32 [B,Hout,k]), identical on
     every rank.  block_table_local is this rank's slice [B, max_blocks_global/world] of the table.
@@ -67,6 +68,7 @@ def sharded_hamming_topk(codes_local, q_codes, block_table_local, seq_lens_globa
     extra = {}
     if candidates_fn is _default_candidates:
         extra["inputs_stable"] = inputs_stable
+        extra["cache_append_only"] = cache_append_only
     direct = send_buffer is not None and candidates_fn is _default_candidates
     if direct:
         extra.update(out_scores=send_buffer[0].view(torch.float32), out_ids=send_buffer[1])
@@ -156,6 +158,7 @@ def sharded_hamming_topk_p2p(codes_local, q_codes, block_table_local, seq_lens_g
                              reduce_kvhead: bool = False, must_select: Sequence[int] = (), sink_tokens: int = 0,
                              recent_tokens: int = 0, workspace=None, plan: Optional[ShardPlan] = None,
                              status: Optional[torch.Tensor] = None, inputs_stable: bool = False,
+                             cache_append_only: bool = False,
                              out_scores=None, out_ids=None):
     """``sharded_hamming_topk`` with the all-gather folded into the two kernels (see ``PeerExchange``): two launches
     per step and no collective call.  The step number is counted on the device, so the call may be captured in a
@@ -170,7 +173,8 @@ def sharded_hamming_topk_p2p(codes_local, q_codes, block_table_local, seq_lens_g
     ops.topk_candidates_p2p_step(codes_local, q_codes, block_table_local, plan.seq_lens_local, seq_lens_global, kl,
                                  plan.block_offset, score_scale, ps, pi, pf, exchange.state[0:1], reduce=reduce,
                                  reduce_kvhead=reduce_kvhead, must_select=must_select, sink_tokens=sink_tokens,
-                                 recent_tokens=recent_tokens, workspace=workspace, inputs_stable=inputs_stable)
+                                 recent_tokens=recent_tokens, workspace=workspace, inputs_stable=inputs_stable,
+                                 cache_append_only=cache_append_only)
     scores, ids, flags = exchange.views(0)
     return ops.merge_topk_wait_step(scores, ids, k, flags, exchange.words_per_parity, exchange.words_per_parity,
                                     exchange.state, status=status, out_scores=out_scores, out_ids=out_ids)
