@@ -18,6 +18,8 @@
 
 #include <cooperative_groups.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace ucmr {
@@ -58,7 +60,8 @@ constexpr int kBinsPerThread = kBins / kSelThreads;
 struct SelScratch {
     int hist[3][kBins];  // one histogram per radix pass (keys have at most 32 bits: 3 passes of <= 11)
     int warp_a[kSelWarps], warp_b[kSelWarps];
-    uint32_t w_lo[kSelWarps], w_hi[kSelWarps];
+    uint32_t w_lo[kSelWarps], w_hi[kSelWarps];  // per-warp partials of the key range ...
+    int w_zero[kSelWarps], w_norm[kSelWarps];   // ... and of the forced / ordinary key counts (written once)
     uint32_t prefix;
     int remaining;
     uint32_t kmin, kmax;  // range of the ordinary keys
@@ -88,6 +91,21 @@ struct SelScratch {
 // and every CTA derives the same threshold from that sum, so no result has to be broadcast.  A few very long
 // rows (sequence shards) would otherwise leave most SMs idle during the selection.
 // s_keys caches the first n_cached keys of the CTA's slice.
+// Per-warp totals w[0..kSelWarps) -> (sum of the totals of the warps before `warp`, sum of all), by a shuffle scan
+// over one lane per warp.  Called by whole warps.
+__device__ __forceinline__ int2 warp_exclusive(const int* w, int warp, int lane)
+{
+    static_assert(kSelWarps <= 32 && (kSelWarps & (kSelWarps - 1)) == 0, "one lane per warp total");
+    const int v = lane < kSelWarps ? w[lane] : 0;
+    int incl = v;
+#pragma unroll
+    for (int off = 1; off < kSelWarps; off <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += o;
+    }
+    return make_int2(__shfl_sync(0xffffffffu, incl - v, warp), __shfl_sync(0xffffffffu, incl, kSelWarps - 1));
+}
+
 template <bool CL, typename KeyFn, typename EmitFn>
 __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emit, uint32_t* s_keys, int n_cached,
                            SelScratch& sc)
@@ -114,7 +132,8 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
     const int len = j_hi - j_lo;
     n_cached = min(n_cached, len);
 
-    for (int i = tid; i < 3 * kBins; i += kSelThreads) (&sc.hist[0][0])[i] = 0;
+    // (the first pass's histogram; a later pass clears its own while the one before it runs)
+    for (int i = tid; i < kBins; i += kSelThreads) sc.hist[0][i] = 0;
     const uint32_t key_top = key_bits >= 32 ? 0xFFFFFFFFu : (1u << key_bits) - 1u;  // "past the end" marker
     // Range of the ordinary keys (neither 0 = forced nor key_top).  Block scores cluster in a narrow band,
     // so radix digits are taken from (key - kmin): the histogram spreads over the band instead of piling
@@ -130,28 +149,34 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
     // until the range is known.  Long rows use key_fast, which leaves out the forced-block rule; fixup() then applies
     // it to the few entries it concerns, and the range comes from a pass over the cached keys.
     const bool inline_rule = len <= kSelInlineKeys;
-    constexpr int kU = 8;
-    for (int i0 = tid; i0 < n_cached; i0 += kSelThreads * kU) {
-        decltype(key_of.raw(0)) raw[kU];
+    // (U loads in flight per thread; short rows take the narrow form: predicated-off copies of the body still cost
+    // issue slots, and a selection of a thousand keys is bound by those)
+    auto load_keys = [&](auto u_tag) {
+        constexpr int kU = decltype(u_tag)::value;
+        for (int i0 = tid; i0 < n_cached; i0 += kSelThreads * kU) {
+            decltype(key_of.raw(0)) raw[kU];
 #pragma unroll
-        for (int u = 0; u < kU; ++u) {
-            const int i = i0 + u * kSelThreads;
-            if (i < n_cached) raw[u] = key_of.raw(j_lo + i);
-        }
+            for (int u = 0; u < kU; ++u) {
+                const int i = i0 + u * kSelThreads;
+                if (i < n_cached) raw[u] = key_of.raw(j_lo + i);
+            }
 #pragma unroll
-        for (int u = 0; u < kU; ++u) {
-            const int i = i0 + u * kSelThreads;
-            if (i < n_cached) {
-                if (inline_rule) {
-                    const uint32_t key = key_of.key(j_lo + i, raw[u]);
-                    s_keys[i] = key;
-                    tally(key);
-                } else {
-                    s_keys[i] = key_of.key_fast(j_lo + i, raw[u]);
+            for (int u = 0; u < kU; ++u) {
+                const int i = i0 + u * kSelThreads;
+                if (i < n_cached) {
+                    if (inline_rule) {
+                        const uint32_t key = key_of.key(j_lo + i, raw[u]);
+                        s_keys[i] = key;
+                        tally(key);
+                    } else {
+                        s_keys[i] = key_of.key_fast(j_lo + i, raw[u]);
+                    }
                 }
             }
         }
-    }
+    };
+    if (n_cached <= 2 * kSelThreads) load_keys(std::integral_constant<int, 2>{});
+    else load_keys(std::integral_constant<int, 8>{});
     auto get = [&](int j) -> uint32_t { return j - j_lo < n_cached ? s_keys[j - j_lo] : key_of.key(j, key_of.raw(j)); };
     if (inline_rule) {
         for (int j = j_lo + n_cached + tid; j < j_hi; j += kSelThreads) tally(get(j));  // (keys beyond the cache)
@@ -161,28 +186,22 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
         __syncthreads();
         for (int j = j_lo + tid; j < j_hi; j += kSelThreads) tally(get(j));
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        r_lo = min(r_lo, __shfl_xor_sync(0xffffffffu, r_lo, off));
-        r_hi = max(r_hi, __shfl_xor_sync(0xffffffffu, r_hi, off));
-        zeros += __shfl_xor_sync(0xffffffffu, zeros, off);
-        normals += __shfl_xor_sync(0xffffffffu, normals, off);
-    }
-    if (lane == 0) { sc.w_lo[warp] = r_lo; sc.w_hi[warp] = r_hi; sc.warp_a[warp] = zeros; sc.warp_b[warp] = normals; }
+    r_lo = __reduce_min_sync(0xffffffffu, r_lo);
+    r_hi = __reduce_max_sync(0xffffffffu, r_hi);
+    zeros = __reduce_add_sync(0xffffffffu, zeros);
+    normals = __reduce_add_sync(0xffffffffu, normals);
+    if (lane == 0) { sc.w_lo[warp] = r_lo; sc.w_hi[warp] = r_hi; sc.w_zero[warp] = zeros; sc.w_norm[warp] = normals; }
     __syncthreads();
     // every warp folds the per-warp partials itself (no atomics, no second barrier)
     static_assert(kSelWarps <= 32, "one lane per warp partial");
     r_lo = lane < kSelWarps ? sc.w_lo[lane] : 0xFFFFFFFFu;
     r_hi = lane < kSelWarps ? sc.w_hi[lane] : 0u;
-    zeros = lane < kSelWarps ? sc.warp_a[lane] : 0;
-    normals = lane < kSelWarps ? sc.warp_b[lane] : 0;
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        r_lo = min(r_lo, __shfl_xor_sync(0xffffffffu, r_lo, off));
-        r_hi = max(r_hi, __shfl_xor_sync(0xffffffffu, r_hi, off));
-        zeros += __shfl_xor_sync(0xffffffffu, zeros, off);
-        normals += __shfl_xor_sync(0xffffffffu, normals, off);
-    }
+    zeros = lane < kSelWarps ? sc.w_zero[lane] : 0;
+    normals = lane < kSelWarps ? sc.w_norm[lane] : 0;
+    r_lo = __reduce_min_sync(0xffffffffu, r_lo);
+    r_hi = __reduce_max_sync(0xffffffffu, r_hi);
+    zeros = __reduce_add_sync(0xffffffffu, zeros);
+    normals = __reduce_add_sync(0xffffffffu, normals);
     int n_zero = zeros, n_normal = normals;
     uint32_t kmin = r_lo, kmax = r_hi;
     if constexpr (CL) {
@@ -225,6 +244,8 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
             const int shift = hi - width;
             const uint32_t dmask = (1u << width) - 1u;
             int* hist = sc.hist[pass];
+            if (shift > 0)  // another pass will follow: its histogram is cleared now (used two barriers from here)
+                for (int i = tid; i < kBins; i += kSelThreads) sc.hist[pass + 1][i] = 0;
             const int len_round = (len + kSelThreads - 1) / kSelThreads * kSelThreads;
             for (int i = tid; i < len_round; i += kSelThreads) {
                 const uint32_t key = i < len ? get(j_lo + i) : 0u;
@@ -269,8 +290,7 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
             }
             if (lane == 31) sc.warp_a[warp] = incl;
             __syncthreads();
-            int excl = incl - sum;
-            for (int w = 0; w < warp; ++w) excl += sc.warp_a[w];
+            int excl = incl - sum + warp_exclusive(sc.warp_a, warp, lane).x;
             if (rem > excl && rem <= excl + sum) {  // exactly one thread
                 int run = excl;
 #pragma unroll
@@ -308,12 +328,9 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
     }
     if (lane == 31) { sc.warp_a[warp] = lt_incl; sc.warp_b[warp] = eq_incl; }
     __syncthreads();
-    int lt_before = lt_incl - lt, eq_before = eq_incl - eq;
-    int cta_lt = 0, cta_eq = 0;
-    for (int w = 0; w < kSelWarps; ++w) {
-        if (w < warp) { lt_before += sc.warp_a[w]; eq_before += sc.warp_b[w]; }
-        cta_lt += sc.warp_a[w]; cta_eq += sc.warp_b[w];
-    }
+    const int2 wl = warp_exclusive(sc.warp_a, warp, lane), we = warp_exclusive(sc.warp_b, warp, lane);
+    int lt_before = lt_incl - lt + wl.x, eq_before = eq_incl - eq + we.x;
+    const int cta_lt = wl.y, cta_eq = we.y;
     // entries of the row that precede this CTA's slice
     int base_lt = 0, base_eq = 0;
     if constexpr (CL) {
