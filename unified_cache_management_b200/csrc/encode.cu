@@ -576,7 +576,9 @@ __global__ void __launch_bounds__(kTileThreads) encode_tile_kernel(const TilePar
 
     grid_launch_dependents();  // a scan launched right after this kernel may set itself up meanwhile
     const bool second = (int64_t)blockIdx.x >= p.job[0].tiles;
-    const TileJob& jb = p.job[second ? 1 : 0];
+    // (a copy picked with compile-time offsets: a run-time index into the kernel parameter would turn every field
+    // access into a load through a generic address, which is slow)
+    const TileJob jb = second ? p.job[1] : p.job[0];
     const int64_t tile = (int64_t)blockIdx.x - (second ? p.job[0].tiles : 0);
     const int H_out = jb.H_in / jb.G;
     const int64_t rows = jb.T * H_out;
@@ -1213,108 +1215,150 @@ static bool step_simt_enabled()
 // ---------------------------------------------------------------------------------------------
 // The two encodes of a decode step (B*Hq query rows, B*Hkv new key rows) are some 10 MFLOP: the tensor-core tile
 // kernel spends its time on the set-up chain around the MMA (TMEM allocation, swizzled staging, commit / wait, four
-// tcgen05.ld round trips, dealloc), not on the math.  Here a warp owns one output row: the CTA stages R (32 KiB) in
-// shared memory with one round of 16-byte loads while every warp fetches its row (from device memory or, across the
-// bus, from page-locked host memory), then each lane accumulates four adjacent columns over the 128 inputs in float32
-// (x broadcast from shared memory, four inputs per load; R read with one 8-byte shared-memory load per input) and the 128 sign bits are packed with
-// three shuffle steps.  One memory round trip, about 1300 instructions per warp, one store.
+// tcgen05.ld round trips, dealloc), not on the math, and a kernel of one warp per row is bound by that warp's
+// instruction stream (128 inputs x 4 columns per lane, about a thousand instructions on one scheduler).  Here four
+// warps share a row, each taking 32 of the 128 inputs: a lane fetches its warp's 32 rows of R straight into
+// registers (8 bytes per row: its four columns; no staging of R in shared memory) together with one input of the
+// row (from device memory or, across the bus, from page-locked host memory) - a single memory round trip - then
+// accumulates four columns over the warp's 32 inputs in float32 (inputs broadcast from shared memory, four per
+// load).  The four partial sums meet in shared memory; the row's first warp adds them, packs the 128 sign bits with
+// three shuffle steps and stores the code.
 constexpr int kStepThreads = 256;
-constexpr int kStepRowsPerCta = kStepThreads / 32;
+constexpr int kStepKSplit = 4;                                      // warps per row
+constexpr int kStepRowsPerRound = kStepThreads / 32 / kStepKSplit;  // 2 rows at a time
+constexpr int kStepKPerWarp = kEncD / kStepKSplit;                  // 32 inputs per warp
+static_assert(kStepKPerWarp == 32 && kEncBits == 128, "one input per lane, four columns per lane");
 
+// ROUNDS: row pairs a CTA works through with the same registers of R.  One round spreads a small step over as many
+// SMs as it has row pairs; four rounds keep a step of several hundred rows on about half of the SMs, so that the
+// scan launched behind it (whose CTAs need an SM to themselves) sets itself up on the others meanwhile.
+template <int ROUNDS>
 __global__ void __launch_bounds__(kStepThreads) encode_step_kernel(const TileParams p)
 {
-    __shared__ __align__(16) __nv_bfloat16 s_r[kEncD * kEncBits];
-    __shared__ __align__(16) float s_x[kStepRowsPerCta][kEncD];
+    constexpr int kRowsPerCta = kStepRowsPerRound * ROUNDS;
+    __shared__ __align__(16) float s_x[ROUNDS][kStepRowsPerRound][kEncD];
+    __shared__ __align__(16) float s_part[ROUNDS][kStepRowsPerRound][kStepKSplit][kEncBits];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r_in = warp / kStepKSplit, ks = warp % kStepKSplit, k0 = ks * kStepKPerWarp;
     grid_launch_dependents();  // a scan launched right after this kernel may set itself up meanwhile
     grid_dependency_wait();    // q and the new keys come from the kernel before this one
-    // R: 2048 16-byte chunks over 256 threads, all loads in flight before the first store
+    // rows k0 .. k0+31 of R, columns 4*lane .. 4*lane+3: 32 independent 8-byte loads per lane
+    uint2 rr[kStepKPerWarp];
     {
-        uint4 v[8];
-        const uint4* src = reinterpret_cast<const uint4*>(p.R);
+        const uint2* src = reinterpret_cast<const uint2*>(p.R) + (int64_t)k0 * (kEncBits / 4) + lane;
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = __ldg(src + tid + u * kStepThreads);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) reinterpret_cast<uint4*>(s_r)[tid + u * kStepThreads] = v[u];
+        for (int i = 0; i < kStepKPerWarp; ++i) rr[i] = __ldg(src + i * (kEncBits / 4));
     }
-    // this warp's row: job 0 rows first, then job 1
+    // job 0 rows first, then job 1
     const int H_out0 = p.job[0].H_in / p.job[0].G, H_out1 = p.job[1].x ? p.job[1].H_in / p.job[1].G : 1;
-    const int64_t rows0 = p.job[0].T * H_out0, rows1 = p.job[1].x ? p.job[1].T * H_out1 : 0;
-    int64_t row = (int64_t)blockIdx.x * kStepRowsPerCta + warp;
-    const bool second = row >= rows0;
-    if (second) row -= rows0;
-    const TileJob& jb = p.job[second ? 1 : 0];
-    const int H_out = second ? H_out1 : H_out0;
-    const bool live = row < (second ? rows1 : rows0);
-    float xv[4] = {0.f, 0.f, 0.f, 0.f};  // inputs 4*lane .. 4*lane+3 of the row
-    int64_t slot = -1;
-    int64_t tok = 0;
-    int ho = 0;
-    if (live) {
-        tok = row / H_out;
-        ho = (int)(row - tok * H_out);
-        const __nv_bfloat16* src = jb.x + tok * jb.stride_t + (int64_t)ho * jb.G * jb.stride_h + 4 * lane;
-        if (jb.slot_mapping != nullptr)
-            slot = jb.slot_is_int64 ? static_cast<const int64_t*>(jb.slot_mapping)[tok]
-                                    : (int64_t) static_cast<const int32_t*>(jb.slot_mapping)[tok];
-        for (int g = 0; g < jb.G; ++g) {
-            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)g * jb.stride_h));
-            const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
+    // (the launch is limited to kStepMaxRows rows: 32-bit arithmetic, whose division costs a tenth of the 64-bit one)
+    const int rows0 = (int)p.job[0].T * H_out0, rows1 = p.job[1].x ? (int)p.job[1].T * H_out1 : 0;
+    // Where a row comes from and goes to.  (Fields picked with compile-time offsets: a run-time index into the
+    // kernel parameter would turn every access into a load through a generic address, which is slow.)
+    struct RowRef { bool live; int row, tok, ho, H_out; };
+    auto locate = [&](int it, bool& second) -> RowRef {
+        RowRef r;
+        r.row = (int)blockIdx.x * kRowsPerCta + it * kStepRowsPerRound + r_in;
+        second = r.row >= rows0;
+        if (second) r.row -= rows0;
+        r.H_out = second ? H_out1 : H_out0;
+        r.live = r.row < (second ? rows1 : rows0);
+        r.tok = r.live ? r.row / r.H_out : 0;
+        r.ho = r.row - r.tok * r.H_out;
+        return r;
+    };
+    // input k0 + lane of each of this warp's rows.  Addresses first, then the loads of all rounds back to back (a
+    // load placed behind the previous round's branch and store would wait for that round's memory round trip).
+    const __nv_bfloat16* xsrc[ROUNDS];
+    int64_t xstride[ROUNDS];
+    int xg[ROUNDS];
+    int g_max = 0;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) xv[i] += __bfloat162float(e[i]);
-        }
-        if (jb.G > 1) {  // the group mean, rounded once to bf16 as torch's mean of a bf16 tensor is
-#pragma unroll
-            for (int i = 0; i < 4; ++i) xv[i] = __bfloat162float(__float2bfloat16_rn(xv[i] / (float)jb.G));
-        }
+    for (int it = 0; it < ROUNDS; ++it) {
+        bool second;
+        const RowRef r = locate(it, second);
+        const TileJob jb = second ? p.job[1] : p.job[0];
+        xg[it] = r.live ? jb.G : 0;
+        xstride[it] = jb.stride_h;
+        xsrc[it] = jb.x;
+        if (r.live) xsrc[it] += (int64_t)r.tok * jb.stride_t + (int64_t)r.ho * jb.G * jb.stride_h + k0 + lane;
+        g_max = max(g_max, xg[it]);
     }
-    // the row goes through shared memory: one 16-byte broadcast load then serves four inputs
-    reinterpret_cast<float4*>(s_x[warp])[lane] = make_float4(xv[0], xv[1], xv[2], xv[3]);
+    float xv[ROUNDS];
+#pragma unroll
+    for (int it = 0; it < ROUNDS; ++it) xv[it] = 0.f;
+    for (int g = 0; g < g_max; ++g) {
+        __nv_bfloat16 e[ROUNDS];
+#pragma unroll
+        for (int it = 0; it < ROUNDS; ++it)
+            e[it] = g < xg[it] ? __ldg(xsrc[it] + (int64_t)g * xstride[it]) : __float2bfloat16(0.f);
+#pragma unroll
+        for (int it = 0; it < ROUNDS; ++it) xv[it] += __bfloat162float(e[it]);
+    }
+#pragma unroll
+    for (int it = 0; it < ROUNDS; ++it) {
+        // the group mean, rounded once to bf16 as torch's mean of a bf16 tensor is
+        if (xg[it] > 1) xv[it] = __bfloat162float(__float2bfloat16_rn(xv[it] / (float)xg[it]));
+        s_x[it][r_in][k0 + lane] = xv[it];
+    }
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < ROUNDS; ++it) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};  // columns 4*lane .. 4*lane+3 over this warp's inputs
+        const float4* xrow = reinterpret_cast<const float4*>(&s_x[it][r_in][k0]);
+#pragma unroll
+        for (int i4 = 0; i4 < kStepKPerWarp / 4; ++i4) {
+            const float4 x4 = xrow[i4];
+            const float xs[4] = {x4.x, x4.y, x4.z, x4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint2 r = rr[i4 * 4 + i];
+                acc[0] = fmaf(xs[i], __uint_as_float(r.x << 16), acc[0]);
+                acc[1] = fmaf(xs[i], __uint_as_float(r.x & 0xFFFF0000u), acc[1]);
+                acc[2] = fmaf(xs[i], __uint_as_float(r.y << 16), acc[2]);
+                acc[3] = fmaf(xs[i], __uint_as_float(r.y & 0xFFFF0000u), acc[3]);
+            }
+        }
+        reinterpret_cast<float4*>(s_part[it][r_in][ks])[lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    }
     __syncthreads();
-    // columns 4*lane .. 4*lane+3, accumulated as two independent chains (even and odd groups of four inputs)
-    float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc_b[4] = {0.f, 0.f, 0.f, 0.f};
-    const uint2* rcol = reinterpret_cast<const uint2*>(s_r) + lane;  // row k of R: 32 pieces of 4 columns
-    const float4* xrow = reinterpret_cast<const float4*>(s_x[warp]);
-#pragma unroll 4
-    for (int k4 = 0; k4 < kEncD / 4; k4 += 2) {
-        const float4 xa = xrow[k4], xb = xrow[k4 + 1];
-        const float xs[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-        uint2 rr[8];
+    // warp ks of a row pair finishes rounds ks, ks + 4, ...: adds the four partial sums, packs, stores
+    for (int it = ks; it < ROUNDS; it += kStepKSplit) {
+        float4 a = reinterpret_cast<const float4*>(s_part[it][r_in][0])[lane];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) rr[i] = rcol[(k4 * 4 + i) * (kEncBits / 4)];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            float* a = i < 4 ? acc : acc_b;
-            a[0] = fmaf(xs[i], __uint_as_float(rr[i].x << 16), a[0]);
-            a[1] = fmaf(xs[i], __uint_as_float(rr[i].x & 0xFFFF0000u), a[1]);
-            a[2] = fmaf(xs[i], __uint_as_float(rr[i].y << 16), a[2]);
-            a[3] = fmaf(xs[i], __uint_as_float(rr[i].y & 0xFFFF0000u), a[3]);
+        for (int w = 1; w < kStepKSplit; ++w) {
+            const float4 o = reinterpret_cast<const float4*>(s_part[it][r_in][w])[lane];
+            a.x += o.x; a.y += o.y; a.z += o.z; a.w += o.w;
         }
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[i] += acc_b[i];
-    // word w of the code = columns 32w .. 32w+31 = lanes 8w .. 8w+7, four bits each
-    uint32_t nib = (uint32_t)(acc[0] > 0.f) | ((uint32_t)(acc[1] > 0.f) << 1) | ((uint32_t)(acc[2] > 0.f) << 2) |
-                   ((uint32_t)(acc[3] > 0.f) << 3);
-    uint32_t word = nib << (4 * (lane & 7));
-    word |= __shfl_xor_sync(0xffffffffu, word, 1);
-    word |= __shfl_xor_sync(0xffffffffu, word, 2);
-    word |= __shfl_xor_sync(0xffffffffu, word, 4);
-    // lanes 0, 8, 16, 24 hold words 0..3: gather them into lane 0
-    const uint32_t w1 = __shfl_sync(0xffffffffu, word, 8), w2 = __shfl_sync(0xffffffffu, word, 16),
-                   w3 = __shfl_sync(0xffffffffu, word, 24);
-    if (live && lane == 0) {
-        const uint4 code = make_uint4(word, w1, w2, w3);
-        if (jb.slot_mapping == nullptr) {
-            *reinterpret_cast<uint4*>(jb.out + row * 4) = code;
-        } else if (slot >= 0 && slot < jb.n_slots) {
-            *reinterpret_cast<uint4*>(jb.out + (slot * H_out + ho) * 4) = code;
+        // word w of the code = columns 32w .. 32w+31 = lanes 8w .. 8w+7, four bits each
+        const uint32_t nib = (uint32_t)(a.x > 0.f) | ((uint32_t)(a.y > 0.f) << 1) | ((uint32_t)(a.z > 0.f) << 2) |
+                             ((uint32_t)(a.w > 0.f) << 3);
+        uint32_t word = nib << (4 * (lane & 7));
+        word |= __shfl_xor_sync(0xffffffffu, word, 1);
+        word |= __shfl_xor_sync(0xffffffffu, word, 2);
+        word |= __shfl_xor_sync(0xffffffffu, word, 4);
+        // lanes 0, 8, 16, 24 hold words 0..3: gather them into lane 0
+        const uint32_t w1 = __shfl_sync(0xffffffffu, word, 8), w2 = __shfl_sync(0xffffffffu, word, 16),
+                       w3 = __shfl_sync(0xffffffffu, word, 24);
+        bool second;
+        const RowRef r = locate(it, second);
+        if (r.live && lane == 0) {
+            const TileJob jb = second ? p.job[1] : p.job[0];
+            const uint4 code = make_uint4(word, w1, w2, w3);
+            if (jb.slot_mapping == nullptr) {
+                *reinterpret_cast<uint4*>(jb.out + (int64_t)r.row * 4) = code;
+            } else {
+                const int64_t slot = jb.slot_is_int64 ? static_cast<const int64_t*>(jb.slot_mapping)[r.tok]
+                                                      : (int64_t) static_cast<const int32_t*>(jb.slot_mapping)[r.tok];
+                if (slot >= 0 && slot < jb.n_slots)
+                    *reinterpret_cast<uint4*>(jb.out + (slot * r.H_out + r.ho) * 4) = code;
+            }
         }
     }
 }
 
 // Rows of a decode step up to which the CUDA-core kernel is used (beyond it the tensor-core tiles win).
-constexpr int64_t kStepMaxRows = 4096;
+constexpr int64_t kStepMaxRows = 2048;
 
 static int launch_step(const TileJob& jq, const TileJob& jk, const void* R, int32_t* status, cudaStream_t st)
 {
@@ -1324,9 +1368,16 @@ static int launch_step(const TileJob& jq, const TileJob& jk, const void* R, int3
     p.R = static_cast<const __nv_bfloat16*>(R);
     p.status = status;
     const int64_t rows = jq.T * (jq.H_in / jq.G) + jk.T * (jk.H_in / jk.G);
-    const int64_t grid = (rows + kStepRowsPerCta - 1) / kStepRowsPerCta;
-    if (grid <= 0) return UCMR_OK;
-    return launch_kernel_ex(encode_step_kernel, dim3((unsigned)grid), dim3(kStepThreads), 0, st, 1, true, p);
+    if (rows <= 0) return UCMR_OK;
+    // up to 74 row pairs (half of the SMs): one pair per CTA; more: four pairs per CTA
+    constexpr int64_t kSpreadRows = 74 * kStepRowsPerRound;
+    if (rows <= kSpreadRows) {
+        const int64_t grid = (rows + kStepRowsPerRound - 1) / kStepRowsPerRound;
+        return launch_kernel_ex(encode_step_kernel<1>, dim3((unsigned)grid), dim3(kStepThreads), 0, st, 1, true, p);
+    }
+    const int64_t per_cta = kStepRowsPerRound * 4;
+    const int64_t grid = (rows + per_cta - 1) / per_cta;
+    return launch_kernel_ex(encode_step_kernel<4>, dim3((unsigned)grid), dim3(kStepThreads), 0, st, 1, true, p);
 }
 
 extern "C" int ucmr_hash_encode_decode_step(const void* q, int64_t Tq, int Hq, int64_t q_stride_t, int64_t q_stride_h,

@@ -60,8 +60,9 @@ struct GatherLocator {
         const int64_t left = p.block_bytes - off;
         bytes = (uint32_t)(left < kGatherChunk ? left : kGatherChunk);
         if (phys < 0 || phys >= p.NB) return false;
-        src = p.pool[which] + (int64_t)phys * p.block_bytes + off;
-        dst = p.out[which] + s * p.block_bytes + off;
+        // (picked with compile-time offsets: a run-time index into the kernel parameter means generic-address loads)
+        src = (which ? p.pool[1] : p.pool[0]) + (int64_t)phys * p.block_bytes + off;
+        dst = (which ? p.out[1] : p.out[0]) + s * p.block_bytes + off;
         return true;
     }
     __device__ int32_t* status() const { return p.status; }
@@ -216,12 +217,16 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const GatherRowsParams
                 continue;
             }
             const int64_t srci = (((int64_t)phys * p.BS + t) * p.Hkv + h) * p.u4_per_row + piece;
-            for (int w = 0; w < p.n_pools; ++w) v[w][u] = ld_stream_u4(p.pool[w] + srci);
+#pragma unroll
+            for (int w = 0; w < 2; ++w)  // (compile-time pool index, see GatherLocator)
+                if (w < p.n_pools) v[w][u] = ld_stream_u4(p.pool[w] + srci);
         }
 #pragma unroll
         for (int u = 0; u < UN; ++u) {
             if (!ok[u]) continue;
-            for (int w = 0; w < p.n_pools; ++w) st_stream_u4(p.out[w] + dsti[u], v[w][u]);
+#pragma unroll
+            for (int w = 0; w < 2; ++w)
+                if (w < p.n_pools) st_stream_u4(p.out[w] + dsti[u], v[w][u]);
         }
     }
 }

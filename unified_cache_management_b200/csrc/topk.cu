@@ -151,6 +151,9 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
     const bool inline_rule = len <= kSelInlineKeys;
     // (U loads in flight per thread; short rows take the narrow form: predicated-off copies of the body still cost
     // issue slots, and a selection of a thousand keys is bound by those)
+    // (inline_rule) what the thread needs to apply the rules to its keys tid, tid + kSelThreads, ... of the cached
+    // slice without walking a list per key
+    const auto ctx = key_of.thread_ctx(j_lo, inline_rule ? n_cached : 0, tid);
     auto load_keys = [&](auto u_tag) {
         constexpr int kU = decltype(u_tag)::value;
         for (int i0 = tid; i0 < n_cached; i0 += kSelThreads * kU) {
@@ -165,7 +168,7 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
                 const int i = i0 + u * kSelThreads;
                 if (i < n_cached) {
                     if (inline_rule) {
-                        const uint32_t key = key_of.key(j_lo + i, raw[u]);
+                        const uint32_t key = key_of.key_ctx(j_lo + i, raw[u], i / kSelThreads, ctx);
                         s_keys[i] = key;
                         tally(key);
                     } else {
@@ -176,6 +179,7 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
         }
     };
     if (n_cached <= 2 * kSelThreads) load_keys(std::integral_constant<int, 2>{});
+    else if (n_cached <= 4 * kSelThreads) load_keys(std::integral_constant<int, 4>{});
     else load_keys(std::integral_constant<int, 8>{});
     auto get = [&](int j) -> uint32_t { return j - j_lo < n_cached ? s_keys[j - j_lo] : key_of.key(j, key_of.raw(j)); };
     if (inline_rule) {
@@ -426,7 +430,12 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
 {
     extern __shared__ uint32_t s_keys[];
     __shared__ SelScratch sc;
+    // The forced-block rule walks its list with a run-time index.  On the kernel parameter that means loads through
+    // a generic address into parameter space - measured at about a microsecond per selection - so the rule reads a
+    // shared-memory copy (made with compile-time offsets, published by the barrier before the selection).
+    __shared__ ForcedSpec s_forced;
     const int tid = threadIdx.x;
+    if (tid == 0) s_forced = p.forced;
     const int row = CL ? blockIdx.x / p.cluster : blockIdx.x;
     const bool lead = !CL || blockIdx.x % p.cluster == 0;  // the CTA that writes the row's padding and scalars
     const int b = row / p.Hout;
@@ -447,8 +456,23 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         step_no = *p.step_word + 1;
         par = step_no & 1;
     }
-    float* const* const peer_scores = p.peer_scores[par];
-    int32_t* const* const peer_ids = p.peer_ids[par];
+    // the pointer set of this parity, in shared memory for the same reason as the forced-block list
+    __shared__ float* s_peer_scores[kMaxPeers];
+    __shared__ int32_t* s_peer_ids[kMaxPeers];
+    __shared__ int32_t* s_peer_flags[kMaxPeers];
+    if (CANDIDATES && p.n_peers > 0) {
+        if (tid == 0) {
+#pragma unroll
+            for (int r = 0; r < kMaxPeers; ++r) {
+                s_peer_scores[r] = par ? p.peer_scores[1][r] : p.peer_scores[0][r];
+                s_peer_ids[r] = par ? p.peer_ids[1][r] : p.peer_ids[0][r];
+                s_peer_flags[r] = par ? p.peer_flags[1][r] : p.peer_flags[0][r];
+            }
+        }
+        __syncthreads();
+    }
+    float* const* const peer_scores = s_peer_scores;
+    int32_t* const* const peer_ids = s_peer_ids;
 
     if (masked) grid_dependency_wait();  // pass-through rows copy scores below
     // padding first; the chosen entries overwrite positions [0, kb) (in a cluster: after its first barrier)
@@ -495,10 +519,12 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     __syncthreads();  // padding stores precede the emits of the same CTA
 
     const uint32_t key_invalid = p.key_bits >= 32 ? kKeyInvalid : (1u << p.key_bits) - 1u;
+    // (the functors below hold copies of what they need, never a reference to the kernel parameter: reached through
+    // a reference that the compiler does not fold away, every field is a load through a generic address)
     struct KeyOf {
-        const SelectParams& p;
+        const ForcedSpec& forced;
         const int32_t* srow;
-        int nb_l, nb_g, seq_g;
+        int nb_l, nb_g, seq_g, id_offset, BS;
         uint32_t key_invalid;
         // (unconditional: j is below max_blocks, and the load then does not wait for the sequence length)
         __device__ int raw(int j) const { return srow[j]; }
@@ -506,15 +532,40 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         __device__ uint32_t key(int j, int s) const
         {
             if (j >= nb_l || s < 0) return key_invalid;
-            if (block_is_forced(p.forced, j + p.id_offset, nb_g, seq_g, p.BS)) return 0u;
+            if (block_is_forced(forced, j + id_offset, nb_g, seq_g, BS)) return 0u;
             return (uint32_t)s + 1u;
+        }
+        // Rows of a few keys per thread: bit t of the context says that the thread's t-th cached key (index tid +
+        // t * kSelThreads of the slice) is a listed must-select block, so the list is walked once per thread
+        // instead of once per key; sink and recent window are two comparisons.
+        __device__ uint32_t thread_ctx(int j_lo, int n_cached, int tid) const
+        {
+            static_assert(kSelInlineKeys <= 32 * kSelThreads, "one context bit per key of the thread");
+            uint32_t mask = 0u;
+            if (n_cached == 0) return mask;
+            for (int m = 0; m < forced.n_must; ++m) {
+                const int jg = forced.must[m] >= 0 ? forced.must[m] : nb_g + forced.must[m];
+                const int c = jg - id_offset - j_lo;
+                if (jg >= 0 && jg < nb_g && c >= 0 && c < n_cached && c % kSelThreads == tid) mask |= 1u << (c / kSelThreads);
+            }
+            return mask;
+        }
+        __device__ uint32_t key_ctx(int j, int s, int t, uint32_t ctx) const
+        {
+            if (j >= nb_l || s < 0) return key_invalid;
+            const int jg = j + id_offset;
+            if (jg >= nb_g) return (uint32_t)s + 1u;
+            const int lo = jg * BS, hi = min(lo + BS, seq_g);
+            const bool f = ((ctx >> t) & 1u) || (forced.sink > 0 && lo < forced.sink) ||
+                           (forced.recent > 0 && hi > seq_g - forced.recent);
+            return f ? 0u : (uint32_t)s + 1u;
         }
         // Forced blocks are few: the listed ones, the first blocks (sink) and the last ones (recent window).
         __device__ void fixup(uint32_t* s_keys, int j_lo, int n_cached) const
         {
-            const ForcedSpec& f = p.forced;
-            const int n_sink = f.sink > 0 ? min(nb_g, (f.sink + p.BS - 1) / p.BS) : 0;
-            const int first_recent = f.recent > 0 ? max(0, (seq_g - f.recent) / p.BS) : nb_g;
+            const ForcedSpec& f = forced;
+            const int n_sink = f.sink > 0 ? min(nb_g, (f.sink + BS - 1) / BS) : 0;
+            const int first_recent = f.recent > 0 ? max(0, (seq_g - f.recent) / BS) : nb_g;
             const int n_recent = max(0, nb_g - first_recent);
             const int total = f.n_must + n_sink + n_recent;
             for (int i = threadIdx.x; i < total; i += blockDim.x) {
@@ -522,35 +573,43 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
                 if (i < f.n_must) jg = f.must[i] >= 0 ? f.must[i] : nb_g + f.must[i];
                 else if (i < f.n_must + n_sink) jg = i - f.n_must;
                 else jg = first_recent + (i - f.n_must - n_sink);
-                const int j = jg - p.id_offset;
+                const int j = jg - id_offset;
                 const int c = j - j_lo;  // index in this CTA's cached slice
                 if (jg >= 0 && jg < nb_g && j >= 0 && j < nb_l && c >= 0 && c < n_cached && s_keys[c] != key_invalid &&
-                    block_is_forced(f, jg, nb_g, seq_g, p.BS))
+                    block_is_forced(f, jg, nb_g, seq_g, BS))
                     s_keys[c] = 0u;
             }
         }
     };
-    const KeyOf key_of{p, srow, nb_l, nb_g, seq_g, key_invalid};
-    auto emit = [&](int pos, int j) {
+    const int id_offset = p.id_offset, BS = p.BS, n_peers = p.n_peers;
+    const float scale = p.scale;
+    float* const cand_scores = p.cand_scores;
+    int32_t* const cand_ids = p.cand_ids;
+    int32_t* const out_phys = p.out_phys;
+    int32_t* const out_logical = p.out_logical;
+    int32_t* const out_scores = p.out_scores;
+    const ForcedSpec& forced = s_forced;
+    const KeyOf key_of{forced, srow, nb_l, nb_g, seq_g, id_offset, BS, key_invalid};
+    auto emit = [=, &forced](int pos, int j) {
         const bool valid = j < nb_l && srow[j] >= 0;
         if (CANDIDATES) {
             if (valid) {
-                const bool forced = block_is_forced(p.forced, j + p.id_offset, nb_g, seq_g, p.BS);
-                const float sc_v = forced ? -1.0f : (float)srow[j] * p.scale;
-                if (p.n_peers > 0) {
-                    for (int r = 0; r < p.n_peers; ++r) {
+                const bool is_forced = block_is_forced(forced, j + id_offset, nb_g, seq_g, BS);
+                const float sc_v = is_forced ? -1.0f : (float)srow[j] * scale;
+                if (n_peers > 0) {
+                    for (int r = 0; r < n_peers; ++r) {
                         peer_scores[r][obase + pos] = sc_v;
-                        peer_ids[r][obase + pos] = j + p.id_offset;
+                        peer_ids[r][obase + pos] = j + id_offset;
                     }
                 } else {
-                    p.cand_scores[obase + pos] = sc_v;
-                    p.cand_ids[obase + pos] = j + p.id_offset;
+                    cand_scores[obase + pos] = sc_v;
+                    cand_ids[obase + pos] = j + id_offset;
                 }
             }
         } else {
-            p.out_phys[obase + pos] = btrow[j];
-            if (p.out_logical) p.out_logical[obase + pos] = j;
-            if (p.out_scores) p.out_scores[obase + pos] = valid ? srow[j] : -1;
+            out_phys[obase + pos] = btrow[j];
+            if (out_logical) out_logical[obase + pos] = j;
+            if (out_scores) out_scores[obase + pos] = valid ? srow[j] : -1;
         }
     };
     select_row<CL>(n, kb, p.key_bits, key_of, emit, s_keys, p.n_cached, sc);
@@ -565,7 +624,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
             if (done == (int)gridDim.x - 1) {
                 *p.arrive = 0;
                 __threadfence_system();
-                for (int r = 0; r < p.n_peers; ++r) st_release_sys(p.peer_flags[par][r], step_no);
+                for (int r = 0; r < p.n_peers; ++r) st_release_sys(s_peer_flags[r], step_no);
             }
         }
     }
@@ -657,20 +716,17 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
         }
     }
     __syncthreads();
-    auto at = [&](int i) -> int64_t {
-        const int r = i / p.kl, c = i - r * p.kl;
-        return (int64_t)r * p.rank_stride + (int64_t)row * p.kl + c;
-    };
     struct Rec { int32_t id; float score; };
     struct KeyOf {
-        const MergeParams& p;
+        int kl, largest;
+        int64_t rank_stride;
         int row;
         const float* cand_scores;
         const int32_t* cand_ids;
         __device__ int64_t at(int i) const
         {
-            const int r = i / p.kl, c = i - r * p.kl;
-            return (int64_t)r * p.rank_stride + (int64_t)row * p.kl + c;
+            const int r = i / kl, c = i - r * kl;
+            return (int64_t)r * rank_stride + (int64_t)row * kl + c;
         }
         __device__ Rec raw(int i) const
         {
@@ -680,19 +736,23 @@ __global__ void __launch_bounds__(kSelThreads) merge_kernel(const MergeParams p)
         __device__ uint32_t key(int, Rec r) const
         {
             if (r.id < 0) return kKeyInvalid;
-            const uint32_t k = f32_order_key(p.largest ? -r.score : r.score);
+            const uint32_t k = f32_order_key(largest ? -r.score : r.score);
             return k == kKeyInvalid ? kKeyInvalid - 1u : k;
         }
         __device__ uint32_t key_fast(int i, Rec r) const { return key(i, r); }
+        __device__ int thread_ctx(int, int, int) const { return 0; }
+        __device__ uint32_t key_ctx(int i, Rec r, int, int) const { return key(i, r); }
         __device__ void fixup(uint32_t*, int, int) const {}
     };
-    const KeyOf key_of{p, row, cand_scores, cand_ids};
-    auto emit = [&](int pos, int i) {
-        const int64_t a = at(i);
+    const KeyOf key_of{p.kl, p.largest, p.rank_stride, row, cand_scores, cand_ids};
+    float* const out_scores = p.out_scores;
+    int32_t* const out_ids = p.out_ids;
+    auto emit = [=](int pos, int i) {
+        const int64_t a = key_of.at(i);
         const int32_t id = __ldcg(cand_ids + a);
         if (id >= 0) {
-            p.out_scores[obase + pos] = __ldcg(cand_scores + a);
-            p.out_ids[obase + pos] = id;
+            out_scores[obase + pos] = __ldcg(cand_scores + a);
+            out_ids[obase + pos] = id;
         }
     };
     select_row<false>(n, min(p.k, n), 32, key_of, emit, s_keys, p.n_cached, sc);
