@@ -933,6 +933,70 @@ def run_profile_case(what: str) -> None:
 
 
 # ----------------------------------------------------------------------------------------------
+# where one decode step spends its time: device-timer stamps taken inside the kernels (trace build of the library)
+# ----------------------------------------------------------------------------------------------
+TIMELINE_POINTS = [
+    ("encode", 0, "encode: entry"), ("encode", 1, "encode: dependency wait passed"), ("encode", 2, "encode: inputs staged"),
+    ("encode", 3, "encode: end"),
+    ("scan", 0, "scan: entry"), ("scan", 1, "scan: work items counted"), ("scan", 2, "scan: first item resolved"),
+    ("scan", 3, "scan: first copy issued"), ("scan", 4, "scan: dependency wait passed"), ("scan", 5, "scan: first block landed"),
+    ("scan", 6, "scan: first item scored"), ("scan", 7, "scan: first warp out of items"),
+    ("select", 0, "select: entry"), ("select", 1, "select: dependency wait passed"), ("select", 2, "select: keys staged"),
+    ("select", 3, "select: threshold known"), ("select", 4, "select: chosen blocks listed"), ("select", 5, "select: end"),
+]
+
+
+def run_timeline(shape: str) -> None:
+    """One decode step (encode -> scan -> selection, one CUDA graph per layer) replayed back to back; after each of a
+    few runs the stamps of the last step are read back.  Times are relative to the encode kernel's entry, thread 0
+    of CTA 0 of each kernel.  decode16 = the headline shape, tp8 = config 3 as one of 8 ranks sees it."""
+    trace_lib = os.path.join(ROOT, "unified_cache_management_b200", "libucmr_b200_trace.so")
+    if not os.path.exists(trace_lib):
+        raise SystemExit("no trace build: run  python -m unified_cache_management_b200.build --trace")
+    os.environ["UCMR_LIBRARY"] = trace_lib
+    import torch
+    from unified_cache_management_b200 import ops
+    dev = torch.device("cuda:0")
+    B, Hkv, Hq, seq, BS, k, L = (16, 8, 32, 131072, 128, 16, 4) if shape == "decode16" else (8, 1, 8, 262144, 128, 32, 8)
+    D, Wd = 128, 4
+    mb = seq // BS
+    NB = B * mb
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    caches = [rand_codes((NB, BS, Hkv, Wd), dev, g) for _ in range(L)]
+    bt = torch.randperm(NB, device=dev, generator=g).to(torch.int32).view(B, mb).contiguous()
+    sl = torch.full((B,), seq, dtype=torch.int32, device=dev)
+    R = (torch.randn((D, 32 * Wd), device=dev, generator=g) / D ** 0.5).to(torch.bfloat16)
+    qf = torch.randn((L, B, Hq, D), device=dev, generator=g).to(torch.bfloat16)
+    kn = torch.randn((L, B, Hkv, D), device=dev, generator=g).to(torch.bfloat16)
+    slots = (bt[:, mb - 1].to(torch.int64) * BS + (BS - 1)).contiguous()
+    qc = torch.empty((B, Hq, Wd), dtype=torch.int32, device=dev)
+    ws = ops.new_workspace(B, Hkv, mb, dev)
+    out = new_retrieval(B, Hkv, k, dev)
+
+    def step(layer):
+        ops.hash_encode_decode_step(qf[layer], kn[layer], slots, caches[layer], R, q_codes_out=qc)
+        ops.hamming_topk(caches[layer], qc, bt, sl, k, reduce="sum", must_select=MUST_SELECT, workspace=ws, out=out,
+                         want_scores=False, **STABLE)
+
+    graphs = capture_graphs(step, L)
+    runs = []
+    for trial in range(5):
+        for i in range(16 + trial):
+            graphs[i % L].replay()
+        torch.cuda.synchronize()
+        tables = {u: ops.trace_read(u) for u in ("encode", "scan", "select")}
+        t0 = tables["encode"][0]
+        runs.append([(tables[u][i] - t0) / 1e3 for u, i, _ in TIMELINE_POINTS])
+    med = [sorted(r[i] for r in runs)[len(runs) // 2] for i in range(len(TIMELINE_POINTS))]
+    for (u, i, name), v, lo, hi in zip(TIMELINE_POINTS, med, [min(r[j] for r in runs) for j in range(len(med))],
+                                       [max(r[j] for r in runs) for j in range(len(med))]):
+        print(f"{name:34s} {v:8.2f} us   ({lo:.2f} .. {hi:.2f})")
+    print(json.dumps({"timeline": shape, "unit": "us after the encode kernel's entry (median of 5 runs)",
+                      "points": {name: round(v, 2) for (_, _, name), v in zip(TIMELINE_POINTS, med)}}))
+
+
+# ----------------------------------------------------------------------------------------------
 def run_reference_arm(args, cfg, config, ranks):
     """The reference's CPU implementation of the path on the headline workload.  Loads nothing of the CUDA library:
     the inputs are made with numpy."""
@@ -988,6 +1052,9 @@ def main():
                     help="upper bound of the repetitions of a timed region (a profiler run wants few)")
     ap.add_argument("--exchange", default="both", choices=["both", "p2p", "nccl"],
                     help="million_token_sharded on several GPUs: how the candidate records travel")
+    ap.add_argument("--timeline", default=None, choices=["decode16", "tp8"],
+                    help="print where the time of one decode step goes (device-timer stamps inside the three kernels) "
+                         "and exit; needs the trace build: python -m unified_cache_management_b200.build --trace")
     ap.add_argument("--ncu-case", default=None,
                     help="run a small single-kernel case for a profiler capture and exit "
                          "(scan, scan_min, scan_256bit, scan_mla, scan_bs16, scan_bs32, scan_tp8, select, encode, "
@@ -996,6 +1063,9 @@ def main():
 
     if args.ncu_case:
         run_profile_case(args.ncu_case)
+        return
+    if args.timeline:
+        run_timeline(args.timeline)
         return
     global MAX_REPS
     MAX_REPS = max(3, args.max_reps)

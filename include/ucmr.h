@@ -80,6 +80,23 @@ const char* ucmr_status_string(int status);
 /* Text of the last CUDA runtime error seen by this thread inside the library ("" if none). */
 const char* ucmr_last_cuda_error(void);
 
+/* Step timeline, for a library built with -DUCMR_TRACE (python -m unified_cache_management_b200.build --trace);
+ * any other build returns UCMR_ERR_UNSUPPORTED.  Thread 0 of CTA 0 of the decode-step kernels stores the device's
+ * nanosecond timer at numbered points; this copies the table of one kernel (UCMR_TRACE_SLOTS values, as left by the
+ * kernel's last launch; a synchronising device-to-host copy) to `stamps`.
+ *   UCMR_TRACE_ENCODE (decode-step encode): 0 entry, 1 dependency wait passed, 2 inputs staged, 3 end
+ *   UCMR_TRACE_SCAN (staged Hamming scan):  0 entry, 1 work items counted, 2 first item resolved, 3 first copy issued,
+ *                                           4 dependency wait passed, 5 first block landed, 6 first item scored,
+ *                                           7 this warp out of items
+ *   UCMR_TRACE_SELECT (selection kernel):   0 entry, 1 dependency wait passed, 2 keys staged, 3 threshold known,
+ *                                           4 chosen blocks listed, 5 end
+ * No reference counterpart (the reference times its kernels from the host). */
+#define UCMR_TRACE_SLOTS 32
+#define UCMR_TRACE_ENCODE 0
+#define UCMR_TRACE_SCAN 1
+#define UCMR_TRACE_SELECT 2
+int ucmr_trace_read(int unit, unsigned long long* stamps);
+
 /* ------------------------------------------------------------------------------------------
  * (1) Hash encode.  Replaces HashEncoder.compute_hash / triton_hash_code
  *     (ucm/sparse/gsa_on_device/hash_encoder.py:37-134, 450-507; CPU form torch_hash_code :359-370).

@@ -46,3 +46,7 @@ def test_host_argument_validation_needs_no_gpu():
     assert lib.ucmr_gather_kv(null, null, 1, 16, null, 1, 1, 0, 1, 1, 16, null, null, null, null) == L.UCMR_ERR_BAD_ARG
     assert lib.ucmr_hash_encode(null, 1, 128, null, 128, 128, null, null, null) == L.UCMR_ERR_BAD_ARG
     assert lib.ucmr_workspace_init(null, 0, null) == L.UCMR_ERR_WORKSPACE
+    # the step timeline only exists in the trace build
+    stamps = (ctypes.c_ulonglong * 32)()
+    assert lib.ucmr_trace_read(0, null) == L.UCMR_ERR_BAD_ARG
+    assert lib.ucmr_trace_read(0, ctypes.cast(stamps, ctypes.c_void_p)) == L.UCMR_ERR_UNSUPPORTED

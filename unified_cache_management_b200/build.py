@@ -24,25 +24,33 @@ def _deps():
     return [d for d in deps if os.path.exists(d)]
 
 
-def up_to_date() -> bool:
-    if not os.path.exists(LIB_PATH):
+TRACE_LIB_PATH = os.path.join(PKG_DIR, "libucmr_b200_trace.so")
+
+
+def up_to_date(path: str = LIB_PATH) -> bool:
+    if not os.path.exists(path):
         return False
-    t = os.path.getmtime(LIB_PATH)
+    t = os.path.getmtime(path)
     return all(os.path.getmtime(d) <= t for d in _deps())
 
 
-def build_library(force: bool = False, verbose: bool = False) -> str:
-    if not force and up_to_date():
-        return LIB_PATH
+def build_library(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
+    """Builds the library; ``trace`` builds the step-timeline variant (-DUCMR_TRACE, see ucmr_trace_read in ucmr.h)
+    next to it as ``libucmr_b200_trace.so`` (load it through the UCMR_LIBRARY environment variable)."""
+    out = TRACE_LIB_PATH if trace else LIB_PATH
+    if not force and up_to_date(out):
+        return out
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
            "-shared", "-Xcompiler", "-fPIC", "-I" + INCLUDE, "-I" + CSRC, "--threads", "4"]
+    if trace:
+        cmd += ["-DUCMR_TRACE"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += _sources() + ["-o", LIB_PATH]
+    cmd += _sources() + ["-o", out]
     subprocess.check_call(cmd)
-    return LIB_PATH
+    return out
 
 
 if __name__ == "__main__":
-    print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv))

@@ -16,6 +16,30 @@ void note_cuda_error(cudaError_t e)
 
 }  // namespace ucmr
 
+#ifdef UCMR_TRACE
+namespace ucmr {
+int trace_read_encode(unsigned long long* host);
+int trace_read_scan(unsigned long long* host);
+int trace_read_select(unsigned long long* host);
+}  // namespace ucmr
+#endif
+
+extern "C" int ucmr_trace_read(int unit, unsigned long long* stamps)
+{
+    if (stamps == nullptr) return UCMR_ERR_BAD_ARG;
+#ifdef UCMR_TRACE
+    switch (unit) {
+        case UCMR_TRACE_ENCODE: return ucmr::trace_read_encode(stamps);
+        case UCMR_TRACE_SCAN: return ucmr::trace_read_scan(stamps);
+        case UCMR_TRACE_SELECT: return ucmr::trace_read_select(stamps);
+        default: return UCMR_ERR_BAD_ARG;
+    }
+#else
+    (void)unit;
+    return UCMR_ERR_UNSUPPORTED;
+#endif
+}
+
 extern "C" int ucmr_version(void) { return UCMR_VERSION; }
 
 extern "C" const char* ucmr_last_cuda_error(void) { return ucmr::g_last_error; }

@@ -280,6 +280,24 @@ __device__ __forceinline__ unsigned long long global_timer_ns()
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+// Step timeline (builds with -DUCMR_TRACE only): thread 0 of CTA 0 stores %globaltimer at numbered points of the
+// decode-step kernels (encode, scan, selection: one table per translation unit) and ucmr_trace_read copies a table
+// to the host.  Without the define the macro expands to nothing and ucmr_trace_read reports "unsupported".
+#ifdef UCMR_TRACE
+static __device__ unsigned long long g_trace[UCMR_TRACE_SLOTS];
+#define UCMR_STAMP(i)                                                                    \
+    do {                                                                                 \
+        if (blockIdx.x == 0 && threadIdx.x == 0) g_trace[(i)] = global_timer_ns();       \
+    } while (0)
+#define UCMR_TRACE_READER(name)                                                                             \
+    int name(unsigned long long* host)                                                                      \
+    {                                                                                                       \
+        return cudaMemcpyFromSymbol(host, g_trace, sizeof(g_trace)) == cudaSuccess ? UCMR_OK : UCMR_ERR_LAUNCH; \
+    }
+#else
+#define UCMR_STAMP(i) ((void)0)
+#endif
+
 // Bounded wait.  Returns false when the time limit ran out (the caller must stop using the
 // barrier's data, flag the status word and leave).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)

@@ -1240,8 +1240,10 @@ __global__ void __launch_bounds__(kStepThreads) encode_step_kernel(const TilePar
     __shared__ __align__(16) float s_part[ROUNDS][kStepRowsPerRound][kStepKSplit][kEncBits];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r_in = warp / kStepKSplit, ks = warp % kStepKSplit, k0 = ks * kStepKPerWarp;
+    UCMR_STAMP(0);
     grid_launch_dependents();  // a scan launched right after this kernel may set itself up meanwhile
     grid_dependency_wait();    // q and the new keys come from the kernel before this one
+    UCMR_STAMP(1);
     // rows k0 .. k0+31 of R, columns 4*lane .. 4*lane+3: 32 independent 8-byte loads per lane
     uint2 rr[kStepKPerWarp];
     {
@@ -1302,6 +1304,7 @@ __global__ void __launch_bounds__(kStepThreads) encode_step_kernel(const TilePar
         s_x[it][r_in][k0 + lane] = xv[it];
     }
     __syncwarp();
+    UCMR_STAMP(2);
 #pragma unroll
     for (int it = 0; it < ROUNDS; ++it) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f};  // columns 4*lane .. 4*lane+3 over this warp's inputs
@@ -1355,6 +1358,7 @@ __global__ void __launch_bounds__(kStepThreads) encode_step_kernel(const TilePar
             }
         }
     }
+    UCMR_STAMP(3);
 }
 
 // Rows of a decode step up to which the CUDA-core kernel is used (beyond it the tensor-core tiles win).
@@ -1463,3 +1467,7 @@ extern "C" int ucmr_hash_encode_blocks_at(const void* k_cache, int64_t NB, int B
     return encode_blocks_impl(k_cache, NB, BS, H, stride_block, stride_t, stride_h, block_ids, block_tokens, n_blocks, R,
                               in_dim, hash_bits, cache, NB_codes, row_words, word_offset, status_word, stream);
 }
+
+#ifdef UCMR_TRACE
+namespace ucmr { UCMR_TRACE_READER(trace_read_encode) }
+#endif

@@ -513,6 +513,7 @@ scan_ring_kernel(const RingParams p)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int Hout = p.reduce_kvhead ? 1 : p.Hkv;
+    UCMR_STAMP(0);
     grid_launch_dependents();  // a scan launched right behind this one (the next layer's) may set itself up
 
     if (tid == 0) {
@@ -553,6 +554,7 @@ scan_ring_kernel(const RingParams p)
         if (lane == 0) s_cum[p.B] = run;
     }
     __syncthreads();
+    UCMR_STAMP(1);
     const int total_items = s_cum[p.B];
 
     // Work split.  Static part: CTA c takes flat items c, c + grid, ... and warp w every n_active-th of
@@ -637,6 +639,7 @@ scan_ring_kernel(const RingParams p)
 
     Item cur = resolve(claim_finish(claim_start()));
     int token = claim_start();
+    UCMR_STAMP(2);
     // (early_setup) up to here only the sequence lengths and the block table were read; the code cache, the query
     // codes and the score buffer may still be in use by the kernel before this one
     // (early_loads) the kernels still in flight only write the block that holds a request's newest token: the first
@@ -644,11 +647,14 @@ scan_ring_kernel(const RingParams p)
     // - query codes, score stores, the work counter - stays behind the wait.
     const bool first_early = p.early_loads && cur.valid && (int64_t)(cur.j0 + p.bps) * p.BS < (int64_t)cur.seq;
     if (first_early) issue(cur);
+    if (first_early) UCMR_STAMP(3);
     if (p.early_setup) {
         grid_dependency_wait();
         if (fused && tid == 0) s_epoch = ld_acquire_gpu(p.sel.all_scored);  // (the kernel before this one may set it)
     }
+    UCMR_STAMP(4);
     if (!first_early) issue(cur);
+    if (!first_early) UCMR_STAMP(3);
     mark_past_end();  // while the first block is on its way
     Item nxt = resolve(claim_finish(token));
     token = claim_start();
@@ -950,6 +956,7 @@ scan_ring_kernel(const RingParams p)
         constexpr int QP = (RW_T == 64) ? 2 : 1;
         uint32_t qw[QP][GMAX];
         const bool q_kept = passes <= QP;  // every pass has its own register set: loaded once per request
+        [[maybe_unused]] bool first_item = true;  // (step timeline only)
         while (cur.valid) {
             if (q_kept && cur.b != cur_b) {  // (before the wait: the query words travel while the block does)
 #pragma unroll
@@ -964,6 +971,7 @@ scan_ring_kernel(const RingParams p)
                 cur_b = cur.b;
             }
             if (!mbar_wait(full, phase)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
+            if (first_item) UCMR_STAMP(5);
             phase ^= 1u;
             const StageMeta m = s_meta[warp];
             bool reissued = false;
@@ -1025,6 +1033,8 @@ scan_ring_kernel(const RingParams p)
                 __syncwarp();
                 advance();
             }
+            if (first_item) UCMR_STAMP(6);
+            first_item = false;
         }
         }  // (!small_done)
     } else {
@@ -1146,6 +1156,7 @@ scan_ring_kernel(const RingParams p)
             }
         }
     }
+    UCMR_STAMP(7);
     if (fused) {
         // Out of work items: arrive (after this warp's score stores are visible device-wide).  The last warp of the
         // CTA to arrive speaks for the CTA: it makes the grid-level arrival and, unless that was the final one, polls
@@ -1334,5 +1345,9 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     if (e != cudaSuccess) { note_cuda_error(e); return UCMR_ERR_LAUNCH; }
     return launch_kernel_ex(kernel, dim3(grid), dim3(kRingThreads), smem, st, 1, true, p);
 }
+
+#ifdef UCMR_TRACE
+UCMR_TRACE_READER(trace_read_scan)
+#endif
 
 }  // namespace ucmr

@@ -196,6 +196,7 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
     normals = __reduce_add_sync(0xffffffffu, normals);
     if (lane == 0) { sc.w_lo[warp] = r_lo; sc.w_hi[warp] = r_hi; sc.w_zero[warp] = zeros; sc.w_norm[warp] = normals; }
     __syncthreads();
+    UCMR_STAMP(2);
     // every warp folds the per-warp partials itself (no atomics, no second barrier)
     static_assert(kSelWarps <= 32, "one lane per warp partial");
     r_lo = lane < kSelWarps ? sc.w_lo[lane] : 0xFFFFFFFFu;
@@ -315,6 +316,7 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
         need = rem;  // how many keys equal to T are taken, lowest positions first
     }
 
+    UCMR_STAMP(3);
     const int ipt = (len + kSelThreads - 1) / kSelThreads;
     const int j_begin = min(j_hi, j_lo + tid * ipt), j_end = min(j_hi, j_begin + ipt);
     int lt = 0, eq = 0;
@@ -381,6 +383,7 @@ __device__ void select_row(int n, int kb, int key_bits, KeyFn key_of, EmitFn emi
         }
     }
     __syncthreads();
+    UCMR_STAMP(4);
     if (listed)
         for (int i = tid; i < n_mine; i += kSelThreads) emit(pos_base + i, sel[i]);
     __syncthreads();
@@ -436,6 +439,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     __shared__ ForcedSpec s_forced;
     const int tid = threadIdx.x;
     if (tid == 0) s_forced = p.forced;
+    UCMR_STAMP(0);
     const int row = CL ? blockIdx.x / p.cluster : blockIdx.x;
     const bool lead = !CL || blockIdx.x % p.cluster == 0;  // the CTA that writes the row's padding and scalars
     const int b = row / p.Hout;
@@ -511,6 +515,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     // Up to here only the sequence lengths and the block table were read and only outputs written: the scan
     // that produces the scores may still be running (programmatic dependent launch).
     grid_dependency_wait();
+    UCMR_STAMP(1);
     if (blockIdx.x == 0 && tid == 0 && p.sched != nullptr) *p.sched = 0;
     if (masked) {
         write_scalars();
@@ -613,6 +618,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         }
     };
     select_row<CL>(n, kb, p.key_bits, key_of, emit, s_keys, p.n_cached, sc);
+    UCMR_STAMP(5);
     write_scalars();
     if (CANDIDATES && p.n_peers > 0) {
         // records are in the peers' memory: make them visible system-wide, then the last CTA of the launch
@@ -1135,3 +1141,7 @@ extern "C" int ucmr_merge_topk_wait_step(const float* cand_scores, const int32_t
     return run_merge_wait(cand_scores, cand_ids, rank_stride, R, B, Hout, kl, k, 0, out_scores, out_ids, flags, 0,
                           status_word, static_cast<cudaStream_t>(stream), &ms);
 }
+
+#ifdef UCMR_TRACE
+namespace ucmr { UCMR_TRACE_READER(trace_read_select) }
+#endif

@@ -43,6 +43,7 @@ SIGNATURES = {
     "ucmr_version": (_i, []),
     "ucmr_status_string": (C.c_char_p, [_i]),
     "ucmr_last_cuda_error": (C.c_char_p, []),
+    "ucmr_trace_read": (_i, [_i, _vp]),
     "ucmr_hash_encode": (_i, [_vp, _i64, _i64, _vp, _i, _i, _vp, _vp, _vp]),
     "ucmr_hash_encode_query": (_i, [_vp, _i64, _i, _i64, _i64, _i, _vp, _i, _i, _vp, _vp, _vp]),
     "ucmr_hash_encode_and_cache": (_i, [_vp, _i64, _i, _i64, _i64, _vp, _i, _i, _vp, _i, _vp, _i64, _i, _vp, _vp]),

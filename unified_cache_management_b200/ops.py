@@ -249,6 +249,19 @@ def workspace_bytes(batch: int, num_kv_heads: int, max_blocks: int, reduce_kvhea
                                                                    int(bool(reduce_kvhead))))
 
 
+TRACE_UNITS = {"encode": 0, "scan": 1, "select": 2}  # UCMR_TRACE_ENCODE / _SCAN / _SELECT
+TRACE_SLOTS = 32                                      # UCMR_TRACE_SLOTS
+
+
+def trace_read(unit: str):
+    """Device-timer stamps (ns) left by the last launch of one decode-step kernel; needs the library built with
+    ``python -m unified_cache_management_b200.build --trace`` (any other build raises: unsupported).  Slot
+    meanings: ucmr.h, ucmr_trace_read."""
+    buf = (C.c_ulonglong * TRACE_SLOTS)()
+    _l.check(_l.load_library().ucmr_trace_read(TRACE_UNITS[unit], C.cast(buf, C.c_void_p)), "ucmr_trace_read")
+    return list(buf)
+
+
 def new_workspace(batch: int, num_kv_heads: int, max_blocks: int, device, reduce_kvhead: bool = False) -> torch.Tensor:
     """Allocates and clears a workspace big enough for the given shapes (either head mode)."""
     n = max(workspace_bytes(batch, num_kv_heads, max_blocks, False),
