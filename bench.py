@@ -996,6 +996,79 @@ def run_timeline(shape: str) -> None:
                       "points": {name: round(v, 2) for (_, _, name), v in zip(TIMELINE_POINTS, med)}}))
 
 
+SHARD_TIMELINE_POINTS = [
+    ("scan", 0, "scan: entry"), ("scan", 3, "scan: first copy issued"), ("scan", 7, "scan: first warp out of items"),
+    ("select", 0, "select: entry"), ("select", 1, "select: dependency wait passed"), ("select", 5, "select: records stored"),
+    ("select", 6, "select: records fenced"), ("select", 7, "select: step number published"),
+    ("select", 8, "merge: entry"), ("select", 9, "merge: every rank's step number seen"), ("select", 2, "merge: keys staged"),
+    ("select", 3, "merge: threshold known"), ("select", 10, "merge: merged"),
+]
+
+
+def run_shard_timeline() -> None:
+    """Config 4 over the ranks of this launch (torchrun), peer-memory exchange, one CUDA graph per layer-step: every
+    rank prints where its step spends its time, relative to its own scan's entry (the device timers of different
+    GPUs are not comparable).  "merge: every rank's step number seen" minus "merge: entry" is the time a rank waits
+    for the slowest peer's records."""
+    trace_lib = os.path.join(ROOT, "unified_cache_management_b200", "libucmr_b200_trace.so")
+    if not os.path.exists(trace_lib):
+        raise SystemExit("no trace build: run  python -m unified_cache_management_b200.build --trace")
+    os.environ["UCMR_LIBRARY"] = trace_lib
+    import torch
+    from unified_cache_management_b200 import ops, sharded
+    ranks = Ranks()
+    ranks.init()
+    cfg = EXTRA_WORKLOADS["million_token_sharded"]
+    dev, world, rank = ranks.dev, ranks.world, ranks.rank
+    if world < 2:
+        raise SystemExit("--timeline shards needs at least two ranks (torchrun)")
+    B, seq_total, Hkv, Hq, BS, k, L = cfg["B"], cfg["seq"], cfg["Hkv"], cfg["Hq"], cfg["BS"], cfg["k"], cfg["layers"]
+    Wd, nblk_total = cfg["bits"] // 32, cfg["seq"] // cfg["BS"]
+    per = nblk_total // world
+    NB, kl = B * per, min(k, per)
+    g = torch.Generator(device=dev)
+    g.manual_seed(4000 + rank)
+    caches = [rand_codes((NB, BS, Hkv, Wd), dev, g) for _ in range(L)]
+    bt_local = torch.randperm(NB, device=dev, generator=g).to(torch.int32).view(B, per).contiguous()
+    g.manual_seed(44)
+    q = rand_codes((B, Hq, Wd), dev, g)
+    seq_g = torch.full((B,), seq_total, dtype=torch.int32, device=dev)
+    ws = ops.new_workspace(B, Hkv, per, dev)
+    plan = sharded.shard_plan(seq_g, BS, nblk_total, world, rank)
+    o_s = torch.empty((B, Hkv, k), dtype=torch.float32, device=dev)
+    o_i = torch.empty((B, Hkv, k), dtype=torch.int32, device=dev)
+    st_word = torch.zeros(1, dtype=torch.int32, device=dev)
+    ex = sharded.PeerExchange(B, Hkv, kl, dev)
+
+    def step(layer):
+        sharded.sharded_hamming_topk_p2p(caches[layer], q, bt_local, seq_g, k, BS, nblk_total, 1.0 / (BS * (Hq // Hkv)), ex,
+                                         reduce="sum", must_select=MUST_SELECT, workspace=ws, plan=plan, status=st_word,
+                                         out_scores=o_s, out_ids=o_i, **STABLE)
+
+    for i in range(4):
+        step(i % L)
+    ranks.barrier()
+    graphs = capture_graphs(step, L, warm=False)
+    runs = []
+    for trial in range(5):
+        ranks.barrier()
+        for i in range(16):
+            graphs[i % L].replay()
+        torch.cuda.synchronize()
+        tables = {u: ops.trace_read(u) for u in ("scan", "select")}
+        t0 = tables["scan"][0]
+        runs.append([(tables[u][i] - t0) / 1e3 for u, i, _ in SHARD_TIMELINE_POINTS])
+    med = [sorted(r[i] for r in runs)[len(runs) // 2] for i in range(len(SHARD_TIMELINE_POINTS))]
+    line = {"timeline": "shards", "rank": rank, "ranks": world, "status_word": int(st_word.item()),
+            "unit": "us after this rank's scan entry (median of 5 runs)",
+            "points": {name: round(v, 2) for (_, _, name), v in zip(SHARD_TIMELINE_POINTS, med)}}
+    for r in range(world):   # one rank after the other, rank 0 last
+        ranks.barrier()
+        if rank == (r + 1) % world:
+            print(json.dumps(line), flush=True)
+    ranks.close()
+
+
 # ----------------------------------------------------------------------------------------------
 def run_reference_arm(args, cfg, config, ranks):
     """The reference's CPU implementation of the path on the headline workload.  Loads nothing of the CUDA library:
@@ -1052,7 +1125,7 @@ def main():
                     help="upper bound of the repetitions of a timed region (a profiler run wants few)")
     ap.add_argument("--exchange", default="both", choices=["both", "p2p", "nccl"],
                     help="million_token_sharded on several GPUs: how the candidate records travel")
-    ap.add_argument("--timeline", default=None, choices=["decode16", "tp8"],
+    ap.add_argument("--timeline", default=None, choices=["decode16", "tp8", "shards"],
                     help="print where the time of one decode step goes (device-timer stamps inside the three kernels) "
                          "and exit; needs the trace build: python -m unified_cache_management_b200.build --trace")
     ap.add_argument("--ncu-case", default=None,
@@ -1063,6 +1136,9 @@ def main():
 
     if args.ncu_case:
         run_profile_case(args.ncu_case)
+        return
+    if args.timeline == "shards":
+        run_shard_timeline()
         return
     if args.timeline:
         run_timeline(args.timeline)

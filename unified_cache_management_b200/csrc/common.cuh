@@ -289,6 +289,7 @@ static __device__ unsigned long long g_trace[UCMR_TRACE_SLOTS];
     do {                                                                                 \
         if (blockIdx.x == 0 && threadIdx.x == 0) g_trace[(i)] = global_timer_ns();       \
     } while (0)
+#define UCMR_STAMP_ANY(i) (g_trace[(i)] = global_timer_ns()) /* whichever thread gets there */
 #define UCMR_TRACE_READER(name)                                                                             \
     int name(unsigned long long* host)                                                                      \
     {                                                                                                       \
@@ -296,6 +297,7 @@ static __device__ unsigned long long g_trace[UCMR_TRACE_SLOTS];
     }
 #else
 #define UCMR_STAMP(i) ((void)0)
+#define UCMR_STAMP_ANY(i) ((void)0)
 #endif
 
 // Bounded wait.  Returns false when the time limit ran out (the caller must stop using the
