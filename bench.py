@@ -999,7 +999,9 @@ def run_timeline(shape: str) -> None:
 SHARD_TIMELINE_POINTS = [
     ("scan", 0, "scan: entry"), ("scan", 3, "scan: first copy issued"), ("scan", 7, "scan: first warp out of items"),
     ("select", 0, "select: entry"), ("select", 1, "select: dependency wait passed"), ("select", 5, "select: records stored"),
-    ("select", 6, "select: records fenced"), ("select", 7, "select: step number published"),
+    ("select", 6, "select: records fenced"), ("select", 13, "select: dependency wait passed (last CTA)"),
+    ("select", 11, "select: records stored (last CTA)"), ("select", 12, "select: records fenced (last CTA)"),
+    ("select", 7, "select: step number published"),
     ("select", 8, "merge: entry"), ("select", 9, "merge: every rank's step number seen"), ("select", 2, "merge: keys staged"),
     ("select", 3, "merge: threshold known"), ("select", 10, "merge: merged"),
 ]

@@ -91,7 +91,8 @@ const char* ucmr_last_cuda_error(void);
  *   UCMR_TRACE_SELECT (selection kernel):   0 entry, 1 dependency wait passed, 2 keys staged, 3 threshold known,
  *                                           4 chosen blocks listed, 5 end; peer exchange: 6 records fenced (CTA 0),
  *                                           7 step number published (the launch's last CTA); merge kernel (same
- *                                           table): 8 entry, 9 every rank's step number seen, 10 merged
+ *                                           table): 8 entry, 9 every rank's step number seen, 10 merged; over all CTAs of the
+ *                                           selection, the latest: 11 records stored, 12 records fenced, 13 wait passed
  * No reference counterpart (the reference times its kernels from the host). */
 #define UCMR_TRACE_SLOTS 32
 #define UCMR_TRACE_ENCODE 0

@@ -290,6 +290,10 @@ static __device__ unsigned long long g_trace[UCMR_TRACE_SLOTS];
         if (blockIdx.x == 0 && threadIdx.x == 0) g_trace[(i)] = global_timer_ns();       \
     } while (0)
 #define UCMR_STAMP_ANY(i) (g_trace[(i)] = global_timer_ns()) /* whichever thread gets there */
+#define UCMR_STAMP_LAST(i) /* thread 0 of every CTA: the latest one stays */ \
+    do {                                                                      \
+        if (threadIdx.x == 0) atomicMax(&g_trace[(i)], global_timer_ns());     \
+    } while (0)
 #define UCMR_TRACE_READER(name)                                                                             \
     int name(unsigned long long* host)                                                                      \
     {                                                                                                       \
@@ -298,6 +302,7 @@ static __device__ unsigned long long g_trace[UCMR_TRACE_SLOTS];
 #else
 #define UCMR_STAMP(i) ((void)0)
 #define UCMR_STAMP_ANY(i) ((void)0)
+#define UCMR_STAMP_LAST(i) ((void)0)
 #endif
 
 // Bounded wait.  Returns false when the time limit ran out (the caller must stop using the

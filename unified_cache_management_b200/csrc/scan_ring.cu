@@ -9,7 +9,7 @@
 //   block-table entry, arm the barrier, launch the copy: several hundred cycles) is spread over twelve
 //   instruction streams and overlaps their math.  Up to 12 x 16 KiB are in flight per SM.  Each
 //   barrier has a single waiter that sees every phase in order, so a parity wait is never ambiguous.
-//   Work split: the first 7/8 of the items statically (CTA c, warp w), the rest claimed one by one from an
+//   Work split: the first 7/8 (3/4 in long scans) of the items statically (CTA c, warp w), the rest claimed one by one from an
 //   atomic counter so that all SMs finish together; claim and block-table load run one item ahead of use.
 //
 //     sum mode: the distance sum over a block only depends on how many of its tokens have each code
@@ -580,7 +580,10 @@ scan_ring_kernel(const RingParams p)
     const int lanes_total = gridDim.x * p.n_active;
     // (small launches stay static: every warp pays at least one atomic to learn that the pool is empty)
     const bool dynamic = p.sched != nullptr && total_items >= 4 * lanes_total;
-    const int static_items = dynamic ? (total_items - total_items / 8) / lanes_total * lanes_total : total_items;
+    // (long scans - 16 items per warp or more - keep a quarter for the pool: SMs drift apart by some 10 % over
+    // 150 us, and an SM that is still on its static share when the pool runs dry finishes that much later)
+    const int pool_share = total_items >= 16 * lanes_total ? 4 : 8;
+    const int static_items = dynamic ? (total_items - total_items / pool_share) / lanes_total * lanes_total : total_items;
     int static_k = 0;
     // claim_start returns a token (meaningful in lane 0); claim_finish turns it into a flat item index or
     // -1.  They are called one item apart so that the atomic's latency is hidden.
