@@ -959,6 +959,9 @@ static int run_select(bool candidates, const uint32_t* codes, int64_t NB, int BS
     // Few long rows: split each over a thread-block cluster so that the selection uses more than `rows` SMs.
     p.cluster = 1;
     while (p.cluster < 8 && rows * p.cluster * 2 <= 160 && max_blocks > p.cluster * kSelClusterSlice) p.cluster *= 2;
+    // (8 CTAs per row only while each still gets more than 4096 keys: 16 rows x 8 CTAs do not always fit the GPCs in
+    // one wave; rows of 32768 blocks measured 5 us faster with 4, rows of 65536 blocks 11 us faster with 8)
+    if (p.cluster == 8 && max_blocks <= 8 * 2 * kSelClusterSlice) p.cluster = 4;
     bool use_cluster = p.cluster > 1;
     {   // tuning aid UCMR_SEL_CLUSTER (read once per process): 0 = never split, 1/2/4/8 = force that size
         const int v = sel_cluster_override();
