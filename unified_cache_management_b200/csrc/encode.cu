@@ -222,11 +222,50 @@ encode_tc_kernel(const __grid_constant__ CUtensorMap x_map, const EncParams p)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
+    const int64_t first = blockIdx.x, step = gridDim.x;
+    const int64_t my_tiles = first < p.n_tiles ? (p.n_tiles - first + step - 1) / step : 0;
+    const int tok_per_tile = kEncTileM / p.H;
+    // Starts the copy of this CTA's it-th tile into its stage (which must be free).  Thread 0 only.
+    auto issue_tile = [&](int64_t it) {
+        const int s = (int)(it % kEncStages);
+        const int64_t tile = first + it * step;
+        uint8_t* dst = s_a + (size_t)s * kEncStageBytes;
+        mbar_expect_tx(&full[s], kEncStageBytes);
+        if (p.src_blocks == nullptr) {
+            const int t0 = (int)(tile * tok_per_tile);
+            tma_load_3d(dst, &x_map, 0, 0, t0, &full[s]);
+            tma_load_3d(dst + kEncHalfBytes, &x_map, 64, 0, t0, &full[s]);
+        } else if (p.rpb >= kEncTileM) {
+            // the tile is one slice of one listed block
+            const int parts = p.rpb / kEncTileM;
+            const int64_t bi = tile / parts;
+            int id = p.src_blocks[bi];
+            if (id < 0 || id >= p.NB_src) id = 0;  // rows of a bad id are dropped by the epilogue
+            const int tok0 = (int)(tile - bi * parts) * tok_per_tile;
+            tma_load_4d(dst, &x_map, 0, 0, tok0, id, &full[s]);
+            tma_load_4d(dst + kEncHalfBytes, &x_map, 64, 0, tok0, id, &full[s]);
+        } else {
+            // the tile holds several whole blocks, each a box of rpb rows
+            const int sub = kEncTileM / p.rpb;
+            for (int u = 0; u < sub; ++u) {
+                const int64_t bi = tile * sub + u;
+                int id = bi < p.n_src_blocks ? p.src_blocks[bi] : 0;
+                if (id < 0 || id >= p.NB_src) id = 0;
+                uint8_t* d = dst + (size_t)u * p.rpb * 128;
+                tma_load_4d(d, &x_map, 0, 0, 0, id, &full[s]);
+                tma_load_4d(d + kEncHalfBytes, &x_map, 64, 0, 0, id, &full[s]);
+            }
+        }
+    };
+    int64_t prefilled = 0;  // (thread 0) tiles whose copies were started before the set-up below
     if (tid == 0) {
         for (int s = 0; s < kEncStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int a = 0; a < kEncAccs; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
         fence_mbar_init();
         asm volatile("prefetch.tensormap [%0];" ::"l"(&x_map) : "memory");
+        // every stage is free at the start: the first tiles travel while the CTA transposes R and allocates TMEM
+        // (a few microseconds during which the copy engine would otherwise idle)
+        for (; prefilled < my_tiles && prefilled < kEncStages; ++prefilled) issue_tile(prefilled);
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
@@ -241,44 +280,13 @@ encode_tc_kernel(const __grid_constant__ CUtensorMap x_map, const EncParams p)
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int64_t first = blockIdx.x, step = gridDim.x;
-    const int64_t my_tiles = first < p.n_tiles ? (p.n_tiles - first + step - 1) / step : 0;
-    const int tok_per_tile = kEncTileM / p.H;
-
     if (warp == 0) {
         if (lane == 0) {
-            for (int64_t it = 0; it < my_tiles; ++it) {
+            for (int64_t it = prefilled; it < my_tiles; ++it) {
                 const int s = (int)(it % kEncStages);
                 const uint32_t ph = (uint32_t)((it / kEncStages) & 1);
                 if (!mbar_wait(&empty[s], ph ^ 1u)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
-                const int64_t tile = first + it * step;
-                uint8_t* dst = s_a + (size_t)s * kEncStageBytes;
-                mbar_expect_tx(&full[s], kEncStageBytes);
-                if (p.src_blocks == nullptr) {
-                    const int t0 = (int)(tile * tok_per_tile);
-                    tma_load_3d(dst, &x_map, 0, 0, t0, &full[s]);
-                    tma_load_3d(dst + kEncHalfBytes, &x_map, 64, 0, t0, &full[s]);
-                } else if (p.rpb >= kEncTileM) {
-                    // the tile is one slice of one listed block
-                    const int parts = p.rpb / kEncTileM;
-                    const int64_t bi = tile / parts;
-                    int id = p.src_blocks[bi];
-                    if (id < 0 || id >= p.NB_src) id = 0;  // rows of a bad id are dropped by the epilogue
-                    const int tok0 = (int)(tile - bi * parts) * tok_per_tile;
-                    tma_load_4d(dst, &x_map, 0, 0, tok0, id, &full[s]);
-                    tma_load_4d(dst + kEncHalfBytes, &x_map, 64, 0, tok0, id, &full[s]);
-                } else {
-                    // the tile holds several whole blocks, each a box of rpb rows
-                    const int sub = kEncTileM / p.rpb;
-                    for (int u = 0; u < sub; ++u) {
-                        const int64_t bi = tile * sub + u;
-                        int id = bi < p.n_src_blocks ? p.src_blocks[bi] : 0;
-                        if (id < 0 || id >= p.NB_src) id = 0;
-                        uint8_t* d = dst + (size_t)u * p.rpb * 128;
-                        tma_load_4d(d, &x_map, 0, 0, 0, id, &full[s]);
-                        tma_load_4d(d + kEncHalfBytes, &x_map, 64, 0, 0, id, &full[s]);
-                    }
-                }
+                issue_tile(it);
             }
         }
     } else if (warp == 1) {
@@ -326,15 +334,22 @@ encode_tc_kernel(const __grid_constant__ CUtensorMap x_map, const EncParams p)
             if (!mbar_wait(&acc_full[a], aph)) { flag_status(p.status, UCMR_DEV_WAIT_TIMEOUT); break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kEncBits);
+            // the row's 128 accumulator columns in one round trip; the accumulator goes back to the MMA thread before
+            // the sign bits are packed
             uint4 code;
-            uint32_t r[32];
-            tc_ld32(taddr + 0, r);  tc_wait_ld(); code.x = pack_signs(r);
-            tc_ld32(taddr + 32, r); tc_wait_ld(); code.y = pack_signs(r);
-            tc_ld32(taddr + 64, r); tc_wait_ld(); code.z = pack_signs(r);
-            tc_ld32(taddr + 96, r); tc_wait_ld(); code.w = pack_signs(r);
+            uint32_t r0[32], r1[32], r2[32], r3[32];
+            tc_ld32(taddr + 0, r0);
+            tc_ld32(taddr + 32, r1);
+            tc_ld32(taddr + 64, r2);
+            tc_ld32(taddr + 96, r3);
+            tc_wait_ld();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[a]);
+            code.x = pack_signs(r0);
+            code.y = pack_signs(r1);
+            code.z = pack_signs(r2);
+            code.w = pack_signs(r3);
             const int64_t tile = first + it * step;
             const int64_t row = tile * kEncTileM + q * 32 + lane;
             if (p.src_blocks != nullptr) {
