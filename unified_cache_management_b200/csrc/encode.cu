@@ -1233,9 +1233,9 @@ static bool step_simt_enabled()
 // tcgen05.ld round trips, dealloc), not on the math, and a kernel of one warp per row is bound by that warp's
 // instruction stream (128 inputs x 4 columns per lane, about a thousand instructions on one scheduler).  Here four
 // warps share a row, each taking 32 of the 128 inputs: a lane fetches its warp's 32 rows of R straight into
-// registers (8 bytes per row: its four columns; no staging of R in shared memory) together with one input of the
-// row (from device memory or, across the bus, from page-locked host memory) - a single memory round trip - then
-// accumulates four columns over the warp's 32 inputs in float32 (inputs broadcast from shared memory, four per
+// registers (8 bytes per row: its four columns; no staging of R in shared memory) while the row's first warp fetches
+// the row itself (from device memory or, across the bus, from page-locked host memory) - a single memory round trip
+// - then accumulates four columns over the warp's 32 inputs in float32 (inputs broadcast from shared memory, four per
 // load).  The four partial sums meet in shared memory; the row's first warp adds them, packs the 128 sign bits with
 // three shuffle steps and stores the code.
 constexpr int kStepThreads = 256;
@@ -1284,41 +1284,56 @@ __global__ void __launch_bounds__(kStepThreads) encode_step_kernel(const TilePar
         r.ho = r.row - r.tok * r.H_out;
         return r;
     };
-    // input k0 + lane of each of this warp's rows.  Addresses first, then the loads of all rounds back to back (a
-    // load placed behind the previous round's branch and store would wait for that round's memory round trip).
-    const __nv_bfloat16* xsrc[ROUNDS];
-    int64_t xstride[ROUNDS];
-    int xg[ROUNDS];
-    int g_max = 0;
+    // The rows: the first warp of a row fetches all of it, 8 bytes per lane (a 256-byte request per row and group
+    // member: rows that sit in page-locked host memory cross the bus in few, wide requests), and leaves it in shared
+    // memory as float32 for the row's four warps.  Addresses first, then the loads of all rounds back to back (a load
+    // placed behind the previous round's branch and store would wait for that round's memory round trip).
+    if (ks == 0) {
+        const __nv_bfloat16* xsrc[ROUNDS];
+        int64_t xstride[ROUNDS];
+        int xg[ROUNDS];
+        int g_max = 0;
 #pragma unroll
-    for (int it = 0; it < ROUNDS; ++it) {
-        bool second;
-        const RowRef r = locate(it, second);
-        const TileJob jb = second ? p.job[1] : p.job[0];
-        xg[it] = r.live ? jb.G : 0;
-        xstride[it] = jb.stride_h;
-        xsrc[it] = jb.x;
-        if (r.live) xsrc[it] += (int64_t)r.tok * jb.stride_t + (int64_t)r.ho * jb.G * jb.stride_h + k0 + lane;
-        g_max = max(g_max, xg[it]);
-    }
-    float xv[ROUNDS];
-#pragma unroll
-    for (int it = 0; it < ROUNDS; ++it) xv[it] = 0.f;
-    for (int g = 0; g < g_max; ++g) {
-        __nv_bfloat16 e[ROUNDS];
+        for (int it = 0; it < ROUNDS; ++it) {
+            bool second;
+            const RowRef r = locate(it, second);
+            const TileJob jb = second ? p.job[1] : p.job[0];
+            xg[it] = r.live ? jb.G : 0;
+            xstride[it] = jb.stride_h;
+            xsrc[it] = jb.x;
+            if (r.live) xsrc[it] += (int64_t)r.tok * jb.stride_t + (int64_t)r.ho * jb.G * jb.stride_h + 4 * lane;
+            g_max = max(g_max, xg[it]);
+        }
+        float xv[ROUNDS][4];
 #pragma unroll
         for (int it = 0; it < ROUNDS; ++it)
-            e[it] = g < xg[it] ? __ldg(xsrc[it] + (int64_t)g * xstride[it]) : __float2bfloat16(0.f);
 #pragma unroll
-        for (int it = 0; it < ROUNDS; ++it) xv[it] += __bfloat162float(e[it]);
-    }
+            for (int i = 0; i < 4; ++i) xv[it][i] = 0.f;
+        for (int g = 0; g < g_max; ++g) {
+            uint2 raw[ROUNDS];
 #pragma unroll
-    for (int it = 0; it < ROUNDS; ++it) {
-        // the group mean, rounded once to bf16 as torch's mean of a bf16 tensor is
-        if (xg[it] > 1) xv[it] = __bfloat162float(__float2bfloat16_rn(xv[it] / (float)xg[it]));
-        s_x[it][r_in][k0 + lane] = xv[it];
+            for (int it = 0; it < ROUNDS; ++it)
+                raw[it] = g < xg[it] ? __ldg(reinterpret_cast<const uint2*>(xsrc[it] + (int64_t)g * xstride[it]))
+                                     : make_uint2(0u, 0u);
+#pragma unroll
+            for (int it = 0; it < ROUNDS; ++it) {
+                xv[it][0] += __uint_as_float(raw[it].x << 16);
+                xv[it][1] += __uint_as_float(raw[it].x & 0xFFFF0000u);
+                xv[it][2] += __uint_as_float(raw[it].y << 16);
+                xv[it][3] += __uint_as_float(raw[it].y & 0xFFFF0000u);
+            }
+        }
+#pragma unroll
+        for (int it = 0; it < ROUNDS; ++it) {
+            // the group mean, rounded once to bf16 as torch's mean of a bf16 tensor is
+            if (xg[it] > 1) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) xv[it][i] = __bfloat162float(__float2bfloat16_rn(xv[it][i] / (float)xg[it]));
+            }
+            reinterpret_cast<float4*>(s_x[it][r_in])[lane] = make_float4(xv[it][0], xv[it][1], xv[it][2], xv[it][3]);
+        }
     }
-    __syncwarp();
+    __syncthreads();
     UCMR_STAMP(2);
 #pragma unroll
     for (int it = 0; it < ROUNDS; ++it) {
