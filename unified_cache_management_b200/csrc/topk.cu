@@ -479,8 +479,12 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     int32_t* const* const peer_ids = s_peer_ids;
 
     if (masked) grid_dependency_wait();  // pass-through rows copy scores below
-    // padding first; the chosen entries overwrite positions [0, kb) (in a cluster: after its first barrier)
-    for (int i = tid; lead && i < p.k; i += kSelThreads) {
+    // Padding of the positions the selection will not write: it emits exactly min(kb, max_blocks) entries, each of
+    // which stores its position (a record that turns out invalid stores the padding values itself), so only the
+    // tail [min(kb, max_blocks), k) is padded here - usually nothing, and over peer memory every store saved before
+    // the wait is a remote one.  Rows that are passed through unselected are written here in full.
+    const int pad_from = masked ? 0 : max(0, min(kb, n));
+    for (int i = pad_from + tid; lead && i < p.k; i += kSelThreads) {
         if (CANDIDATES) {
             if (p.n_peers > 0) {
                 for (int r = 0; r < p.n_peers; ++r) {
@@ -611,6 +615,14 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
                     cand_scores[obase + pos] = sc_v;
                     cand_ids[obase + pos] = j + id_offset;
                 }
+            } else if (n_peers > 0) {  // no block behind this position: the padding record
+                for (int r = 0; r < n_peers; ++r) {
+                    peer_scores[r][obase + pos] = INFINITY;
+                    peer_ids[r][obase + pos] = -1;
+                }
+            } else {
+                cand_scores[obase + pos] = INFINITY;
+                cand_ids[obase + pos] = -1;
             }
         } else {
             out_phys[obase + pos] = btrow[j];
