@@ -7,7 +7,8 @@
 //   registers while that load is in flight.  There is no producer warp and no "stage empty" barrier:
 //   the warp that frees a stage is the one that refills it, so the issue latency (resolve request and
 //   block-table entry, arm the barrier, launch the copy: several hundred cycles) is spread over twelve
-//   instruction streams and overlaps their math.  Up to 12 x 16 KiB are in flight per SM.  Each
+//   instruction streams and overlaps their math.  Up to 12 x 16 KiB are in flight per SM (sum mode uses ten of the
+//   stages, see run_scan_ring).  Each
 //   barrier has a single waiter that sees every phase in order, so a parity wait is never ambiguous.
 //   Work split: the first 7/8 (3/4 in long scans) of the items statically (CTA c, warp w), the rest claimed one by one from an
 //   atomic counter so that all SMs finish together; claim and block-table load run one item ahead of use.
@@ -33,6 +34,7 @@
 // (ucm/sparse/gsa_on_device/csrc/cuda/ham_dist/paged_ham_dist_mla.cu:111-248,
 //  ucm/sparse/gsa_on_device/hamming_topk.py:45-47).
 #include <limits.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -1303,6 +1305,13 @@ int run_scan_ring(const uint32_t* codes, int64_t NB, int BS, int Hkv, int W, con
     p.stage_bytes = bps * p.block_stride;
     p.n_active = kRingBytes / p.stage_bytes;
     if (p.n_active > kRingWarps) p.n_active = kRingWarps;
+    // Sum mode keeps ten of the twelve stages in use: 148 x 10 x 16 KiB in flight still saturate the memory system,
+    // and what is in flight beyond that only lengthens the queue - the first wave and the drain of a launch (measured
+    // on 268 MB, block 128: 46.0 -> 45.0 us per launch, the decode step 57.5 -> 56.6 us; eight stages make the launch
+    // faster still, 44.4 us, but not the step, whose scan starts on half of the SMs first and needs the headroom to
+    // even that out; six lose bandwidth: 54 us).  The min and token-row modes need all twelve warps for their
+    // arithmetic (block 128, G = 4: 54 us with twelve, 59-60 us with eight or ten).
+    if (!is_min && !row_mode && p.n_active > 10) p.n_active = 10;
     if (p.n_active < 4) return UCMR_ERR_UNSUPPORTED;
     const size_t smem = (size_t)p.n_active * p.stage_bytes;
 
