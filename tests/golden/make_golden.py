@@ -26,7 +26,9 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("UCM_REFERENCE_ROOT")
+if not REF:
+    raise SystemExit("usage: make_golden.py <reference checkout>   (or set UCM_REFERENCE_ROOT)")
 
 
 def _load(name, rel):
